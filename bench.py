@@ -1,0 +1,319 @@
+"""Benchmark of the tile-program hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Default workload (N=1): the fused element-wise + broadcast tile program
+Y = relu(exp(s*A) * b + C) on 8192x8192 bf16 with fp32 intermediates, metric = HBM GB/s
+(algorithmic bytes / device time).  One "step" is one pass of the program over the whole
+tensor.  With N>1 each rank runs its own replica (the program has no cross-GPU exchange), so
+scaling is weak and the value is the sum over ranks divided by the slowest rank's time.
+
+The JSON line carries: value (inputs resident in HBM, CUDA-event timed), e2e (the same program
+called through the public `ttl`/`ttnn` API with pinned host buffers: host->device copies,
+kernel, device->host copy inside the timed region), roofline of the dominant kernel,
+cpu_baseline (the CPU oracle timed on a bounded row slab on this host), SM clocks sampled
+during the timed region, and the number of kernels launched.
+
+`--impl reference` times the CPU implementation of the same program (the oracle port of the
+reference simulator's numerics) on the host cores instead.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+for p in (ROOT, ROOT / "tt-lang_b200", ROOT / "tests"):
+    if str(p) not in sys.path:
+        sys.path.insert(0, str(p))
+
+N = 8192
+ALGO_BYTES = (3 * N * N + N + 1) * 2  # A, C, Y full; b row vector; s scalar (bf16)
+FUSED_EXPR = ("relu", ("add", ("mul", ("exp", ("mul", 0, 1)), 2), 3))
+
+
+def measured_peak_hbm():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU through NVML (read-only) while the
+    timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                break
+            time.sleep(self.period)
+
+    def stop(self):
+        self._stop.set()
+        self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except Exception:
+            return local
+    return local
+
+
+def make_inputs():
+    import cases
+
+    a = cases.gen((N, N), "normal", 0)
+    s = cases.gen((1, 1), "const:0.1", 0)
+    b = cases.gen((1, N), "uniform", 1)
+    c = cases.gen((N, N), "normal", 2)
+    return a, s, b, c
+
+
+def cpu_baseline(sample_rows: int, repeats: int):
+    """Oracle port on a slab of `sample_rows` rows, GB/s of algorithmic bytes on the host cores."""
+    import torch
+
+    import cases
+    from oracle import tile_oracle
+
+    a = cases.gen((sample_rows, N), "normal", 0)
+    s = cases.gen((1, 1), "const:0.1", 0)
+    b = cases.gen((1, N), "uniform", 1)
+    c = cases.gen((sample_rows, N), "normal", 2)
+    tile_oracle.eval_expression(FUSED_EXPR, [a, s, b, c], (sample_rows, N), "f32")
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        tile_oracle.eval_expression(FUSED_EXPR, [a, s, b, c], (sample_rows, N), "f32")
+    dt = (time.perf_counter() - t0) / repeats
+    nbytes = (3 * sample_rows * N + N + 1) * 2
+    return nbytes / dt / 1e9, dt, torch.get_num_threads()
+
+
+def run_reference(args):
+    """Reference arm: the CPU implementation of the same program on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 1024
+    for _ in range(max(args.warmup, 1)):
+        cpu_baseline(rows, 1)
+    t0 = time.perf_counter()
+    vals = []
+    for _ in range(args.steps):
+        v, dt, cores = cpu_baseline(rows, 1)
+        vals.append(v)
+    total = time.perf_counter() - t0
+    value = sum(vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": "eltwise HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "fused_eltwise_bcast_8192: Y=relu(exp(s*A)*b+C), bf16 in/out, fp32 intermediates",
+                   "sample": f"{rows} of {N} rows per step"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"oracle/tile_oracle.eval_expression on a {rows}x{N} row slab per step "
+                                   "(the reference simulator's numerics: torch CPU ops, fp32 intermediates)"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="fused_eltwise_bcast_8192")
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the backend has no CPU fallback")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # noqa: F811
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    import importlib.util
+
+    import ttl_b200
+
+    ttl_b200.install()
+    import ttnn
+
+    from ttl_b200 import capi
+
+    spec = importlib.util.spec_from_file_location("bench_programs_eltwise", ROOT / "tests" / "programs" / "eltwise.py")
+    programs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(programs)
+    program = programs.fused_exp_bcast_f32acc
+
+    host = [t.pin_memory() for t in make_inputs()]
+    dev = [ttnn.from_torch(t) for t in host]
+    out = ttnn.empty((N, N), dtype=ttnn.bfloat16)
+    t_trace0 = time.perf_counter()
+    plan = program.plan(*dev, out)
+    trace_s = time.perf_counter() - t_trace0
+    assert len(plan.launches) == 1, plan.describe()
+    desc = plan.launches[0].desc(dev + [out])
+    ctx = capi.context(local)
+    stream = capi.current_stream()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        ctx.eltwise(desc, stream)
+    barrier()
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    l0 = ctx.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        ctx.eltwise(desc, stream)
+    e1.record()
+    barrier()
+    launches = ctx.launch_count() - l0
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    per_gpu_gbs = ALGO_BYTES / (ms_per_step * 1e-3) / 1e9
+    value = per_gpu_gbs * world
+
+    # ---- end to end through the public API: pinned host -> HBM -> kernel -> pinned host
+    host_out = torch.empty((N, N), dtype=torch.bfloat16).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in host)
+    d2h = host_out.numel() * host_out.element_size()
+
+    def e2e_step():
+        tensors = [ttnn.from_torch(t) for t in host]
+        y = ttnn.empty((N, N), dtype=ttnn.bfloat16)
+        program(*tensors, y)
+        ttnn.to_torch(y, out=host_out)
+
+    e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    e2e_ms = f0.elapsed_time(f1) / args.e2e_steps
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = ALGO_BYTES / (e2e_ms * 1e-3) / 1e9 * world
+
+    if rank == 0:
+        peak, peak_src = measured_peak_hbm()
+        line = {
+            "metric": "eltwise HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "fused_eltwise_bcast_8192: Y=relu(exp(s*A)*b+C), A,C,Y bf16 [8192,8192], "
+                                   "b bf16 [1,8192], s bf16 [1,1], fp32 intermediates",
+                       "replicas": world, "l2": "inputs+output 403 MB > 126 MB L2, no flush needed",
+                       "algorithmic_bytes_per_step": ALGO_BYTES, "trace_and_recognise_s": round(trace_s, 3)},
+            "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s",
+                         "frac": per_gpu_gbs / peak, "traffic": None, "peak_source": peak_src,
+                         "kernel": "ttlb_eltwise_kernel<bf16>"},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_ms, "steps": args.e2e_steps},
+            "gpu_launches": launches,
+            "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, dt, cores = cpu_baseline(1024, 5)
+            line["cpu_baseline"] = {
+                "value": v, "unit": "GB/s", "cores": cores, "kind": "port",
+                "sample": f"oracle/tile_oracle.eval_expression on a 1024x{N} row slab, mean of 5 runs ({dt * 1e3:.1f} ms each)"}
+        traffic_file = ROOT / "profiles" / "eltwise_fused_8192.traffic.json"
+        if traffic_file.exists():
+            try:
+                line["roofline"]["traffic"] = json.loads(traffic_file.read_text())["dram_bytes_per_launch"]
+            except Exception:
+                pass
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

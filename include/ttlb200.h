@@ -1,0 +1,159 @@
+/*
+ * ttlb200 — C ABI of the B200 (sm_100a) execution backend for tt-lang tile programs.
+ *
+ * Style follows the reference's own C API (include/ttlang-c/Dialects.h:17-28,
+ * include/ttlang-c/TTLAttrs.h:19-34): extern "C", plain value types, no exceptions
+ * across the boundary.  Every entry point returns 0 (TTLB_OK) or a negative
+ * TTLB_ERR_* code; a human-readable reason is kept per context and read with
+ * ttlb_last_error().
+ *
+ * What this library replaces: the device-dispatch boundary of the reference,
+ * run_kernel_on_device(kernel_specs, tensors, cb_configs, core_ranges)
+ * (python/ttl/kernel_runner.py:188-255), which hands a compiled tile program to
+ * ttnn.generic_op.  Here a recognised tile program is handed, as a plain
+ * descriptor, to a hand-written CUDA kernel.
+ *
+ * Conventions
+ *  - Tensors are row-major 2-D arrays; "32x32 tiles" are an indexing convention
+ *    (tile (r,c) = elements [32r:32r+32, 32c:32c+32], python/sim/tensoraccessor.py:125-159),
+ *    except bfloat8_b weights which are physically tiled (1088-byte tiles).
+ *  - Device pointers are borrowed: the caller keeps them alive until the stream
+ *    has synchronised.  Outputs are written in place.  Nothing user-visible is
+ *    allocated inside the library.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = default stream).
+ *  - A context is bound to one device and used by one thread at a time
+ *    (the reference is single-threaded too: python/ttl/ttl_api.py:71).
+ */
+#ifndef TTLB200_H
+#define TTLB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define TTLB_EXPORT __declspec(dllexport)
+#else
+#define TTLB_EXPORT __attribute__((visibility("default")))
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define TTLB_OK 0
+#define TTLB_ERR_INVALID_ARG (-1)
+#define TTLB_ERR_UNSUPPORTED (-2)
+#define TTLB_ERR_CUDA (-3)
+#define TTLB_ERR_TIMEOUT (-4) /* a bounded device-side wait ran out */
+#define TTLB_ERR_NCCL (-5)
+
+/* ---- element types (python/ttl/dtype_utils.py:151-181 gives the tile byte sizes) */
+#define TTLB_BF16 0   /* 2048-byte tiles */
+#define TTLB_F32 1    /* 4096-byte tiles */
+#define TTLB_BFP8_B 2 /* 1088-byte tiles: 64 shared exponents + 1024 sign/mantissa bytes */
+
+#define TTLB_TILE 32
+#define TTLB_BFP8_TILE_BYTES 1088
+
+typedef struct ttlb_ctx ttlb_ctx;
+
+/* Library version string, static storage. */
+TTLB_EXPORT const char *ttlb_version(void);
+
+/* Create / destroy a context bound to CUDA device `device_ordinal`.
+ * Replaces ttnn.open_device / close_device in user code
+ * (python/sim/ttnnsim.py:218-226).  ttlb_init fails with TTLB_ERR_CUDA when no
+ * usable sm_100 device is present: there is no CPU fallback. */
+TTLB_EXPORT int ttlb_init(int device_ordinal, ttlb_ctx **out);
+TTLB_EXPORT void ttlb_destroy(ttlb_ctx *ctx);
+
+/* Context-owned message of the last failing call (valid until the next call). */
+TTLB_EXPORT const char *ttlb_last_error(ttlb_ctx *ctx);
+
+/* Number of kernels this context has launched since creation. */
+TTLB_EXPORT int64_t ttlb_launch_count(ttlb_ctx *ctx);
+
+/* ------------------------------------------------------------------------ *
+ * Fused element-wise / broadcast tile programs.
+ *
+ * Replaces the fused compute kernel the reference generates for a chain of
+ * element-wise ops (lib/Dialect/TTL/Transforms/ConvertTTLToCompute.cpp:113-229;
+ * op table include/ttlang/Dialect/TTL/TTLElementwiseOps.def:61-82) together
+ * with its reader/writer data-movement kernels, and the simulator's per-tile
+ * torch ops (python/sim/block.py:870-1010, python/sim/ttnnsim.py:67-109).
+ *
+ * The expression is an accumulator program: LOAD sets the accumulator from an
+ * input, a binary op combines the accumulator with an input (arg >= 0) or with
+ * the value popped from a two-deep stack (arg == TTLB_ARG_STACK), PUSH saves the
+ * accumulator.  The final accumulator is the output element.
+ * ------------------------------------------------------------------------ */
+#define TTLB_MAX_IN 6
+#define TTLB_MAX_OPS 32
+#define TTLB_ARG_STACK (-1)
+
+enum ttlb_opcode {
+  TTLB_OP_LOAD = 0, /* acc = in[arg] */
+  TTLB_OP_ADD = 1,  /* acc = acc + x */
+  TTLB_OP_SUB = 2,  /* acc = acc - x */
+  TTLB_OP_RSUB = 3, /* acc = x - acc */
+  TTLB_OP_MUL = 4,
+  TTLB_OP_DIV = 5,  /* acc = acc / x */
+  TTLB_OP_RDIV = 6, /* acc = x / acc */
+  TTLB_OP_MAX = 7,
+  TTLB_OP_MIN = 8,
+  TTLB_OP_EXP = 16,
+  TTLB_OP_LOG = 17,
+  TTLB_OP_SQRT = 18,
+  TTLB_OP_RSQRT = 19,
+  TTLB_OP_TANH = 20,
+  TTLB_OP_SIGMOID = 21,
+  TTLB_OP_NEG = 22,
+  TTLB_OP_ABS = 23,
+  TTLB_OP_RELU = 24,
+  TTLB_OP_PUSH = 32 /* push acc on the stack */
+};
+
+/* How an input is indexed from an output element (i, j):
+ *  SAME  index = i + off                 (same-shape operand, optionally shifted)
+ *  ZERO  index = 0                       (degenerate tensor dim: [1,N] row vector,
+ *                                         [N,1] column, [1,1] scalar;
+ *                                         python/sim/copyhandlers.py:103-131)
+ *  TILE  index = off + (i mod 32)        (one fixed tile repeated over the tile
+ *                                         grid: the simulator's tile-grid
+ *                                         broadcast, python/sim/ttnnsim.py:67-109) */
+enum ttlb_index_mode { TTLB_IDX_SAME = 0, TTLB_IDX_ZERO = 1, TTLB_IDX_TILE = 2 };
+
+typedef struct {
+  const void *ptr; /* element (0,0) of the tensor */
+  int64_t ld;      /* row pitch in elements */
+  int32_t row_mode, col_mode;
+  int64_t row_off, col_off; /* in elements */
+} ttlb_operand;
+
+typedef struct {
+  int16_t opcode;
+  int16_t arg;
+} ttlb_instr;
+
+typedef struct {
+  int32_t dtype;         /* TTLB_BF16 or TTLB_F32: type of every input and of the output */
+  int32_t round_each_op; /* 1: round the accumulator to `dtype` after every op (what the
+                            simulator does on bf16 tensors, python/sim/block.py:856-864);
+                            0: fp32 intermediates, one final rounding */
+  int32_t n_in, n_ops;
+  ttlb_operand in[TTLB_MAX_IN];
+  ttlb_instr ops[TTLB_MAX_OPS];
+  void *out;      /* element (0,0) of the output tensor */
+  int64_t out_ld; /* row pitch in elements */
+  int64_t row0, col0, rows, cols; /* rectangle of the output to compute, in elements;
+                                     col0 and cols must be multiples of 8 */
+} ttlb_eltwise_desc;
+
+TTLB_EXPORT int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *desc, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* TTLB200_H */

@@ -1,0 +1,70 @@
+"""Extra block math for the reference simulator, in the simulator's own idiom.
+
+TEST INFRASTRUCTURE ONLY.  The reference simulator's `ttl.math` has only `broadcast`
+(python/sim/__init__.py:22-29); the element-wise functions exist on the compiler side
+(include/ttlang/Dialect/TTL/TTLElementwiseOps.def:61-82) with torch goldens
+(test/me2e/ops/__init__.py:27-41).  To obtain simulator outputs for programs that use them,
+this module adds `ttl.math.{exp,log,sqrt,rsqrt,tanh,sigmoid,neg,abs,relu,max,min}` to an
+imported simulator: each applies the torch golden per tile and returns a temporary block,
+keeping the source-block tracking the way python/sim/math.py:87-106 does for `broadcast`.
+Nothing under the reference tree is modified.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Callable
+
+import torch
+
+# torch goldens, as test/me2e/ops/__init__.py:27-41 pairs them with the op names
+UNARY_GOLDEN = {
+    "exp": torch.exp,
+    "log": torch.log,
+    "sqrt": torch.sqrt,
+    "rsqrt": torch.rsqrt,
+    "tanh": torch.tanh,
+    "sigmoid": torch.sigmoid,
+    "neg": torch.neg,
+    "abs": torch.abs,
+    "relu": torch.relu,
+}
+BINARY_GOLDEN = {"max": torch.maximum, "min": torch.minimum}
+
+
+def install(sim_module: Any) -> None:
+    """Add the functions to `sim_module.ttl.math` (sim_module is the imported `sim` package)."""
+    from sim.block import Block, BlockAcquisition, ThreadType  # type: ignore
+    from sim.ttnnsim import Tensor  # type: ignore
+
+    def track(result: Any, actual: Any) -> None:
+        result._source_blocks = list(getattr(actual, "_source_blocks", []))
+        if (not actual._is_temporary and actual._acquisition == BlockAcquisition.WAIT
+                and actual._thread_type == ThreadType.COMPUTE):
+            result._source_blocks.append(actual)
+
+    def make_unary(fn: Callable[[torch.Tensor], torch.Tensor]) -> Callable[[Any], Any]:
+        def op(block: Any) -> Any:
+            actual = block.block() if hasattr(block, "block") else block
+            tiles = [Tensor(fn(t.to_torch())) for t in actual.to_list()]
+            res = Block.from_list(tiles, actual._shape)
+            track(res, actual)
+            return res
+        return op
+
+    def make_binary(fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor]) -> Callable[[Any, Any], Any]:
+        def tile_op(a: Any, b: Any) -> Any:
+            if isinstance(a, Tensor):
+                return Tensor(fn(a.to_torch(), b.to_torch()))
+            return fn(a, b)
+
+        def op(a: Any, b: Any) -> Any:
+            la = a.block() if hasattr(a, "block") else a
+            lb = b.block() if hasattr(b, "block") else b
+            return la._binary_op(lb, tile_op)
+        return op
+
+    m = sim_module.ttl.math
+    for name, fn in UNARY_GOLDEN.items():
+        setattr(m, name, make_unary(fn))
+    for name, fn in BINARY_GOLDEN.items():
+        setattr(m, name, make_binary(fn))

@@ -1,0 +1,100 @@
+"""CPU restatement of what the reference simulator computes for the recognised tile programs.
+
+TEST INFRASTRUCTURE ONLY (see oracle/__init__.py).  Pinned by tests/golden/*.npz, which hold
+outputs of the unmodified reference simulator (python/sim) on the programs in tests/programs/
+(generator: tests/golden/make_golden.py), and by tests/test_oracle.py which, when the reference
+tree is present, also runs the simulator live beside these functions.
+
+Numerics follow the simulator: every block op is a torch CPU op on tiles held in the tensor's
+own dtype (python/sim/block.py:870-920, python/sim/ttnnsim.py:67-109, 384-460), so on bf16
+tensors each op rounds to bf16 (mode "native"); "f32" mode is the same program run on the
+values upcast to fp32 with one final round-to-nearest-even to bf16 - which is what "fp32
+intermediate / fp32 accumulate, bf16 out" means for a simulator that computes in the
+tensor dtype.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Dict, List, Sequence, Tuple
+
+import torch
+
+TILE = 32
+
+UNARY: Dict[str, Callable[[torch.Tensor], torch.Tensor]] = {
+    # torch goldens of the element-wise op table (test/me2e/ops/__init__.py:27-41)
+    "exp": torch.exp, "log": torch.log, "sqrt": torch.sqrt, "rsqrt": torch.rsqrt, "tanh": torch.tanh,
+    "sigmoid": torch.sigmoid, "neg": torch.neg, "abs": torch.abs, "relu": torch.relu,
+}
+BINARY: Dict[str, Callable[[torch.Tensor, torch.Tensor], torch.Tensor]] = {
+    "add": torch.add, "sub": torch.sub, "mul": torch.mul, "div": torch.div,
+    "max": torch.maximum, "min": torch.minimum,
+}
+
+
+def expand_operand(t: torch.Tensor, out_shape: Tuple[int, int]) -> torch.Tensor:
+    """Bring an operand to the output's shape the way the simulator's tile-grid broadcast does
+    (python/sim/ttnnsim.py:67-109 with tiles cut by python/sim/copyhandlers.py:312-333):
+    a size-1 dim broadcasts element-wise (degenerate tiles); a dim of exactly one tile (32)
+    repeats that tile along the tile grid; otherwise the dim must match."""
+    out = t
+    for dim in (0, 1):
+        n, want = out.shape[dim], out_shape[dim]
+        if n == want:
+            continue
+        if n == 1:
+            shape = list(out.shape)
+            shape[dim] = want
+            out = out.expand(*shape)
+        elif n == TILE and want % TILE == 0:
+            reps = [1, 1]
+            reps[dim] = want // TILE
+            out = out.repeat(*reps)
+        else:
+            raise ValueError(f"operand dim {dim} of size {n} cannot be broadcast to {want}")
+    return out
+
+
+def eval_expression(expr: Sequence, inputs: Sequence[torch.Tensor], out_shape: Tuple[int, int], mode: str) -> torch.Tensor:
+    """Evaluate a nested-tuple expression, e.g. ("relu", ("add", ("mul", ("exp", ("mul", 0, 1)), 2), 3)),
+    integers naming inputs.  mode "native": ops run in the inputs' dtype (bf16 ops round each
+    time, as the simulator on bf16 tensors); mode "f32": inputs upcast to fp32, result rounded
+    once to the inputs' dtype."""
+    dt = inputs[0].dtype
+    work = [t.to(torch.float32) if mode == "f32" else t for t in inputs]
+
+    def ev(e):
+        if isinstance(e, int):
+            return expand_operand(work[e], out_shape)
+        op = e[0]
+        if op in UNARY:
+            return UNARY[op](ev(e[1]))
+        return BINARY[op](ev(e[1]), ev(e[2]))
+
+    return ev(expr).to(dt).contiguous()
+
+
+def matmul_tiles(a: torch.Tensor, b: torch.Tensor, mode: str) -> torch.Tensor:
+    """`for k: out_blk.store(a_blk @ b_blk, acc=True)` for every output tile
+    (examples/singlecore_matmul.py:36-45; accumulate rule python/sim/block.py:856-864):
+    the first K tile assigns, later ones add, every partial product and every running sum held
+    in the tensor dtype ("native") or in fp32 with one final rounding ("f32").  All output tiles
+    of one K step are computed at once as a slab product."""
+    dt = a.dtype
+    if mode == "f32":
+        a, b = a.to(torch.float32), b.to(torch.float32)
+    kt = a.shape[1] // TILE
+    acc = None
+    for k in range(kt):
+        p = a[:, k * TILE:(k + 1) * TILE] @ b[k * TILE:(k + 1) * TILE, :]
+        acc = p if acc is None else acc + p
+    assert acc is not None
+    return acc.to(dt)
+
+
+def bf16_ulp_diff(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """Distance in bf16 units-in-the-last-place between two bf16 tensors (monotone integer map)."""
+    def key(t: torch.Tensor) -> torch.Tensor:
+        i = t.contiguous().view(torch.int16).to(torch.int32)
+        return torch.where(i < 0, -(i & 0x7FFF), i)
+    return (key(x) - key(y)).abs()

@@ -1,0 +1,119 @@
+"""Seeded parity cases shared by the golden generator and the tests.
+
+Inputs are generated on the CPU with torch.Generator().manual_seed(seed) in fp32 and cast,
+the way the reference's own tests seed theirs (examples/broadcast.py:126-133,
+test/me2e/ops/__init__.py:141-148).
+"""
+
+from __future__ import annotations
+
+from typing import Any, Callable, Dict, List, Tuple
+
+import torch
+
+
+def gen(shape: Tuple[int, int], dist: str, seed: int, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    if dist == "normal":
+        t = torch.randn(shape, generator=g, dtype=torch.float32)
+    elif dist == "uniform":           # U(-1, 1)
+        t = torch.rand(shape, generator=g, dtype=torch.float32) * 2 - 1
+    elif dist == "positive":          # U(0.01, 10): log / sqrt / rsqrt domain (test/me2e/ops/__init__.py:44-48)
+        t = torch.rand(shape, generator=g, dtype=torch.float32) * 9.99 + 0.01
+    elif dist.startswith("const:"):
+        t = torch.full(shape, float(dist.split(":")[1]), dtype=torch.float32)
+    elif dist.startswith("normal*"):  # N(0, sigma)
+        t = torch.randn(shape, generator=g, dtype=torch.float32) * float(dist.split("*")[1])
+    else:
+        raise ValueError(dist)
+    return t.to(dtype)
+
+
+class Case:
+    def __init__(self, name: str, module: str, program: str, inputs: List[Tuple[Tuple[int, int], str, int]],
+                 out_shape: Tuple[int, int], mode: str, expr: Any, check: str, factory_args: Tuple = (),
+                 dtype: torch.dtype = torch.bfloat16, store: str = "full"):
+        self.name, self.module, self.program, self.inputs, self.out_shape = name, module, program, inputs, out_shape
+        self.mode, self.expr, self.check, self.factory_args, self.dtype, self.store = (
+            mode, expr, check, factory_args, dtype, store)
+
+    def make_inputs(self) -> List[torch.Tensor]:
+        return [gen(s, d, seed, self.dtype) for (s, d, seed) in self.inputs]
+
+    def get_program(self, modules: Dict[str, Any], f32acc: bool = False) -> Callable[..., None]:
+        obj = getattr(modules[self.module], self.program)
+        if self.factory_args or self.program.startswith("make_"):
+            args = self.factory_args
+            if self.program == "make_unary_chain":
+                return obj(*args, fp32_dest_acc_en=f32acc)
+            return obj(*args)
+        if f32acc and hasattr(modules[self.module], self.program + "_f32acc"):
+            return getattr(modules[self.module], self.program + "_f32acc")
+        return obj
+
+
+_FUSED = ("relu", ("add", ("mul", ("exp", ("mul", 0, 1)), 2), 3))
+_MAB = ("add", ("mul", 0, 1), 2)
+
+CASES: List[Case] = [
+    # configs[0]: eltwise add 1024x1024 bf16, seeds 0/1, simulator-native numerics
+    Case("add_1024", "eltwise", "eltwise_add", [((1024, 1024), "normal", 0), ((1024, 1024), "normal", 1)],
+         (1024, 1024), "native", ("add", 0, 1), "exact", store="digest"),
+    Case("add_f32_256", "eltwise", "eltwise_add", [((256, 256), "normal", 0), ((256, 256), "normal", 1)],
+         (256, 256), "native", ("add", 0, 1), "exact", dtype=torch.float32),
+    # configs[1] at reduced size: Y = relu(exp(s*A) * b + C), both numerics modes
+    Case("fused_native_256x512", "eltwise", "fused_exp_bcast",
+         [((256, 512), "normal", 0), ((1, 1), "const:0.1", 0), ((1, 512), "uniform", 1), ((256, 512), "normal", 2)],
+         (256, 512), "native", _FUSED, "ulp1"),
+    Case("fused_f32_256x512", "eltwise", "fused_exp_bcast",
+         [((256, 512), "normal", 0), ((1, 1), "const:0.1", 0), ((1, 512), "uniform", 1), ((256, 512), "normal", 2)],
+         (256, 512), "f32", _FUSED, "ulp1"),
+    Case("fused_f32_ragged_96x160", "eltwise", "fused_exp_bcast",
+         [((96, 160), "normal", 3), ((1, 1), "const:0.1", 0), ((1, 160), "uniform", 4), ((96, 160), "normal", 5)],
+         (96, 160), "f32", _FUSED, "ulp1"),
+    # broadcast forms of A*B + C (general_broadcast.py): column, row vector, one tile row/col, scalar
+    Case("bcast_col", "eltwise", "mul_add_bcast", [((128, 128), "uniform", 10), ((128, 128), "uniform", 11), ((128, 1), "uniform", 12)],
+         (128, 128), "native", _MAB, "exact"),
+    Case("bcast_row_tilecol", "eltwise", "mul_add_bcast", [((128, 128), "uniform", 13), ((1, 128), "uniform", 14), ((128, 32), "uniform", 15)],
+         (128, 128), "native", _MAB, "exact"),
+    Case("bcast_tilerow_scalar", "eltwise", "mul_add_bcast", [((128, 128), "uniform", 16), ((32, 128), "uniform", 17), ((1, 1), "uniform", 18)],
+         (128, 128), "native", _MAB, "exact"),
+    Case("bcast_tile_full", "eltwise", "mul_add_bcast", [((128, 128), "uniform", 19), ((32, 32), "uniform", 20), ((128, 128), "uniform", 21)],
+         (128, 128), "native", _MAB, "exact"),
+    Case("bcast_col_f32", "eltwise", "mul_add_bcast", [((128, 128), "uniform", 10), ((128, 128), "uniform", 11), ((128, 1), "uniform", 12)],
+         (128, 128), "native", _MAB, "exact", dtype=torch.float32),
+    # expression with temporaries
+    Case("sum_of_products", "eltwise", "sum_of_products",
+         [((64, 96), "uniform", 30), ((64, 96), "uniform", 31), ((64, 96), "uniform", 32), ((64, 96), "positive", 33)],
+         (64, 96), "native", ("div", ("sub", ("mul", 0, 1), ("mul", 2, 3)), ("add", ("mul", 0, 0), 3)), "exact"),
+    # multicast pipe: only the 4 cores of the pipe compute (columns 0..3 of the output)
+    Case("eltwise_pipe", "eltwise", "eltwise_pipe", [((128, 2048), "uniform", 40), ((128, 2048), "uniform", 41), ((32, 32), "uniform", 42)],
+         (128, 2048), "native", _MAB, "exact"),
+]
+
+# one case per element-wise function of the compiler's op table
+for _i, (_op, _dist, _check) in enumerate([
+        ("exp", "uniform", "ulp1"), ("log", "positive", "ulp1"), ("sqrt", "positive", "exact"),
+        ("rsqrt", "positive", "exact"), ("tanh", "normal", "ulp1"), ("sigmoid", "normal", "ulp1"),
+        ("neg", "normal", "exact"), ("abs", "normal", "exact"), ("relu", "normal", "exact")]):
+    CASES.append(Case(f"unary_{_op}", "eltwise", "make_unary_chain", [((64, 64), _dist, 50 + _i), ((64, 64), "uniform", 70 + _i)],
+                      (64, 64), "native", ("add", (_op, 0), 1), _check, factory_args=([_op],)))
+
+MATMUL_CASES: List[Case] = [
+    # the reference's own simulator test sizes (examples/metal_examples/*/ttlang: 256^3) and smaller
+    Case("mm_single_128x256x64", "matmul", "singlecore_matmul", [((128, 256), "normal*0.0625", 0), ((256, 64), "normal*0.0625", 1)],
+         (128, 64), "f32", None, "rel1e-2"),
+    Case("mm_multi_256", "matmul", "multicore_matmul", [((256, 256), "normal*0.0625", 2), ((256, 256), "normal*0.0625", 3)],
+         (256, 256), "f32", None, "rel1e-2"),
+    Case("mm_blocked_256x512x256", "matmul", "make_blocked_matmul", [((256, 512), "normal*0.0442", 4), ((512, 256), "normal*0.0442", 5)],
+         (256, 256), "f32", None, "rel1e-2", factory_args=(2, 4)),
+    Case("mm_multi_native_128", "matmul", "multicore_matmul", [((128, 128), "normal*0.09", 6), ((128, 128), "normal*0.09", 7)],
+         (128, 128), "native", None, "rel1e-2"),
+]
+
+
+def by_name(name: str) -> Case:
+    for c in CASES + MATMUL_CASES:
+        if c.name == name:
+            return c
+    raise KeyError(name)

@@ -1,0 +1,159 @@
+"""GPU parity of the fused element-wise / broadcast kernel, called the way a user calls it:
+a tt-lang program run through the backend (tracer -> recogniser -> C ABI -> CUDA kernel),
+checked against the simulator's committed outputs and against the CPU oracle."""
+
+import ctypes
+
+import pytest
+import torch
+
+import cases
+from conftest import golden_tensor, load_golden
+from oracle import tile_oracle
+from test_oracle import oracle_output
+
+pytestmark = pytest.mark.gpu
+
+
+def run_case(case, mods, ttnn):
+    ins = [ttnn.from_torch(t) for t in case.make_inputs()]
+    out = ttnn.from_torch(torch.zeros(case.out_shape, dtype=case.dtype))
+    case.get_program(mods, f32acc=(case.mode == "f32"))(*ins, out)
+    assert out._tensor.is_cuda
+    return ttnn.to_torch(out)
+
+
+def check(got, want, how, what):
+    if how == "exact":
+        same = torch.equal(got.view(torch.int16), want.view(torch.int16)) if got.dtype == torch.bfloat16 \
+            else torch.equal(got, want)
+        assert same, f"{what}: not bit-identical ({(got != want).sum().item()} elements differ)"
+    else:
+        # transcendental ops: the GPU's expf/logf/tanhf and the CPU's differ in the last fp32 ulp for a few
+        # arguments, which can flip the final bf16 rounding: at most 1 bf16 ulp, on at most 0.1% of elements
+        ulp = tile_oracle.bf16_ulp_diff(got, want)
+        assert ulp.max().item() <= 1, f"{what}: max bf16 ulp {ulp.max().item()}"
+        frac = (ulp > 0).float().mean().item()
+        assert frac <= 1e-3, f"{what}: {frac:.2e} of elements differ"
+
+
+@pytest.mark.parametrize("case", cases.CASES, ids=lambda c: c.name)
+def test_program_matches_simulator_and_oracle(case, backend):
+    _, mods = backend
+    import ttnn
+    before = _launches()
+    got = run_case(case, mods, ttnn)
+    assert _launches() > before, "no CUDA kernel was launched"
+    check(got, oracle_output(case), case.check, "vs oracle")
+    g = load_golden(case.name)
+    if case.store == "digest":
+        from conftest import digest
+        assert digest([got]) == str(g["out_digest"]), "output bytes differ from the simulator's"
+    else:
+        check(got, golden_tensor(g["out"], case.dtype), case.check, "vs simulator golden")
+
+
+def _launches():
+    from ttl_b200 import capi
+    return capi.context().launch_count()
+
+
+def test_config2_full_size_against_oracle(backend):
+    """configs[1] at full size: 8192x8192, fp32 intermediates, bf16 out."""
+    _, mods = backend
+    import ttnn
+    n = 8192
+    a = cases.gen((n, n), "normal", 0)
+    s = cases.gen((1, 1), "const:0.1", 0)
+    b = cases.gen((1, n), "uniform", 1)
+    c = cases.gen((n, n), "normal", 2)
+    out = ttnn.from_torch(torch.zeros((n, n), dtype=torch.bfloat16))
+    mods["eltwise"].fused_exp_bcast_f32acc(*[ttnn.from_torch(t) for t in (a, s, b, c)], out)
+    got = ttnn.to_torch(out)
+    want = tile_oracle.eval_expression(("relu", ("add", ("mul", ("exp", ("mul", 0, 1)), 2), 3)), [a, s, b, c], (n, n), "f32")
+    check(got, want, "ulp1", "config 2 full size")
+    # properties that hold at any size: relu output is non-negative; zero exactly where the pre-activation is <= 0
+    assert (got.float() >= 0).all()
+    pre = torch.exp(a.float() * s.float()) * b.float() + c.float()
+    assert ((got == 0) == (pre.to(torch.bfloat16) <= 0)).float().mean().item() > 0.9999
+
+
+def test_repeated_calls_reuse_plan_and_stay_correct(backend):
+    _, mods = backend
+    import ttnn
+    case = cases.by_name("bcast_row_tilecol")
+    want = oracle_output(case)
+    prog = case.get_program(mods)
+    for i in range(3):
+        ins = [ttnn.from_torch(t) for t in case.make_inputs()]
+        out = ttnn.from_torch(torch.full(case.out_shape, float(i), dtype=case.dtype))
+        prog(*ins, out)
+        assert torch.equal(ttnn.to_torch(out), want)
+    assert len(prog._plans) == 1
+
+
+# ---- the C ABI itself: error behaviour and edge cases --------------------------------------
+def _desc(capi, x, y, out, ops, rows, cols, n_in=2):
+    d = capi.EltwiseDesc()
+    d.dtype, d.round_each_op, d.n_in, d.n_ops = capi.TTLB_BF16, 1, n_in, len(ops)
+    for k, t in enumerate((x, y)[:n_in]):
+        d.inp[k].ptr, d.inp[k].ld = t.data_ptr(), t.stride(0)
+    for k, (op, arg) in enumerate(ops):
+        d.ops[k].opcode, d.ops[k].arg = capi.OPCODES[op], arg
+    d.out, d.out_ld, d.rows, d.cols = out.data_ptr(), out.stride(0), rows, cols
+    return d
+
+
+def test_c_abi_rejects_malformed_descriptors_before_launching():
+    from ttl_b200 import capi
+    ctx = capi.context()
+    lib = capi.lib()
+    x = torch.ones(64, 64, dtype=torch.bfloat16, device="cuda")
+    y = torch.ones(64, 64, dtype=torch.bfloat16, device="cuda")
+    o = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
+    n0 = ctx.launch_count()
+
+    def rc(d):
+        return lib.ttlb_eltwise(ctx.handle, ctypes.byref(d), None)
+
+    assert rc(_desc(capi, x, y, o, [("add", 1)], 64, 64)) == capi.TTLB_ERR_INVALID_ARG          # no LOAD first
+    assert b"LOAD" in lib.ttlb_last_error(ctx.handle)
+    assert rc(_desc(capi, x, y, o, [("load", 0), ("add", 5)], 64, 64)) == capi.TTLB_ERR_INVALID_ARG   # bad input index
+    assert rc(_desc(capi, x, y, o, [("load", 0), ("add", -1)], 64, 64)) == capi.TTLB_ERR_INVALID_ARG  # pop of empty stack
+    assert rc(_desc(capi, x, y, o, [("load", 0), ("push", 0)], 64, 64)) == capi.TTLB_ERR_INVALID_ARG  # value left on stack
+    assert rc(_desc(capi, x, y, o, [("load", 0), ("add", 1)], 64, 60)) == capi.TTLB_ERR_INVALID_ARG   # cols not multiple of 8
+    d = _desc(capi, x, y, o, [("load", 0), ("add", 1)], 64, 64)
+    d.dtype = capi.TTLB_BFP8_B
+    assert rc(d) == capi.TTLB_ERR_UNSUPPORTED
+    d = _desc(capi, x, y, o, [("load", 0), ("add", 1)], 64, 64)
+    d.inp[1].ptr = None
+    assert rc(d) == capi.TTLB_ERR_INVALID_ARG
+    assert lib.ttlb_eltwise(ctx.handle, None, None) == capi.TTLB_ERR_INVALID_ARG
+    assert lib.ttlb_eltwise(None, ctypes.byref(d), None) == capi.TTLB_ERR_INVALID_ARG
+    assert ctx.launch_count() == n0, "a rejected descriptor must not launch anything"
+    # empty rectangle: accepted, nothing launched, output untouched
+    assert rc(_desc(capi, x, y, o, [("load", 0), ("add", 1)], 0, 64)) == capi.TTLB_OK
+    torch.cuda.synchronize()
+    assert ctx.launch_count() == n0 and (o == 0).all()
+    # and a valid one still works afterwards
+    assert rc(_desc(capi, x, y, o, [("load", 0), ("add", 1)], 64, 64)) == capi.TTLB_OK
+    torch.cuda.synchronize()
+    assert (o == 2).all() and ctx.launch_count() == n0 + 1
+
+
+def test_c_abi_sub_rectangle_and_offsets_leave_the_rest_untouched():
+    from ttl_b200 import capi
+    ctx = capi.context()
+    g = torch.Generator().manual_seed(5)
+    xc = torch.randn(96, 128, generator=g).to(torch.bfloat16)
+    yc = torch.randn(96, 128, generator=g).to(torch.bfloat16)
+    x, y = xc.cuda(), yc.cuda()
+    o = torch.full((96, 128), 7.0, dtype=torch.bfloat16, device="cuda")
+    d = _desc(capi, x, y, o, [("load", 0), ("mul", 1)], 32, 64)
+    d.row0, d.col0 = 32, 32
+    d.inp[1].row_off, d.inp[1].col_off = 32, -32   # y is read shifted by one tile down / one tile left
+    ctx.eltwise(d, 0)
+    torch.cuda.synchronize()
+    want = torch.full((96, 128), 7.0, dtype=torch.bfloat16)
+    want[32:64, 32:96] = xc[32:64, 32:96] * yc[64:96, 0:64]
+    assert torch.equal(o.cpu(), want)

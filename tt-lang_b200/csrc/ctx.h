@@ -1,0 +1,57 @@
+// Internal context shared by the C-ABI entry points (not installed; the public
+// surface is include/ttlb200.h).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "ttlb200.h"
+
+struct ttlb_ctx {
+  int device = 0;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  int64_t launches = 0;
+  std::string err;
+  // Device-side status word for kernels with bounded waits (GEMM / attention):
+  // 0 = ok, otherwise a code telling which wait gave up.
+  int *d_status = nullptr;
+  int *h_status = nullptr;  // pinned mirror
+};
+
+inline int ttlb_fail(ttlb_ctx *ctx, int code, const char *fmt, ...) {
+  if (ctx) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    ctx->err = buf;
+  }
+  return code;
+}
+
+#define TTLB_CUDA_CHECK(ctx, expr)                                                     \
+  do {                                                                                 \
+    cudaError_t e__ = (expr);                                                          \
+    if (e__ != cudaSuccess)                                                            \
+      return ttlb_fail((ctx), TTLB_ERR_CUDA, "%s failed: %s", #expr,                   \
+                       cudaGetErrorString(e__));                                       \
+  } while (0)
+
+// RAII guard: make the context's device current for the duration of a call.
+struct ttlb_device_guard {
+  int prev = -1;
+  bool ok = true;
+  explicit ttlb_device_guard(int dev) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    if (prev != dev) ok = (cudaSetDevice(dev) == cudaSuccess);
+  }
+  ~ttlb_device_guard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};

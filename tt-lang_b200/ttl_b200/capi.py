@@ -1,0 +1,136 @@
+"""ctypes binding of libttlb200.so (declarations: include/ttlb200.h).
+
+The reference reaches its native code through a compiled Python module
+(python/TTLangModule.cpp:14-46 over lib/CAPI); here the native side is a plain C ABI
+and this file is the whole binding.  There is no fallback: if the library is missing
+or no B200 is present, calls raise.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+from typing import Dict, Optional
+
+TTLB_OK = 0
+TTLB_ERR_INVALID_ARG = -1
+TTLB_ERR_UNSUPPORTED = -2
+TTLB_ERR_CUDA = -3
+TTLB_ERR_TIMEOUT = -4
+TTLB_ERR_NCCL = -5
+
+TTLB_BF16, TTLB_F32, TTLB_BFP8_B = 0, 1, 2
+TTLB_MAX_IN, TTLB_MAX_OPS, TTLB_ARG_STACK = 6, 32, -1
+IDX_SAME, IDX_ZERO, IDX_TILE = 0, 1, 2
+
+OPCODES = {
+    "load": 0, "add": 1, "sub": 2, "rsub": 3, "mul": 4, "div": 5, "rdiv": 6, "max": 7, "min": 8,
+    "exp": 16, "log": 17, "sqrt": 18, "rsqrt": 19, "tanh": 20, "sigmoid": 21, "neg": 22, "abs": 23, "relu": 24,
+    "push": 32,
+}
+
+
+class Operand(C.Structure):
+    _fields_ = [("ptr", C.c_void_p), ("ld", C.c_int64), ("row_mode", C.c_int32), ("col_mode", C.c_int32),
+                ("row_off", C.c_int64), ("col_off", C.c_int64)]
+
+
+class Instr(C.Structure):
+    _fields_ = [("opcode", C.c_int16), ("arg", C.c_int16)]
+
+
+class EltwiseDesc(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("round_each_op", C.c_int32), ("n_in", C.c_int32), ("n_ops", C.c_int32),
+                ("inp", Operand * TTLB_MAX_IN), ("ops", Instr * TTLB_MAX_OPS),
+                ("out", C.c_void_p), ("out_ld", C.c_int64),
+                ("row0", C.c_int64), ("col0", C.c_int64), ("rows", C.c_int64), ("cols", C.c_int64)]
+
+
+class BackendError(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"ttlb200 error {code}: {message}")
+        self.code = code
+
+
+_LIB: Optional[C.CDLL] = None
+LIB_PATH = Path(__file__).resolve().parent / "libttlb200.so"
+
+
+def lib() -> C.CDLL:
+    """Load the native library (once).  Raises if it has not been built."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build the CUDA extension first (python tt-lang_b200/build.py). "
+            "The B200 backend has no CPU fallback.")
+    l = C.CDLL(str(LIB_PATH))
+    l.ttlb_version.restype = C.c_char_p
+    l.ttlb_init.argtypes = [C.c_int, C.POINTER(C.c_void_p)]
+    l.ttlb_init.restype = C.c_int
+    l.ttlb_destroy.argtypes = [C.c_void_p]
+    l.ttlb_destroy.restype = None
+    l.ttlb_last_error.argtypes = [C.c_void_p]
+    l.ttlb_last_error.restype = C.c_char_p
+    l.ttlb_launch_count.argtypes = [C.c_void_p]
+    l.ttlb_launch_count.restype = C.c_int64
+    l.ttlb_eltwise.argtypes = [C.c_void_p, C.POINTER(EltwiseDesc), C.c_void_p]
+    l.ttlb_eltwise.restype = C.c_int
+    _LIB = l
+    return l
+
+
+class Context:
+    """One ttlb_ctx, bound to one CUDA device."""
+
+    def __init__(self, device: int):
+        self._lib = lib()
+        h = C.c_void_p()
+        rc = self._lib.ttlb_init(device, C.byref(h))
+        if rc != TTLB_OK:
+            raise BackendError(rc, f"ttlb_init(device={device}) failed: no usable B200 "
+                                   "(this backend has no CPU fallback)")
+        self.handle = h
+        self.device = device
+
+    def check(self, rc: int) -> None:
+        if rc != TTLB_OK:
+            raise BackendError(rc, (self._lib.ttlb_last_error(self.handle) or b"").decode())
+
+    def launch_count(self) -> int:
+        return int(self._lib.ttlb_launch_count(self.handle))
+
+    def eltwise(self, desc: EltwiseDesc, stream: int) -> None:
+        self.check(self._lib.ttlb_eltwise(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def close(self) -> None:
+        if self.handle:
+            self._lib.ttlb_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+
+_CONTEXTS: Dict[int, Context] = {}
+
+
+def context(device: Optional[int] = None) -> Context:
+    """Context of `device` (default: torch's current CUDA device), created on first use."""
+    import torch
+
+    if device is None:
+        if not torch.cuda.is_available():
+            raise BackendError(TTLB_ERR_CUDA, "no CUDA device: the B200 backend has no CPU fallback")
+        device = torch.cuda.current_device()
+    ctx = _CONTEXTS.get(device)
+    if ctx is None:
+        ctx = Context(device)
+        _CONTEXTS[device] = ctx
+    return ctx
+
+
+def current_stream() -> int:
+    import torch
+
+    return int(torch.cuda.current_stream().cuda_stream)

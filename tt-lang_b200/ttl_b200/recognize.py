@@ -1,0 +1,426 @@
+"""From the trace of a tile program to GPU launches.
+
+The reference decides what can be fused into one compute kernel by walking the IR:
+a chain is fusable when every leaf comes straight from a circular buffer and every
+interior node is an element-wise op or a broadcast of such a leaf
+(lib/Dialect/TTL/IR/TTLOpsUtils.cpp:9-63, lib/Dialect/TTL/Transforms/ConvertTTLToCompute.cpp:113-229).
+The trace already has that shape: every write is `output region <- expression over
+input regions`.  Two families are recognised:
+
+  * element-wise / broadcast expressions -> one `ttlb_eltwise` launch per maximal
+    output rectangle sharing the same expression and operand addressing;
+  * `out <- sum_k A[rows, k] @ B[k, cols]` over all K tiles -> a GEMM launch
+    (block forms (1,1)@(1,1) and (M,1)@(1,N) only: those are the ones that mean a block
+    matmul in the simulator, python/sim/block.py:870-920, 1012-1013).
+
+Anything else raises Unsupported: there is no CPU fallback.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import capi
+from . import ttnn as _ttnn
+from .trace import Acc, Bin, Expr, Leaf, Trace, Un, Write, Zero
+
+TILE = 32
+
+
+class Unsupported(NotImplementedError):
+    """The tile program is valid tt-lang but not (yet) runnable on the B200 backend."""
+
+
+_REVERSE = {"add": "add", "mul": "mul", "max": "max", "min": "min", "sub": "rsub", "div": "rdiv"}
+_UNARY = {"exp", "log", "sqrt", "rsqrt", "tanh", "sigmoid", "neg", "abs", "relu"}
+_BINARY = {"add", "sub", "mul", "div", "max", "min"}
+
+
+# --------------------------------------------------------------------------- #
+# helpers
+# --------------------------------------------------------------------------- #
+def merge_rects(rects: Sequence[Tuple[int, int, int, int]]) -> List[Tuple[int, int, int, int]]:
+    """Merge tile rectangles (r0, r1, c0, c1) that touch along a full edge."""
+    cur = list(rects)
+    while True:
+        n = len(cur)
+        cur.sort(key=lambda r: (r[0], r[1], r[2]))
+        out: List[Tuple[int, int, int, int]] = []
+        for r in cur:
+            if out and out[-1][0] == r[0] and out[-1][1] == r[1] and out[-1][3] == r[2]:
+                out[-1] = (r[0], r[1], out[-1][2], r[3])
+            else:
+                out.append(r)
+        out.sort(key=lambda r: (r[2], r[3], r[0]))
+        cur = []
+        for r in out:
+            if cur and cur[-1][2] == r[2] and cur[-1][3] == r[3] and cur[-1][1] == r[0]:
+                cur[-1] = (cur[-1][0], r[1], r[2], r[3])
+            else:
+                cur.append(r)
+        if len(cur) == n:
+            return sorted(cur)
+
+
+def _contains_matmul(e: Expr) -> bool:
+    stack = [e]
+    while stack:
+        x = stack.pop()
+        if isinstance(x, Bin):
+            if x.op == "matmul":
+                return True
+            stack.append(x.a)
+            stack.append(x.b)
+        elif isinstance(x, Un):
+            stack.append(x.x)
+        elif isinstance(x, Acc):
+            stack.extend(x.terms)
+    return False
+
+
+class _TensorTable:
+    """Maps tensor objects of a trace to kernel-argument positions."""
+
+    def __init__(self, args: Sequence[_ttnn.Tensor]):
+        self.args = list(args)
+        self.extras: List[_ttnn.Tensor] = []
+
+    def index(self, t: _ttnn.Tensor) -> int:
+        for i, a in enumerate(self.args):
+            if a is t:
+                return i
+        for i, a in enumerate(self.extras):
+            if a is t:
+                return len(self.args) + i
+        self.extras.append(t)
+        return len(self.args) + len(self.extras) - 1
+
+
+# --------------------------------------------------------------------------- #
+# element-wise linearisation
+# --------------------------------------------------------------------------- #
+def _classify(leaf: Leaf, w: Write) -> Tuple[int, int, int, int]:
+    """Index modes and element offsets of `leaf` relative to the write region `w`."""
+    t = leaf.tensor
+    trows, tcols = t.shape
+    tt = t.tile_shape()
+    res = []
+    for (lo, hi, wlo, whi, n_elem, n_tiles) in (
+            (leaf.r0, leaf.r1, w.r0, w.r1, trows, tt[0]),
+            (leaf.c0, leaf.c1, w.c0, w.c1, tcols, tt[1])):
+        if n_elem == 1:
+            res += [capi.IDX_ZERO, 0]
+        elif n_tiles == 1 or (hi - lo == 1 and whi - wlo > 1):
+            res += [capi.IDX_TILE, lo * TILE]
+        elif hi - lo == whi - wlo:
+            res += [capi.IDX_SAME, (lo - wlo) * TILE]
+        else:
+            raise Unsupported(f"operand region {hi - lo} tiles does not line up with output region {whi - wlo} tiles")
+    return res[0], res[1], res[2], res[3]
+
+
+def _need(e: Expr) -> int:
+    if isinstance(e, Leaf):
+        return 0
+    if isinstance(e, Un):
+        return _need(e.x)
+    if isinstance(e, Bin):
+        if isinstance(e.b, Leaf):
+            return _need(e.a)
+        if isinstance(e.a, Leaf):
+            return _need(e.b)
+        na, nb = _need(e.a), _need(e.b)
+        return min(max(na, nb + 1), max(nb, na + 1))
+    raise Unsupported(f"cannot lower {type(e).__name__}")
+
+
+class _Lin:
+    def __init__(self, w: Write, table: _TensorTable):
+        self.w, self.table = w, table
+        self.inputs: List[Tuple[int, int, int, int, int]] = []
+        self.ops: List[Tuple[str, int]] = []
+
+    def slot(self, leaf: Leaf) -> int:
+        rm, ro, cm, co = _classify(leaf, self.w)
+        key = (self.table.index(leaf.tensor), rm, ro, cm, co)
+        if key in self.inputs:
+            return self.inputs.index(key)
+        self.inputs.append(key)
+        return len(self.inputs) - 1
+
+    def emit(self, e: Expr) -> None:
+        if isinstance(e, Acc):
+            # sequential sum, each partial held in the block dtype
+            self.emit(e.terms[0])
+            for t in e.terms[1:]:
+                self._bin_rhs("add", t)
+            return
+        if isinstance(e, Leaf):
+            self.ops.append(("load", self.slot(e)))
+        elif isinstance(e, Un):
+            if e.op not in _UNARY:
+                raise Unsupported(f"unary op {e.op}")
+            self.emit(e.x)
+            self.ops.append((e.op, 0))
+        elif isinstance(e, Bin):
+            if e.op not in _BINARY:
+                raise Unsupported(f"binary op {e.op} inside an element-wise expression")
+            a, b = _unwrap(e.a), _unwrap(e.b)
+            if isinstance(b, Leaf):
+                self.emit(a)
+                self.ops.append((e.op, self.slot(b)))
+            elif isinstance(a, Leaf):
+                self.emit(b)
+                self.ops.append((_REVERSE[e.op], self.slot(a)))
+            elif _need(b) > _need(a):
+                self.emit(b)
+                self.ops.append(("push", 0))
+                self.emit(a)
+                self.ops.append((e.op, capi.TTLB_ARG_STACK))          # acc = a, popped = b
+            else:
+                self.emit(a)
+                self.ops.append(("push", 0))
+                self.emit(b)
+                self.ops.append((_REVERSE[e.op], capi.TTLB_ARG_STACK))  # acc = b, popped = a
+        elif isinstance(e, Zero):
+            raise Unsupported("reading a reserved block that was never written")
+        else:
+            raise Unsupported(f"cannot lower {type(e).__name__}")
+
+    def _bin_rhs(self, op: str, rhs: Expr) -> None:
+        rhs = _unwrap(rhs)
+        if isinstance(rhs, Leaf):
+            self.ops.append((op, self.slot(rhs)))
+        else:
+            self.ops.append(("push", 0))
+            self.emit(rhs)
+            self.ops.append((_REVERSE[op], capi.TTLB_ARG_STACK))
+
+
+def _unwrap(e: Expr) -> Expr:
+    if isinstance(e, Acc) and len(e.terms) == 1:
+        return _unwrap(e.terms[0])
+    return e
+
+
+def _stack_depth(ops: Sequence[Tuple[str, int]]) -> int:
+    d = m = 0
+    for op, arg in ops:
+        if op == "push":
+            d += 1
+            m = max(m, d)
+        elif arg == capi.TTLB_ARG_STACK:
+            d -= 1
+    return m
+
+
+# --------------------------------------------------------------------------- #
+# launches
+# --------------------------------------------------------------------------- #
+def _torch_of(t: _ttnn.Tensor) -> torch.Tensor:
+    x = t._tensor
+    if not x.is_cuda:
+        raise capi.BackendError(capi.TTLB_ERR_CUDA,
+                                "tensor is not in GPU memory: the B200 backend has no CPU fallback")
+    if x.dim() != 2 or (x.shape[1] > 1 and x.stride(1) != 1):
+        raise Unsupported("tensors must be 2-D with unit column stride")
+    return x
+
+
+def _dtype_code(dt: Any) -> int:
+    if dt == torch.bfloat16:
+        return capi.TTLB_BF16
+    if dt == torch.float32:
+        return capi.TTLB_F32
+    raise Unsupported(f"element type {dt} (bfloat16 and float32 only)")
+
+
+class EltwiseLaunch:
+    def __init__(self, out_index: int, rect: Tuple[int, int, int, int], inputs: List[Tuple[int, int, int, int, int]],
+                 ops: List[Tuple[str, int]], dtype: Any, round_each_op: bool, out_degenerate: Tuple[bool, bool]):
+        self.out_index, self.rect, self.inputs, self.ops = out_index, rect, inputs, ops
+        self.dtype, self.round_each_op, self.out_degenerate = dtype, round_each_op, out_degenerate
+
+    def describe(self) -> Dict[str, Any]:
+        return {"kind": "eltwise", "out": self.out_index, "rect_tiles": self.rect, "inputs": self.inputs,
+                "ops": self.ops, "round_each_op": self.round_each_op}
+
+    def desc(self, tensors: Sequence[_ttnn.Tensor]) -> capi.EltwiseDesc:
+        d = capi.EltwiseDesc()
+        d.dtype = _dtype_code(self.dtype)
+        d.round_each_op = 1 if self.round_each_op else 0
+        d.n_in, d.n_ops = len(self.inputs), len(self.ops)
+        for k, (ti, rm, ro, cm, co) in enumerate(self.inputs):
+            x = _torch_of(tensors[ti])
+            d.inp[k].ptr = x.data_ptr()
+            d.inp[k].ld = x.stride(0) if x.shape[0] > 1 else x.shape[1]
+            d.inp[k].row_mode, d.inp[k].row_off = rm, ro
+            d.inp[k].col_mode, d.inp[k].col_off = cm, co
+        for k, (op, arg) in enumerate(self.ops):
+            d.ops[k].opcode, d.ops[k].arg = capi.OPCODES[op], arg
+        o = _torch_of(tensors[self.out_index])
+        d.out = o.data_ptr()
+        d.out_ld = o.stride(0) if o.shape[0] > 1 else o.shape[1]
+        r0, r1, c0, c1 = self.rect
+        d.row0, d.rows = (0, 1) if self.out_degenerate[0] else (r0 * TILE, (r1 - r0) * TILE)
+        d.col0, d.cols = (0, 1) if self.out_degenerate[1] else (c0 * TILE, (c1 - c0) * TILE)
+        return d
+
+    def run(self, ctx: capi.Context, tensors: Sequence[_ttnn.Tensor], stream: int) -> None:
+        ctx.eltwise(self.desc(tensors), stream)
+
+
+class GemmLaunch:
+    def __init__(self, a_index: int, b_index: int, out_index: int, rect: Tuple[int, int, int, int], k_tiles: int,
+                 b_is_bfp8: bool):
+        self.a_index, self.b_index, self.out_index, self.rect = a_index, b_index, out_index, rect
+        self.k_tiles, self.b_is_bfp8 = k_tiles, b_is_bfp8
+
+    def describe(self) -> Dict[str, Any]:
+        return {"kind": "matmul_bfp8w" if self.b_is_bfp8 else "matmul_bf16", "a": self.a_index, "b": self.b_index,
+                "out": self.out_index, "rect_tiles": self.rect, "k_tiles": self.k_tiles}
+
+    def run(self, ctx: capi.Context, tensors: Sequence[_ttnn.Tensor], stream: int) -> None:
+        from . import ops
+
+        r0, r1, c0, c1 = self.rect
+        ops.launch_gemm(ctx, tensors[self.a_index], tensors[self.b_index], tensors[self.out_index],
+                        (r0 * TILE, r1 * TILE, c0 * TILE, c1 * TILE), stream)
+
+
+class Plan:
+    """The launches one kernel call turns into."""
+
+    def __init__(self, launches: List[Any], extras: List[_ttnn.Tensor], n_args: int):
+        self.launches, self.extras, self.n_args = launches, extras, n_args
+
+    @property
+    def cacheable(self) -> bool:
+        return not self.extras
+
+    def describe(self) -> List[Dict[str, Any]]:
+        return [l.describe() for l in self.launches]
+
+    def run(self, tensors: Sequence[_ttnn.Tensor]) -> None:
+        allt = list(tensors) + self.extras
+        dev = None
+        for t in allt:
+            if t._packed is not None:
+                x = t._packed
+            else:
+                x = t._tensor
+            if x.is_cuda:
+                dev = x.device.index
+                break
+        ctx = capi.context(dev)
+        stream = capi.current_stream()
+        for l in self.launches:
+            l.run(ctx, allt, stream)
+
+
+# --------------------------------------------------------------------------- #
+# plan construction
+# --------------------------------------------------------------------------- #
+def _matmul_terms(w: Write) -> Optional[List[Bin]]:
+    e = w.expr
+    terms = e.terms if isinstance(e, Acc) else [e]
+    if all(isinstance(t, Bin) and t.op == "matmul" for t in terms):
+        return terms  # type: ignore[return-value]
+    return None
+
+
+def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermediates: bool = False) -> Plan:
+    table = _TensorTable(arg_tensors)
+    # 1. writes must not overlap (the result would depend on thread interleaving)
+    cover: Dict[int, np.ndarray] = {}
+    out_tensors: Dict[int, _ttnn.Tensor] = {}
+    for w in trace.writes:
+        oi = table.index(w.tensor)
+        out_tensors[oi] = w.tensor
+        tr, tc = w.tensor.tile_shape()
+        if not (0 <= w.r0 < w.r1 <= tr and 0 <= w.c0 < w.c1 <= tc):
+            raise ValueError(f"write region [{w.r0}:{w.r1}, {w.c0}:{w.c1}] is outside the {tr}x{tc}-tile tensor")
+        grid = cover.setdefault(oi, np.zeros((tr, tc), dtype=bool))
+        region = grid[w.r0:w.r1, w.c0:w.c1]
+        if region.any():
+            raise Unsupported(f"output tiles [{w.r0}:{w.r1}, {w.c0}:{w.c1}] are written more than once")
+        region[...] = True
+
+    elt_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
+    elt_meta: Dict[Any, Any] = {}
+    mm_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
+    for w in trace.writes:
+        oi = table.index(w.tensor)
+        terms = _matmul_terms(w)
+        if terms is not None:
+            key = _recognise_matmul(w, terms, table, oi)
+            mm_groups.setdefault(key, []).append((w.r0, w.r1, w.c0, w.c1))
+            continue
+        if _contains_matmul(w.expr):
+            raise Unsupported("matmul mixed with element-wise ops in one store is not supported yet")
+        lin = _Lin(w, table)
+        lin.emit(w.expr)
+        if len(lin.inputs) > capi.TTLB_MAX_IN:
+            raise Unsupported(f"expression reads {len(lin.inputs)} distinct operands (max {capi.TTLB_MAX_IN})")
+        if len(lin.ops) > capi.TTLB_MAX_OPS:
+            raise Unsupported(f"expression needs {len(lin.ops)} ops (max {capi.TTLB_MAX_OPS})")
+        if _stack_depth(lin.ops) > 2:
+            raise Unsupported("expression needs more than two temporaries")
+        odt = w.tensor.dtype
+        for (ti, *_rest) in lin.inputs:
+            t = table.args[ti] if ti < len(table.args) else table.extras[ti - len(table.args)]
+            if t.dtype != odt:
+                raise Unsupported(f"mixed element types ({t.dtype} operand, {odt} output)")
+            for dim in (0, 1):
+                if w.tensor.shape[dim] == 1 and t.shape[dim] != 1:
+                    raise Unsupported("a degenerate output dimension needs degenerate operands")
+        key = (oi, tuple(lin.inputs), tuple(lin.ops))
+        elt_groups.setdefault(key, []).append((w.r0, w.r1, w.c0, w.c1))
+        elt_meta[key] = (odt, (w.tensor.shape[0] == 1, w.tensor.shape[1] == 1))
+
+    launches: List[Any] = []
+    for key, rects in elt_groups.items():
+        oi, inputs, ops = key
+        odt, degen = elt_meta[key]
+        for rect in merge_rects(rects):
+            launches.append(EltwiseLaunch(oi, rect, list(inputs), list(ops), odt,
+                                          round_each_op=not fp32_intermediates, out_degenerate=degen))
+    for key, rects in mm_groups.items():
+        ai, bi, oi, kt, b8 = key
+        for rect in merge_rects(rects):
+            launches.append(GemmLaunch(ai, bi, oi, rect, kt, b8))
+    return Plan(launches, table.extras, len(table.args))
+
+
+def _recognise_matmul(w: Write, terms: List[Bin], table: _TensorTable, oi: int) -> Any:
+    a0, b0 = terms[0].a, terms[0].b
+    if not (isinstance(a0, Leaf) and isinstance(b0, Leaf)):
+        raise Unsupported("matmul operands must come straight from circular buffers")
+    ta, tb = a0.tensor, b0.tensor
+    kt = ta.tile_shape()[1]
+    if tb.tile_shape()[0] != kt:
+        raise ValueError(f"Incompatible matrix shapes for multiplication: {ta.shape} @ {tb.shape}")
+    ks = []
+    for t in terms:
+        a, b = t.a, t.b
+        if not (isinstance(a, Leaf) and isinstance(b, Leaf)) or a.tensor is not ta or b.tensor is not tb:
+            raise Unsupported("matmul accumulation must read the same A and B tensors in every step")
+        if a.shape[1] != 1 or b.shape[0] != 1:
+            # (M,K)@(K,N) with K>1 raises in the simulator; equal-shape blocks mean a tile-wise
+            # product there (python/sim/block.py:885-905) - neither is a block matmul
+            raise Unsupported(f"matmul of blocks {a.shape} @ {b.shape}: only (M,1)@(1,N) is a block matmul")
+        if (a.r0, a.r1) != (w.r0, w.r1) or (b.c0, b.c1) != (w.c0, w.c1):
+            raise Unsupported("matmul operand rows/columns do not line up with the output block")
+        if a.c0 != b.r0:
+            raise Unsupported("matmul step multiplies different K tiles of A and B")
+        ks.append(a.c0)
+    if sorted(ks) != list(range(kt)):
+        raise Unsupported(f"matmul accumulates K tiles {sorted(set(ks))[:4]}... instead of all {kt} exactly once")
+    b8 = tb._packed is not None
+    if ta.dtype != torch.bfloat16 or (not b8 and tb.dtype != torch.bfloat16) or w.tensor.dtype != torch.bfloat16:
+        raise Unsupported(f"matmul element types A={ta.dtype} B={tb.dtype} out={w.tensor.dtype}: "
+                          "bfloat16 (and bfloat8_b weights) only")
+    return (table.index(ta), table.index(tb), oi, kt, b8)

@@ -1,0 +1,955 @@
+"""Symbolic execution of a tt-lang tile program.
+
+The reference runs a `@ttl.kernel` either by compiling its three threads to MLIR
+(python/ttl/ttl_api.py:818-1122) or by stepping them on real data in the simulator
+(python/sim/program.py:100-682).  This module runs the very same thread functions,
+on every core of the grid, with circular buffers and blocks that carry *expressions
+over tile regions* instead of data.  The outcome is the list of writes the program
+performs, `output region <- expression over input regions`, which the recogniser
+turns into GPU launches.
+
+Semantics kept from the simulator:
+  * per-core fresh circular buffers, thread closures rebound per core
+    (python/sim/program.py:69-97, 152-194); cores numbered 0..prod(grid)-1
+    (python/sim/program.py:213-223);
+  * reserve/push/wait/pop FIFO discipline, one pending reserve and one pending wait
+    per buffer (python/sim/cb.py:249-408), `with` sugar pushes/pops on exit
+    (python/sim/cb.py:24-71);
+  * `store(acc=True)`: first store assigns, later ones add (python/sim/block.py:805-868);
+  * block shapes broadcast NumPy-style over the tile grid (python/sim/block.py:783-803),
+    copy shape rule with size-1 dims kept as one tile (python/sim/copyhandlers.py:103-131,
+    295-380);
+  * pipes deliver a sent block to each destination core (python/sim/copyhandlers.py:228-292,
+    383-470); a program where every thread is blocked is reported as a deadlock
+    (python/sim/program.py:603-647).
+"""
+
+from __future__ import annotations
+
+import copy as _copy
+import threading
+import types
+from collections import deque
+from typing import Any, Callable, Deque, Dict, List, Optional, Sequence, Tuple
+
+from . import ttnn as _ttnn
+
+TILE_SHAPE = (32, 32)
+MAX_CBS = 32
+
+
+# --------------------------------------------------------------------------- #
+# Expression IR (block level: every node stands for a grid of tiles)
+# --------------------------------------------------------------------------- #
+class Expr:
+    __slots__ = ("shape",)
+    shape: Tuple[int, int]
+
+
+class Leaf(Expr):
+    """Tile region [r0:r1, c0:c1] (tile coordinates) of input tensor `tensor`."""
+
+    __slots__ = ("tensor", "r0", "r1", "c0", "c1")
+
+    def __init__(self, tensor: "_ttnn.Tensor", r0: int, r1: int, c0: int, c1: int):
+        self.tensor, self.r0, self.r1, self.c0, self.c1 = tensor, r0, r1, c0, c1
+        self.shape = (r1 - r0, c1 - c0)
+
+
+class Zero(Expr):
+    """A freshly reserved block: all zeros (python/sim/cb.py:343-346)."""
+
+    __slots__ = ()
+
+    def __init__(self, shape: Tuple[int, int]):
+        self.shape = shape
+
+
+class Un(Expr):
+    __slots__ = ("op", "x")
+
+    def __init__(self, op: str, x: Expr):
+        self.op, self.x, self.shape = op, x, x.shape
+
+
+class Bin(Expr):
+    __slots__ = ("op", "a", "b")
+
+    def __init__(self, op: str, a: Expr, b: Expr, shape: Tuple[int, int]):
+        self.op, self.a, self.b, self.shape = op, a, b, shape
+
+
+class Acc(Expr):
+    """Running sum built by repeated `store(..., acc=True)`: terms are added in order,
+    each partial sum held in the block's dtype."""
+
+    __slots__ = ("terms",)
+
+    def __init__(self, terms: List[Expr], shape: Tuple[int, int]):
+        self.terms, self.shape = terms, shape
+
+
+class Write:
+    """`tensor[r0:r1, c0:c1] <- expr` (tile coordinates)."""
+
+    __slots__ = ("tensor", "r0", "r1", "c0", "c1", "expr", "core")
+
+    def __init__(self, tensor: "_ttnn.Tensor", r0: int, r1: int, c0: int, c1: int, expr: Expr, core: int):
+        self.tensor, self.r0, self.r1, self.c0, self.c1, self.expr, self.core = tensor, r0, r1, c0, c1, expr, core
+
+
+def infer_broadcast_shape(left: Tuple[int, ...], right: Tuple[int, ...]) -> Tuple[int, int]:
+    if len(left) != len(right):
+        raise ValueError(f"Shape dimension mismatch: {left} vs {right}")
+    out = []
+    for i, (l, r) in enumerate(zip(left, right)):
+        if l != r and l != 1 and r != 1:
+            raise ValueError(
+                f"Cannot broadcast: incompatible shapes {left} and {right}. "
+                f"Dimension {i} has sizes {l} and {r} which are incompatible "
+                f"(must be equal or one must be 1).")
+        out.append(max(l, r))
+    return tuple(out)  # type: ignore[return-value]
+
+
+# --------------------------------------------------------------------------- #
+# Cooperative scheduler: one OS thread per tile-program thread, one runs at a time
+# --------------------------------------------------------------------------- #
+_tls = threading.local()
+
+
+def current_core() -> int:
+    c = getattr(_tls, "core", None)
+    if c is None:
+        raise RuntimeError("core not available - function must be called within Program context")
+    return c
+
+
+def current_grid() -> Tuple[int, ...]:
+    g = getattr(_tls, "grid", None)
+    if g is None:
+        raise RuntimeError("grid not available - function must be called within a kernel context")
+    return g
+
+
+def set_grid(grid: Optional[Tuple[int, ...]]) -> None:
+    _tls.grid = grid
+
+
+class DeadlockError(RuntimeError):
+    pass
+
+
+class _Worker:
+    def __init__(self, sched: "Scheduler", name: str, fn: Callable[[], Any], core: int, kind: str):
+        self.sched, self.name, self.fn, self.core, self.kind = sched, name, fn, core, kind
+        self.go = threading.Event()
+        self.done = False
+        self.error: Optional[BaseException] = None
+        self.blocked_on: Optional[Callable[[], bool]] = None
+        self.blocked_desc = ""
+        self.thread = threading.Thread(target=self._run, name=name, daemon=True)
+
+    def _run(self) -> None:
+        self.go.wait()
+        self.go.clear()
+        _tls.core = self.core
+        _tls.grid = self.sched.grid
+        _tls.kind = self.kind
+        _tls.worker = self
+        _tls.trace = self.sched.trace
+        try:
+            if not self.sched.aborting:
+                self.fn()
+        except _Abort:
+            pass
+        except BaseException as e:  # noqa: BLE001 - reported to the caller of the kernel
+            self.error = e
+        finally:
+            self.done = True
+            self.sched.back.set()
+
+    def block(self, ready: Callable[[], bool], desc: str) -> None:
+        """Park this worker until `ready()` holds."""
+        while not ready():
+            self.blocked_on, self.blocked_desc = ready, desc
+            self.sched.back.set()
+            self.go.wait()
+            self.go.clear()
+            if self.sched.aborting:
+                raise _Abort()
+        self.blocked_on = None
+
+
+class _Abort(BaseException):
+    pass
+
+
+class Scheduler:
+    def __init__(self, grid: Tuple[int, ...], trace: "Trace"):
+        self.grid = grid
+        self.trace = trace
+        self.workers: List[_Worker] = []
+        self.back = threading.Event()
+        self.aborting = False
+
+    def add(self, name: str, fn: Callable[[], Any], core: int, kind: str) -> None:
+        self.workers.append(_Worker(self, name, fn, core, kind))
+
+    def _resume(self, w: _Worker) -> None:
+        self.back.clear()
+        w.go.set()
+        self.back.wait()
+
+    def run(self) -> None:
+        for w in self.workers:
+            w.thread.start()
+        pending = deque(self.workers)
+        error: Optional[BaseException] = None
+        failed: Optional[_Worker] = None
+        while pending and error is None:
+            progressed = False
+            for _ in range(len(pending)):
+                w = pending.popleft()
+                if w.blocked_on is not None and not w.blocked_on():
+                    pending.append(w)
+                    continue
+                self._resume(w)
+                progressed = True
+                if w.error is not None:
+                    error, failed = w.error, w
+                    break
+                if not w.done:
+                    pending.append(w)
+            if not progressed and error is None:
+                lines = [f"  {w.name}: blocked on {w.blocked_desc}" for w in pending]
+                error = DeadlockError("Deadlock detected: all threads are blocked\n" + "\n".join(lines))
+        if error is not None:
+            self.aborting = True
+            for w in self.workers:
+                if not w.done:
+                    self._resume(w)
+        for w in self.workers:
+            w.thread.join()
+        if error is not None:
+            if failed is not None and not isinstance(error, DeadlockError):
+                try:
+                    error.add_note(f"(raised in tile-program thread {failed.name})")
+                except Exception:  # pragma: no cover
+                    pass
+            raise error
+
+
+def _worker() -> _Worker:
+    w = getattr(_tls, "worker", None)
+    if w is None:
+        raise RuntimeError("Thread context not set. Must be called within a kernel thread.")
+    return w
+
+
+# --------------------------------------------------------------------------- #
+# Blocks and circular buffers
+# --------------------------------------------------------------------------- #
+class Block:
+    """A reserved or waited window of a circular buffer, or a temporary (the value of
+    an expression).  Holds the symbolic value of its tiles."""
+
+    __slots__ = ("_shape", "expr", "dtype", "state", "kind", "temporary")
+
+    # states: "MW" must-write (reserved), "NAW" copy in flight into it, "FULL" holds a value,
+    #         "ACC" accumulating, "OS" out of scope (pushed / popped)
+    def __init__(self, shape: Tuple[int, int], dtype: Any, expr: Optional[Expr], state: str, kind: str,
+                 temporary: bool = False):
+        self._shape, self.dtype, self.expr, self.state, self.kind, self.temporary = (
+            tuple(shape), dtype, expr, state, kind, temporary)
+
+    @property
+    def shape(self) -> Tuple[int, int]:
+        return self._shape  # type: ignore[return-value]
+
+    def __len__(self) -> int:
+        return self._shape[0] * self._shape[1]
+
+    def block(self) -> "Block":
+        return self
+
+    def __getitem__(self, idx: Any) -> Any:
+        raise RuntimeError(
+            "Block indexing (block[index]) is not allowed. "
+            "Blocks must be used as whole units in operations like store() or arithmetic. "
+            "Use block directly without indexing.")
+
+    def __setitem__(self, idx: Any, value: Any) -> None:
+        raise RuntimeError("Direct assignment to Block is not allowed. Use block.store() or copy() instead.")
+
+    # -- reading ---------------------------------------------------------
+    def value(self) -> Expr:
+        if self.state == "MW":
+            raise RuntimeError(
+                "Cannot read from Block: Block is in must-write (MW) state. "
+                "Current state: MW, Expected operations: [STORE, STORE_ACC]")
+        if self.state in ("NAW", "OS"):
+            raise RuntimeError(
+                f"Cannot read from Block: Block has no access ({self.state} state). Current state: {self.state}")
+        assert self.expr is not None
+        return self.expr
+
+    # -- writing ---------------------------------------------------------
+    def store(self, items: Any, acc: bool = False) -> None:
+        src = _as_block(items)
+        if not isinstance(src, Block):
+            raise TypeError("store() takes a block or a block expression")
+        if len(src) != len(self):
+            raise ValueError("Length mismatch in store()")
+        if self.state == "NAW":
+            raise RuntimeError(
+                "Cannot write to Block: Block is locked as copy destination until tx.wait() completes "
+                "(copy lock error). Current state: NAW, Expected operations: [TX_WAIT]")
+        if self.state == "OS":
+            raise RuntimeError("Cannot write to Block: Block has no access (OS state). Current state: OS")
+        if not self.temporary and self.kind == "wait":
+            raise RuntimeError("Cannot write to Block: a waited block is read-only in a compute thread")
+        v = src.value()
+        if acc:
+            if self.state == "MW":  # first accumulating store assigns
+                self.expr = Acc([v], self._shape)
+            elif isinstance(self.expr, Acc):
+                self.expr.terms.append(v)
+            else:
+                assert self.expr is not None
+                self.expr = Acc([self.expr, v], self._shape)
+            self.state = "ACC"
+        else:
+            self.expr = v
+            self.state = "FULL"
+
+    # -- arithmetic ------------------------------------------------------
+    def _binary(self, other: Any, op: str) -> "Block":
+        o = _as_block(other)
+        if not isinstance(o, Block):
+            raise TypeError(f"unsupported operand type(s) for {op}: 'Block' and '{type(other).__name__}'")
+        a, b = self.value(), o.value()
+        if self._shape == o._shape:
+            shape = self._shape
+        else:
+            shape = infer_broadcast_shape(self._shape, o._shape)
+        return Block(shape, self.dtype, Bin(op, a, b, shape), "FULL", "temp", temporary=True)
+
+    def __add__(self, o: Any) -> "Block": return self._binary(o, "add")
+    def __sub__(self, o: Any) -> "Block": return self._binary(o, "sub")
+    def __mul__(self, o: Any) -> "Block": return self._binary(o, "mul")
+    def __truediv__(self, o: Any) -> "Block": return self._binary(o, "div")
+    def __matmul__(self, o: Any) -> "Block": return self._binary(o, "matmul")
+
+    def __pow__(self, o: Any) -> "Block":
+        if isinstance(o, int) and not isinstance(o, bool):
+            if o < 1 or o > 8:
+                raise ValueError("block ** n is supported for 1 <= n <= 8")
+            v = self.value()
+            e: Expr = v
+            for _ in range(o - 1):
+                e = Bin("mul", e, v, self._shape)
+            return Block(self._shape, self.dtype, e, "FULL", "temp", temporary=True)
+        raise TypeError("block ** block is not supported by the B200 backend")
+
+    def _unary(self, op: str) -> "Block":
+        return Block(self._shape, self.dtype, Un(op, self.value()), "FULL", "temp", temporary=True)
+
+
+class _BlockContext:
+    """`with cb.reserve() as blk` / `with cb.wait() as blk` wrapper; also usable without
+    `with`, in which case it stands for the block (python/sim/cb.py:24-156)."""
+
+    def __init__(self, cb: "CircularBuffer", block: Block, on_exit: Callable[[], None]):
+        self._cb, self._block, self._on_exit = cb, block, on_exit
+
+    def block(self) -> Block:
+        return self._block
+
+    @property
+    def shape(self) -> Tuple[int, int]:
+        return self._block.shape
+
+    @property
+    def _shape(self) -> Tuple[int, int]:
+        return self._block.shape
+
+    def __enter__(self) -> Block:
+        return self._block
+
+    def __exit__(self, exc_type: Any, exc: Any, tb: Any) -> None:
+        try:
+            self._on_exit()
+        except Exception:
+            if exc_type is None:
+                raise
+
+    def __len__(self) -> int:
+        return len(self._block)
+
+    def __getitem__(self, idx: Any) -> Any:
+        return self._block[idx]
+
+    def __setitem__(self, idx: Any, v: Any) -> None:
+        self._block[idx] = v
+
+    def store(self, items: Any, acc: bool = False) -> None:
+        self._block.store(items, acc=acc)
+
+    def __add__(self, o: Any) -> Block: return self._block + o
+    def __sub__(self, o: Any) -> Block: return self._block - o
+    def __mul__(self, o: Any) -> Block: return self._block * o
+    def __truediv__(self, o: Any) -> Block: return self._block / o
+    def __matmul__(self, o: Any) -> Block: return self._block @ o
+    def __pow__(self, o: Any) -> Block: return self._block ** o
+
+
+class ReserveContext(_BlockContext):
+    pass
+
+
+class WaitContext(_BlockContext):
+    pass
+
+
+def _as_block(obj: Any) -> Any:
+    if isinstance(obj, _BlockContext):
+        return obj.block()
+    return obj
+
+
+class CircularBuffer:
+    """Symbolic circular buffer.  `shape` is the block shape in tiles handed out by
+    reserve()/wait(); capacity is shape[0]*shape[1]*buffer_factor tiles
+    (python/sim/cb.py:184-225, python/ttl/circular_buffer.py:45-164)."""
+
+    def __init__(self, element: Any, shape: Sequence[int], buffer_factor: int = 2, _live: bool = False):
+        if len(shape) != 2:
+            raise ValueError(f"Shape must be a 2-tuple, got {tuple(shape)}")
+        if any((not isinstance(s, int)) or s <= 0 for s in shape):
+            raise ValueError(f"Shape entries must be positive integers, got {tuple(shape)}")
+        if not isinstance(buffer_factor, int) or not (1 <= buffer_factor <= 32):
+            raise ValueError(f"buffer_factor must be in range [1, 32], got {buffer_factor}")
+        self.element = element
+        self._shape = (int(shape[0]), int(shape[1]))
+        self._buffer_factor = buffer_factor
+        self._live = _live
+        self._name = "cb"
+        self._queue: Deque[Block] = deque()
+        self._pending_reserved: Optional[Block] = None
+        self._pending_waited: Optional[Block] = None
+        self._strict = False
+
+    @property
+    def shape(self) -> Tuple[int, int]:
+        return self._shape
+
+    @property
+    def buffer_factor(self) -> int:
+        return self._buffer_factor
+
+    @property
+    def capacity_tiles(self) -> int:
+        return self._shape[0] * self._shape[1] * self._buffer_factor
+
+    def _check_live(self) -> None:
+        if not self._live:
+            raise RuntimeError(
+                "CircularBuffer was not properly initialized with a CBAPI instance. "
+                "This likely means it was created outside of a kernel context. "
+                "CircularBuffers must be created within @ttl.kernel decorated functions.")
+
+    def _dtype(self) -> Any:
+        return getattr(self.element, "dtype", None)
+
+    def can_reserve(self) -> bool:
+        if not self._strict:
+            return True
+        used = len(self._queue) + (1 if self._pending_waited is not None else 0)
+        return used < self._buffer_factor
+
+    def can_wait(self) -> bool:
+        return len(self._queue) > 0
+
+    def reserve(self) -> ReserveContext:
+        self._check_live()
+        if self._pending_reserved is not None:
+            raise RuntimeError(
+                "Cannot call reserve() again before push(): "
+                "CircularBuffer already has a pending reserved block. "
+                "You must call push() before calling reserve() again.")
+        if not self.can_reserve():
+            _worker().block(self.can_reserve, f"{self._name}.reserve()")
+        blk = Block(self._shape, self._dtype(), Zero(self._shape), "MW", "reserve")
+        self._pending_reserved = blk
+        return ReserveContext(self, blk, self.push)
+
+    def push(self) -> None:
+        self._check_live()
+        blk = self._pending_reserved
+        if blk is None:
+            raise RuntimeError("push() without a pending reserve()")
+        if blk.state == "MW":
+            raise RuntimeError(
+                "Cannot push Block: it was reserved but never written "
+                "(expected copy(..., blk) or blk.store(...))")
+        if blk.state == "NAW":
+            raise RuntimeError("Cannot push Block: copy into it has not been waited on (expected tx.wait())")
+        self._pending_reserved = None
+        self._queue.append(Block(blk.shape, blk.dtype, blk.expr, "FULL", "wait"))
+        blk.state = "OS"
+
+    def wait(self) -> WaitContext:
+        self._check_live()
+        if self._pending_waited is not None:
+            raise RuntimeError(
+                "Cannot call wait() again before pop(): "
+                "CircularBuffer already has a pending waited block. "
+                "You must call pop() before calling wait() again.")
+        if not self._queue:
+            _worker().block(self.can_wait, f"{self._name}.wait()")
+        blk = self._queue[0]
+        self._pending_waited = blk
+        return WaitContext(self, blk, self.pop)
+
+    def pop(self) -> None:
+        self._check_live()
+        blk = self._pending_waited
+        if blk is None:
+            raise RuntimeError("pop() without a pending wait()")
+        self._pending_waited = None
+        self._queue.popleft()
+        blk.state = "OS"
+
+    def validate_no_pending_blocks(self) -> None:
+        errs = []
+        if self._pending_reserved is not None:
+            errs.append("Pending reserved block. Did you forget to call push()?")
+        if self._pending_waited is not None:
+            errs.append("Pending waited block. Did you forget to call pop()?")
+        if self._queue:
+            errs.append(f"{len(self._queue)} pushed block(s) were never consumed")
+        if errs:
+            raise RuntimeError(f"CircularBuffer {self._name} has incomplete blocks at end of execution:\n"
+                               + "\n".join(f"  - {e}" for e in errs))
+
+    def __repr__(self) -> str:
+        return (f"CircularBuffer(shape={self._shape}, capacity_tiles={self.capacity_tiles}, "
+                f"buffer_factor={self._buffer_factor})")
+
+
+def make_circular_buffer_like(element: Any, shape: Sequence[int], buffer_factor: int = 2) -> CircularBuffer:
+    return CircularBuffer(element, shape, buffer_factor)
+
+
+# --------------------------------------------------------------------------- #
+# Pipes
+# --------------------------------------------------------------------------- #
+def core_coords(cid: int, grid: Tuple[int, ...], dims: int) -> Any:
+    """Coordinates of linear core id `cid` (last grid dim fastest), flattened or padded
+    to `dims` entries exactly as python/sim/kernel.py:158-199 does."""
+    coords: List[int] = []
+    for s in reversed(grid):
+        coords.append(cid % s)
+        cid //= s
+    coords.reverse()
+    if dims < len(coords):
+        flat = coords[0]
+        for i in range(1, len(coords) - dims + 1):
+            flat = flat * grid[i] + coords[i]
+        coords = [flat] + coords[len(coords) - dims + 1:]
+    while len(coords) < dims:
+        coords.append(0)
+    return coords[0] if dims == 1 else tuple(coords)
+
+
+def grid_size_of(grid: Tuple[int, ...], dims: int) -> Any:
+    """python/sim/kernel.py:89-155."""
+    if dims <= 0:
+        raise ValueError(f"dims must be positive, got {dims}")
+    n = len(grid)
+    if dims == n:
+        res = tuple(grid)
+    elif dims < n:
+        flat = 1
+        for d in grid[dims - 1:]:
+            flat *= d
+        res = tuple(grid[:dims - 1]) + (flat,)
+    else:
+        res = tuple(grid) + (1,) * (dims - n)
+    return res[0] if dims == 1 else res
+
+
+def flatten_core_index(core_coord: Any, grid: Tuple[int, ...]) -> int:
+    if isinstance(core_coord, int):
+        return core_coord
+    coords = list(core_coord)
+    lin = coords[0]
+    for i in range(1, len(coords)):
+        lin = lin * grid[i] + coords[i]
+    return int(lin)
+
+
+def _dst_cores(dst: Any, grid: Tuple[int, ...]) -> List[int]:
+    """Linear ids of the destination cores of a pipe (python/sim/pipe.py:73-203)."""
+    total = 1
+    for g in grid:
+        total *= g
+    if isinstance(dst, int):
+        return [dst]
+    if isinstance(dst, tuple) and any(isinstance(i, slice) for i in dst):
+        dims = len(dst)
+        gs = grid_size_of(grid, dims)
+        gs = gs if isinstance(gs, tuple) else (gs,)
+        out = []
+        for cid in range(total):
+            cc = core_coords(cid, grid, dims)
+            cc = cc if isinstance(cc, tuple) else (cc,)
+            ok = True
+            for i, item in enumerate(dst):
+                if isinstance(item, slice):
+                    start = item.start if item.start is not None else 0
+                    stop = item.stop if item.stop is not None else gs[i]
+                    step = item.step if item.step is not None else 1
+                    if not (start <= cc[i] < stop and (cc[i] - start) % step == 0):
+                        ok = False
+                        break
+                elif cc[i] != item:
+                    ok = False
+                    break
+            if ok:
+                out.append(cid)
+        return out
+    if isinstance(dst, tuple) and len(dst) == 2 and all(isinstance(i, tuple) for i in dst):
+        first, second = dst
+        dims = len(first)
+        out = []
+        for cid in range(total):
+            cc = core_coords(cid, grid, dims)
+            cc = cc if isinstance(cc, tuple) else (cc,)
+            if all(min(first[i], second[i]) <= cc[i] <= max(first[i], second[i]) for i in range(dims)):
+                out.append(cid)
+        return out
+    if isinstance(dst, tuple):
+        dims = len(dst)
+        return [cid for cid in range(total) if core_coords(cid, grid, dims) == dst]
+    return []
+
+
+class Pipe:
+    """Description of a core-to-core(s) transfer (python/sim/typedefs.py:41-101)."""
+
+    def __init__(self, src_core: Any, dst_core_range: Any):
+        self.src_core = src_core
+        self.dst_core_range = dst_core_range
+
+    def _key(self) -> Any:
+        def h(o: Any) -> Any:
+            if isinstance(o, slice):
+                return ("slice", o.start, o.stop, o.step)
+            if isinstance(o, (tuple, list)):
+                return tuple(h(i) for i in o)
+            return o
+        return (h(self.src_core), h(self.dst_core_range))
+
+    def __hash__(self) -> int:
+        return hash(self._key())
+
+    def __eq__(self, other: object) -> bool:
+        return isinstance(other, Pipe) and self._key() == other._key()
+
+    def __repr__(self) -> str:
+        return f"Pipe(src_core={self.src_core}, dst_core_range={self.dst_core_range})"
+
+    def has_current_core(self) -> bool:
+        grid = current_grid()
+        cid = current_core()
+        return cid == flatten_core_index(self.src_core, grid) or cid in _dst_cores(self.dst_core_range, grid)
+
+
+class SrcPipeIdentity:
+    def __init__(self, pipe: Pipe):
+        self.pipe = pipe
+
+    @property
+    def dst(self) -> Any:
+        return self.pipe.dst_core_range
+
+
+class DstPipeIdentity:
+    def __init__(self, pipe: Pipe):
+        self.pipe = pipe
+
+    @property
+    def src(self) -> Any:
+        return self.pipe.src_core
+
+
+class PipeNet:
+    """python/sim/pipe.py:203-270."""
+
+    def __init__(self, pipes: List[Pipe]):
+        self._pipes = list(pipes)
+
+    def if_src(self, cond_fun: Callable[[SrcPipeIdentity], Any]) -> None:
+        grid, cid = current_grid(), current_core()
+        for p in self._pipes:
+            if cid == flatten_core_index(p.src_core, grid):
+                cond_fun(SrcPipeIdentity(p))
+
+    def if_dst(self, cond_fun: Callable[[DstPipeIdentity], Any]) -> None:
+        grid, cid = current_grid(), current_core()
+        for p in self._pipes:
+            if cid in _dst_cores(p.dst_core_range, grid):
+                cond_fun(DstPipeIdentity(p))
+
+
+# --------------------------------------------------------------------------- #
+# copy
+# --------------------------------------------------------------------------- #
+def _shape_in_tiles_with_skip(shape: Tuple[int, ...]) -> Tuple[int, ...]:
+    return tuple(1 if d == 1 else d // t for d, t in zip(shape, TILE_SHAPE))
+
+
+class CopyTransaction:
+    """Handle returned by ttl.copy; the transfer takes effect at wait()
+    (python/sim/copy.py:37-153)."""
+
+    def __init__(self, src: Any, dst: Any):
+        self._src, self._dst = src, dst
+        self._completed = False
+        s, d = _as_block(src), _as_block(dst)
+        s = s.pipe if isinstance(s, (SrcPipeIdentity, DstPipeIdentity)) else s
+        d = d.pipe if isinstance(d, (SrcPipeIdentity, DstPipeIdentity)) else d
+        self._s, self._d = s, d
+        if isinstance(s, _ttnn.Tensor) and isinstance(d, Block):
+            self._mode = "t2b"
+            if len(s.shape) != 2:
+                raise ValueError(f"Tensor must be 2-dimensional, got shape {s.shape}")
+            self._check_dst_block(d)
+            st = _shape_in_tiles_with_skip(s.shape)
+            if st != d.shape:
+                raise ValueError(
+                    f"Tensor shape {s.shape} (={st} tiles) does not match "
+                    f"Block shape {d.shape} tiles (={tuple(a * b for a, b in zip(d.shape, TILE_SHAPE))} elements)")
+            d.state = "NAW"
+        elif isinstance(s, Block) and isinstance(d, _ttnn.Tensor):
+            self._mode = "b2t"
+            if len(d.shape) != 2:
+                raise ValueError(f"Tensor must be 2-dimensional, got shape {d.shape}")
+            dt = _shape_in_tiles_with_skip(d.shape)
+            if dt != s.shape:
+                raise ValueError(
+                    f"Tensor shape {d.shape} (={dt} tiles) does not match "
+                    f"Block shape {s.shape} tiles (={tuple(a * b for a, b in zip(s.shape, TILE_SHAPE))} elements)")
+            s.value()
+        elif isinstance(s, Block) and isinstance(d, Pipe):
+            self._mode = "b2p"
+            s.value()
+        elif isinstance(s, Pipe) and isinstance(d, Block):
+            self._mode = "p2b"
+            self._check_dst_block(d)
+            d.state = "NAW"
+        else:
+            raise ValueError(f"No copy handler registered for ({type(src).__name__}, {type(dst).__name__})")
+
+    @staticmethod
+    def _check_dst_block(d: Block) -> None:
+        if d.state == "OS":
+            raise RuntimeError("Cannot write to Block: Block has no access (OS state). Current state: OS")
+        if d.kind == "wait":
+            raise RuntimeError("Cannot copy into a waited block")
+        if d.state == "NAW":
+            raise RuntimeError(
+                "Cannot write to Block: Block is locked as copy destination until tx.wait() completes "
+                "(copy lock error). Current state: NAW, Expected operations: [TX_WAIT]")
+
+    def can_wait(self) -> bool:
+        if self._mode == "p2b":
+            return _trace().pipe_ready(self._s, current_core())
+        return True
+
+    @property
+    def is_completed(self) -> bool:
+        return self._completed
+
+    def wait(self) -> None:
+        if self._completed:
+            return
+        tr = _trace()
+        s, d = self._s, self._d
+        if self._mode == "t2b":
+            base, r0, r1, c0, c1 = s._origin if s._origin is not None else (s, 0, s.tile_shape()[0], 0, s.tile_shape()[1])
+            tr.note_input(base)
+            d.expr = Leaf(base, r0, r1, c0, c1)
+            d.expr.shape = d.shape
+            d.state = "FULL"
+        elif self._mode == "b2t":
+            base, r0, r1, c0, c1 = d._origin if d._origin is not None else (d, 0, d.tile_shape()[0], 0, d.tile_shape()[1])
+            tr.writes.append(Write(base, r0, r1, c0, c1, s.value(), current_core()))
+        elif self._mode == "b2p":
+            tr.pipe_send(d, s.value(), len(_dst_cores(d.dst_core_range, current_grid())))
+        else:  # p2b
+            cid = current_core()
+            if not tr.pipe_ready(s, cid):
+                _worker().block(lambda: tr.pipe_ready(s, cid), f"copy({s!r}, block).wait()")
+            v = tr.pipe_recv(s)
+            if v.shape[0] * v.shape[1] != len(d):
+                raise ValueError(
+                    f"Destination Block length ({len(d)}) does not match pipe data length ({v.shape[0] * v.shape[1]})")
+            d.expr = v
+            d.state = "FULL"
+        self._completed = True
+
+
+def copy(src: Any, dst: Any) -> CopyTransaction:
+    return CopyTransaction(src, dst)
+
+
+# --------------------------------------------------------------------------- #
+# Trace of one kernel call
+# --------------------------------------------------------------------------- #
+class Trace:
+    def __init__(self, grid: Tuple[int, ...]):
+        self.grid = grid
+        self.writes: List[Write] = []
+        self.inputs: List[_ttnn.Tensor] = []
+        self._pipes: Dict[Pipe, Deque[List[Any]]] = {}
+
+    def note_input(self, t: "_ttnn.Tensor") -> None:
+        for x in self.inputs:
+            if x is t:
+                return
+        self.inputs.append(t)
+
+    def pipe_send(self, pipe: Pipe, value: Expr, receivers: int) -> None:
+        self._pipes.setdefault(pipe, deque()).append([value, max(1, receivers)])
+
+    def pipe_ready(self, pipe: Pipe, core: int) -> bool:
+        q = self._pipes.get(pipe)
+        return bool(q)
+
+    def pipe_recv(self, pipe: Pipe) -> Expr:
+        q = self._pipes[pipe]
+        head = q[0]
+        head[1] -= 1
+        if head[1] == 0:
+            q.popleft()
+        return head[0]
+
+
+def _trace() -> Trace:
+    t = getattr(_tls, "trace", None)
+    if t is None:
+        raise RuntimeError("ttl.copy must be called within a kernel thread")
+    return t
+
+
+def thread_kind() -> str:
+    return getattr(_tls, "kind", "")
+
+
+# --------------------------------------------------------------------------- #
+# Running a program on every core
+# --------------------------------------------------------------------------- #
+def _make_cell(value: Any) -> Any:
+    def inner() -> Any:
+        return value
+    assert inner.__closure__ is not None
+    return inner.__closure__[0]
+
+
+def _rebind(func: types.FunctionType, per_core: Dict[int, Any]) -> types.FunctionType:
+    """New function object whose closure cells holding circular buffers (or containers
+    of per-core state) point at this core's private copies (python/sim/program.py:69-97)."""
+    free = func.__code__.co_freevars
+    cells = []
+    for name, cell in zip(free, func.__closure__ or ()):
+        try:
+            v = cell.cell_contents
+        except ValueError:
+            cells.append(cell)
+            continue
+        cells.append(_make_cell(per_core[id(v)]) if id(v) in per_core else cell)
+    return types.FunctionType(func.__code__, func.__globals__, func.__name__, func.__defaults__, tuple(cells))
+
+
+def run_program(threads: List[Tuple[str, types.FunctionType]], grid: Tuple[int, ...], strict_cb: bool = False) -> Trace:
+    """Execute the thread functions of one kernel call on every core and return the trace.
+
+    `threads` is [(kind, function)] with kind "compute" or "dm".
+    """
+    total = 1
+    for g in grid:
+        total *= g
+    trace = Trace(grid)
+    sched = Scheduler(grid, trace)
+    all_cbs: List[Tuple[int, CircularBuffer]] = []
+    # closure values shared by the thread functions
+    shared: Dict[int, Any] = {}
+    for _, fn in threads:
+        for cell in fn.__closure__ or ():
+            try:
+                v = cell.cell_contents
+            except ValueError:
+                continue
+            shared[id(v)] = v
+    n_cbs = sum(1 for v in shared.values() if isinstance(v, CircularBuffer)) + sum(
+        sum(1 for x in v if isinstance(x, CircularBuffer)) for v in shared.values() if isinstance(v, (list, tuple)))
+    if n_cbs > MAX_CBS:
+        raise RuntimeError(f"A kernel may use at most {MAX_CBS} circular buffers, got {n_cbs}")
+    for core in range(total):
+        per_core: Dict[int, Any] = {}
+
+        def fresh_cb(v: CircularBuffer) -> CircularBuffer:
+            if id(v) not in per_core:
+                cb = CircularBuffer(v.element, v.shape, v.buffer_factor, _live=True)
+                cb._strict = strict_cb
+                per_core[id(v)] = cb
+                all_cbs.append((core, cb))
+            return per_core[id(v)]
+
+        def clone(v: Any) -> Any:
+            """Per-core copy of a container; circular buffers inside it become this core's."""
+            if isinstance(v, CircularBuffer):
+                return fresh_cb(v)
+            if isinstance(v, list):
+                return [clone(x) for x in v]
+            if isinstance(v, tuple) and any(isinstance(x, (CircularBuffer, list, tuple, dict)) for x in v):
+                return tuple(clone(x) for x in v)
+            if isinstance(v, dict):
+                return {k: clone(x) for k, x in v.items()}
+            if isinstance(v, set):
+                return _copy.deepcopy(v)
+            return v
+
+        for key, v in shared.items():
+            if isinstance(v, CircularBuffer):
+                fresh_cb(v)
+            elif isinstance(v, (list, dict, set, tuple)):
+                c = clone(v)
+                if c is not v:
+                    per_core[key] = c
+        # name buffers after the variables that hold them (for deadlock reports)
+        for _, fn in threads:
+            for name, cell in zip(fn.__code__.co_freevars, fn.__closure__ or ()):
+                try:
+                    v = cell.cell_contents
+                except ValueError:
+                    continue
+                if isinstance(v, CircularBuffer) and id(v) in per_core:
+                    per_core[id(v)]._name = name
+        order = sorted(range(len(threads)), key=lambda i: 0 if threads[i][0] == "dm" else 1)
+        for i in order:
+            kind, fn = threads[i]
+            sched.add(f"core{core}-{fn.__name__}", _rebind(fn, per_core), core, kind)
+    sched.run()
+    errs = []
+    for core, cb in all_cbs:
+        try:
+            cb.validate_no_pending_blocks()
+        except RuntimeError as e:
+            errs.append(f"core{core}.{cb._name}: {e}")
+    if errs:
+        raise RuntimeError("Kernel execution completed with incomplete CircularBuffer operations:\n" + "\n".join(errs))
+    return trace
