@@ -57,7 +57,7 @@ class ClockSampler(threading.Thread):
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = None
-        self._stop = threading.Event()
+        self._halt = threading.Event()
         self.ok = False
         try:
             import pynvml
@@ -80,7 +80,7 @@ class ClockSampler(threading.Thread):
             getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
             getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
         }
-        while not self._stop.is_set():
+        while not self._halt.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
                 try:
@@ -95,7 +95,7 @@ class ClockSampler(threading.Thread):
             time.sleep(self.period)
 
     def stop(self):
-        self._stop.set()
+        self._halt.set()
         self.join(timeout=2)
         s = sorted(self.samples)
         return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
@@ -180,6 +180,8 @@ def main():
     ap.add_argument("--workload", default="fused_eltwise_bcast_8192")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (for profiler runs)")
+    ap.add_argument("--eltwise-mode", default="auto", choices=["auto", "generic", "specialised"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -224,6 +226,8 @@ def main():
     assert len(plan.launches) == 1, plan.describe()
     desc = plan.launches[0].desc(dev + [out])
     ctx = capi.context(local)
+    ctx.set_eltwise_mode({"auto": capi.ELTWISE_AUTO, "generic": capi.ELTWISE_GENERIC,
+                          "specialised": capi.ELTWISE_SPECIALISED}[args.eltwise_mode])
     stream = capi.current_stream()
 
     def barrier():
@@ -266,15 +270,17 @@ def main():
         program(*tensors, y)
         ttnn.to_torch(y, out=host_out)
 
-    e2e_step()
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    for _ in range(args.e2e_steps):
+    e2e_ms = float("nan")
+    if not args.no_e2e:
         e2e_step()
-    f1.record()
-    barrier()
-    e2e_ms = f0.elapsed_time(f1) / args.e2e_steps
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(args.e2e_steps):
+            e2e_step()
+        f1.record()
+        barrier()
+        e2e_ms = f0.elapsed_time(f1) / args.e2e_steps
     if dist is not None:
         t = torch.tensor([e2e_ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -293,7 +299,8 @@ def main():
                        "algorithmic_bytes_per_step": ALGO_BYTES, "trace_and_recognise_s": round(trace_s, 3)},
             "roofline": {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s",
                          "frac": per_gpu_gbs / peak, "traffic": None, "peak_source": peak_src,
-                         "kernel": "ttlb_eltwise_kernel<bf16>"},
+                         "kernel": "ttlb_eltwise_jit" if ctx.eltwise_last_path() == capi.ELTWISE_SPECIALISED
+                         else "ttlb_eltwise_kernel<bf16>"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": args.e2e_steps},
             "gpu_launches": launches,

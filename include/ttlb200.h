@@ -152,6 +152,28 @@ typedef struct {
 
 TTLB_EXPORT int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *desc, void *stream);
 
+/* How ttlb_eltwise executes a program.  The reference generates one C++ compute
+ * kernel per tile program and has the device runtime compile it
+ * (python/ttl/ttl_api.py:425-440, 556-559); likewise a program is normally run by a
+ * kernel specialised for it (the streaming skeleton instantiated for the program's
+ * operand addressing and op sequence, compiled once for sm_100a with NVRTC and
+ * cached in the context).  The generic kernel interprets the same program on the
+ * GPU and needs no run-time compiler.
+ *   AUTO         specialised kernel; generic kernel if NVRTC cannot be loaded
+ *   GENERIC      always the generic (interpreting) kernel
+ *   SPECIALISED  specialised kernel or an error */
+#define TTLB_ELTWISE_AUTO 0
+#define TTLB_ELTWISE_GENERIC 1
+#define TTLB_ELTWISE_SPECIALISED 2
+TTLB_EXPORT int ttlb_eltwise_set_mode(ttlb_ctx *ctx, int mode);
+/* Which kernel the last successful ttlb_eltwise used: TTLB_ELTWISE_GENERIC or
+ * TTLB_ELTWISE_SPECIALISED; -1 before the first launch. */
+TTLB_EXPORT int ttlb_eltwise_last_path(ttlb_ctx *ctx);
+/* CUDA source of the specialised kernel for `desc` (no GPU needed).  Writes at most
+ * `len` bytes including the terminating NUL; returns the full length needed, or a
+ * negative status for an invalid descriptor. */
+TTLB_EXPORT int64_t ttlb_eltwise_source(const ttlb_eltwise_desc *desc, char *buf, size_t len);
+
 #ifdef __cplusplus
 }
 #endif

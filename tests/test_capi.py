@@ -46,3 +46,30 @@ def test_init_without_gpu_returns_error():
     assert not h.value
     with pytest.raises(capi.BackendError):
         capi.context()
+
+
+def test_specialised_kernel_source_is_generated_without_a_gpu():
+    """ttlb_eltwise_source: the streaming skeleton instantiated for one program."""
+    from ttl_b200 import capi
+    d = capi.EltwiseDesc()
+    d.dtype, d.round_each_op, d.n_in = capi.TTLB_BF16, 0, 4
+    modes = [(capi.IDX_SAME, capi.IDX_SAME), (capi.IDX_ZERO, capi.IDX_ZERO), (capi.IDX_ZERO, capi.IDX_SAME),
+             (capi.IDX_SAME, capi.IDX_SAME)]
+    for k, (rm, cm) in enumerate(modes):
+        d.inp[k].ptr, d.inp[k].ld, d.inp[k].row_mode, d.inp[k].col_mode = 0x10000, 8192, rm, cm
+    ops = [("load", 0), ("mul", 1), ("exp", 0), ("mul", 2), ("add", 3), ("relu", 0)]
+    d.n_ops = len(ops)
+    for k, (op, arg) in enumerate(ops):
+        d.ops[k].opcode, d.ops[k].arg = capi.OPCODES[op], arg
+    d.out, d.out_ld, d.rows, d.cols = 0x20000, 8192, 8192, 8192
+    src = capi.eltwise_source(d)
+    assert 'extern "C" __global__' in src and "expf(a)" in src
+    assert src.count("ld_stream(") == 2 * 4 + 1   # A and C stream, 4 rows in flight per thread (+ the helper's definition)
+    loop = src.index("for (u32 r")
+    assert src.index("v2 = ld_cached") < loop    # the row vector is fetched once, before the row loop
+    assert "pack_bf16x2(acc[e], acc[e + 1])" not in src   # fp32 intermediates: no per-op rounding
+    d.round_each_op = 1
+    assert "pack_bf16x2(acc[e], acc[e + 1])" in capi.eltwise_source(d)
+    d.n_ops = 0
+    with pytest.raises(capi.BackendError):
+        capi.eltwise_source(d)

@@ -1,5 +1,6 @@
 // Context management for the ttlb200 C ABI (include/ttlb200.h).
 #include "ctx.h"
+#include "eltwise_jit.h"
 
 extern "C" {
 
@@ -39,6 +40,7 @@ void ttlb_destroy(ttlb_ctx *ctx) {
     ttlb_device_guard g(ctx->device);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    ttlb_jit_cache_destroy(ctx->jit);
   }
   delete ctx;
 }

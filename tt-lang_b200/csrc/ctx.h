@@ -11,6 +11,8 @@
 
 #include "ttlb200.h"
 
+struct ttlb_jit_cache;
+
 struct ttlb_ctx {
   int device = 0;
   int sm_count = 0;
@@ -21,6 +23,10 @@ struct ttlb_ctx {
   // 0 = ok, otherwise a code telling which wait gave up.
   int *d_status = nullptr;
   int *h_status = nullptr;  // pinned mirror
+  // Element-wise programs: specialised (NVRTC) kernels cached per program signature.
+  ttlb_jit_cache *jit = nullptr;
+  int eltwise_mode = TTLB_ELTWISE_AUTO;
+  int eltwise_last_path = -1;
 };
 
 inline int ttlb_fail(ttlb_ctx *ctx, int code, const char *fmt, ...) {

@@ -10,7 +10,11 @@
 // go through the normal cached path since every row / column re-reads them.
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "ctx.h"
+#include "eltwise_jit.h"
 
 namespace {
 
@@ -193,8 +197,8 @@ bool is_unary(int op) { return op >= TTLB_OP_EXP && op <= TTLB_OP_RELU; }
 
 }  // namespace
 
-extern "C" int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, void *stream) {
-  if (!ctx) return TTLB_ERR_INVALID_ARG;
+// Host-side validation shared by every execution path.  Returns 1 for "valid but empty".
+static int validate_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d) {
   if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: null descriptor");
   if (d->dtype != TTLB_BF16 && d->dtype != TTLB_F32)
     return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "eltwise: dtype %d (bf16 and f32 only)", d->dtype);
@@ -207,7 +211,6 @@ extern "C" int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, void *str
                      TTLB_MAX_OPS);
   if (d->rows < 0 || d->cols < 0 || d->row0 < 0 || d->col0 < 0)
     return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: negative rectangle");
-  if (d->rows == 0 || d->cols == 0) return TTLB_OK;  // empty program: nothing to do
   if (!d->out) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: null output");
   if ((d->cols % vec) || (d->col0 % vec) || (d->out_ld % vec) || ((uintptr_t)d->out % 16))
     return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG,
@@ -257,6 +260,53 @@ extern "C" int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, void *str
   }
   if (depth != 0) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: %d value(s) left on the stack", depth);
 
+  if (d->rows == 0 || d->cols == 0) return 1;  // empty program: nothing to do
+  return TTLB_OK;
+}
+
+extern "C" int ttlb_eltwise_set_mode(ttlb_ctx *ctx, int mode) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  if (mode < TTLB_ELTWISE_AUTO || mode > TTLB_ELTWISE_SPECIALISED)
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: unknown mode %d", mode);
+  ctx->eltwise_mode = mode;
+  return TTLB_OK;
+}
+
+extern "C" int ttlb_eltwise_last_path(ttlb_ctx *ctx) { return ctx ? ctx->eltwise_last_path : -1; }
+
+extern "C" int64_t ttlb_eltwise_source(const ttlb_eltwise_desc *d, char *buf, size_t len) {
+  const int rc = validate_eltwise(nullptr, d);
+  if (rc < 0) return rc;
+  const std::string src = ttlb_eltwise_jit_source(d);
+  if (buf && len) {
+    const size_t n = src.size() < len - 1 ? src.size() : len - 1;
+    memcpy(buf, src.data(), n);
+    buf[n] = 0;
+  }
+  return (int64_t)src.size() + 1;
+}
+
+extern "C" int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  {
+    const int rc = validate_eltwise(ctx, d);
+    if (rc < 0) return rc;
+    if (rc == 1) return TTLB_OK;
+  }
+  const int vec = d->dtype == TTLB_BF16 ? 8 : 4;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  ttlb_device_guard g(ctx->device);
+  if (!g.ok) return ttlb_fail(ctx, TTLB_ERR_CUDA, "eltwise: cannot select device %d", ctx->device);
+  if (ctx->eltwise_mode != TTLB_ELTWISE_GENERIC) {
+    const int rc = ttlb_eltwise_jit_launch(ctx, &ctx->jit, d, s);
+    if (rc == TTLB_OK) {
+      ctx->launches += 1;
+      ctx->eltwise_last_path = TTLB_ELTWISE_SPECIALISED;
+      return TTLB_OK;
+    }
+    // AUTO falls back to the generic GPU kernel only when the run-time compiler is absent
+    if (ctx->eltwise_mode == TTLB_ELTWISE_SPECIALISED || ttlb_eltwise_jit_available()) return rc;
+  }
   const unsigned long long vpr = (unsigned long long)(d->cols / vec);
   if (vpr > 0xffffffffull) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "eltwise: row too long");
   EltParams p;
@@ -272,18 +322,16 @@ extern "C" int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, void *str
   p.vpr = (unsigned)vpr;
   p.items = vpr * (unsigned long long)d->rows;
 
-  ttlb_device_guard g(ctx->device);
-  if (!g.ok) return ttlb_fail(ctx, TTLB_ERR_CUDA, "eltwise: cannot select device %d", ctx->device);
   const unsigned long long want = (p.items + 255ull) / 256ull;
   // Persistent-style grid: a whole number of waves of resident CTAs (4 per SM).
   const unsigned long long resident = (unsigned long long)ctx->sm_count * 4ull;
   const unsigned grid = (unsigned)(want < resident ? want : resident * 2ull < want ? resident * 2ull : resident);
-  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (d->dtype == TTLB_BF16)
     ttlb_eltwise_kernel<true><<<grid, 256, 0, s>>>(p);
   else
     ttlb_eltwise_kernel<false><<<grid, 256, 0, s>>>(p);
   TTLB_CUDA_CHECK(ctx, cudaGetLastError());
   ctx->launches += 1;
+  ctx->eltwise_last_path = TTLB_ELTWISE_GENERIC;
   return TTLB_OK;
 }

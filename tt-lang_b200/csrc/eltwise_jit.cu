@@ -1,0 +1,375 @@
+// Per-program specialisation of the fused element-wise kernel.
+//
+// The reference emits one C++ compute kernel per tile program and lets the device
+// runtime compile it (python/ttl/ttl_api.py:425-440, 556-559: generated source is
+// written out and JIT-compiled by tt-metal, cached by content hash).  The B200
+// counterpart: the hand-written streaming skeleton below is instantiated for one
+// accumulator program - operand addressing modes and the op sequence become
+// straight-line code - compiled for sm_100a with NVRTC (loaded at run time with
+// dlopen, so the library itself has no link dependency on it) and cached per context.
+//
+// Geometry: a CTA is BX x BY threads (BX*BY = 256); thread (tx, ty) owns the
+// 16-byte column vector cv = blockIdx.x*BX + tx and walks rows
+// r = blockIdx.y*BY + ty, += gridDim.y*BY.  No integer division anywhere.  Operands
+// that do not depend on the row (row vectors, scalars) are fetched once before the
+// row loop; streaming operands use evict-first loads, the output evict-first stores.
+// --fmad=false keeps `a*b + c` as two roundings, which is what the simulator computes.
+#include <dlfcn.h>
+
+#include <map>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "ctx.h"
+#include "eltwise_jit.h"
+
+namespace {
+
+// ---- NVRTC through dlopen --------------------------------------------------
+typedef struct _nvrtcProgram *nvrtcProgram;
+struct Nvrtc {
+  void *h = nullptr;
+  int (*CreateProgram)(nvrtcProgram *, const char *, const char *, int, const char *const *,
+                       const char *const *) = nullptr;
+  int (*CompileProgram)(nvrtcProgram, int, const char *const *) = nullptr;
+  int (*GetCUBINSize)(nvrtcProgram, size_t *) = nullptr;
+  int (*GetCUBIN)(nvrtcProgram, char *) = nullptr;
+  int (*GetProgramLogSize)(nvrtcProgram, size_t *) = nullptr;
+  int (*GetProgramLog)(nvrtcProgram, char *) = nullptr;
+  int (*DestroyProgram)(nvrtcProgram *) = nullptr;
+  bool ok = false;
+};
+
+Nvrtc &nvrtc() {
+  static Nvrtc n;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    const char *names[] = {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12",
+                           "/usr/local/cuda/lib64/libnvrtc.so"};
+    for (const char *nm : names) {
+      n.h = dlopen(nm, RTLD_NOW | RTLD_LOCAL);
+      if (n.h) break;
+    }
+    if (!n.h) return;
+#define TTLB_SYM(field, name)                                    \
+  n.field = reinterpret_cast<decltype(n.field)>(dlsym(n.h, name)); \
+  if (!n.field) return;
+    TTLB_SYM(CreateProgram, "nvrtcCreateProgram")
+    TTLB_SYM(CompileProgram, "nvrtcCompileProgram")
+    TTLB_SYM(GetCUBINSize, "nvrtcGetCUBINSize")
+    TTLB_SYM(GetCUBIN, "nvrtcGetCUBIN")
+    TTLB_SYM(GetProgramLogSize, "nvrtcGetProgramLogSize")
+    TTLB_SYM(GetProgramLog, "nvrtcGetProgramLog")
+    TTLB_SYM(DestroyProgram, "nvrtcDestroyProgram")
+#undef TTLB_SYM
+    n.ok = true;
+  });
+  return n;
+}
+
+// ---- launch parameters (must match the struct in the generated source) ------
+struct JitParams {
+  const void *in[TTLB_MAX_IN];
+  long long ld[TTLB_MAX_IN];
+  long long roff[TTLB_MAX_IN];
+  long long coff[TTLB_MAX_IN];
+  void *out;
+  long long out_ld, row0, col0;
+  unsigned vpr, rows, bx_log2, pad;
+};
+
+const char *kPrelude = R"SRC(
+typedef unsigned int u32;
+typedef long long i64;
+struct JitParams {
+  const void* in[6]; i64 ld[6]; i64 roff[6]; i64 coff[6];
+  void* out; i64 out_ld, row0, col0; u32 vpr, rows, bx_log2, pad;
+};
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v; asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_cached(const void* p) {
+  uint4 v; asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" :: "l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ u32 pack_bf16x2(float lo, float hi) {
+  u32 r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r;
+}
+__device__ __forceinline__ float nan_max(float a, float b) { return (a > b || a != a) ? a : b; }
+__device__ __forceinline__ float nan_min(float a, float b) { return (a < b || a != a) ? a : b; }
+)SRC";
+
+const char *binary_expr(int op) {
+  switch (op) {
+    case TTLB_OP_ADD: return "a + b";
+    case TTLB_OP_SUB: return "a - b";
+    case TTLB_OP_RSUB: return "b - a";
+    case TTLB_OP_MUL: return "a * b";
+    case TTLB_OP_DIV: return "a / b";
+    case TTLB_OP_RDIV: return "b / a";
+    case TTLB_OP_MAX: return "nan_max(a, b)";
+    case TTLB_OP_MIN: return "nan_min(a, b)";
+  }
+  return nullptr;
+}
+
+const char *unary_expr(int op) {
+  switch (op) {
+    case TTLB_OP_EXP: return "expf(a)";
+    case TTLB_OP_LOG: return "logf(a)";
+    case TTLB_OP_SQRT: return "sqrtf(a)";
+    case TTLB_OP_RSQRT: return "1.0f / sqrtf(a)";
+    case TTLB_OP_TANH: return "tanhf(a)";
+    case TTLB_OP_SIGMOID: return "1.0f / (1.0f + expf(-a))";
+    case TTLB_OP_NEG: return "-a";
+    case TTLB_OP_ABS: return "fabsf(a)";
+    case TTLB_OP_RELU: return "(a < 0.f ? 0.f : a)";
+  }
+  return nullptr;
+}
+
+// `var` is the register the 16-byte vector lands in, `gi` the name of the row index.
+void emit_load(std::ostringstream &s, const ttlb_eltwise_desc *d, int k, bool bf16, const char *indent,
+               const std::string &var, const std::string &gi) {
+  const ttlb_operand &o = d->in[k];
+  const int esz = bf16 ? 2 : 4;
+  std::string row = o.row_mode == TTLB_IDX_SAME   ? "(" + gi + " + p.roff[" + std::to_string(k) + "])"
+                    : o.row_mode == TTLB_IDX_ZERO ? std::string("0")
+                                                  : "(p.roff[" + std::to_string(k) + "] + (" + gi + " & 31))";
+  s << indent << "{ const char* rp = (const char*)p.in[" << k << "] + " << row << " * p.ld[" << k << "] * " << esz
+    << ";\n";
+  if (o.col_mode == TTLB_IDX_ZERO) {
+    if (bf16)
+      s << indent << "  u32 h = *(const unsigned short*)rp; h |= h << 16; " << var << " = make_uint4(h, h, h, h); }\n";
+    else
+      s << indent << "  u32 w = *(const u32*)rp; " << var << " = make_uint4(w, w, w, w); }\n";
+    return;
+  }
+  std::string col = o.col_mode == TTLB_IDX_SAME ? "(gj + p.coff[" + std::to_string(k) + "])"
+                                                : "(p.coff[" + std::to_string(k) + "] + (gj & 31))";
+  const bool stream = o.row_mode == TTLB_IDX_SAME && o.col_mode == TTLB_IDX_SAME;
+  s << indent << "  " << var << " = " << (stream ? "ld_stream" : "ld_cached") << "(rp + " << col << " * " << esz
+    << "); }\n";
+}
+
+void emit_unpack(std::ostringstream &s, const std::string &var, const char *dst, bool bf16) {
+  static const char *comp[4] = {"x", "y", "z", "w"};
+  for (int q = 0; q < 4; ++q) {
+    if (bf16) {
+      s << "        " << dst << "[" << 2 * q << "] = __uint_as_float(" << var << "." << comp[q] << " << 16); " << dst
+        << "[" << 2 * q + 1 << "] = __uint_as_float(" << var << "." << comp[q] << " & 0xffff0000u);\n";
+    } else {
+      s << "        " << dst << "[" << q << "] = __uint_as_float(" << var << "." << comp[q] << ");\n";
+    }
+  }
+}
+
+// Rows handled per loop iteration: all their loads are issued before any arithmetic, so a
+// thread keeps U x (streaming operands) 16-byte loads in flight.  Bounded by registers.
+int rows_per_iteration(const ttlb_eltwise_desc *d) {
+  int streaming = 0;
+  for (int k = 0; k < d->n_in; ++k)
+    if (d->in[k].row_mode != TTLB_IDX_ZERO) ++streaming;
+  int u = 8 / (streaming > 0 ? streaming : 1);
+  return u < 1 ? 1 : u > 4 ? 4 : u;
+}
+
+}  // namespace
+
+std::string ttlb_eltwise_jit_key(const ttlb_eltwise_desc *d) {
+  std::ostringstream k;
+  k << d->dtype << ':' << (d->round_each_op ? 1 : 0) << ':' << d->n_in << ':';
+  for (int i = 0; i < d->n_in; ++i) k << d->in[i].row_mode << d->in[i].col_mode << ',';
+  k << ':';
+  for (int i = 0; i < d->n_ops; ++i) k << d->ops[i].opcode << '/' << d->ops[i].arg << ',';
+  return k.str();
+}
+
+std::string ttlb_eltwise_jit_source(const ttlb_eltwise_desc *d) {
+  const bool bf16 = d->dtype == TTLB_BF16;
+  const int V = bf16 ? 8 : 4;
+  const bool rnd = bf16 && d->round_each_op;
+  std::ostringstream s;
+  s << kPrelude;
+  s << "#define V " << V << "\n";
+  s << "extern \"C\" __global__ void __launch_bounds__(256) ttlb_eltwise_jit(const __grid_constant__ JitParams p) {\n"
+       "  const u32 tx = threadIdx.x & ((1u << p.bx_log2) - 1u), ty = threadIdx.x >> p.bx_log2;\n"
+       "  const u32 by = 256u >> p.bx_log2;\n"
+       "  const u32 cv = (blockIdx.x << p.bx_log2) + tx;\n"
+       "  if (cv >= p.vpr) return;\n"
+       "  const i64 gj = p.col0 + (i64)cv * V;\n";
+  const int U = rows_per_iteration(d);
+  auto var = [&](int k, int u) {
+    return d->in[k].row_mode == TTLB_IDX_ZERO ? "v" + std::to_string(k) : "v" + std::to_string(k) + "_" + std::to_string(u);
+  };
+  // row-invariant operands: fetched once
+  for (int k = 0; k < d->n_in; ++k)
+    if (d->in[k].row_mode == TTLB_IDX_ZERO) {
+      s << "  uint4 v" << k << ";\n";
+      emit_load(s, d, k, bf16, "  ", "v" + std::to_string(k), "0");
+    }
+  s << "  const u32 rstride = gridDim.y * by;\n"
+       "  for (u32 r = blockIdx.y * by + ty; r < p.rows; r += rstride * " << U << ") {\n";
+  for (int u = 0; u < U; ++u) {
+    s << "    const i64 gi" << u << " = p.row0 + (i64)r + (i64)rstride * " << u << ";\n";
+    if (u) s << "    const bool ok" << u << " = r + rstride * " << u << " < p.rows;\n";
+  }
+  for (int u = 0; u < U; ++u)
+    for (int k = 0; k < d->n_in; ++k)
+      if (d->in[k].row_mode != TTLB_IDX_ZERO) {
+        s << "    uint4 " << var(k, u) << " = make_uint4(0, 0, 0, 0);\n";
+        if (u) s << "    if (ok" << u << ")\n";
+        emit_load(s, d, k, bf16, "    ", var(k, u), "gi" + std::to_string(u));
+      }
+  for (int u = 0; u < U; ++u) {
+    s << "    " << (u ? "if (ok" + std::to_string(u) + ") " : "") << "{  // row " << u << "\n";
+    s << "      float acc[V], x[V], stk0[V], stk1[V];\n"
+         "      (void)x; (void)stk0; (void)stk1;\n";
+    int depth = 0;
+    for (int pc = 0; pc < d->n_ops; ++pc) {
+      const int op = d->ops[pc].opcode, arg = d->ops[pc].arg;
+      s << "      {  // op " << pc << "\n";
+      if (op == TTLB_OP_LOAD) {
+        emit_unpack(s, var(arg, u), "acc", bf16);
+      } else if (op == TTLB_OP_PUSH) {
+        s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) stk" << depth << "[e] = acc[e];\n";
+        ++depth;
+      } else if (const char *be = binary_expr(op)) {
+        if (arg >= 0) {
+          emit_unpack(s, var(arg, u), "x", bf16);
+        } else {
+          --depth;
+          s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) x[e] = stk" << depth << "[e];\n";
+        }
+        s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { const float a = acc[e], b = x[e]; acc[e] = "
+          << be << "; }\n";
+      } else if (const char *ue = unary_expr(op)) {
+        s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { const float a = acc[e]; acc[e] = " << ue
+          << "; }\n";
+      }
+      if (rnd && op != TTLB_OP_LOAD && op != TTLB_OP_PUSH) {
+        s << "        _Pragma(\"unroll\") for (int e = 0; e < V; e += 2) { const u32 w = pack_bf16x2(acc[e], acc[e + 1]); "
+             "acc[e] = __uint_as_float(w << 16); acc[e + 1] = __uint_as_float(w & 0xffff0000u); }\n";
+      }
+      s << "      }\n";
+    }
+    s << "      uint4 o;\n";
+    if (bf16) {
+      s << "      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);\n"
+           "      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);\n";
+    } else {
+      s << "      o.x = __float_as_uint(acc[0]); o.y = __float_as_uint(acc[1]);\n"
+           "      o.z = __float_as_uint(acc[2]); o.w = __float_as_uint(acc[3]);\n";
+    }
+    s << "      st_stream((char*)p.out + (gi" << u << " * p.out_ld + gj) * " << (bf16 ? 2 : 4) << ", o);\n";
+    s << "    }\n";
+  }
+  s << "  }\n}\n";
+  return s.str();
+}
+
+bool ttlb_eltwise_jit_available() { return nvrtc().ok; }
+
+struct JitKernel {
+  cudaKernel_t kern;
+  int blocks_per_sm;  // resident 256-thread CTAs per SM
+};
+
+struct ttlb_jit_cache {
+  std::map<std::string, JitKernel> kernels;
+  std::vector<cudaLibrary_t> libs;
+};
+
+void ttlb_jit_cache_destroy(ttlb_jit_cache *c) {
+  if (!c) return;
+  for (cudaLibrary_t l : c->libs) cudaLibraryUnload(l);
+  delete c;
+}
+
+// Returns TTLB_OK and launches, or an error (the caller may then use the interpreter).
+int ttlb_eltwise_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_eltwise_desc *d, cudaStream_t stream) {
+  Nvrtc &n = nvrtc();
+  if (!n.ok) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "eltwise: NVRTC (libnvrtc.so.12) is not available");
+  if (!*cachep) *cachep = new ttlb_jit_cache();
+  ttlb_jit_cache *cache = *cachep;
+  const std::string key = ttlb_eltwise_jit_key(d);
+  auto it = cache->kernels.find(key);
+  JitKernel jk;
+  if (it == cache->kernels.end()) {
+    cudaKernel_t kern;
+    const std::string src = ttlb_eltwise_jit_source(d);
+    nvrtcProgram prog;
+    if (n.CreateProgram(&prog, src.c_str(), "ttlb_eltwise_jit.cu", 0, nullptr, nullptr) != 0)
+      return ttlb_fail(ctx, TTLB_ERR_CUDA, "eltwise: nvrtcCreateProgram failed");
+    const char *opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "-lineinfo", "--std=c++17"};
+    const int rc = n.CompileProgram(prog, 4, opts);
+    if (rc != 0) {
+      size_t ls = 0;
+      n.GetProgramLogSize(prog, &ls);
+      std::string log(ls, '\0');
+      if (ls) n.GetProgramLog(prog, log.data());
+      n.DestroyProgram(&prog);
+      return ttlb_fail(ctx, TTLB_ERR_CUDA, "eltwise: NVRTC compile failed: %.400s", log.c_str());
+    }
+    size_t cs = 0;
+    n.GetCUBINSize(prog, &cs);
+    std::vector<char> cubin(cs);
+    n.GetCUBIN(prog, cubin.data());
+    n.DestroyProgram(&prog);
+    cudaLibrary_t lib;
+    TTLB_CUDA_CHECK(ctx, cudaLibraryLoadData(&lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+    cudaError_t e = cudaLibraryGetKernel(&kern, lib, "ttlb_eltwise_jit");
+    if (e != cudaSuccess) {
+      cudaLibraryUnload(lib);
+      return ttlb_fail(ctx, TTLB_ERR_CUDA, "eltwise: cudaLibraryGetKernel failed: %s", cudaGetErrorString(e));
+    }
+    cache->libs.push_back(lib);
+    jk.kern = kern;
+    jk.blocks_per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&jk.blocks_per_sm, reinterpret_cast<const void *>(kern), 256, 0) !=
+            cudaSuccess ||
+        jk.blocks_per_sm < 1) {
+      cudaGetLastError();
+      jk.blocks_per_sm = 4;
+    }
+    cache->kernels[key] = jk;
+  } else {
+    jk = it->second;
+  }
+
+  const int vec = d->dtype == TTLB_BF16 ? 8 : 4;
+  JitParams p{};
+  for (int k = 0; k < d->n_in; ++k) {
+    p.in[k] = d->in[k].ptr;
+    p.ld[k] = d->in[k].ld;
+    p.roff[k] = d->in[k].row_off;
+    p.coff[k] = d->in[k].col_off;
+  }
+  p.out = d->out;
+  p.out_ld = d->out_ld;
+  p.row0 = d->row0;
+  p.col0 = d->col0;
+  p.vpr = (unsigned)(d->cols / vec);
+  p.rows = (unsigned)d->rows;
+  unsigned bx_log2 = 0;
+  while (bx_log2 < 8 && (1u << bx_log2) < p.vpr) ++bx_log2;
+  p.bx_log2 = bx_log2;
+  const unsigned bx = 1u << bx_log2, by = 256u / bx;
+  const unsigned gx = (p.vpr + bx - 1) / bx;
+  const unsigned row_blocks = (p.rows + by - 1) / by;
+  // exactly one wave of resident CTAs: no tail wave at reduced occupancy
+  unsigned gy = (unsigned)(ctx->sm_count * jk.blocks_per_sm) / (gx ? gx : 1);
+  if (gy < 1) gy = 1;
+  if (gy > row_blocks) gy = row_blocks;
+  if (gy > 65535u) gy = 65535u;
+  void *args[] = {&p};
+  TTLB_CUDA_CHECK(ctx, cudaLaunchKernel(reinterpret_cast<const void *>(jk.kern), dim3(gx, gy, 1), dim3(256, 1, 1), args, 0,
+                                        stream));
+  return TTLB_OK;
+}

@@ -1,0 +1,17 @@
+// Internal interface of the per-program specialiser (eltwise_jit.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <string>
+
+#include "ttlb200.h"
+
+struct ttlb_ctx;
+struct ttlb_jit_cache;
+
+bool ttlb_eltwise_jit_available();
+std::string ttlb_eltwise_jit_key(const ttlb_eltwise_desc *d);
+std::string ttlb_eltwise_jit_source(const ttlb_eltwise_desc *d);
+int ttlb_eltwise_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cache, const ttlb_eltwise_desc *d, cudaStream_t stream);
+void ttlb_jit_cache_destroy(ttlb_jit_cache *c);

@@ -46,6 +46,20 @@ class EltwiseDesc(C.Structure):
                 ("row0", C.c_int64), ("col0", C.c_int64), ("rows", C.c_int64), ("cols", C.c_int64)]
 
 
+ELTWISE_AUTO, ELTWISE_GENERIC, ELTWISE_SPECIALISED = 0, 1, 2
+
+
+def eltwise_source(desc: "EltwiseDesc") -> str:
+    """CUDA source of the kernel specialised for `desc` (works without a GPU)."""
+    l = lib()
+    n = l.ttlb_eltwise_source(C.byref(desc), None, 0)
+    if n < 0:
+        raise BackendError(int(n), "invalid element-wise descriptor")
+    buf = C.create_string_buffer(int(n))
+    l.ttlb_eltwise_source(C.byref(desc), buf, int(n))
+    return buf.value.decode()
+
+
 class BackendError(RuntimeError):
     """A C-ABI call returned a negative status."""
 
@@ -79,6 +93,12 @@ def lib() -> C.CDLL:
     l.ttlb_launch_count.restype = C.c_int64
     l.ttlb_eltwise.argtypes = [C.c_void_p, C.POINTER(EltwiseDesc), C.c_void_p]
     l.ttlb_eltwise.restype = C.c_int
+    l.ttlb_eltwise_set_mode.argtypes = [C.c_void_p, C.c_int]
+    l.ttlb_eltwise_set_mode.restype = C.c_int
+    l.ttlb_eltwise_last_path.argtypes = [C.c_void_p]
+    l.ttlb_eltwise_last_path.restype = C.c_int
+    l.ttlb_eltwise_source.argtypes = [C.POINTER(EltwiseDesc), C.c_char_p, C.c_size_t]
+    l.ttlb_eltwise_source.restype = C.c_int64
     _LIB = l
     return l
 
@@ -105,6 +125,13 @@ class Context:
 
     def eltwise(self, desc: EltwiseDesc, stream: int) -> None:
         self.check(self._lib.ttlb_eltwise(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def set_eltwise_mode(self, mode: int) -> None:
+        """ELTWISE_AUTO / ELTWISE_GENERIC / ELTWISE_SPECIALISED (include/ttlb200.h)."""
+        self.check(self._lib.ttlb_eltwise_set_mode(self.handle, mode))
+
+    def eltwise_last_path(self) -> int:
+        return int(self._lib.ttlb_eltwise_last_path(self.handle))
 
     def close(self) -> None:
         if self.handle:
