@@ -174,6 +174,40 @@ TTLB_EXPORT int ttlb_eltwise_last_path(ttlb_ctx *ctx);
  * negative status for an invalid descriptor. */
 TTLB_EXPORT int64_t ttlb_eltwise_source(const ttlb_eltwise_desc *desc, char *buf, size_t len);
 
+/* ------------------------------------------------------------------------ *
+ * Matmul tile programs: C[M,N] = A[M,K] x B[K,N], bf16 in, fp32 accumulate,
+ * bf16 out, all row-major.
+ *
+ * Replaces the accumulate-over-K program `out_blk.store(a_blk @ b_blk, acc=True)`
+ * (examples/singlecore_matmul.py:36-45, examples/multicore_matmul.py:92-139) and
+ * the Tensix kernels it stands for: reader / matmul_tiles compute / writer
+ * (examples/metal_examples/multicore_matmul/metal/kernels/mm_reader.cpp:39-68,
+ * mm_compute.cpp:30-65, mm_writer.cpp:29-42).
+ * To compute a sub-rectangle of a larger output, pass pointers to its first
+ * element and the full row pitches.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void *a; /* bf16 [m, k] */
+  int64_t lda;   /* row pitches in elements */
+  const void *b; /* bf16 [k, n] */
+  int64_t ldb;
+  void *c; /* bf16 [m, n] */
+  int64_t ldc;
+  int64_t m, n, k; /* k, n and the pitches must be multiples of 8 */
+} ttlb_gemm_desc;
+
+TTLB_EXPORT int ttlb_matmul_bf16(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, void *stream);
+
+/* Kernels that wait on hardware barriers (matmul, attention) bound every wait; when
+ * one runs out the kernel unwinds normally and records which role gave up.
+ * ttlb_check_status synchronises `stream`, returns TTLB_ERR_TIMEOUT if that happened
+ * since the last check (and clears the record), else TTLB_OK.  The reference's
+ * simulator bounds its waits the same way (CB_DEFAULT_TIMEOUT / COPY_PIPE_TIMEOUT,
+ * python/sim/constants.py:47-48). */
+TTLB_EXPORT int ttlb_check_status(ttlb_ctx *ctx, void *stream);
+/* Bound of a device-side wait in SM clock cycles (default 4e9, about two seconds). */
+TTLB_EXPORT int ttlb_set_wait_limit(ttlb_ctx *ctx, int64_t cycles);
+
 #ifdef __cplusplus
 }
 #endif

@@ -27,6 +27,10 @@ struct ttlb_ctx {
   ttlb_jit_cache *jit = nullptr;
   int eltwise_mode = TTLB_ELTWISE_AUTO;
   int eltwise_last_path = -1;
+  // tcgen05 kernels: opt-in shared memory set once per context; bound for device-side waits
+  bool gemm_attr_set = false;
+  bool attn_attr_set = false;
+  long long wait_limit_cycles = 4000000000LL;  // ~2 s at 1.9 GHz
 };
 
 inline int ttlb_fail(ttlb_ctx *ctx, int code, const char *fmt, ...) {

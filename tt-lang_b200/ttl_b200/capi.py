@@ -46,6 +46,11 @@ class EltwiseDesc(C.Structure):
                 ("row0", C.c_int64), ("col0", C.c_int64), ("rows", C.c_int64), ("cols", C.c_int64)]
 
 
+class GemmDesc(C.Structure):
+    _fields_ = [("a", C.c_void_p), ("lda", C.c_int64), ("b", C.c_void_p), ("ldb", C.c_int64),
+                ("c", C.c_void_p), ("ldc", C.c_int64), ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64)]
+
+
 ELTWISE_AUTO, ELTWISE_GENERIC, ELTWISE_SPECIALISED = 0, 1, 2
 
 
@@ -99,6 +104,12 @@ def lib() -> C.CDLL:
     l.ttlb_eltwise_last_path.restype = C.c_int
     l.ttlb_eltwise_source.argtypes = [C.POINTER(EltwiseDesc), C.c_char_p, C.c_size_t]
     l.ttlb_eltwise_source.restype = C.c_int64
+    l.ttlb_matmul_bf16.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]
+    l.ttlb_matmul_bf16.restype = C.c_int
+    l.ttlb_check_status.argtypes = [C.c_void_p, C.c_void_p]
+    l.ttlb_check_status.restype = C.c_int
+    l.ttlb_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
+    l.ttlb_set_wait_limit.restype = C.c_int
     _LIB = l
     return l
 
@@ -125,6 +136,16 @@ class Context:
 
     def eltwise(self, desc: EltwiseDesc, stream: int) -> None:
         self.check(self._lib.ttlb_eltwise(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def matmul_bf16(self, desc: "GemmDesc", stream: int) -> None:
+        self.check(self._lib.ttlb_matmul_bf16(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def check_status(self, stream: int = 0) -> None:
+        """Synchronise `stream` and raise if a bounded device-side wait ran out since the last check."""
+        self.check(self._lib.ttlb_check_status(self.handle, C.c_void_p(stream)))
+
+    def set_wait_limit(self, cycles: int) -> None:
+        self.check(self._lib.ttlb_set_wait_limit(self.handle, cycles))
 
     def set_eltwise_mode(self, mode: int) -> None:
         """ELTWISE_AUTO / ELTWISE_GENERIC / ELTWISE_SPECIALISED (include/ttlb200.h)."""

@@ -1,13 +1,52 @@
-"""Operator-level entry points over the C ABI (used by recognised programs and by
-callers that already know which kernel they want)."""
+"""Operator-level entry points over the C ABI: used by recognised programs, and directly by
+callers that already know which kernel they want (the way a `ttnn` op is called next to a
+tt-lang kernel in the reference's examples, e.g. ttnn.multiply in examples/general_broadcast.py:184)."""
 
 from __future__ import annotations
 
-from typing import Any, Tuple
+from typing import Any, Optional, Tuple
+
+import torch
 
 from . import capi
+from . import ttnn as _ttnn
 from .recognize import Unsupported
 
 
-def launch_gemm(ctx: capi.Context, a: Any, b: Any, out: Any, rect: Tuple[int, int, int, int], stream: int) -> None:
-    raise Unsupported("matmul kernels are not built into this library yet")
+def _dev2d(t: "_ttnn.Tensor", what: str) -> torch.Tensor:
+    x = t._tensor
+    if not x.is_cuda:
+        raise capi.BackendError(capi.TTLB_ERR_CUDA, f"{what} is not in GPU memory: the B200 backend has no CPU fallback")
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise Unsupported(f"{what} must be 2-D with unit column stride")
+    return x
+
+
+def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_ttnn.Tensor",
+                rect: Tuple[int, int, int, int], stream: int) -> None:
+    """out[r0:r1, c0:c1] = a[r0:r1, :] @ b[:, c0:c1] (element coordinates)."""
+    r0, r1, c0, c1 = rect
+    if b._packed is not None:
+        raise Unsupported("bfloat8_b weights: kernel not built into this library yet")
+    xa, xb, xo = _dev2d(a, "A"), _dev2d(b, "B"), _dev2d(out, "out")
+    if xa.dtype != torch.bfloat16 or xb.dtype != torch.bfloat16 or xo.dtype != torch.bfloat16:
+        raise Unsupported("matmul: bfloat16 tensors only")
+    d = capi.GemmDesc()
+    es = 2
+    d.a, d.lda = xa.data_ptr() + r0 * xa.stride(0) * es, xa.stride(0)
+    d.b, d.ldb = xb.data_ptr() + c0 * es, xb.stride(0)
+    d.c, d.ldc = xo.data_ptr() + (r0 * xo.stride(0) + c0) * es, xo.stride(0)
+    d.m, d.n, d.k = r1 - r0, c1 - c0, xa.shape[1]
+    ctx.matmul_bf16(d, stream)
+
+
+def matmul(a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: Optional["_ttnn.Tensor"] = None) -> "_ttnn.Tensor":
+    """C = A @ B on the tensor cores (bf16 in, fp32 accumulate, bf16 out)."""
+    m, n = a.shape[0], b.shape[1]
+    if a.shape[1] != b.shape[0]:
+        raise ValueError(f"Incompatible matrix shapes for multiplication: {a.shape} @ {b.shape}")
+    if out is None:
+        out = _ttnn.empty((m, n), dtype=_ttnn.bfloat16)
+    dev = a._tensor.device.index if a._tensor.is_cuda else None
+    launch_gemm(capi.context(dev), a, b, out, (0, m, 0, n), capi.current_stream())
+    return out
