@@ -198,6 +198,44 @@ typedef struct {
 
 TTLB_EXPORT int ttlb_matmul_bf16(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, void *stream);
 
+/* ------------------------------------------------------------------------ *
+ * bfloat8_b block-float weights (quantised inference GEMM):
+ * C[M,N] = A[M,K] (bf16) x W[K,N] where W is stored as 1088-byte bfloat8_b tiles.
+ *
+ * The reference only fixes the tile size, 1088 bytes = 1024 value bytes + 64 shared
+ * exponents, one per 16 values (python/ttl/dtype_utils.py:174-175); it has no
+ * pack/unpack code of its own.  The complete byte layout used by this library is
+ * written down at the top of csrc/bfp8.cu: tiles in row-major tile order, four
+ * 16x16 faces per tile, a block = 16 consecutive values of one face row, exponent =
+ * largest biased fp32 exponent of the block, value byte = sign | 7-bit magnitude,
+ * value = (-1)^s * m * 2^(E-133), round-to-nearest-even, saturating.
+ * ------------------------------------------------------------------------ */
+/* Host-side packer / unpacker (plain CPU code; rows and cols multiples of 32).
+ * dst_tiles must hold (rows/32)*(cols/32)*1088 bytes.  Inf/NaN inputs are rejected. */
+TTLB_EXPORT int ttlb_pack_bfp8_b(const float *src, int64_t rows, int64_t cols, uint8_t *dst_tiles);
+TTLB_EXPORT int ttlb_unpack_bfp8_b(const uint8_t *tiles, int64_t rows, int64_t cols, float *dst);
+/* Device-side unpack of the column window [32*tile_col0, 32*tile_col0 + n) of a packed
+ * [k, 32*tile_cols_total] matrix into a row-major bf16 [k, n] array of pitch ld (exact:
+ * every bfloat8_b value is representable in bf16). */
+TTLB_EXPORT int ttlb_unpack_bfp8_b_device(ttlb_ctx *ctx, const void *tiles, int64_t tile_cols_total,
+                                          int64_t tile_col0, int64_t k, int64_t n, void *out_bf16, int64_t ld,
+                                          void *stream);
+
+typedef struct {
+  const void *a; /* bf16 [m, k] activations, row-major */
+  int64_t lda;
+  const void *b_tiles;  /* packed bfloat8_b weights of a [k, 32*b_tile_cols] matrix (device memory) */
+  int64_t b_tile_cols;  /* tile columns of the whole packed matrix */
+  int64_t b_tile_col0;  /* first tile column used: output column j reads weight column 32*b_tile_col0 + j */
+  void *c; /* bf16 [m, n] */
+  int64_t ldc;
+  int64_t m, n, k; /* n and k multiples of 32 */
+} ttlb_gemm_bfp8_desc;
+
+/* Expands the weight window to bf16 in scratch memory owned by the context (allocated on
+ * first use, grown when a larger window arrives), then runs the tensor-core GEMM. */
+TTLB_EXPORT int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, void *stream);
+
 /* Kernels that wait on hardware barriers (matmul, attention) bound every wait; when
  * one runs out the kernel unwinds normally and records which role gave up.
  * ttlb_check_status synchronises `stream`, returns TTLB_ERR_TIMEOUT if that happened

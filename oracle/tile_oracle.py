@@ -83,7 +83,7 @@ def matmul_tiles(a: torch.Tensor, b: torch.Tensor, mode: str) -> torch.Tensor:
     dt = a.dtype
     if mode == "f32":
         a, b = a.to(torch.float32), b.to(torch.float32)
-    kt = a.shape[1] // TILE
+    kt = -(-a.shape[1] // TILE)   # a ragged last K slab (C-ABI callers may pass K % 32 != 0) is one more step
     acc = None
     for k in range(kt):
         p = a[:, k * TILE:(k + 1) * TILE] @ b[k * TILE:(k + 1) * TILE, :]

@@ -1,0 +1,87 @@
+"""GPU parity for bfloat8_b weights: device unpack is bit-exact against the oracle, and the
+bfp8-weight matmul matches the oracle (dequantised weights, fp32-accumulated tile matmul) within
+1e-2, both through the C ABI and through a tt-lang matmul program whose B tensor is bfloat8_b."""
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import bfp8_oracle, tile_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def rel_err(got, want):
+    return ((got.float() - want.float()).abs().max() / want.float().abs().max()).item()
+
+
+@pytest.mark.parametrize("k,n,col0,cols", [(32, 32, 0, 32), (96, 160, 0, 160), (128, 256, 64, 128), (4096, 512, 32, 448)])
+def test_device_unpack_is_bit_exact(k, n, col0, cols):
+    from ttl_b200 import bfp8, capi
+    w = cases.gen((k, n), "normal*0.02", 1, torch.float32)
+    w[0, :16] = torch.tensor([1e-30] * 8 + [3e-39] * 8)[: 16]   # a block with a tiny exponent
+    tiles = bfp8.pack_bfp8_b(w)
+    want = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))[:, col0:col0 + cols]
+    out = torch.full((k, cols + 8), 9.0, dtype=torch.bfloat16, device="cuda")
+    dev = tiles.cuda()
+    ctx = capi.context()
+    ctx.unpack_bfp8_b(dev.data_ptr(), n // 32, col0 // 32, k, cols, out.data_ptr(), out.stride(0), capi.current_stream())
+    torch.cuda.synchronize()
+    got = out.cpu()
+    assert torch.equal(got[:, :cols].float(), want), "device unpack differs from the oracle"
+    assert (got[:, cols:] == 9.0).all(), "unpack wrote outside its window"
+
+
+@pytest.mark.parametrize("m,k,n", [(64, 128, 96), (256, 512, 1024), (160, 2048, 608)])
+def test_c_abi_matmul_bfp8w(m, k, n):
+    from ttl_b200 import capi, ops, ttnn
+    x = cases.gen((m, k), "normal", 0)
+    w = cases.gen((k, n), "normal*0.02", 1, torch.float32)
+    wq = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))
+    want = tile_oracle.matmul_tiles(x.float(), wq, "f32")
+    W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+    got = ttnn.to_torch(ops.matmul(ttnn.from_torch(x), W))
+    capi.context().check_status(capi.current_stream())
+    assert rel_err(got, want) <= 1e-2
+    # a column window of the same weights (what an N-sharded rank computes)
+    if n >= 96:
+        out = ttnn.from_torch(torch.zeros((m, n), dtype=torch.bfloat16))
+        ops.launch_gemm(capi.context(), ttnn.from_torch(x), W, out, (0, m, 32, 96), capi.current_stream())
+        got2 = ttnn.to_torch(out)
+        assert rel_err(got2[:, 32:96], want[:, 32:96]) <= 1e-2
+        assert (got2[:, :32] == 0).all() and (got2[:, 96:] == 0).all()
+
+
+def test_matmul_program_with_bfloat8_b_weights(backend):
+    """The multicore matmul tile program, unchanged, with B given as a bfloat8_b tensor."""
+    _, mods = backend
+    import ttnn
+    from ttl_b200 import capi
+    m, k, n = 128, 256, 192
+    x = cases.gen((m, k), "normal", 2)
+    w = cases.gen((k, n), "normal*0.02", 3, torch.float32)
+    wq = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))
+    out = ttnn.from_torch(torch.zeros((m, n), dtype=torch.bfloat16))
+    W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+    prog = mods["matmul"].multicore_matmul
+    assert prog.plan(ttnn.from_torch(x), W, out).describe()[0]["kind"] == "matmul_bfp8w"
+    prog(ttnn.from_torch(x), W, out)
+    capi.context().check_status(capi.current_stream())
+    assert rel_err(ttnn.to_torch(out), tile_oracle.matmul_tiles(x.float(), wq, "f32")) <= 1e-2
+
+
+def test_config4_shard_slab():
+    """configs[3] shapes on one 2048-column stripe (what one of 14 column blocks looks like) with 256
+    activation rows checked against the oracle, plus the full 4096 rows for the exact-scaling property."""
+    from ttl_b200 import capi, ops, ttnn
+    k, n = 8192, 2048
+    x = cases.gen((4096, k), "normal", 0)
+    w = cases.gen((k, n), "normal*0.02", 1, torch.float32)
+    wq = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))
+    W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+    got = ttnn.to_torch(ops.matmul(ttnn.from_torch(x), W))
+    capi.context().check_status(capi.current_stream())
+    assert rel_err(got[:256], tile_oracle.matmul_tiles(x[:256].float(), wq, "f32")) <= 1e-2
+    got2 = ttnn.to_torch(ops.matmul(ttnn.from_torch(x * 2), W))
+    assert torch.equal(got2, got * 2)

@@ -40,6 +40,7 @@ void ttlb_destroy(ttlb_ctx *ctx) {
     ttlb_device_guard g(ctx->device);
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    if (ctx->scratch) cudaFree(ctx->scratch);
     ttlb_jit_cache_destroy(ctx->jit);
   }
   delete ctx;

@@ -31,6 +31,9 @@ struct ttlb_ctx {
   bool gemm_attr_set = false;
   bool attn_attr_set = false;
   long long wait_limit_cycles = 4000000000LL;  // ~2 s at 1.9 GHz
+  // Scratch in HBM owned by the context (bf16 expansion of bfloat8_b weights); grows on demand.
+  void *scratch = nullptr;
+  size_t scratch_bytes = 0;
 };
 
 inline int ttlb_fail(ttlb_ctx *ctx, int code, const char *fmt, ...) {

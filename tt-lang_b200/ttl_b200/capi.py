@@ -51,6 +51,12 @@ class GemmDesc(C.Structure):
                 ("c", C.c_void_p), ("ldc", C.c_int64), ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64)]
 
 
+class GemmBfp8Desc(C.Structure):
+    _fields_ = [("a", C.c_void_p), ("lda", C.c_int64), ("b_tiles", C.c_void_p), ("b_tile_cols", C.c_int64),
+                ("b_tile_col0", C.c_int64), ("c", C.c_void_p), ("ldc", C.c_int64),
+                ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64)]
+
+
 ELTWISE_AUTO, ELTWISE_GENERIC, ELTWISE_SPECIALISED = 0, 1, 2
 
 
@@ -106,6 +112,15 @@ def lib() -> C.CDLL:
     l.ttlb_eltwise_source.restype = C.c_int64
     l.ttlb_matmul_bf16.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]
     l.ttlb_matmul_bf16.restype = C.c_int
+    l.ttlb_pack_bfp8_b.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+    l.ttlb_pack_bfp8_b.restype = C.c_int
+    l.ttlb_unpack_bfp8_b.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+    l.ttlb_unpack_bfp8_b.restype = C.c_int
+    l.ttlb_unpack_bfp8_b_device.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                            C.c_void_p, C.c_int64, C.c_void_p]
+    l.ttlb_unpack_bfp8_b_device.restype = C.c_int
+    l.ttlb_matmul_bfp8w.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p]
+    l.ttlb_matmul_bfp8w.restype = C.c_int
     l.ttlb_check_status.argtypes = [C.c_void_p, C.c_void_p]
     l.ttlb_check_status.restype = C.c_int
     l.ttlb_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
@@ -139,6 +154,14 @@ class Context:
 
     def matmul_bf16(self, desc: "GemmDesc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_bf16(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def matmul_bfp8w(self, desc: "GemmBfp8Desc", stream: int) -> None:
+        self.check(self._lib.ttlb_matmul_bfp8w(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def unpack_bfp8_b(self, tiles_ptr: int, tile_cols_total: int, tile_col0: int, k: int, n: int, out_ptr: int,
+                      ld: int, stream: int) -> None:
+        self.check(self._lib.ttlb_unpack_bfp8_b_device(self.handle, C.c_void_p(tiles_ptr), tile_cols_total, tile_col0,
+                                                       k, n, C.c_void_p(out_ptr), ld, C.c_void_p(stream)))
 
     def check_status(self, stream: int = 0) -> None:
         """Synchronise `stream` and raise if a bounded device-side wait ran out since the last check."""

@@ -27,7 +27,20 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
     """out[r0:r1, c0:c1] = a[r0:r1, :] @ b[:, c0:c1] (element coordinates)."""
     r0, r1, c0, c1 = rect
     if b._packed is not None:
-        raise Unsupported("bfloat8_b weights: kernel not built into this library yet")
+        xa, xo = _dev2d(a, "A"), _dev2d(out, "out")
+        if xa.dtype != torch.bfloat16 or xo.dtype != torch.bfloat16:
+            raise Unsupported("matmul with bfloat8_b weights: bfloat16 activations and output only")
+        if not b._packed.is_cuda:
+            raise capi.BackendError(capi.TTLB_ERR_CUDA, "weights are not in GPU memory: the B200 backend has no CPU fallback")
+        if c0 % 32 or c1 % 32:
+            raise Unsupported("bfloat8_b weights are addressed in whole 32-column tiles")
+        g = capi.GemmBfp8Desc()
+        g.a, g.lda = xa.data_ptr() + r0 * xa.stride(0) * 2, xa.stride(0)
+        g.b_tiles, g.b_tile_cols, g.b_tile_col0 = b._packed.data_ptr(), b.shape[1] // 32, c0 // 32
+        g.c, g.ldc = xo.data_ptr() + (r0 * xo.stride(0) + c0) * 2, xo.stride(0)
+        g.m, g.n, g.k = r1 - r0, c1 - c0, xa.shape[1]
+        ctx.matmul_bfp8w(g, stream)
+        return
     xa, xb, xo = _dev2d(a, "A"), _dev2d(b, "B"), _dev2d(out, "out")
     if xa.dtype != torch.bfloat16 or xb.dtype != torch.bfloat16 or xo.dtype != torch.bfloat16:
         raise Unsupported("matmul: bfloat16 tensors only")
@@ -47,6 +60,8 @@ def matmul(a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: Optional["_ttnn.Tensor"] =
         raise ValueError(f"Incompatible matrix shapes for multiplication: {a.shape} @ {b.shape}")
     if out is None:
         out = _ttnn.empty((m, n), dtype=_ttnn.bfloat16)
+    if b._packed is None and b._tensor.dtype != torch.bfloat16:
+        raise Unsupported("matmul: bfloat16 tensors (or bfloat8_b weights) only")
     dev = a._tensor.device.index if a._tensor.is_cuda else None
     launch_gemm(capi.context(dev), a, b, out, (0, m, 0, n), capi.current_stream())
     return out
