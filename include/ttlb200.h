@@ -236,6 +236,26 @@ typedef struct {
  * first use, grown when a larger window arrives), then runs the tensor-core GEMM. */
 TTLB_EXPORT int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, void *stream);
 
+/* ------------------------------------------------------------------------ *
+ * Fused attention forward: O = softmax(scale * Q K^T + causal mask) V per (batch, head),
+ * online softmax with fp32 row max / row sum, bf16 in and out.
+ *
+ * The reference has no attention kernel or example (README.md:83 names a flash-attention
+ * test that is not in its tree); this entry point is the flash-attention tile program
+ * (per KV block: S = Q @ K^T, running max/sum update, O += P @ V) as one kernel.
+ * Q, K, V, O are contiguous [batch_heads, seq, head_dim] arrays (a [B, H, S, D] tensor
+ * with B and H flattened); head_dim must be 128.
+ * ------------------------------------------------------------------------ */
+typedef struct {
+  const void *q, *k, *v; /* bf16 [batch_heads, seq, head_dim] */
+  void *o;               /* bf16 [batch_heads, seq, head_dim] */
+  int64_t batch_heads, seq, head_dim;
+  int32_t causal; /* 1: key j is visible to query i only if j <= i */
+  float scale;    /* multiplies Q K^T, e.g. 1/sqrt(head_dim) */
+} ttlb_attn_desc;
+
+TTLB_EXPORT int ttlb_attention(ttlb_ctx *ctx, const ttlb_attn_desc *desc, void *stream);
+
 /* Kernels that wait on hardware barriers (matmul, attention) bound every wait; when
  * one runs out the kernel unwinds normally and records which role gave up.
  * ttlb_check_status synchronises `stream`, returns TTLB_ERR_TIMEOUT if that happened

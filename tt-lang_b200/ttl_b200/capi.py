@@ -57,6 +57,12 @@ class GemmBfp8Desc(C.Structure):
                 ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64)]
 
 
+class AttnDesc(C.Structure):
+    _fields_ = [("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("o", C.c_void_p),
+                ("batch_heads", C.c_int64), ("seq", C.c_int64), ("head_dim", C.c_int64),
+                ("causal", C.c_int32), ("scale", C.c_float)]
+
+
 ELTWISE_AUTO, ELTWISE_GENERIC, ELTWISE_SPECIALISED = 0, 1, 2
 
 
@@ -121,6 +127,8 @@ def lib() -> C.CDLL:
     l.ttlb_unpack_bfp8_b_device.restype = C.c_int
     l.ttlb_matmul_bfp8w.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p]
     l.ttlb_matmul_bfp8w.restype = C.c_int
+    l.ttlb_attention.argtypes = [C.c_void_p, C.POINTER(AttnDesc), C.c_void_p]
+    l.ttlb_attention.restype = C.c_int
     l.ttlb_check_status.argtypes = [C.c_void_p, C.c_void_p]
     l.ttlb_check_status.restype = C.c_int
     l.ttlb_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
@@ -162,6 +170,9 @@ class Context:
                       ld: int, stream: int) -> None:
         self.check(self._lib.ttlb_unpack_bfp8_b_device(self.handle, C.c_void_p(tiles_ptr), tile_cols_total, tile_col0,
                                                        k, n, C.c_void_p(out_ptr), ld, C.c_void_p(stream)))
+
+    def attention(self, desc: "AttnDesc", stream: int) -> None:
+        self.check(self._lib.ttlb_attention(self.handle, C.byref(desc), C.c_void_p(stream)))
 
     def check_status(self, stream: int = 0) -> None:
         """Synchronise `stream` and raise if a bounded device-side wait ran out since the last check."""

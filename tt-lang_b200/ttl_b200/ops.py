@@ -65,3 +65,32 @@ def matmul(a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: Optional["_ttnn.Tensor"] =
     dev = a._tensor.device.index if a._tensor.is_cuda else None
     launch_gemm(capi.context(dev), a, b, out, (0, m, 0, n), capi.current_stream())
     return out
+
+
+def attention(q: "_ttnn.Tensor", k: "_ttnn.Tensor", v: "_ttnn.Tensor", causal: bool = True,
+              scale: Optional[float] = None, out: Optional["_ttnn.Tensor"] = None) -> "_ttnn.Tensor":
+    """Fused attention forward on [B, H, S, D] (or [BH, S, D]) bf16 tensors, D = 128:
+    softmax(scale * Q K^T + causal mask) V with fp32 scores and online softmax."""
+    xq, xk, xv = q._tensor, k._tensor, v._tensor
+    for x, name in ((xq, "Q"), (xk, "K"), (xv, "V")):
+        if not x.is_cuda:
+            raise capi.BackendError(capi.TTLB_ERR_CUDA, f"{name} is not in GPU memory: the B200 backend has no CPU fallback")
+        if x.dtype != torch.bfloat16 or not x.is_contiguous():
+            raise Unsupported("attention: contiguous bfloat16 tensors only")
+    if xq.shape != xk.shape or xq.shape != xv.shape or xq.dim() not in (3, 4):
+        raise ValueError(f"attention: Q, K, V must share one [B, H, S, D] shape, got {tuple(xq.shape)}, "
+                         f"{tuple(xk.shape)}, {tuple(xv.shape)}")
+    seq, hd = xq.shape[-2], xq.shape[-1]
+    bh = xq.numel() // (seq * hd) if seq * hd else 0
+    if out is None:
+        out = _ttnn.Tensor(torch.empty_like(xq))
+    xo = out._tensor
+    if xo.shape != xq.shape or xo.dtype != torch.bfloat16 or not xo.is_contiguous() or not xo.is_cuda:
+        raise ValueError("attention: output must be a contiguous bfloat16 GPU tensor shaped like Q")
+    d = capi.AttnDesc()
+    d.q, d.k, d.v, d.o = xq.data_ptr(), xk.data_ptr(), xv.data_ptr(), xo.data_ptr()
+    d.batch_heads, d.seq, d.head_dim = bh, seq, hd
+    d.causal = 1 if causal else 0
+    d.scale = float(scale) if scale is not None else float(hd) ** -0.5
+    capi.context(xq.device.index).attention(d, capi.current_stream())
+    return out
