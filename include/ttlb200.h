@@ -236,6 +236,25 @@ typedef struct {
  * first use, grown when a larger window arrives), then runs the tensor-core GEMM. */
 TTLB_EXPORT int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, void *stream);
 
+/* No counterpart in the reference: an addition of this library for callers that must not
+ * allocate.  Same result as ttlb_matmul_bfp8w, but no context is needed and no cudaMalloc,
+ * cudaFree or other allocating routine is called: the bf16 expansion of the weight window goes
+ * into a fixed 32 MiB array in the library's device image.
+ *
+ * For: code that runs after the process has given all free GPU memory to its own pool, code on a
+ * latency-critical path (allocation synchronises the device), plugins restricted to the buffers
+ * they are handed.
+ * Limits: k * n <= TTLB_NOALLOC_MAX_WEIGHT_ELEMS (larger windows return TTLB_ERR_UNSUPPORTED with
+ * a message); every GPU that loads the library holds the 32 MiB until process exit; all calls on
+ * one GPU share the array, so calls that can overlap on the GPU race - serialise them.  The first
+ * call on a device does a one-time set-up (symbol address look-up, kernel attribute); make it
+ * before any stream capture.  The current CUDA device is used.
+ * check != 0: synchronise `stream` and return TTLB_ERR_TIMEOUT if a bounded device wait ran out.
+ * err / err_len: optional buffer that receives a message on failure. */
+#define TTLB_NOALLOC_MAX_WEIGHT_ELEMS (16 * 1024 * 1024)
+TTLB_EXPORT int ttlb_matmul_bfp8w_noalloc(const ttlb_gemm_bfp8_desc *desc, void *stream, int check, char *err,
+                                          size_t err_len);
+
 /* ------------------------------------------------------------------------ *
  * Fused attention forward: O = softmax(scale * Q K^T + causal mask) V per (batch, head),
  * online softmax with fp32 row max / row sum, bf16 in and out.

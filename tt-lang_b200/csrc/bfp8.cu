@@ -195,3 +195,15 @@ extern "C" int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, vo
   if (rc) return rc;
   return ttlb_launch_gemm_bf16(ctx, d->a, d->lda, ctx->scratch, d->n, d->c, d->ldc, d->m, d->n, d->k, s);
 }
+
+// Context-free launch of the unpack kernel (used by the allocation-free entry point).
+int ttlb_bfp8_unpack_launch_raw(const uint8_t *tiles, int64_t tile_cols_total, int64_t tile_col0, int64_t tile_rows,
+                                int64_t tile_cols, void *out, int64_t ld, int sm_count, cudaStream_t s) {
+  const long long blocks = (long long)tile_rows * tile_cols * 64;
+  long long grid = (blocks + 255) / 256;
+  const long long cap = (long long)sm_count * 16;
+  if (grid > cap) grid = cap;
+  ttlb_unpack_bfp8_kernel<<<(unsigned)grid, 256, 0, s>>>(tiles, (int)tile_cols_total, (int)tile_col0, (int)tile_rows,
+                                                         (int)tile_cols, reinterpret_cast<__nv_bfloat16 *>(out), ld);
+  return cudaGetLastError() == cudaSuccess ? TTLB_OK : TTLB_ERR_CUDA;
+}

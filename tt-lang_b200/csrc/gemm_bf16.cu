@@ -330,3 +330,33 @@ extern "C" int ttlb_set_wait_limit(ttlb_ctx *ctx, int64_t cycles) {
   ctx->wait_limit_cycles = cycles;
   return TTLB_OK;
 }
+
+// Context-free launch of the GEMM kernel for callers that bring their own status word and device
+// facts (used by the allocation-free bfp8-weight entry point).  Arguments are assumed validated.
+int ttlb_gemm_bf16_launch_raw(const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc, int64_t m,
+                              int64_t n, int64_t k, int sm_count, int *d_status, long long wait_limit, bool *attr_set,
+                              cudaStream_t stream) {
+  CUtensorMap map_a, map_b;
+  int rc = make_map(nullptr, &map_a, a, (uint64_t)k, (uint64_t)m, (uint64_t)lda * 2, BK, BM);
+  if (rc) return rc;
+  rc = make_map(nullptr, &map_b, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb * 2, 64, BK);
+  if (rc) return rc;
+  if (!*attr_set) {
+    if (cudaFuncSetAttribute(ttlb_gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+      return TTLB_ERR_CUDA;
+    *attr_set = true;
+  }
+  GemmParams p;
+  p.c = reinterpret_cast<__nv_bfloat16 *>(c);
+  p.ldc = ldc;
+  p.m = (int)m;
+  p.n = (int)n;
+  p.k = (int)k;
+  p.tiles_m = (int)((m + BM - 1) / BM);
+  p.tiles_n = (int)((n + BN - 1) / BN);
+  p.status = d_status;
+  p.wait_limit = wait_limit;
+  const int tiles = p.tiles_m * p.tiles_n;
+  ttlb_gemm_bf16_kernel<<<tiles < sm_count ? tiles : sm_count, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+  return cudaGetLastError() == cudaSuccess ? TTLB_OK : TTLB_ERR_CUDA;
+}

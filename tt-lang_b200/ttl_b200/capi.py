@@ -127,6 +127,8 @@ def lib() -> C.CDLL:
     l.ttlb_unpack_bfp8_b_device.restype = C.c_int
     l.ttlb_matmul_bfp8w.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p]
     l.ttlb_matmul_bfp8w.restype = C.c_int
+    l.ttlb_matmul_bfp8w_noalloc.argtypes = [C.POINTER(GemmBfp8Desc), C.c_void_p, C.c_int, C.c_char_p, C.c_size_t]
+    l.ttlb_matmul_bfp8w_noalloc.restype = C.c_int
     l.ttlb_attention.argtypes = [C.c_void_p, C.POINTER(AttnDesc), C.c_void_p]
     l.ttlb_attention.restype = C.c_int
     l.ttlb_check_status.argtypes = [C.c_void_p, C.c_void_p]
