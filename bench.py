@@ -171,6 +171,166 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+
+# --------------------------------------------------------------------------- #
+# Sharded workloads (configs 3-5): --workload matmul_bf16_8192 | matmul_bfp8w | attention
+# --------------------------------------------------------------------------- #
+def measured_peak_tensor():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            j = json.loads(f.read_text())
+            return float(j["bf16_tflops"]), float(j.get("bf16_tflops_sustained", j["bf16_tflops"])), "measured (MEASURED_PEAKS.json bf16_tflops, burst)"
+        except Exception:
+            pass
+    return 1590.0, 1400.0, "fallback (1.59 PFLOP/s, earlier measurement on this pool)"
+
+
+def run_sharded(args):
+    """Strong scaling: the whole problem is split over the ranks (output row tiles / weight column tiles /
+    heads), each rank runs the single-GPU kernel on its shard, the output shards are all-gathered."""
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # noqa: F811
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import cases
+    import ttl_b200
+    from ttl_b200 import capi, ops, shard, ttnn
+
+    ctx = capi.context(local)
+    T = ttnn.Tensor
+    wl = args.workload
+    dev = torch.device("cuda", local)
+    if wl == "matmul_bf16_8192":
+        n = 8192
+        a = cases.gen((n, n), f"normal*{n ** -0.5}", 0)
+        b = cases.gen((n, n), f"normal*{n ** -0.5}", 1)
+        s0, c0 = shard.split_units(n // 32, world)[rank]
+        host_in = [a[s0 * 32:(s0 + c0) * 32].contiguous().pin_memory(), b.pin_memory()]
+        flops = 2.0 * n * n * n
+        kernel = "ttlb_gemm_bf16_kernel"
+
+        def compute(x):
+            return ops.matmul(T(x[0]), T(x[1]))._tensor
+
+        def step(x):
+            return shard.sharded_matmul(x[0], x[1], n, lambda p, q: ops.matmul(T(p), T(q))._tensor)
+        desc = "A,B bf16 [8192,8192] N(0,1/sqrt(8192)) seeds 0/1, fp32 accumulate, bf16 out; output rows sharded"
+    elif wl == "matmul_bfp8w":
+        m, k, n = 4096, 8192, 28672
+        x = cases.gen((m, k), "normal", 0)
+        s0, c0 = shard.split_units(n // 32, world)[rank]
+        # the weight shard is generated and packed per rank (N(0, 0.02), seed 1 + first column tile)
+        w = cases.gen((k, c0 * 32), "normal*0.02", 1 + s0, torch.float32)
+        W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+        host_in = [x.pin_memory()]
+        flops = 2.0 * m * k * n
+        kernel = "ttlb_unpack_bfp8_kernel + ttlb_gemm_bf16_kernel"
+
+        def compute(xs):
+            return ops.matmul(T(xs[0]), W)._tensor
+
+        def step(xs):
+            return shard.sharded_matmul_cols(xs[0], W, n, lambda p, q: ops.matmul(T(p), q)._tensor)
+        desc = ("activations bf16 [4096,8192] N(0,1); weights [8192,28672] N(0,0.02) packed to bfloat8_b tiles "
+                "(resident in HBM); fp32 accumulate, bf16 out; weight columns sharded")
+    elif wl == "attention":
+        B, H, S, D = 8, 32, 4096, 128
+        s0, c0 = shard.split_units(H, world)[rank]
+        host_in = [cases.gen((B * c0 * S, D), "normal", sd + 10 * s0).reshape(B, c0, S, D).pin_memory() for sd in (0, 1, 2)]
+        flops = 4.0 * B * H * S * S * D / 2
+        kernel = "ttlb_attention_kernel"
+
+        def compute(x):
+            return ops.attention(T(x[0]), T(x[1]), T(x[2]), causal=True, scale=D ** -0.5)._tensor
+
+        def step(x):
+            return shard.sharded_attention(x[0], x[1], x[2], H, lambda q, k_, v: ops.attention(T(q), T(k_), T(v), causal=True, scale=D ** -0.5)._tensor)
+        desc = "Q,K,V bf16 [8,32,4096,128] N(0,1), causal, scale 1/sqrt(128); heads sharded; FLOPs counted causal-halved"
+    else:
+        raise SystemExit(f"unknown workload {wl}")
+
+    dev_in = [t.to(dev) for t in host_in]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        for _ in range(args.warmup):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    steps = min(args.steps, 50)
+    sampler = ClockSampler(physical_gpu_index(local))
+    sampler.start()
+    l0 = ctx.launch_count()
+    ms_compute = timed(lambda: compute(dev_in), steps)
+    launches = (ctx.launch_count() - l0) * steps // (steps + args.warmup)
+    clocks = sampler.stop()
+    ms_step = timed(lambda: step(dev_in), steps) if world > 1 else ms_compute
+    ctx.check_status(capi.current_stream())
+
+    result_holder = {}
+
+    def e2e():
+        xs = [t.to(dev, non_blocking=True) for t in host_in]
+        out = step(xs)
+        if "host" not in result_holder:
+            result_holder["host"] = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        result_holder["host"].copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        e2e_ms = timed(e2e, args.e2e_steps)
+    if rank == 0:
+        burst, sustained, src = measured_peak_tensor()
+        tf = flops / (ms_step * 1e-3) / 1e12
+        per_gpu_kernel_tf = flops / world / (ms_compute * 1e-3) / 1e12
+        line = {
+            "metric": "bf16/bfp8 matmul & attention TFLOP/s", "value": tf, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{wl}: {desc}", "ms_compute_only": ms_compute,
+                       "tflops_compute_only": flops / (ms_compute * 1e-3) / 1e12,
+                       "l2": "operands exceed the 126 MB L2" if wl != "attention" else "Q,K,V,O 1 GB total exceed L2"},
+            "roofline": {"bound": "tensor", "achieved": per_gpu_kernel_tf, "peak": burst, "unit": "TFLOP/s",
+                         "frac": per_gpu_kernel_tf / burst, "traffic": None, "peak_source": src,
+                         "peak_sustained": sustained, "kernel": kernel},
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in),
+                    "d2h_bytes_per_step": int(result_holder["host"].numel() * 2) if "host" in result_holder else 0,
+                    "ms_per_step": e2e_ms, "steps": args.e2e_steps},
+            "gpu_launches": launches,
+            "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -191,11 +351,14 @@ def main():
 
     import torch
 
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200: the backend has no CPU fallback")
+    if args.workload != "fused_eltwise_bcast_8192":
+        run_sharded(args)
+        return
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a B200: the backend has no CPU fallback")
     torch.cuda.set_device(local)
     dist = None
     if world > 1:
