@@ -212,8 +212,9 @@ def run_sharded(args):
         n = 8192
         a = cases.gen((n, n), f"normal*{n ** -0.5}", 0)
         b = cases.gen((n, n), f"normal*{n ** -0.5}", 1)
-        s0, c0 = shard.split_units(n // 32, world)[rank]
-        host_in = [a[s0 * 32:(s0 + c0) * 32].contiguous().pin_memory(), b.pin_memory()]
+        chunks = shard.pick_chunks(n // 32, world)
+        mine = shard.cyclic_units(n // 32, world, rank, chunks)
+        host_in = [torch.cat([a[u0 * 32:(u0 + c) * 32] for u0, c in mine]).contiguous().pin_memory(), b.pin_memory()]
         flops = 2.0 * n * n * n
         kernel = "ttlb_gemm_bf16_kernel"
 
@@ -221,8 +222,9 @@ def run_sharded(args):
             return ops.matmul(T(x[0]), T(x[1]))._tensor
 
         def step(x):
-            return shard.sharded_matmul(x[0], x[1], n, lambda p, q: ops.matmul(T(p), T(q))._tensor)
-        desc = "A,B bf16 [8192,8192] N(0,1/sqrt(8192)) seeds 0/1, fp32 accumulate, bf16 out; output rows sharded"
+            return shard.sharded_matmul(x[0], x[1], n, lambda p, q: ops.matmul(T(p), T(q))._tensor, chunks=chunks)
+        desc = ("A,B bf16 [8192,8192] N(0,1/sqrt(8192)) seeds 0/1, fp32 accumulate, bf16 out; output row tiles "
+                f"sharded in {chunks} round(s), all-gather of a round overlaps the next round's GEMM")
     elif wl == "matmul_bfp8w":
         m, k, n = 4096, 8192, 28672
         x = cases.gen((m, k), "normal", 0)
@@ -233,18 +235,22 @@ def run_sharded(args):
         host_in = [x.pin_memory()]
         flops = 2.0 * m * k * n
         kernel = "ttlb_unpack_bfp8_kernel + ttlb_gemm_bf16_kernel"
+        chunks = 2 if world > 1 else 1
 
         def compute(xs):
             return ops.matmul(T(xs[0]), W)._tensor
 
         def step(xs):
-            return shard.sharded_matmul_cols(xs[0], W, n, lambda p, q: ops.matmul(T(p), q)._tensor)
+            return shard.sharded_matmul_cols(xs[0], W, n, lambda p, q: ops.matmul(T(p), q)._tensor, chunks=chunks)
         desc = ("activations bf16 [4096,8192] N(0,1); weights [8192,28672] N(0,0.02) packed to bfloat8_b tiles "
-                "(resident in HBM); fp32 accumulate, bf16 out; weight columns sharded")
+                f"(resident in HBM); fp32 accumulate, bf16 out; weight column tiles sharded, {chunks} row round(s)")
     elif wl == "attention":
         B, H, S, D = 8, 32, 4096, 128
-        s0, c0 = shard.split_units(H, world)[rank]
-        host_in = [cases.gen((B * c0 * S, D), "normal", sd + 10 * s0).reshape(B, c0, S, D).pin_memory() for sd in (0, 1, 2)]
+        chunks = shard.pick_chunks(B * H, world)
+        mine = shard.cyclic_units(B * H, world, rank, chunks)
+        n_local = sum(c for _, c in mine)
+        host_in = [cases.gen((n_local * S, D), "normal", sd + 10 * mine[0][0]).reshape(n_local, S, D).pin_memory()
+                   for sd in (0, 1, 2)]
         flops = 4.0 * B * H * S * S * D / 2
         kernel = "ttlb_attention_kernel"
 
@@ -252,8 +258,10 @@ def run_sharded(args):
             return ops.attention(T(x[0]), T(x[1]), T(x[2]), causal=True, scale=D ** -0.5)._tensor
 
         def step(x):
-            return shard.sharded_attention(x[0], x[1], x[2], H, lambda q, k_, v: ops.attention(T(q), T(k_), T(v), causal=True, scale=D ** -0.5)._tensor)
-        desc = "Q,K,V bf16 [8,32,4096,128] N(0,1), causal, scale 1/sqrt(128); heads sharded; FLOPs counted causal-halved"
+            return shard.sharded_attention(x[0], x[1], x[2], B * H, lambda q, k_, v: ops.attention(
+                T(q), T(k_), T(v), causal=True, scale=D ** -0.5)._tensor, chunks=chunks)
+        desc = ("Q,K,V bf16 [8,32,4096,128] N(0,1), causal, scale 1/sqrt(128); the 256 (batch, head) pairs sharded in "
+                f"{chunks} round(s); FLOPs counted causal-halved")
     else:
         raise SystemExit(f"unknown workload {wl}")
 

@@ -58,37 +58,114 @@ def gather_shards(local: torch.Tensor, counts: List[int], dim: int, group: Optio
     return full.movedim(0, dim).contiguous() if dim != 0 else full
 
 
+def cyclic_units(n_units: int, world: int, rank: int, chunks: int) -> List[Tuple[int, int]]:
+    """Unit ranges (start, count) owned by `rank` when the units are dealt out in `chunks` rounds:
+    round c hands units [c*world*uc + r*uc, +uc) to rank r (uc = n_units / (world*chunks)).  The shards
+    of one round are then contiguous in the full output, so each round's all-gather writes straight into
+    it, and round c's gather overlaps round c+1's compute.  chunks == 1 is the plain contiguous split."""
+    if n_units % (world * chunks):
+        raise ValueError(f"{n_units} units do not divide into {world} ranks x {chunks} rounds")
+    uc = n_units // (world * chunks)
+    return [((c * world + rank) * uc, uc) for c in range(chunks)]
+
+
+def pick_chunks(n_units: int, world: int, want: int = 4) -> int:
+    """Largest number of rounds <= want that divides the units evenly (0: not even one)."""
+    if world <= 1:
+        return 1
+    for c in range(want, 0, -1):
+        if n_units % (world * c) == 0:
+            return c
+    return 0
+
+
+def _pipelined_gather(local_chunks: int, out: torch.Tensor, compute_chunk: Callable[[int], torch.Tensor],
+                      group: Optional[dist.ProcessGroup]) -> torch.Tensor:
+    """Round c: compute this rank's piece, then start the all-gather of that round (async, on NCCL's
+    stream) while the next round computes.  `out` is [chunks * world * rows_per_piece, ...]."""
+    _, world = _world(group)
+    per_round = out.shape[0] // local_chunks
+    handles, keep = [], []
+    for c in range(local_chunks):
+        piece = compute_chunk(c)
+        keep.append(piece)
+        handles.append(dist.all_gather_into_tensor(out[c * per_round:(c + 1) * per_round], piece.contiguous(),
+                                                   group=group, async_op=True))
+    for h in handles:
+        h.wait()
+    return out
+
+
 def sharded_matmul(a_rows: torch.Tensor, b: torch.Tensor, m_total: int, compute: Callable[[torch.Tensor, torch.Tensor], torch.Tensor],
-                   group: Optional[dist.ProcessGroup] = None, tile: int = 32) -> torch.Tensor:
-    """C = A @ B with A's rows sharded: this rank holds `a_rows` = rows of the tile range
-    split_units(m_total / tile, world)[rank]; B is replicated.  Returns the full C on every rank."""
+                   group: Optional[dist.ProcessGroup] = None, tile: int = 32, chunks: int = 1) -> torch.Tensor:
+    """C = A @ B with A's row tiles sharded; B is replicated.  `a_rows` holds this rank's rows, round
+    after round, for the unit ranges cyclic_units(m_total / tile, world, rank, chunks) (chunks == 1: one
+    contiguous range, the first m % world ranks one tile more).  Returns the full C on every rank."""
     rank, world = _world(group)
+    if world == 1:
+        return compute(a_rows, b)
+    if chunks >= 1 and (m_total // tile) % (world * chunks) == 0:
+        mc = m_total // (world * chunks)
+        if a_rows.shape[0] != mc * chunks:
+            raise ValueError(f"rank {rank}: A shard has {a_rows.shape[0]} rows, expected {mc * chunks}")
+        out = torch.empty((m_total, b.shape[1]), dtype=a_rows.dtype, device=a_rows.device)
+        return _pipelined_gather(chunks, out, lambda c: compute(a_rows[c * mc:(c + 1) * mc], b), group)
     counts = [c * tile for _, c in split_units(m_total // tile, world)]
     if a_rows.shape[0] != counts[rank]:
         raise ValueError(f"rank {rank}: A shard has {a_rows.shape[0]} rows, expected {counts[rank]}")
-    c_local = compute(a_rows, b)
-    return gather_shards(c_local, counts, 0, group)
+    return gather_shards(compute(a_rows, b), counts, 0, group)
 
 
 def sharded_matmul_cols(x: torch.Tensor, w_cols, n_total: int, compute: Callable, group: Optional[dist.ProcessGroup] = None,
-                        tile: int = 32) -> torch.Tensor:
-    """C = X @ W with W's columns sharded (tile columns split_units(n_total / tile, world)[rank]);
-    X is replicated.  `compute(x, w_cols)` returns this rank's [M, n_local] block."""
+                        tile: int = 32, chunks: int = 1) -> torch.Tensor:
+    """C = X @ W with W's column tiles sharded (split_units(n_total / tile, world)[rank]); X is replicated.
+    `compute(x_rows, w_cols)` returns this rank's [rows, n_local] block.  With chunks > 1 the rows of X are
+    processed in rounds so that the gather of one round overlaps the next round's compute; the gathered
+    [world, rows, n_local] pieces are interleaved into C by one strided copy per round."""
     rank, world = _world(group)
+    if world == 1:
+        return compute(x, w_cols)
     counts = [c * tile for _, c in split_units(n_total // tile, world)]
+    m = x.shape[0]
+    if chunks >= 1 and len(set(counts)) == 1 and m % chunks == 0:
+        nl, mc = counts[0], m // chunks
+        out = torch.empty((m, n_total), dtype=x.dtype, device=x.device)
+        staging = torch.empty((chunks, world, mc, nl), dtype=x.dtype, device=x.device)
+        handles, keep = [], []
+        for c in range(chunks):
+            piece = compute(x[c * mc:(c + 1) * mc], w_cols)
+            if piece.shape != (mc, nl):
+                raise ValueError(f"rank {rank}: output shard is {tuple(piece.shape)}, expected {(mc, nl)}")
+            keep.append(piece)
+            handles.append(dist.all_gather_into_tensor(staging[c].view(world * mc, nl), piece.contiguous(), group=group,
+                                                       async_op=True))
+        for c, h in enumerate(handles):
+            h.wait()
+            out[c * mc:(c + 1) * mc].view(mc, world, nl).copy_(staging[c].permute(1, 0, 2))
+        return out
     c_local = compute(x, w_cols)
     if c_local.shape[1] != counts[rank]:
         raise ValueError(f"rank {rank}: output shard has {c_local.shape[1]} columns, expected {counts[rank]}")
     return gather_shards(c_local, counts, 1, group)
 
 
-def sharded_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, h_total: int, compute: Callable,
-                      group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
-    """Attention with heads sharded: this rank holds [B, h_local, S, D] slices of Q, K, V for the head
-    range split_units(h_total, world)[rank].  Returns the full [B, H, S, D] output on every rank."""
+def sharded_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, units_total: int, compute: Callable,
+                      group: Optional[dist.ProcessGroup] = None, chunks: int = 1) -> torch.Tensor:
+    """Attention with the (batch, head) pairs sharded: Q, K, V are [units_local, S, D] slices of the
+    flattened [B*H, S, D] tensors for the unit ranges cyclic_units(units_total, world, rank, chunks)
+    (heads of one batch entry are independent, so any split of the flattened index is a head split).
+    Returns the full [B*H, S, D] output on every rank."""
     rank, world = _world(group)
-    counts = [c for _, c in split_units(h_total, world)]
-    if q.shape[1] != counts[rank]:
-        raise ValueError(f"rank {rank}: Q shard has {q.shape[1]} heads, expected {counts[rank]}")
-    o_local = compute(q, k, v)
-    return gather_shards(o_local, counts, 1, group)
+    if world == 1:
+        return compute(q, k, v)
+    if chunks >= 1 and units_total % (world * chunks) == 0:
+        uc = units_total // (world * chunks)
+        if q.shape[0] != uc * chunks:
+            raise ValueError(f"rank {rank}: Q shard has {q.shape[0]} heads, expected {uc * chunks}")
+        out = torch.empty((units_total,) + tuple(q.shape[1:]), dtype=q.dtype, device=q.device)
+        return _pipelined_gather(chunks, out, lambda c: compute(q[c * uc:(c + 1) * uc], k[c * uc:(c + 1) * uc],
+                                                                v[c * uc:(c + 1) * uc]), group)
+    counts = [c for _, c in split_units(units_total, world)]
+    if q.shape[0] != counts[rank]:
+        raise ValueError(f"rank {rank}: Q shard has {q.shape[0]} heads, expected {counts[rank]}")
+    return gather_shards(compute(q, k, v), counts, 0, group)
