@@ -5,16 +5,18 @@
 // in the tree); this is the tile program "for each KV block: S = Q @ K^T; online-softmax update;
 // O += P @ V" written directly as a B200 kernel.
 //
-// One CTA per (batch*head, 128-query tile), 320 threads:
+// One CTA per (batch*head, 128-query tile), 576 threads:
 //   warp 0      TMA producer: Q tile once; K and V blocks (128 keys) through 2-stage rings
 //   warp 1      UMMA issuer: S_j = Q K_j^T (128x128x128) into one of two TMEM score buffers,
 //               then PV_{j-1} = P_{j-1} V_{j-1} into one of two TMEM output buffers, so the
 //               tensor pipe computes the next scores while the softmax warps work
-//   warps 2..9  softmax: thread (row, column half) reads 64 scores with tcgen05.ld, exchanges
-//               the row max with its partner warp, writes P (bf16) into shared memory in the
-//               swizzled K-major layout the next UMMA reads, and folds the finished P V
-//               product into its 64 fp32 output accumulators (O = O * alpha + PV), which live
-//               in registers - no TMEM read-modify-write, no correction pass
+//   warps 2..17 softmax: thread (row, one of four 32-column parts) reads its 32 scores with
+//               tcgen05.ld, exchanges the row max with the three partner warps through shared
+//               memory, writes P (bf16) into shared memory in the swizzled K-major layout the
+//               next UMMA reads, and folds the finished P V product into its 32 fp32 output
+//               accumulators (O = O * alpha + PV), which live in registers - no TMEM
+//               read-modify-write, no correction pass.  Four softmax warps per scheduler hide
+//               each other's barrier and TMEM-load latency.
 // Heavy (late) query tiles are scheduled first.  All waits are bounded.
 #include <cuda_bf16.h>
 
@@ -29,10 +31,12 @@ constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int TILE_BYTES = 128 * 128 * 2;    // 32 KB: a 128 x 128 bf16 tile (Q, K block, V block, P)
 constexpr int CHUNK_BYTES = 128 * 64 * 2;    // 16 KB: 128 rows x 64 elements (one 128-byte swizzle span)
 constexpr int KV_STAGES = 2;
-constexpr int ATT_THREADS = 320;
+constexpr int NPART = 4;                      // column parts per row: softmax thread = (row, part)
+constexpr int PCOLS = 128 / NPART;            // score / output columns per softmax thread
+constexpr int ATT_THREADS = 64 + 128 * NPART;
 constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = OFF_K + KV_STAGES * TILE_BYTES,
               OFF_P = OFF_V + KV_STAGES * TILE_BYTES, OFF_X = OFF_P + TILE_BYTES;  // X: row-max exchange
-constexpr int XCH_BYTES = 2 * 2 * 128 * 4;   // [parity][half][row] floats
+constexpr int XCH_BYTES = 2 * NPART * 128 * 4;   // [parity][part][row] floats
 constexpr int OFF_BAR = OFF_X + XCH_BYTES;
 constexpr int ATT_SMEM = OFF_BAR + 512 + 1024;
 
@@ -53,12 +57,12 @@ enum {
   B_VFULL = 5,    // [2]
   B_VEMPTY = 7,   // [2]
   B_SFULL = 9,    // [2]
-  B_SEMPTY = 11,  // [2]  count 8
-  B_PFULL = 13,   //      count 8
+  B_SEMPTY = 11,  // [2]  count 4*NPART (one arrival per softmax warp)
+  B_PFULL = 13,   //      count 4*NPART
   B_PEMPTY = 14,
   B_OFULL = 15,   // [2]
-  B_OEMPTY = 17,  // [2]  count 8
-  B_XCH = 19,     // [4]  count 64
+  B_OEMPTY = 17,  // [2]  count 4*NPART
+  B_XCH = 19,     // [4]  count 32*NPART (all threads that share a TMEM lane quarter)
   B_COUNT = 23
 };
 
@@ -90,8 +94,8 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     *abort_flag = 0;
     for (int i = 0; i < B_COUNT; ++i) {
       uint32_t count = 1;
-      if (i == B_SEMPTY || i == B_SEMPTY + 1 || i == B_PFULL || i == B_OEMPTY || i == B_OEMPTY + 1) count = 8;
-      if (i >= B_XCH) count = 64;
+      if (i == B_SEMPTY || i == B_SEMPTY + 1 || i == B_PFULL || i == B_OEMPTY || i == B_OEMPTY + 1) count = 4 * NPART;
+      if (i >= B_XCH) count = 32 * NPART;
       mbar_init(bar(i), count);
     }
     fence_barrier_init();
@@ -172,30 +176,27 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (!fail && !issue_pv(nblk - 1)) fail = 2;
     }
   } else {
-    // ---- softmax warps: thread = (query row, half of the columns) --------------------
-    const int q = warp & 3;             // TMEM lane quarter this warp may access
-    const int half = (warp - 2) >> 2;   // 0: key / head-dim columns 0..63, 1: columns 64..127
-    const int row = q * 32 + lane;      // row inside the query tile
+    // ---- softmax warps: thread = (query row, one of NPART column parts) -------------------
+    const int q = warp & 3;               // TMEM lane quarter this warp may access
+    const int part = (warp - 2) >> 2;     // which PCOLS-wide slice of the key / head-dim columns
+    const int row = q * 32 + lane;        // row inside the query tile
     const int q_idx = qt * BQ + row;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const float sl2e = p.scale_log2e;
-    float o[64];
+    float o[PCOLS];
 #pragma unroll
-    for (int c = 0; c < 64; ++c) o[c] = 0.f;
+    for (int c = 0; c < PCOLS; ++c) o[c] = 0.f;
     float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
 
-    auto fold = [&](int jj, float a) -> bool {  // O = O * a + PV_jj (this thread's 64 output columns)
+    auto fold = [&](int jj, float a) -> bool {  // O = O * a + PV_jj (this thread's PCOLS output columns)
       const int s = jj & 1;
       if (!mbar_wait(bar(B_OFULL + s), (uint32_t)((jj >> 1) & 1), abort_flag, p.wait_limit)) return false;
       tc_fence_after();
+      uint32_t r[32];
+      tmem_ld_32x32(tm_o + lane_addr + s * HD + part * PCOLS, r);
+      tmem_ld_wait_dep(r);
 #pragma unroll
-      for (int h2 = 0; h2 < 2; ++h2) {
-        uint32_t r[32];
-        tmem_ld_32x32(tm_o + lane_addr + s * HD + half * 64 + h2 * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) o[h2 * 32 + c] = fmaf(o[h2 * 32 + c], a, __uint_as_float(r[c]));
-      }
+      for (int c = 0; c < 32; ++c) o[c] = fmaf(o[c], a, __uint_as_float(r[c]));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_OEMPTY + s));
@@ -206,59 +207,58 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const int s = j & 1;
       if (!mbar_wait(bar(B_SFULL + s), (uint32_t)((j >> 1) & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
       tc_fence_after();
-      uint32_t sr[64];
-      {
-        uint32_t r0[32], r1[32];
-        tmem_ld_32x32(tm_s + lane_addr + s * BKV + half * 64, r0);
-        tmem_ld_32x32(tm_s + lane_addr + s * BKV + half * 64 + 32, r1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          sr[c] = r0[c];
-          sr[32 + c] = r1[c];
-        }
-      }
+      uint32_t sr[32];
+      tmem_ld_32x32(tm_s + lane_addr + s * BKV + part * PCOLS, sr);
+      tmem_ld_wait_dep(sr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_SEMPTY + s));
 
-      const int key0 = j * BKV + half * 64;
+      const int key0 = j * BKV + part * PCOLS;
       if ((p.causal && j == qt) || (j + 1) * BKV > p.seq) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int c = 0; c < 32; ++c) {
           const int key = key0 + c;
           if ((p.causal && key > q_idx) || key >= p.seq) sr[c] = 0xff800000u;  // -inf
         }
       }
-      float mx = -INFINITY;
+      float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
-      // exchange the row max with the partner warp (other column half of the same rows)
-      xch[((j & 1) * 2 + half) * 128 + row] = mx;
+      for (int c = 0; c < 32; c += 4) {
+        mx0 = max3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
+        mx1 = max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+      }
+      const float mx = fmaxf(mx0, mx1);
+      // exchange the row max with the partner warps (the other column parts of the same rows)
+      float *xrow = xch + (j & 1) * NPART * 128 + row;
+      xrow[part * 128] = mx;
       mbar_arrive(bar(B_XCH + q));
       if (!mbar_wait(bar(B_XCH + q), (uint32_t)(j & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
-      const float other = xch[((j & 1) * 2 + (1 - half)) * 128 + row];
-      const float m_new = fmaxf(m_run, fmaxf(mx, other));
+      float m_new = fmaxf(m_run, mx);
+#pragma unroll
+      for (int k = 1; k < NPART; ++k) m_new = fmaxf(m_new, xrow[((part + k) & (NPART - 1)) * 128]);
       const float alpha = fast_exp2((m_run - m_new) * sl2e);
       const float neg = -m_new * sl2e;
-      float rowsum = 0.f;
-      uint32_t pk[32];
+      float rs0 = 0.f, rs1 = 0.f;
+      uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
+      for (int c = 0; c < 32; c += 2) {
         const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c]), sl2e, neg));
         const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), sl2e, neg));
-        rowsum += p0 + p1;
+        rs0 += p0;
+        rs1 += p1;
         pk[c >> 1] = pack_bf16x2(p0, p1);
       }
-      l_run = l_run * alpha + rowsum;
+      l_run = l_run * alpha + (rs0 + rs1);
       m_run = m_new;
       // P buffer is free once PV_{j-1} has been consumed by the tensor core
       if (j > 0 && !mbar_wait(bar(B_PEMPTY), (uint32_t)((j - 1) & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
       {
-        uint8_t *prow = gen + OFF_P + half * CHUNK_BYTES + row * 128;
+        // this thread's 32 bf16 = four 16-byte units of the row's 128-byte swizzle span
+        uint8_t *prow = gen + OFF_P + (part >> 1) * CHUNK_BYTES + row * 128;
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
-          *reinterpret_cast<uint4 *>(prow + ((u ^ (row & 7)) << 4)) =
+        for (int u = 0; u < 4; ++u)
+          *reinterpret_cast<uint4 *>(prow + ((((part & 1) * 4 + u) ^ (row & 7)) << 4)) =
               make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
       }
       fence_proxy_async();
@@ -270,14 +270,18 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (!fail && !fold(nblk - 1, alpha_prev)) fail = 4;
     if (!fail) {
       const int slot = nblk & 1;
-      xch[(slot * 2 + half) * 128 + row] = l_run;
+      float *xrow = xch + slot * NPART * 128 + row;
+      xrow[part * 128] = l_run;
       mbar_arrive(bar(B_XCH + q));
       if (!mbar_wait(bar(B_XCH + q), (uint32_t)slot, abort_flag, p.wait_limit)) fail = 4;
       if (!fail && q_idx < p.seq) {
-        const float inv = 1.0f / (l_run + xch[(slot * 2 + (1 - half)) * 128 + row]);
-        __nv_bfloat16 *dst = p.o + ((long long)bh * p.seq + q_idx) * HD + half * 64;
+        float l_tot = l_run;
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
+        for (int k = 1; k < NPART; ++k) l_tot += xrow[((part + k) & (NPART - 1)) * 128];
+        const float inv = 1.0f / l_tot;
+        __nv_bfloat16 *dst = p.o + ((long long)bh * p.seq + q_idx) * HD + part * PCOLS;
+#pragma unroll
+        for (int u = 0; u < PCOLS / 8; ++u) {
           uint4 v;
           v.x = pack_bf16x2(o[8 * u + 0] * inv, o[8 * u + 1] * inv);
           v.y = pack_bf16x2(o[8 * u + 2] * inv, o[8 * u + 3] * inv);
