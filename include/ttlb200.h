@@ -197,6 +197,10 @@ typedef struct {
 } ttlb_gemm_desc;
 
 TTLB_EXPORT int ttlb_matmul_bf16(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, void *stream);
+/* The same program on float32 tensors (the reference's matmul examples call their kernels with
+ * fp32 tensors and check against an fp32 golden at rtol 1e-4: examples/singlecore_matmul.py:73-88).
+ * a, b, c are fp32; fp32 FMA accumulation on the CUDA cores, no alignment requirement beyond 4 bytes. */
+TTLB_EXPORT int ttlb_matmul_f32(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, void *stream);
 
 /* ------------------------------------------------------------------------ *
  * bfloat8_b block-float weights (quantised inference GEMM):

@@ -108,3 +108,35 @@ def test_config3_full_size_slabs_and_scaling_property():
         assert rel_err(got[r0:r0 + 64], want) <= TOL, f"rows {r0}..{r0 + 63}"
     C4 = ops.matmul(ttnn.from_torch(a * 4), B)
     assert torch.equal(ttnn.to_torch(C4), got * 4), "matmul(4A, B) must equal 4 * matmul(A, B) bit for bit"
+
+
+@pytest.mark.parametrize("name", ["singlecore_matmul", "multicore_matmul"])
+def test_fp32_matmul_program(backend, name):
+    """The reference's matmul examples call their kernels on float32 tensors (128x256 @ 256x64) and
+    check at rtol = atol = 1e-4 against an fp32 golden (examples/singlecore_matmul.py:73-88)."""
+    from ttl_b200 import capi
+    _, mods = backend
+    import ttnn
+    a = cases.gen((128, 256), "uniform", 0, torch.float32)
+    b = cases.gen((256, 64), "uniform", 1, torch.float32)
+    out = ttnn.from_torch(torch.zeros((128, 64), dtype=torch.float32))
+    getattr(mods["matmul"], name)(ttnn.from_torch(a), ttnn.from_torch(b), out)
+    got = ttnn.to_torch(out)
+    assert torch.allclose(got, tile_oracle.matmul_tiles(a, b, "native"), rtol=1e-4, atol=1e-4)
+    assert torch.allclose(got, a @ b, rtol=1e-4, atol=1e-4)
+
+
+def test_c_abi_matmul_f32_ragged():
+    from ttl_b200 import capi
+    m, n, k = 100, 72, 40
+    g = torch.Generator().manual_seed(3)
+    a, b = torch.randn(m, k, generator=g), torch.randn(k, n, generator=g)
+    A, B = a.cuda(), b.cuda()
+    C = torch.full((m + 2, n + 3), 7.0, device="cuda")
+    d = capi.GemmDesc()
+    d.a, d.lda, d.b, d.ldb, d.c, d.ldc, d.m, d.n, d.k = A.data_ptr(), k, B.data_ptr(), n, C.data_ptr(), n + 3, m, n, k
+    capi.context().matmul_f32(d, capi.current_stream())
+    torch.cuda.synchronize()
+    got = C.cpu()
+    assert torch.allclose(got[:m, :n], a @ b, rtol=1e-5, atol=1e-5)
+    assert (got[m:] == 7.0).all() and (got[:, n:] == 7.0).all()

@@ -267,7 +267,7 @@ def test_overlapping_writes_rejected(tt):
         @ttl.datamovement()
         def r():
             with a_cb.reserve() as x:
-                tx = ttl.copy(a[0, 0], x)
+                tx = ttl.copy(a[0, ttl.core(dims=1) if distinct else 0], x)
                 tx.wait()
 
         @ttl.datamovement()
@@ -276,8 +276,12 @@ def test_overlapping_writes_rejected(tt):
                 tx = ttl.copy(y, out[0, 0])   # both cores write tile (0, 0)
                 tx.wait()
 
+    distinct = True     # the two cores write different values to the same tile: order-dependent
     with pytest.raises(Unsupported, match="written more than once"):
-        k.plan(_t(ttnn, (32, 32)), _t(ttnn, (32, 32)))
+        k.plan(_t(ttnn, (32, 64)), _t(ttnn, (32, 32)))
+    distinct = False    # every core writes the same value (a program that ignores the grid): one write
+    d = k.plan(_t(ttnn, (32, 64)), _t(ttnn, (32, 32), torch.bfloat16)).describe()
+    assert len(d) == 1 and d[0]["rect_tiles"] == (0, 1, 0, 1)
 
 
 def test_merge_rects():

@@ -131,6 +131,8 @@ def lib() -> C.CDLL:
     l.ttlb_matmul_bfp8w_noalloc.restype = C.c_int
     l.ttlb_attention.argtypes = [C.c_void_p, C.POINTER(AttnDesc), C.c_void_p]
     l.ttlb_attention.restype = C.c_int
+    l.ttlb_matmul_f32.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]
+    l.ttlb_matmul_f32.restype = C.c_int
     l.ttlb_check_status.argtypes = [C.c_void_p, C.c_void_p]
     l.ttlb_check_status.restype = C.c_int
     l.ttlb_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
@@ -164,6 +166,9 @@ class Context:
 
     def matmul_bf16(self, desc: "GemmDesc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_bf16(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def matmul_f32(self, desc: "GemmDesc", stream: int) -> None:
+        self.check(self._lib.ttlb_matmul_f32(self.handle, C.byref(desc), C.c_void_p(stream)))
 
     def matmul_bfp8w(self, desc: "GemmBfp8Desc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_bfp8w(self.handle, C.byref(desc), C.c_void_p(stream)))

@@ -42,15 +42,19 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
         ctx.matmul_bfp8w(g, stream)
         return
     xa, xb, xo = _dev2d(a, "A"), _dev2d(b, "B"), _dev2d(out, "out")
-    if xa.dtype != torch.bfloat16 or xb.dtype != torch.bfloat16 or xo.dtype != torch.bfloat16:
-        raise Unsupported("matmul: bfloat16 tensors only")
+    if not (xa.dtype == xb.dtype == xo.dtype) or xa.dtype not in (torch.bfloat16, torch.float32):
+        raise Unsupported(f"matmul: A, B and the output must all be bfloat16 or all float32 "
+                          f"(got {xa.dtype}, {xb.dtype}, {xo.dtype})")
     d = capi.GemmDesc()
-    es = 2
+    es = xa.element_size()
     d.a, d.lda = xa.data_ptr() + r0 * xa.stride(0) * es, xa.stride(0)
     d.b, d.ldb = xb.data_ptr() + c0 * es, xb.stride(0)
     d.c, d.ldc = xo.data_ptr() + (r0 * xo.stride(0) + c0) * es, xo.stride(0)
     d.m, d.n, d.k = r1 - r0, c1 - c0, xa.shape[1]
-    ctx.matmul_bf16(d, stream)
+    if xa.dtype == torch.float32:
+        ctx.matmul_f32(d, stream)
+    else:
+        ctx.matmul_bf16(d, stream)
 
 
 def matmul(a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: Optional["_ttnn.Tensor"] = None) -> "_ttnn.Tensor":
@@ -59,9 +63,7 @@ def matmul(a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: Optional["_ttnn.Tensor"] =
     if a.shape[1] != b.shape[0]:
         raise ValueError(f"Incompatible matrix shapes for multiplication: {a.shape} @ {b.shape}")
     if out is None:
-        out = _ttnn.empty((m, n), dtype=_ttnn.bfloat16)
-    if b._packed is None and b._tensor.dtype != torch.bfloat16:
-        raise Unsupported("matmul: bfloat16 tensors (or bfloat8_b weights) only")
+        out = _ttnn.empty((m, n), dtype=a._tensor.dtype)
     dev = a._tensor.device.index if a._tensor.is_cuda else None
     launch_gemm(capi.context(dev), a, b, out, (0, m, 0, n), capi.current_stream())
     return out

@@ -278,9 +278,10 @@ class GemmLaunch:
                  b_is_bfp8: bool):
         self.a_index, self.b_index, self.out_index, self.rect = a_index, b_index, out_index, rect
         self.k_tiles, self.b_is_bfp8 = k_tiles, b_is_bfp8
+        self.kind = "matmul_bf16"   # set to "matmul_f32" by the recogniser for float32 programs
 
     def describe(self) -> Dict[str, Any]:
-        return {"kind": "matmul_bfp8w" if self.b_is_bfp8 else "matmul_bf16", "a": self.a_index, "b": self.b_index,
+        return {"kind": "matmul_bfp8w" if self.b_is_bfp8 else self.kind, "a": self.a_index, "b": self.b_index,
                 "out": self.out_index, "rect_tiles": self.rect, "k_tiles": self.k_tiles}
 
     def run(self, ctx: capi.Context, tensors: Sequence[_ttnn.Tensor], stream: int) -> None:
@@ -334,64 +335,71 @@ def _matmul_terms(w: Write) -> Optional[List[Bin]]:
 
 def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermediates: bool = False) -> Plan:
     table = _TensorTable(arg_tensors)
-    # 1. writes must not overlap (the result would depend on thread interleaving)
+    # 1. every write gets a key (what is computed, from where); 2. writes must not overlap, except that
+    # several cores writing the very same region with the very same expression (programs that do not
+    # partition their loops over the grid) are one write.
     cover: Dict[int, np.ndarray] = {}
+    seen: Dict[Any, Any] = {}
     out_tensors: Dict[int, _ttnn.Tensor] = {}
+    elt_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
+    elt_meta: Dict[Any, Any] = {}
+    mm_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
     for w in trace.writes:
         oi = table.index(w.tensor)
         out_tensors[oi] = w.tensor
         tr, tc = w.tensor.tile_shape()
         if not (0 <= w.r0 < w.r1 <= tr and 0 <= w.c0 < w.c1 <= tc):
             raise ValueError(f"write region [{w.r0}:{w.r1}, {w.c0}:{w.c1}] is outside the {tr}x{tc}-tile tensor")
-        grid = cover.setdefault(oi, np.zeros((tr, tc), dtype=bool))
-        region = grid[w.r0:w.r1, w.c0:w.c1]
-        if region.any():
-            raise Unsupported(f"output tiles [{w.r0}:{w.r1}, {w.c0}:{w.c1}] are written more than once")
-        region[...] = True
-
-    elt_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
-    elt_meta: Dict[Any, Any] = {}
-    mm_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
-    for w in trace.writes:
-        oi = table.index(w.tensor)
+        region = (w.r0, w.r1, w.c0, w.c1)
         terms = _matmul_terms(w)
         if terms is not None:
-            key = _recognise_matmul(w, terms, table, oi)
-            mm_groups.setdefault(key, []).append((w.r0, w.r1, w.c0, w.c1))
-            continue
-        if _contains_matmul(w.expr):
-            raise Unsupported("matmul mixed with element-wise ops in one store is not supported yet")
-        lin = _Lin(w, table)
-        lin.emit(w.expr)
-        if len(lin.inputs) > capi.TTLB_MAX_IN:
-            raise Unsupported(f"expression reads {len(lin.inputs)} distinct operands (max {capi.TTLB_MAX_IN})")
-        if len(lin.ops) > capi.TTLB_MAX_OPS:
-            raise Unsupported(f"expression needs {len(lin.ops)} ops (max {capi.TTLB_MAX_OPS})")
-        if _stack_depth(lin.ops) > 2:
-            raise Unsupported("expression needs more than two temporaries")
-        odt = w.tensor.dtype
-        for (ti, *_rest) in lin.inputs:
-            t = table.args[ti] if ti < len(table.args) else table.extras[ti - len(table.args)]
-            if t.dtype != odt:
-                raise Unsupported(f"mixed element types ({t.dtype} operand, {odt} output)")
-            for dim in (0, 1):
-                if w.tensor.shape[dim] == 1 and t.shape[dim] != 1:
-                    raise Unsupported("a degenerate output dimension needs degenerate operands")
-        key = (oi, tuple(lin.inputs), tuple(lin.ops))
-        elt_groups.setdefault(key, []).append((w.r0, w.r1, w.c0, w.c1))
-        elt_meta[key] = (odt, (w.tensor.shape[0] == 1, w.tensor.shape[1] == 1))
+            key = ("mm",) + tuple(_recognise_matmul(w, terms, table, oi))
+        else:
+            if _contains_matmul(w.expr):
+                raise Unsupported("matmul mixed with element-wise ops in one store is not supported yet")
+            lin = _Lin(w, table)
+            lin.emit(w.expr)
+            if len(lin.inputs) > capi.TTLB_MAX_IN:
+                raise Unsupported(f"expression reads {len(lin.inputs)} distinct operands (max {capi.TTLB_MAX_IN})")
+            if len(lin.ops) > capi.TTLB_MAX_OPS:
+                raise Unsupported(f"expression needs {len(lin.ops)} ops (max {capi.TTLB_MAX_OPS})")
+            if _stack_depth(lin.ops) > 2:
+                raise Unsupported("expression needs more than two temporaries")
+            odt = w.tensor.dtype
+            for (ti, *_rest) in lin.inputs:
+                t = table.args[ti] if ti < len(table.args) else table.extras[ti - len(table.args)]
+                if t.dtype != odt:
+                    raise Unsupported(f"mixed element types ({t.dtype} operand, {odt} output)")
+                for dim in (0, 1):
+                    if w.tensor.shape[dim] == 1 and t.shape[dim] != 1:
+                        raise Unsupported("a degenerate output dimension needs degenerate operands")
+            key = ("elt", oi, tuple(lin.inputs), tuple(lin.ops))
+            elt_meta[key] = (odt, (w.tensor.shape[0] == 1, w.tensor.shape[1] == 1))
+        grid = cover.setdefault(oi, np.zeros((tr, tc), dtype=bool))
+        covered = grid[w.r0:w.r1, w.c0:w.c1]
+        if covered.any():
+            if seen.get((oi, region)) == key:
+                continue   # the same write again, from another core
+            raise Unsupported(f"output tiles [{w.r0}:{w.r1}, {w.c0}:{w.c1}] are written more than once")
+        covered[...] = True
+        seen[(oi, region)] = key
+        (mm_groups if key[0] == "mm" else elt_groups).setdefault(key, []).append(region)
 
     launches: List[Any] = []
     for key, rects in elt_groups.items():
-        oi, inputs, ops = key
+        _, oi, inputs, ops = key
         odt, degen = elt_meta[key]
         for rect in merge_rects(rects):
             launches.append(EltwiseLaunch(oi, rect, list(inputs), list(ops), odt,
                                           round_each_op=not fp32_intermediates, out_degenerate=degen))
     for key, rects in mm_groups.items():
-        ai, bi, oi, kt, b8 = key
+        _, ai, bi, oi, kt, b8 = key
+        f32 = out_tensors[oi].dtype == torch.float32
         for rect in merge_rects(rects):
-            launches.append(GemmLaunch(ai, bi, oi, rect, kt, b8))
+            gl = GemmLaunch(ai, bi, oi, rect, kt, b8)
+            if f32:
+                gl.kind = "matmul_f32"
+            launches.append(gl)
     return Plan(launches, table.extras, len(table.args))
 
 
@@ -420,7 +428,9 @@ def _recognise_matmul(w: Write, terms: List[Bin], table: _TensorTable, oi: int) 
     if sorted(ks) != list(range(kt)):
         raise Unsupported(f"matmul accumulates K tiles {sorted(set(ks))[:4]}... instead of all {kt} exactly once")
     b8 = tb._packed is not None
-    if ta.dtype != torch.bfloat16 or (not b8 and tb.dtype != torch.bfloat16) or w.tensor.dtype != torch.bfloat16:
-        raise Unsupported(f"matmul element types A={ta.dtype} B={tb.dtype} out={w.tensor.dtype}: "
-                          "bfloat16 (and bfloat8_b weights) only")
+    all_bf16 = ta.dtype == torch.bfloat16 and (b8 or tb.dtype == torch.bfloat16) and w.tensor.dtype == torch.bfloat16
+    all_f32 = ta.dtype == torch.float32 and not b8 and tb.dtype == torch.float32 and w.tensor.dtype == torch.float32
+    if not (all_bf16 or all_f32):
+        raise Unsupported(f"matmul element types A={ta.dtype} B={tb.dtype} out={w.tensor.dtype}: all bfloat16 "
+                          "(optionally bfloat8_b weights) or all float32")
     return (table.index(ta), table.index(tb), oi, kt, b8)
