@@ -54,32 +54,53 @@ inline uint8_t quantise(uint32_t bits, int E) {
   return (uint8_t)(((bits >> 31) << 7) | m);
 }
 
-__global__ void __launch_bounds__(256) ttlb_unpack_bfp8_kernel(const uint8_t *__restrict__ tiles, int tile_cols_total,
-                                                             int tile_col0, int tile_rows, int tile_cols,
-                                                             __nv_bfloat16 *__restrict__ out, long long ld) {
-  // one thread per block of 16 values
-  const long long blocks = (long long)tile_rows * tile_cols * 64;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < blocks;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int blk = (int)(i & 63);
-    const long long t = i >> 6;
-    const int tc = (int)(t % tile_cols), tr = (int)(t / tile_cols);
-    const uint8_t *tile = tiles + ((long long)tr * tile_cols_total + tile_col0 + tc) * TTLB_BFP8_TILE_BYTES;
-    const int f = blk >> 4, fr = blk & 15;
-    const int E = tile[blk];
-    const uint4 v = *reinterpret_cast<const uint4 *>(tile + 64 + f * 256 + fr * 16);
-    const float scale = E >= 7 ? __uint_as_float((uint32_t)(E - 6) << 23) : ldexpf(1.0f, E - 133);
-    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-    uint32_t o[8];
+// 16 magnitudes/signs (one block) -> 16 bf16, exact.  Fast path on packed bf16 pairs: the byte is
+// spliced under the exponent byte of 128.0 (0x43), giving bf16(128 + m) exactly; one fused
+// multiply-add (128 + m) * 2^(E-133) - 128 * 2^(E-133) leaves m * 2^(E-133) with no rounding, and
+// the sign bit is moved into place.  Five instructions per pair of values.
+__device__ __forceinline__ void unpack_block(const uint4 v, const int E, uint32_t (&o)[8]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  if (E >= 7 && E <= 250) {
+    const uint32_t sc = (uint32_t)(E - 6) << 7, nb = 0x8000u | ((uint32_t)(E + 1) << 7);
+    const uint32_t sc2 = sc | (sc << 16), nb2 = nb | (nb << 16);
+    const __nv_bfloat162 scale = *reinterpret_cast<const __nv_bfloat162 *>(&sc2);
+    const __nv_bfloat162 nbias = *reinterpret_cast<const __nv_bfloat162 *>(&nb2);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const uint32_t pr = __byte_perm(w[q >> 1], 0x43434343u, (q & 1) ? 0x4342u : 0x4140u);  // [b, 0x43, b', 0x43]
+      const uint32_t xb = pr & 0xff7fff7fu;
+      const __nv_bfloat162 y = __hfma2(*reinterpret_cast<const __nv_bfloat162 *>(&xb), scale, nbias);
+      o[q] = *reinterpret_cast<const uint32_t *>(&y) ^ ((pr << 8) & 0x80008000u);
+    }
+  } else {  // exponents at the edge of the range (denormal results / overflowing bias): fp32 route
+    const float scale = ldexpf(1.0f, E - 133);
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
       const uint32_t b0 = (w[q >> 1] >> ((q & 1) * 16)) & 0xffu, b1 = (w[q >> 1] >> ((q & 1) * 16 + 8)) & 0xffu;
       float x0 = (float)(b0 & 0x7fu) * scale, x1 = (float)(b1 & 0x7fu) * scale;
       x0 = (b0 & 0x80u) ? -x0 : x0;
       x1 = (b1 & 0x80u) ? -x1 : x1;
-      __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);  // exact: 7 significant bits
+      __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
       o[q] = *reinterpret_cast<uint32_t *>(&h);
     }
+  }
+}
+
+// One thread per block of 16 values; a 256-thread CTA expands 4 consecutive tiles of one tile row
+// (blockIdx.y = tile row, blockIdx.x = group of 4 tile columns): no integer division.
+__global__ void __launch_bounds__(256) ttlb_unpack_bfp8_kernel(const uint8_t *__restrict__ tiles, int tile_cols_total,
+                                                             int tile_col0, int tile_rows, int tile_cols,
+                                                             __nv_bfloat16 *__restrict__ out, long long ld) {
+  const int blk = threadIdx.x & 63;
+  const int tc = blockIdx.x * 4 + (threadIdx.x >> 6);
+  if (tc >= tile_cols) return;
+  const int f = blk >> 4, fr = blk & 15;
+  for (int tr = blockIdx.y; tr < tile_rows; tr += gridDim.y) {
+    const uint8_t *tile = tiles + ((long long)tr * tile_cols_total + tile_col0 + tc) * TTLB_BFP8_TILE_BYTES;
+    const int E = tile[blk];
+    const uint4 v = __ldcs(reinterpret_cast<const uint4 *>(tile + 64 + f * 256 + fr * 16));
+    uint32_t o[8];
+    unpack_block(v, E, o);
     const long long row = (long long)tr * 32 + (f >> 1) * 16 + fr;
     const long long col = (long long)tc * 32 + (f & 1) * 16;
     uint4 *dst = reinterpret_cast<uint4 *>(out + row * ld + col);
@@ -135,11 +156,9 @@ extern "C" int ttlb_unpack_bfp8_b(const uint8_t *tiles, int64_t rows, int64_t co
 
 static int launch_unpack(ttlb_ctx *ctx, const uint8_t *tiles, int64_t tile_cols_total, int64_t tile_col0,
                          int64_t tile_rows, int64_t tile_cols, void *out, int64_t ld, cudaStream_t s) {
-  const long long blocks = (long long)tile_rows * tile_cols * 64;
-  long long grid = (blocks + 255) / 256;
-  const long long cap = (long long)ctx->sm_count * 16;
-  if (grid > cap) grid = cap;
-  ttlb_unpack_bfp8_kernel<<<(unsigned)grid, 256, 0, s>>>(tiles, (int)tile_cols_total, (int)tile_col0, (int)tile_rows,
+  const unsigned gx = (unsigned)((tile_cols + 3) / 4);
+  const unsigned gy = (unsigned)(tile_rows < 65535 ? tile_rows : 65535);
+  ttlb_unpack_bfp8_kernel<<<dim3(gx, gy), 256, 0, s>>>(tiles, (int)tile_cols_total, (int)tile_col0, (int)tile_rows,
                                                          (int)tile_cols, reinterpret_cast<__nv_bfloat16 *>(out), ld);
   TTLB_CUDA_CHECK(ctx, cudaGetLastError());
   ctx->launches += 1;
@@ -199,11 +218,10 @@ extern "C" int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, vo
 // Context-free launch of the unpack kernel (used by the allocation-free entry point).
 int ttlb_bfp8_unpack_launch_raw(const uint8_t *tiles, int64_t tile_cols_total, int64_t tile_col0, int64_t tile_rows,
                                 int64_t tile_cols, void *out, int64_t ld, int sm_count, cudaStream_t s) {
-  const long long blocks = (long long)tile_rows * tile_cols * 64;
-  long long grid = (blocks + 255) / 256;
-  const long long cap = (long long)sm_count * 16;
-  if (grid > cap) grid = cap;
-  ttlb_unpack_bfp8_kernel<<<(unsigned)grid, 256, 0, s>>>(tiles, (int)tile_cols_total, (int)tile_col0, (int)tile_rows,
+  (void)sm_count;
+  const unsigned gx = (unsigned)((tile_cols + 3) / 4);
+  const unsigned gy = (unsigned)(tile_rows < 65535 ? tile_rows : 65535);
+  ttlb_unpack_bfp8_kernel<<<dim3(gx, gy), 256, 0, s>>>(tiles, (int)tile_cols_total, (int)tile_col0, (int)tile_rows,
                                                          (int)tile_cols, reinterpret_cast<__nv_bfloat16 *>(out), ld);
   return cudaGetLastError() == cudaSuccess ? TTLB_OK : TTLB_ERR_CUDA;
 }
