@@ -37,19 +37,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Same, but the hardware may keep the thread suspended for up to `ns` nanoseconds waiting for the
+// phase to complete: far fewer polling instructions (and less pressure on the memory-I/O queue the
+// barrier operations share with shared-memory and tensor-memory traffic) at no wake-up cost.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false when `limit` clock cycles passed without the phase
 // completing, or when another thread of the CTA already gave up (*abort != 0).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort, long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  unsigned n = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++n & 31u) == 0u) {
-      if (*abort) return false;
-      if (clock64() - t0 > limit) {
-        *abort = 1;
-        return false;
-      }
+  while (!mbar_try_wait_hint(bar, parity, 2000u)) {  // each failed try has already waited up to ~2 us
+    if (*abort) return false;
+    if (clock64() - t0 > limit) {
+      *abort = 1;
+      return false;
     }
   }
   return true;
