@@ -266,6 +266,27 @@ def run_sharded(args):
         raise SystemExit(f"unknown workload {wl}")
 
     dev_in = [t.to(dev) for t in host_in]
+    gather = "nccl all-gather"
+    if world > 1 and not args.nccl_gather:
+        # gather by peer-to-peer copies into a symmetric output buffer, overlapped with compute
+        try:
+            if wl == "matmul_bf16_8192":
+                so = shard.SymmetricOutput((n, n), torch.bfloat16, dev)
+                step = lambda x: shard.symmetric_matmul_rows(  # noqa: E731
+                    so, x[0], x[1], lambda p_, q_, o_: ops.matmul(T(p_), T(q_), out=T(o_)), chunks)
+            elif wl == "matmul_bfp8w":
+                so = shard.SymmetricOutput((world, m, c0 * 32), torch.bfloat16, dev)
+                final = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+                step = lambda xs: shard.symmetric_matmul_cols(  # noqa: E731
+                    so, xs[0], W, final, lambda p_, q_, o_: ops.matmul(T(p_), q_, out=T(o_)), 2)
+            else:
+                so = shard.SymmetricOutput((B * H, S, D), torch.bfloat16, dev)
+                step = lambda x: shard.symmetric_attention(  # noqa: E731
+                    so, x[0], x[1], x[2], lambda q_, k_, v_, o_: ops.attention(T(q_), T(k_), T(v_), causal=True,
+                                                                             scale=D ** -0.5, out=T(o_)), chunks)
+            gather = "peer-to-peer copies into a symmetric buffer (copy engines), overlapped with compute"
+        except Exception as e:  # symmetric memory unavailable: keep the NCCL path
+            gather = f"nccl all-gather (symmetric memory unavailable: {type(e).__name__})"
 
     def barrier():
         if dist is not None:
@@ -321,7 +342,7 @@ def run_sharded(args):
             "metric": "bf16/bfp8 matmul & attention TFLOP/s", "value": tf, "unit": "TFLOP/s", "n_gpus": world,
             "steps": steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"{wl}: {desc}", "ms_compute_only": ms_compute,
+            "config": {"workload": f"{wl}: {desc}", "gather": gather if world > 1 else "none (1 GPU)", "ms_compute_only": ms_compute,
                        "tflops_compute_only": flops / (ms_compute * 1e-3) / 1e12,
                        "l2": "operands exceed the 126 MB L2" if wl != "attention" else "Q,K,V,O 1 GB total exceed L2"},
             "roofline": {"bound": "tensor", "achieved": per_gpu_kernel_tf, "peak": burst, "unit": "TFLOP/s",
@@ -350,6 +371,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (for profiler runs)")
     ap.add_argument("--eltwise-mode", default="auto", choices=["auto", "generic", "specialised"])
+    ap.add_argument("--nccl-gather", action="store_true", help="sharded workloads: gather with NCCL instead of peer copies")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

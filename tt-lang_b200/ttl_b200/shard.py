@@ -169,3 +169,85 @@ def sharded_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, units_t
     if q.shape[0] != counts[rank]:
         raise ValueError(f"rank {rank}: Q shard has {q.shape[0]} heads, expected {counts[rank]}")
     return gather_shards(compute(q, k, v), counts, 0, group)
+
+
+class SymmetricOutput:
+    """Full-size output buffer that exists at the same place on every rank (torch symmetric memory over
+    NVLink peer mappings).  A rank computes its shard straight into its own copy and then `push`es that
+    region into every peer's copy with asynchronous peer-to-peer copies on a side stream: the copy engines
+    do the gather while the SMs carry on with the next round of compute, instead of an SM-based
+    all-gather that has to wait for the persistent GEMM CTAs to leave the SMs.  No kernel of this library
+    reads or writes peer memory; `finish` joins the side stream and runs a cross-rank barrier."""
+
+    def __init__(self, shape: Tuple[int, ...], dtype: torch.dtype, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
+        self.buf = symm.empty(tuple(shape), dtype=dtype, device=device)
+        self.hdl = symm.rendezvous(self.buf, group=self.group)
+        self.peers = [self.buf if r == self.rank else self.hdl.get_buffer(r, tuple(shape), dtype)
+                      for r in range(self.world)]
+        self.side = torch.cuda.Stream(device)
+
+    def push(self, index: Tuple[slice, ...]) -> None:
+        """Send buf[index], just written on the current stream, to the same place on every peer."""
+        ev = torch.cuda.Event()
+        ev.record()
+        with torch.cuda.stream(self.side):
+            self.side.wait_event(ev)
+            for r in range(self.world):
+                if r != self.rank:
+                    self.peers[r][index].copy_(self.buf[index], non_blocking=True)
+
+    def finish(self) -> torch.Tensor:
+        torch.cuda.current_stream().wait_stream(self.side)
+        self.hdl.barrier()
+        return self.buf
+
+
+def symmetric_matmul_rows(out: SymmetricOutput, a_rows: torch.Tensor, b: torch.Tensor,
+                          compute_into: Callable[[torch.Tensor, torch.Tensor, torch.Tensor], None], chunks: int) -> torch.Tensor:
+    """Row-sharded C = A @ B into a SymmetricOutput: round c computes rows [(c*world + rank)*mc, +mc) in
+    place and pushes them to the peers while round c+1 computes (unit layout of cyclic_units)."""
+    m_total = out.buf.shape[0]
+    mc = m_total // (out.world * chunks)
+    if a_rows.shape[0] != mc * chunks:
+        raise ValueError(f"rank {out.rank}: A shard has {a_rows.shape[0]} rows, expected {mc * chunks}")
+    for c in range(chunks):
+        r0 = (c * out.world + out.rank) * mc
+        compute_into(a_rows[c * mc:(c + 1) * mc], b, out.buf[r0:r0 + mc])
+        out.push((slice(r0, r0 + mc),))
+    return out.finish()
+
+
+def symmetric_matmul_cols(out: SymmetricOutput, x: torch.Tensor, w_cols, final: torch.Tensor,
+                          compute_into: Callable, chunks: int) -> torch.Tensor:
+    """Column-sharded C = X @ W.  `out` is a SymmetricOutput of shape [world, M, n_local]: every rank
+    computes its column block into its own contiguous slab (rows of X in `chunks` rounds, each pushed to
+    the peers as one contiguous copy while the next round computes); once all slabs have arrived, one
+    local strided copy interleaves them into `final` [M, world * n_local]."""
+    world, m, n_local = out.buf.shape
+    mc = m // chunks
+    for c in range(chunks):
+        compute_into(x[c * mc:(c + 1) * mc], w_cols, out.buf[out.rank, c * mc:(c + 1) * mc])
+        out.push((out.rank, slice(c * mc, (c + 1) * mc)))
+    slabs = out.finish()
+    final.view(m, world, n_local).copy_(slabs.permute(1, 0, 2))
+    return final
+
+
+def symmetric_attention(out: SymmetricOutput, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                        compute_into: Callable, chunks: int) -> torch.Tensor:
+    """(batch, head)-sharded attention into a SymmetricOutput of shape [units_total, S, D]."""
+    units_total = out.buf.shape[0]
+    uc = units_total // (out.world * chunks)
+    if q.shape[0] != uc * chunks:
+        raise ValueError(f"rank {out.rank}: Q shard has {q.shape[0]} heads, expected {uc * chunks}")
+    for c in range(chunks):
+        u0 = (c * out.world + out.rank) * uc
+        sl = slice(c * uc, (c + 1) * uc)
+        compute_into(q[sl], k[sl], v[sl], out.buf[u0:u0 + uc])
+        out.push((slice(u0, u0 + uc),))
+    return out.finish()
