@@ -70,9 +70,12 @@ def cyclic_units(n_units: int, world: int, rank: int, chunks: int) -> List[Tuple
 
 
 def pick_chunks(n_units: int, world: int, want: int = 4) -> int:
-    """Largest number of rounds <= want that divides the units evenly (0: not even one)."""
+    """Largest number of rounds <= want that divides the units evenly (0: not even one).  With many
+    ranks the per-round pieces get small and per-copy overheads add up, so fewer rounds are asked for."""
     if world <= 1:
         return 1
+    if world >= 8:
+        want = min(want, 2)
     for c in range(want, 0, -1):
         if n_units % (world * c) == 0:
             return c
@@ -197,9 +200,9 @@ class SymmetricOutput:
         ev.record()
         with torch.cuda.stream(self.side):
             self.side.wait_event(ev)
-            for r in range(self.world):
-                if r != self.rank:
-                    self.peers[r][index].copy_(self.buf[index], non_blocking=True)
+            for k in range(1, self.world):   # start with the next rank so that receivers are hit evenly
+                r = (self.rank + k) % self.world
+                self.peers[r][index].copy_(self.buf[index], non_blocking=True)
 
     def finish(self) -> torch.Tensor:
         torch.cuda.current_stream().wait_stream(self.side)
