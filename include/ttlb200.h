@@ -286,6 +286,10 @@ TTLB_EXPORT int ttlb_attention(ttlb_ctx *ctx, const ttlb_attn_desc *desc, void *
  * simulator bounds its waits the same way (CB_DEFAULT_TIMEOUT / COPY_PIPE_TIMEOUT,
  * python/sim/constants.py:47-48). */
 TTLB_EXPORT int ttlb_check_status(ttlb_ctx *ctx, void *stream);
+/* Self-test of that machinery: launches one CTA that waits, with the given limit (at most 2e9
+ * cycles), on a barrier nothing ever arrives on.  The wait gives up, the kernel returns normally,
+ * and the next ttlb_check_status reports TTLB_ERR_TIMEOUT.  Never hangs by construction. */
+TTLB_EXPORT int ttlb_selftest_wait_timeout(ttlb_ctx *ctx, int64_t limit_cycles, void *stream);
 /* Bound of a device-side wait in SM clock cycles (default 4e9, about two seconds). */
 TTLB_EXPORT int ttlb_set_wait_limit(ttlb_ctx *ctx, int64_t cycles);
 

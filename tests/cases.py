@@ -86,6 +86,9 @@ CASES: List[Case] = [
     Case("sum_of_products", "eltwise", "sum_of_products",
          [((64, 96), "uniform", 30), ((64, 96), "uniform", 31), ((64, 96), "uniform", 32), ((64, 96), "positive", 33)],
          (64, 96), "native", ("div", ("sub", ("mul", 0, 1), ("mul", 2, 3)), ("add", ("mul", 0, 0), 3)), "exact"),
+    # intermediate circular buffer filled and drained by the compute thread; rows dealt out over 2 cores
+    Case("intermediate_cb", "eltwise", "intermediate_cb", [((160, 96), "uniform", 34), ((160, 96), "uniform", 35)],
+         (160, 96), "native", ("mul", ("exp", 0), 1), "ulp1"),
     # multicast pipe: only the 4 cores of the pipe compute (columns 0..3 of the output)
     Case("eltwise_pipe", "eltwise", "eltwise_pipe", [((128, 2048), "uniform", 40), ((128, 2048), "uniform", 41), ((32, 32), "uniform", 42)],
          (128, 2048), "native", _MAB, "exact"),

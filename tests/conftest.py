@@ -11,6 +11,15 @@ for p in (ROOT, ROOT / "tt-lang_b200", ROOT / "tests"):
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu on the GPU box)")
+    # the native library is built in-tree and is not under version control: build it when it is missing
+    lib = ROOT / "tt-lang_b200" / "ttl_b200" / "libttlb200.so"
+    if not lib.exists():
+        import importlib.util
+
+        spec = importlib.util.spec_from_file_location("ttlb200_build", ROOT / "tt-lang_b200" / "build.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        mod.build()
 
 
 @pytest.fixture(scope="session")

@@ -361,3 +361,42 @@ def eltwise_pipe(a_in, b_in, c_tile, out):
                 tx = ttl.copy(out_block, out[rs, cs])
                 tx.wait()
                 out_cb.pop()
+
+
+@ttl.kernel(grid=(2, 1))
+def intermediate_cb(a, b, y):
+    """Y = exp(A) * B with the exponential staged through an intermediate circular buffer that the
+    compute thread both fills and drains (the pattern of test/python/test_intermediate_cb.py)."""
+    rt, ct = a.shape[0] // 32, a.shape[1] // 32
+    n_cores = ttl.grid_size(dims=1)
+    a_cb = ttl.make_circular_buffer_like(a, shape=(1, ct), buffer_factor=2)
+    b_cb = ttl.make_circular_buffer_like(b, shape=(1, ct), buffer_factor=2)
+    t_cb = ttl.make_circular_buffer_like(a, shape=(1, ct), buffer_factor=2)
+    y_cb = ttl.make_circular_buffer_like(y, shape=(1, ct), buffer_factor=2)
+
+    def my_rows():
+        return range(ttl.core(dims=1), rt, n_cores)
+
+    @ttl.compute()
+    def compute():
+        for _ in my_rows():
+            with a_cb.wait() as a_blk, t_cb.reserve() as t_blk:
+                t_blk.store(ttl.math.exp(a_blk))
+            with t_cb.wait() as t_blk, b_cb.wait() as b_blk, y_cb.reserve() as y_blk:
+                y_blk.store(t_blk * b_blk)
+
+    @ttl.datamovement()
+    def read():
+        for r in my_rows():
+            with a_cb.reserve() as a_blk, b_cb.reserve() as b_blk:
+                t1 = ttl.copy(a[r:r + 1, 0:ct], a_blk)
+                t2 = ttl.copy(b[r:r + 1, 0:ct], b_blk)
+                t1.wait()
+                t2.wait()
+
+    @ttl.datamovement()
+    def write():
+        for r in my_rows():
+            with y_cb.wait() as y_blk:
+                tx = ttl.copy(y_blk, y[r:r + 1, 0:ct])
+                tx.wait()

@@ -21,7 +21,7 @@ def test_split_units():
     from ttl_b200.shard import cyclic_units, pick_chunks
     assert cyclic_units(16, 2, 1, 2) == [(4, 4), (12, 4)]
     assert cyclic_units(8, 4, 3, 1) == [(6, 2)]
-    assert pick_chunks(256, 8) == 4 and pick_chunks(6, 2) == 3 and pick_chunks(5, 2) == 0 and pick_chunks(7, 1) == 1
+    assert pick_chunks(256, 8) == 2 and pick_chunks(256, 4) == 4 and pick_chunks(6, 2) == 3 and pick_chunks(5, 2) == 0 and pick_chunks(7, 1) == 1
     assert sum(c for _, c in split_units(896, 8)) == 896
     with pytest.raises(ValueError):
         split_units(4, 0)

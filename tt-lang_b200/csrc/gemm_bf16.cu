@@ -318,9 +318,9 @@ extern "C" int ttlb_check_status(ttlb_ctx *ctx, void *stream) {
   if (code != 0) {
     TTLB_CUDA_CHECK(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), s));
     TTLB_CUDA_CHECK(ctx, cudaStreamSynchronize(s));
-    static const char *who[] = {"", "TMA producer", "UMMA issuer", "epilogue", "softmax", "correction"};
+    static const char *who[] = {"", "TMA producer", "UMMA issuer", "epilogue", "softmax", "correction", "self-test"};
     return ttlb_fail(ctx, TTLB_ERR_TIMEOUT, "a bounded device-side wait ran out (%s, code %d)",
-                     code > 0 && code < 6 ? who[code] : "?", code);
+                     code > 0 && code < 7 ? who[code] : "?", code);
   }
   return TTLB_OK;
 }
@@ -359,4 +359,40 @@ int ttlb_gemm_bf16_launch_raw(const void *a, int64_t lda, const void *b, int64_t
   const int tiles = p.tiles_m * p.tiles_n;
   ttlb_gemm_bf16_kernel<<<tiles < sm_count ? tiles : sm_count, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   return cudaGetLastError() == cudaSuccess ? TTLB_OK : TTLB_ERR_CUDA;
+}
+
+// ---- self-test of the bounded-wait machinery ------------------------------------------------
+// One CTA initialises an mbarrier that nothing ever arrives on and waits for it with the given
+// cycle limit.  The wait must give up, raise the abort flag, and the kernel must record code 6 in the
+// status word and return normally - the same path a real kernel takes when a producer never shows
+// up - so that the host-side reporting (ttlb_check_status -> TTLB_ERR_TIMEOUT) can be tested without
+// ever hanging a GPU.
+namespace {
+__global__ void ttlb_wait_selftest_kernel(int *status, long long limit) {
+  __shared__ unsigned long long bar_storage;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar_storage), 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait(smem_u32(&bar_storage), 0, &abort_flag, limit);
+    if (!ok) atomicCAS(status, 0, 6);
+  }
+  __syncthreads();
+}
+}  // namespace
+
+extern "C" int ttlb_selftest_wait_timeout(ttlb_ctx *ctx, int64_t limit_cycles, void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  if (limit_cycles <= 0 || limit_cycles > 2000000000LL)
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "selftest: limit must be in (0, 2e9] cycles");
+  ttlb_device_guard g(ctx->device);
+  if (!g.ok) return ttlb_fail(ctx, TTLB_ERR_CUDA, "selftest: cannot select device %d", ctx->device);
+  ttlb_wait_selftest_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ctx->d_status, limit_cycles);
+  TTLB_CUDA_CHECK(ctx, cudaGetLastError());
+  ctx->launches += 1;
+  return TTLB_OK;
 }

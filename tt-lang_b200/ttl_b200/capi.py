@@ -135,6 +135,8 @@ def lib() -> C.CDLL:
     l.ttlb_matmul_f32.restype = C.c_int
     l.ttlb_check_status.argtypes = [C.c_void_p, C.c_void_p]
     l.ttlb_check_status.restype = C.c_int
+    l.ttlb_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
+    l.ttlb_selftest_wait_timeout.restype = C.c_int
     l.ttlb_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
     l.ttlb_set_wait_limit.restype = C.c_int
     _LIB = l
@@ -184,6 +186,10 @@ class Context:
     def check_status(self, stream: int = 0) -> None:
         """Synchronise `stream` and raise if a bounded device-side wait ran out since the last check."""
         self.check(self._lib.ttlb_check_status(self.handle, C.c_void_p(stream)))
+
+    def selftest_wait_timeout(self, limit_cycles: int, stream: int = 0) -> None:
+        """Launch the bounded-wait self-test (a wait that nothing satisfies, with a short limit)."""
+        self.check(self._lib.ttlb_selftest_wait_timeout(self.handle, limit_cycles, C.c_void_p(stream)))
 
     def set_wait_limit(self, cycles: int) -> None:
         self.check(self._lib.ttlb_set_wait_limit(self.handle, cycles))
