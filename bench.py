@@ -267,26 +267,82 @@ def run_sharded(args):
 
     dev_in = [t.to(dev) for t in host_in]
     gather = "nccl all-gather"
-    if world > 1 and not args.nccl_gather:
-        # gather by peer-to-peer copies into a symmetric output buffer, overlapped with compute
+    if args.gather == "auto":   # measured: peer copies win at 2 ranks, one multicast re-send at 8
+        args.gather = "multicast" if world >= 4 else "p2p"
+    if world > 1 and args.gather != "nccl":
         try:
             if wl == "matmul_bf16_8192":
                 so = shard.SymmetricOutput((n, n), torch.bfloat16, dev)
-                step = lambda x: shard.symmetric_matmul_rows(  # noqa: E731
-                    so, x[0], x[1], lambda p_, q_, o_: ops.matmul(T(p_), T(q_), out=T(o_)), chunks)
             elif wl == "matmul_bfp8w":
-                so = shard.SymmetricOutput((world, m, c0 * 32), torch.bfloat16, dev)
-                final = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
-                step = lambda xs: shard.symmetric_matmul_cols(  # noqa: E731
-                    so, xs[0], W, final, lambda p_, q_, o_: ops.matmul(T(p_), q_, out=T(o_)), 2)
+                so = shard.SymmetricOutput((m, n), torch.bfloat16, dev) if args.gather in ("multicast", "fused") else \
+                    shard.SymmetricOutput((world, m, c0 * 32), torch.bfloat16, dev)
             else:
                 so = shard.SymmetricOutput((B * H, S, D), torch.bfloat16, dev)
-                step = lambda x: shard.symmetric_attention(  # noqa: E731
-                    so, x[0], x[1], x[2], lambda q_, k_, v_, o_: ops.attention(T(q_), T(k_), T(v_), causal=True,
-                                                                             scale=D ** -0.5, out=T(o_)), chunks)
-            gather = "peer-to-peer copies into a symmetric buffer (copy engines), overlapped with compute"
+            if args.gather == "multicast" and so.has_multicast:
+                # compute into the local copy, then one kernel re-sends the shard through the switch
+                # (multimem.st, coalesced): 1x outgoing traffic instead of (world-1)x
+                esz = 2
+                if wl == "matmul_bf16_8192":
+                    ml = n // world
+                    a_contig = a[rank * ml:(rank + 1) * ml].contiguous().to(dev)
+                    mine_view = so.buf[rank * ml:(rank + 1) * ml]
+                    run_local = lambda x: ops.matmul(T(a_contig), T(x[1]), out=T(mine_view))  # noqa: E731
+                elif wl == "matmul_bfp8w":
+                    nl = c0 * 32
+                    mine_view = so.buf[:, rank * nl:(rank + 1) * nl]
+                    run_local = lambda xs: ops.launch_gemm(ctx, T(xs[0]), W, T(mine_view), (0, m, 0, nl),  # noqa: E731
+                                                           capi.current_stream())
+                else:
+                    ul = (B * H) // world
+                    mine_view = so.buf[rank * ul:(rank + 1) * ul]
+                    host_in = [cases.gen((ul * S, D), "normal", sd + 10 * rank).reshape(ul, S, D).pin_memory() for sd in (0, 1, 2)]
+                    dev_in = [t.to(dev) for t in host_in]
+                    run_local = lambda x: ops.attention(T(x[0]), T(x[1]), T(x[2]), causal=True, scale=D ** -0.5,  # noqa: E731
+                                                        out=T(mine_view))
+                v2 = mine_view if mine_view.dim() == 2 else mine_view.reshape(mine_view.shape[0], -1)
+                rows_, row_bytes_, ld_bytes_ = v2.shape[0], v2.shape[1] * esz, v2.stride(0) * esz
+
+                def step(x):
+                    run_local(x)
+                    ctx.multimem_bcast(mine_view.data_ptr(), ld_bytes_, so.multicast_ptr_of(mine_view), ld_bytes_, rows_,
+                                       row_bytes_, capi.current_stream())
+                    return so.barrier()
+                gather = "local compute, then the shard is re-sent once through the NVSwitch (multimem.st kernel), barrier"
+            elif args.gather == "fused" and so.has_multicast and wl != "attention":
+                # publication fused into the GEMM epilogue: every tile is stored once with multimem.st and
+                # the NVSwitch delivers it to all ranks; one launch per rank, then a cross-rank barrier
+                if wl == "matmul_bf16_8192":
+                    ml = n // world
+                    a_contig = a[rank * ml:(rank + 1) * ml].contiguous().to(dev)
+                    mine_view = so.buf[rank * ml:(rank + 1) * ml]
+
+                    def step(x):
+                        ops.matmul(T(a_contig), T(x[1]), out=T(mine_view), multicast_ptr=so.multicast_ptr_of(mine_view))
+                        return so.barrier()
+                else:
+                    nl = c0 * 32
+                    mine_view = so.buf[:, rank * nl:(rank + 1) * nl]
+
+                    def step(xs):
+                        ops.launch_gemm(ctx, T(xs[0]), W, T(mine_view), (0, m, 0, nl), capi.current_stream(),
+                                        so.multicast_ptr_of(mine_view))
+                        return so.barrier()
+                gather = "multimem.st in the GEMM epilogue (NVSwitch multicast), then a cross-rank barrier"
+            else:
+                if wl == "matmul_bf16_8192":
+                    step = lambda x: shard.symmetric_matmul_rows(  # noqa: E731
+                        so, x[0], x[1], lambda p_, q_, o_: ops.matmul(T(p_), T(q_), out=T(o_)), chunks)
+                elif wl == "matmul_bfp8w":
+                    final = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+                    step = lambda xs: shard.symmetric_matmul_cols(  # noqa: E731
+                        so, xs[0], W, final, lambda p_, q_, o_: ops.matmul(T(p_), q_, out=T(o_)), 2)
+                else:
+                    step = lambda x: shard.symmetric_attention(  # noqa: E731
+                        so, x[0], x[1], x[2], lambda q_, k_, v_, o_: ops.attention(T(q_), T(k_), T(v_), causal=True,
+                                                                                 scale=D ** -0.5, out=T(o_)), chunks)
+                gather = "peer-to-peer copies into a symmetric buffer (copy engines), overlapped with compute"
         except Exception as e:  # symmetric memory unavailable: keep the NCCL path
-            gather = f"nccl all-gather (symmetric memory unavailable: {type(e).__name__})"
+            gather = f"nccl all-gather (symmetric memory unavailable: {type(e).__name__}: {e})"[:160]
 
     def barrier():
         if dist is not None:
@@ -371,7 +427,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (for profiler runs)")
     ap.add_argument("--eltwise-mode", default="auto", choices=["auto", "generic", "specialised"])
-    ap.add_argument("--nccl-gather", action="store_true", help="sharded workloads: gather with NCCL instead of peer copies")
+    ap.add_argument("--gather", default="auto", choices=["auto", "p2p", "multicast", "fused", "nccl"],
+                    help="sharded workloads: how output shards reach the other ranks (auto = p2p: peer-to-peer copies overlapped with "
+                         "compute; multicast: one multimem.st kernel after the compute; fused: multimem.st from the GEMM "
+                         "epilogue; nccl: all-gather)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 

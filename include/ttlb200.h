@@ -279,6 +279,25 @@ typedef struct {
 
 TTLB_EXPORT int ttlb_attention(ttlb_ctx *ctx, const ttlb_attn_desc *desc, void *stream);
 
+/* ------------------------------------------------------------------------ *
+ * Publishing an output shard to every GPU of the box through the NVSwitch.
+ *
+ * No counterpart in the reference (it is single-chip).  `mc_dst` is a multicast address: memory
+ * that is bound, at the same offset, on every GPU of a multicast group (for instance
+ * torch.distributed._symmetric_memory's multicast_ptr plus a byte offset).  The region
+ * [rows x row_bytes] at `src` (pitch src_ld_bytes) is written once with multimem.st and the switch
+ * replicates it to all GPUs, this one included.  Completion on the stream means the stores were
+ * issued; a cross-rank barrier after it makes them visible everywhere.
+ * ------------------------------------------------------------------------ */
+/* The matmuls with the publication fused into the epilogue: desc->c is the multicast address of
+ * the output region (same pitch); every output tile is stored once with multimem.st while the tensor
+ * cores work on the next tile, and arrives in the output buffer of every GPU.  n must be a multiple
+ * of 32.  Nothing is written through the ordinary (unicast) mapping. */
+TTLB_EXPORT int ttlb_matmul_bf16_multicast(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, void *stream);
+TTLB_EXPORT int ttlb_matmul_bfp8w_multicast(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, void *stream);
+TTLB_EXPORT int ttlb_multimem_bcast(ttlb_ctx *ctx, const void *src, int64_t src_ld_bytes, void *mc_dst,
+                                    int64_t dst_ld_bytes, int64_t rows, int64_t row_bytes, void *stream);
+
 /* Kernels that wait on hardware barriers (matmul, attention) bound every wait; when
  * one runs out the kernel unwinds normally and records which role gave up.
  * ttlb_check_status synchronises `stream`, returns TTLB_ERR_TIMEOUT if that happened

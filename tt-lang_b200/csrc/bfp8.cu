@@ -26,6 +26,8 @@
 
 int ttlb_launch_gemm_bf16(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
                           int64_t m, int64_t n, int64_t k, cudaStream_t stream);
+int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
+                             int64_t m, int64_t n, int64_t k, bool multicast, cudaStream_t stream);
 
 namespace {
 
@@ -188,7 +190,7 @@ extern "C" int ttlb_unpack_bfp8_b_device(ttlb_ctx *ctx, const void *tiles, int64
                        out_bf16, ld, reinterpret_cast<cudaStream_t>(stream));
 }
 
-extern "C" int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, void *stream) {
+static int matmul_bfp8w_impl(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, bool multicast, void *stream) {
   if (!ctx) return TTLB_ERR_INVALID_ARG;
   if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul_bfp8w: null descriptor");
   if (d->m == 0 || d->n == 0) return TTLB_OK;
@@ -212,7 +214,15 @@ extern "C" int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, vo
   rc = launch_unpack(ctx, reinterpret_cast<const uint8_t *>(d->b_tiles), d->b_tile_cols, d->b_tile_col0, d->k / 32,
                      d->n / 32, ctx->scratch, d->n, s);
   if (rc) return rc;
-  return ttlb_launch_gemm_bf16(ctx, d->a, d->lda, ctx->scratch, d->n, d->c, d->ldc, d->m, d->n, d->k, s);
+  return ttlb_launch_gemm_bf16_ex(ctx, d->a, d->lda, ctx->scratch, d->n, d->c, d->ldc, d->m, d->n, d->k, multicast, s);
+}
+
+extern "C" int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, void *stream) {
+  return matmul_bfp8w_impl(ctx, d, false, stream);
+}
+
+extern "C" int ttlb_matmul_bfp8w_multicast(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, void *stream) {
+  return matmul_bfp8w_impl(ctx, d, true, stream);
 }
 
 // Context-free launch of the unpack kernel (used by the allocation-free entry point).

@@ -60,7 +60,15 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int *status;
   long long wait_limit;
+  int multicast;  // 1: `c` is an NVLink multicast address; the epilogue stores with multimem.st
 };
+
+// 16-byte store to a multicast address: the switch replicates it to every GPU of the group.
+__device__ __forceinline__ void st_multimem_16(void *p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn) {
   const int per_group = GROUP_M * tiles_n;
@@ -206,7 +214,10 @@ ttlb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
               o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
               o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
               o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-              *reinterpret_cast<uint4 *>(crow + c * 32 + v * 8) = o;
+              if (p.multicast)
+                st_multimem_16(crow + c * 32 + v * 8, o);
+              else
+                *reinterpret_cast<uint4 *>(crow + c * 32 + v * 8) = o;
             }
           } else {
 #pragma unroll
@@ -254,9 +265,20 @@ int make_map(ttlb_ctx *ctx, CUtensorMap *map, const void *ptr, uint64_t inner, u
 }  // namespace
 
 // Shared with the bfp8-weight path, which first expands the weights to bf16.
+int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
+                             int64_t m, int64_t n, int64_t k, bool multicast, cudaStream_t stream);
+
 int ttlb_launch_gemm_bf16(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
                           int64_t m, int64_t n, int64_t k, cudaStream_t stream) {
+  return ttlb_launch_gemm_bf16_ex(ctx, a, lda, b, ldb, c, ldc, m, n, k, false, stream);
+}
+
+// multicast: `c` is a multicast address (the output is published to every GPU of the group); needs n % 32 == 0
+int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
+                             int64_t m, int64_t n, int64_t k, bool multicast, cudaStream_t stream) {
   if (m == 0 || n == 0) return TTLB_OK;
+  if (multicast && (n % 32))
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: a multicast output needs N to be a multiple of 32");
   if (!a || !b || !c) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null operand");
   if (m < 0 || n < 0 || k <= 0) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: bad shape %lldx%lldx%lld",
                                                  (long long)m, (long long)n, (long long)k);
@@ -293,6 +315,7 @@ int ttlb_launch_gemm_bf16(ttlb_ctx *ctx, const void *a, int64_t lda, const void 
   p.tiles_n = (int)((n + BN - 1) / BN);
   p.status = ctx->d_status;
   p.wait_limit = ctx->wait_limit_cycles;
+  p.multicast = multicast ? 1 : 0;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
   ttlb_gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
@@ -306,6 +329,13 @@ extern "C" int ttlb_matmul_bf16(ttlb_ctx *ctx, const ttlb_gemm_desc *d, void *st
   if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null descriptor");
   return ttlb_launch_gemm_bf16(ctx, d->a, d->lda, d->b, d->ldb, d->c, d->ldc, d->m, d->n, d->k,
                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ttlb_matmul_bf16_multicast(ttlb_ctx *ctx, const ttlb_gemm_desc *d, void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null descriptor");
+  return ttlb_launch_gemm_bf16_ex(ctx, d->a, d->lda, d->b, d->ldb, d->c, d->ldc, d->m, d->n, d->k, true,
+                                  reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ttlb_check_status(ttlb_ctx *ctx, void *stream) {
@@ -356,6 +386,7 @@ int ttlb_gemm_bf16_launch_raw(const void *a, int64_t lda, const void *b, int64_t
   p.tiles_n = (int)((n + BN - 1) / BN);
   p.status = d_status;
   p.wait_limit = wait_limit;
+  p.multicast = 0;
   const int tiles = p.tiles_m * p.tiles_n;
   ttlb_gemm_bf16_kernel<<<tiles < sm_count ? tiles : sm_count, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   return cudaGetLastError() == cudaSuccess ? TTLB_OK : TTLB_ERR_CUDA;

@@ -135,6 +135,13 @@ def lib() -> C.CDLL:
     l.ttlb_matmul_f32.restype = C.c_int
     l.ttlb_check_status.argtypes = [C.c_void_p, C.c_void_p]
     l.ttlb_check_status.restype = C.c_int
+    l.ttlb_matmul_bf16_multicast.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]
+    l.ttlb_matmul_bf16_multicast.restype = C.c_int
+    l.ttlb_matmul_bfp8w_multicast.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p]
+    l.ttlb_matmul_bfp8w_multicast.restype = C.c_int
+    l.ttlb_multimem_bcast.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
+                                      C.c_void_p]
+    l.ttlb_multimem_bcast.restype = C.c_int
     l.ttlb_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
     l.ttlb_selftest_wait_timeout.restype = C.c_int
     l.ttlb_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
@@ -186,6 +193,17 @@ class Context:
     def check_status(self, stream: int = 0) -> None:
         """Synchronise `stream` and raise if a bounded device-side wait ran out since the last check."""
         self.check(self._lib.ttlb_check_status(self.handle, C.c_void_p(stream)))
+
+    def matmul_bf16_multicast(self, desc: "GemmDesc", stream: int) -> None:
+        self.check(self._lib.ttlb_matmul_bf16_multicast(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def matmul_bfp8w_multicast(self, desc: "GemmBfp8Desc", stream: int) -> None:
+        self.check(self._lib.ttlb_matmul_bfp8w_multicast(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def multimem_bcast(self, src_ptr: int, src_ld_bytes: int, mc_dst_ptr: int, dst_ld_bytes: int, rows: int,
+                       row_bytes: int, stream: int) -> None:
+        self.check(self._lib.ttlb_multimem_bcast(self.handle, C.c_void_p(src_ptr), src_ld_bytes, C.c_void_p(mc_dst_ptr),
+                                                 dst_ld_bytes, rows, row_bytes, C.c_void_p(stream)))
 
     def selftest_wait_timeout(self, limit_cycles: int, stream: int = 0) -> None:
         """Launch the bounded-wait self-test (a wait that nothing satisfies, with a short limit)."""

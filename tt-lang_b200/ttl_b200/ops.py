@@ -23,8 +23,10 @@ def _dev2d(t: "_ttnn.Tensor", what: str) -> torch.Tensor:
 
 
 def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_ttnn.Tensor",
-                rect: Tuple[int, int, int, int], stream: int) -> None:
-    """out[r0:r1, c0:c1] = a[r0:r1, :] @ b[:, c0:c1] (element coordinates)."""
+                rect: Tuple[int, int, int, int], stream: int, multicast_ptr: Optional[int] = None) -> None:
+    """out[r0:r1, c0:c1] = a[r0:r1, :] @ b[:, c0:c1] (element coordinates).  With `multicast_ptr` (the
+    NVLink multicast address of out's element (0, 0)) the result is stored through the switch to every GPU
+    of the multicast group instead of through out's own mapping."""
     r0, r1, c0, c1 = rect
     if b._packed is not None:
         xa, xo = _dev2d(a, "A"), _dev2d(out, "out")
@@ -37,9 +39,13 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
         g = capi.GemmBfp8Desc()
         g.a, g.lda = xa.data_ptr() + r0 * xa.stride(0) * 2, xa.stride(0)
         g.b_tiles, g.b_tile_cols, g.b_tile_col0 = b._packed.data_ptr(), b.shape[1] // 32, c0 // 32
-        g.c, g.ldc = xo.data_ptr() + (r0 * xo.stride(0) + c0) * 2, xo.stride(0)
+        c_base = xo.data_ptr() if multicast_ptr is None else multicast_ptr
+        g.c, g.ldc = c_base + (r0 * xo.stride(0) + c0) * 2, xo.stride(0)
         g.m, g.n, g.k = r1 - r0, c1 - c0, xa.shape[1]
-        ctx.matmul_bfp8w(g, stream)
+        if multicast_ptr is None:
+            ctx.matmul_bfp8w(g, stream)
+        else:
+            ctx.matmul_bfp8w_multicast(g, stream)
         return
     xa, xb, xo = _dev2d(a, "A"), _dev2d(b, "B"), _dev2d(out, "out")
     if not (xa.dtype == xb.dtype == xo.dtype) or xa.dtype not in (torch.bfloat16, torch.float32):
@@ -49,23 +55,29 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
     es = xa.element_size()
     d.a, d.lda = xa.data_ptr() + r0 * xa.stride(0) * es, xa.stride(0)
     d.b, d.ldb = xb.data_ptr() + c0 * es, xb.stride(0)
-    d.c, d.ldc = xo.data_ptr() + (r0 * xo.stride(0) + c0) * es, xo.stride(0)
+    c_base = xo.data_ptr() if multicast_ptr is None else multicast_ptr
+    d.c, d.ldc = c_base + (r0 * xo.stride(0) + c0) * es, xo.stride(0)
     d.m, d.n, d.k = r1 - r0, c1 - c0, xa.shape[1]
     if xa.dtype == torch.float32:
+        if multicast_ptr is not None:
+            raise Unsupported("multicast output: bfloat16 matmuls only")
         ctx.matmul_f32(d, stream)
+    elif multicast_ptr is not None:
+        ctx.matmul_bf16_multicast(d, stream)
     else:
         ctx.matmul_bf16(d, stream)
 
 
-def matmul(a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: Optional["_ttnn.Tensor"] = None) -> "_ttnn.Tensor":
-    """C = A @ B on the tensor cores (bf16 in, fp32 accumulate, bf16 out)."""
+def matmul(a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: Optional["_ttnn.Tensor"] = None,
+           multicast_ptr: Optional[int] = None) -> "_ttnn.Tensor":
+    """C = A @ B on the tensor cores (bf16 in, fp32 accumulate, bf16 out).  `multicast_ptr`: see launch_gemm."""
     m, n = a.shape[0], b.shape[1]
     if a.shape[1] != b.shape[0]:
         raise ValueError(f"Incompatible matrix shapes for multiplication: {a.shape} @ {b.shape}")
     if out is None:
         out = _ttnn.empty((m, n), dtype=a._tensor.dtype)
     dev = a._tensor.device.index if a._tensor.is_cuda else None
-    launch_gemm(capi.context(dev), a, b, out, (0, m, 0, n), capi.current_stream())
+    launch_gemm(capi.context(dev), a, b, out, (0, m, 0, n), capi.current_stream(), multicast_ptr)
     return out
 
 

@@ -194,6 +194,22 @@ class SymmetricOutput:
                       for r in range(self.world)]
         self.side = torch.cuda.Stream(device)
 
+    @property
+    def has_multicast(self) -> bool:
+        return bool(self.hdl.multicast_ptr)
+
+    def multicast_ptr_of(self, view: torch.Tensor) -> int:
+        """Multicast address of element 0 of `view` (a view of this rank's buffer): a store there is
+        replicated by the NVSwitch into the same place of every rank's buffer."""
+        off = view.data_ptr() - self.buf.data_ptr()
+        if not self.hdl.multicast_ptr or off < 0 or off >= self.buf.numel() * self.buf.element_size():
+            raise ValueError("not a view of this symmetric buffer, or no multicast support")
+        return int(self.hdl.multicast_ptr) + off
+
+    def barrier(self) -> torch.Tensor:
+        self.hdl.barrier()
+        return self.buf
+
     def push(self, index: Tuple[slice, ...]) -> None:
         """Send buf[index], just written on the current stream, to the same place on every peer."""
         ev = torch.cuda.Event()
