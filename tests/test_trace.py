@@ -312,3 +312,23 @@ def test_every_case_program_is_recognised(backend, tt):
         plan = case.get_program(mods, f32acc=(case.mode == "f32")).plan(*ins, out)
         kinds = {d["kind"] for d in plan.describe()}
         assert kinds == ({"matmul_bf16"} if case.module == "matmul" else {"eltwise"}), case.name
+
+
+def test_translate_prints_plan_and_cuda_source(tmp_path):
+    """ttlang-b200-translate on a small program file: launch plan + specialised CUDA source, no GPU."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    prog = tmp_path / "prog.py"
+    prog.write_text(
+        "import sys; sys.path.insert(0, %r)\n"
+        "import importlib.util, torch, ttnn\n"
+        "spec = importlib.util.spec_from_file_location('pe', %r); m = importlib.util.module_from_spec(spec); spec.loader.exec_module(m)\n"
+        "z = lambda s: ttnn.from_torch(torch.zeros(s, dtype=torch.bfloat16))\n"
+        "m.fused_exp_bcast_f32acc(z((128, 256)), z((1, 1)), z((1, 256)), z((128, 256)), z((128, 256)))\n"
+        % (str(root / "tests"), str(root / "tests" / "programs" / "eltwise.py")))
+    r = subprocess.run([sys.executable, "-m", "ttl_b200.translate", str(prog)], capture_output=True, text=True,
+                       cwd=root, env={**__import__("os").environ, "PYTHONPATH": str(root / "tt-lang_b200")}, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert '"kind": "eltwise"' in r.stdout and "ttlb_eltwise_jit" in r.stdout and "expf(a)" in r.stdout

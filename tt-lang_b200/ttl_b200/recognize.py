@@ -269,6 +269,26 @@ class EltwiseLaunch:
         d.col0, d.cols = (0, 1) if self.out_degenerate[1] else (c0 * TILE, (c1 - c0) * TILE)
         return d
 
+    def desc_cpu(self, tensors: Sequence[_ttnn.Tensor]) -> capi.EltwiseDesc:
+        """The descriptor with pitches and modes filled in but no device pointers (for translation)."""
+        d = capi.EltwiseDesc()
+        d.dtype = _dtype_code(self.dtype)
+        d.round_each_op = 1 if self.round_each_op else 0
+        d.n_in, d.n_ops = len(self.inputs), len(self.ops)
+        for k, (ti, rm, ro, cm, co) in enumerate(self.inputs):
+            x = tensors[ti]._tensor
+            d.inp[k].ld = x.stride(0) if x.shape[0] > 1 else x.shape[1]
+            d.inp[k].row_mode, d.inp[k].row_off = rm, ro
+            d.inp[k].col_mode, d.inp[k].col_off = cm, co
+        for k, (op, arg) in enumerate(self.ops):
+            d.ops[k].opcode, d.ops[k].arg = capi.OPCODES[op], arg
+        o = tensors[self.out_index]._tensor
+        d.out_ld = o.stride(0) if o.shape[0] > 1 else o.shape[1]
+        r0, r1, c0, c1 = self.rect
+        d.row0, d.rows = (0, 1) if self.out_degenerate[0] else (r0 * TILE, (r1 - r0) * TILE)
+        d.col0, d.cols = (0, 1) if self.out_degenerate[1] else (c0 * TILE, (c1 - c0) * TILE)
+        return d
+
     def run(self, ctx: capi.Context, tensors: Sequence[_ttnn.Tensor], stream: int) -> None:
         ctx.eltwise(self.desc(tensors), stream)
 
