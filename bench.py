@@ -205,6 +205,7 @@ def run_sharded(args):
     from ttl_b200 import capi, ops, shard, ttnn
 
     ctx = capi.context(local)
+    ctx.set_gemm_variant(args.gemm_variant)
     T = ttnn.Tensor
     wl = args.workload
     dev = torch.device("cuda", local)
@@ -216,7 +217,7 @@ def run_sharded(args):
         mine = shard.cyclic_units(n // 32, world, rank, chunks)
         host_in = [torch.cat([a[u0 * 32:(u0 + c) * 32] for u0, c in mine]).contiguous().pin_memory(), b.pin_memory()]
         flops = 2.0 * n * n * n
-        kernel = "ttlb_gemm_bf16_kernel"
+        kernel = "ttlb_gemm_bf16_kernel" if args.gemm_variant == 0 else "ttlb_gemm_bf16_2cta_kernel"
 
         def compute(x):
             return ops.matmul(T(x[0]), T(x[1]))._tensor
@@ -234,7 +235,7 @@ def run_sharded(args):
         W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
         host_in = [x.pin_memory()]
         flops = 2.0 * m * k * n
-        kernel = "ttlb_unpack_bfp8_kernel + ttlb_gemm_bf16_kernel"
+        kernel = "ttlb_unpack_bfp8_kernel + " + ("ttlb_gemm_bf16_kernel" if args.gemm_variant == 0 else "ttlb_gemm_bf16_2cta_kernel")
         chunks = 2 if world > 1 else 1
 
         def compute(xs):
@@ -427,6 +428,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (for profiler runs)")
     ap.add_argument("--eltwise-mode", default="auto", choices=["auto", "generic", "specialised"])
+    ap.add_argument("--gemm-variant", type=int, default=1, choices=[0, 1, 2],
+                    help="tensor-core GEMM kernel: 0 one CTA per 128x256 tile, 1 two-CTA clusters per 256x256 tile for large outputs, 2 two-CTA always")
     ap.add_argument("--gather", default="auto", choices=["auto", "p2p", "multicast", "fused", "nccl"],
                     help="sharded workloads: how output shards reach the other ranks (auto = p2p: peer-to-peer copies overlapped with "
                          "compute; multicast: one multimem.st kernel after the compute; fused: multimem.st from the GEMM "

@@ -298,6 +298,14 @@ TTLB_EXPORT int ttlb_matmul_bfp8w_multicast(ttlb_ctx *ctx, const ttlb_gemm_bfp8_
 TTLB_EXPORT int ttlb_multimem_bcast(ttlb_ctx *ctx, const void *src, int64_t src_ld_bytes, void *mc_dst,
                                     int64_t dst_ld_bytes, int64_t rows, int64_t row_bytes, void *stream);
 
+/* Which tensor-core GEMM kernel the bf16 / bfp8-weight matmuls use:
+ *   0  always one CTA per 128x256 output tile (tcgen05 cta_group::1)
+ *   1  (default) a cluster of two CTAs per 256x256 tile (cta_group::2: each CTA stages half of the
+ *      B tile) when the output has at least one such tile per SM pair; smaller outputs, and the
+ *      multicast-epilogue entry points, keep the one-CTA kernel
+ *   2  the two-CTA kernel for every shape (testing) */
+TTLB_EXPORT int ttlb_set_gemm_variant(ttlb_ctx *ctx, int variant);
+
 /* Kernels that wait on hardware barriers (matmul, attention) bound every wait; when
  * one runs out the kernel unwinds normally and records which role gave up.
  * ttlb_check_status synchronises `stream`, returns TTLB_ERR_TIMEOUT if that happened

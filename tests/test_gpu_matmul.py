@@ -36,11 +36,13 @@ def test_matmul_program_matches_simulator_and_oracle(case, backend):
     assert rel_err(got, golden_tensor(load_golden(case.name)["out"], torch.bfloat16)) <= TOL
 
 
+@pytest.mark.parametrize("variant", [0, 1, 2], ids=["one_cta", "auto", "two_cta"])
 @pytest.mark.parametrize("m,n,k", [(32, 32, 32), (128, 256, 64), (160, 96, 224), (384, 520, 72), (1024, 1536, 512),
-                                   (96, 2048, 4096)])
-def test_c_abi_matmul_shapes_with_ragged_tiles(m, n, k):
-    """Direct C-ABI calls: single tile, shapes that are not multiples of the 128x256x64 CTA tile
-    (TMA zero-fills the out-of-range part, the epilogue masks it), tall-K."""
+                                   (96, 2048, 4096), (256, 256, 64), (300, 264, 136), (2304, 4352, 1024)])
+def test_c_abi_matmul_shapes_with_ragged_tiles(m, n, k, variant):
+    """Direct C-ABI calls: single tile, shapes that are not multiples of the CTA tile (TMA zero-fills
+    the out-of-range part, the epilogue masks it), tall-K; with both tensor-core kernels (the default picks
+    between them by output size)."""
     from ttl_b200 import capi, ops, ttnn
     g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
     a = (torch.randn(m, k, generator=g) / k ** 0.5).to(torch.bfloat16)
@@ -53,8 +55,12 @@ def test_c_abi_matmul_shapes_with_ragged_tiles(m, n, k):
     d.c, d.ldc = full.data_ptr() + (32 * full.stride(0) + 32) * 2, full.stride(0)
     d.m, d.n, d.k = m, n, k
     ctx = capi.context()
-    ctx.matmul_bf16(d, capi.current_stream())
-    ctx.check_status(capi.current_stream())
+    ctx.set_gemm_variant(variant)
+    try:
+        ctx.matmul_bf16(d, capi.current_stream())
+        ctx.check_status(capi.current_stream())
+    finally:
+        ctx.set_gemm_variant(1)
     got = full.cpu()
     assert rel_err(got[32:32 + m, 32:32 + n], tile_oracle.matmul_tiles(a, b, "f32")) <= TOL
     frame = got.clone()

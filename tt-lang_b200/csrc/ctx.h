@@ -29,6 +29,8 @@ struct ttlb_ctx {
   int eltwise_last_path = -1;
   // tcgen05 kernels: opt-in shared memory set once per context; bound for device-side waits
   bool gemm_attr_set = false;
+  bool gemm2_attr_set = false;
+  int gemm_variant = 1;  // 0: always one-CTA 128x256 tiles; 1: two-CTA (cta_group::2) 256x256 tiles for large outputs
   bool attn_attr_set = false;
   long long wait_limit_cycles = 4000000000LL;  // ~2 s at 1.9 GHz
   // Scratch in HBM owned by the context (bf16 expansion of bfloat8_b weights); grows on demand.

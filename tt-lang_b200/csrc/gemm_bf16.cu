@@ -264,6 +264,13 @@ int make_map(ttlb_ctx *ctx, CUtensorMap *map, const void *ptr, uint64_t inner, u
 
 }  // namespace
 
+int ttlb_make_map_bf16_2d(ttlb_ctx *ctx, CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t outer,
+                          uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer) {
+  return make_map(ctx, map, ptr, inner, outer, pitch_bytes, box_inner, box_outer);
+}
+int ttlb_launch_gemm_bf16_2cta(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
+                               int64_t m, int64_t n, int64_t k, cudaStream_t stream);
+
 // Shared with the bfp8-weight path, which first expands the weights to bf16.
 int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
                              int64_t m, int64_t n, int64_t k, bool multicast, cudaStream_t stream);
@@ -291,6 +298,11 @@ int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const vo
   if (lda < k || ldb < n || ldc < n) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: row pitch smaller than the row");
   ttlb_device_guard g(ctx->device);
   if (!g.ok) return ttlb_fail(ctx, TTLB_ERR_CUDA, "matmul: cannot select device %d", ctx->device);
+  // Two-CTA tiles once there are enough 256x256 tiles to give every SM pair one; smaller outputs
+  // spread better as 128x256 tiles.
+  if (!multicast && (ctx->gemm_variant == 2 ||
+                     (ctx->gemm_variant == 1 && ((m + 255) / 256) * ((n + 255) / 256) >= ctx->sm_count / 2)))
+    return ttlb_launch_gemm_bf16_2cta(ctx, a, lda, b, ldb, c, ldc, m, n, k, stream);
 
   CUtensorMap map_a, map_b;
   int rc = make_map(ctx, &map_a, a, (uint64_t)k, (uint64_t)m, (uint64_t)lda * 2, BK, BM);
@@ -352,6 +364,12 @@ extern "C" int ttlb_check_status(ttlb_ctx *ctx, void *stream) {
     return ttlb_fail(ctx, TTLB_ERR_TIMEOUT, "a bounded device-side wait ran out (%s, code %d)",
                      code > 0 && code < 7 ? who[code] : "?", code);
   }
+  return TTLB_OK;
+}
+
+extern "C" int ttlb_set_gemm_variant(ttlb_ctx *ctx, int variant) {
+  if (!ctx || variant < 0 || variant > 2) return TTLB_ERR_INVALID_ARG;
+  ctx->gemm_variant = variant;
   return TTLB_OK;
 }
 

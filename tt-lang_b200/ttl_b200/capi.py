@@ -144,6 +144,8 @@ def lib() -> C.CDLL:
     l.ttlb_multimem_bcast.restype = C.c_int
     l.ttlb_selftest_wait_timeout.argtypes = [C.c_void_p, C.c_int64, C.c_void_p]
     l.ttlb_selftest_wait_timeout.restype = C.c_int
+    l.ttlb_set_gemm_variant.argtypes = [C.c_void_p, C.c_int]
+    l.ttlb_set_gemm_variant.restype = C.c_int
     l.ttlb_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
     l.ttlb_set_wait_limit.restype = C.c_int
     _LIB = l
@@ -208,6 +210,10 @@ class Context:
     def selftest_wait_timeout(self, limit_cycles: int, stream: int = 0) -> None:
         """Launch the bounded-wait self-test (a wait that nothing satisfies, with a short limit)."""
         self.check(self._lib.ttlb_selftest_wait_timeout(self.handle, limit_cycles, C.c_void_p(stream)))
+
+    def set_gemm_variant(self, variant: int) -> None:
+        """0: one-CTA 128x256 tiles; 1 (default): two-CTA 256x256 tiles for large outputs; 2: two-CTA always."""
+        self.check(self._lib.ttlb_set_gemm_variant(self.handle, variant))
 
     def set_wait_limit(self, cycles: int) -> None:
         self.check(self._lib.ttlb_set_wait_limit(self.handle, cycles))
