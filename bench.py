@@ -206,6 +206,8 @@ def run_sharded(args):
 
     ctx = capi.context(local)
     ctx.set_gemm_variant(args.gemm_variant)
+    if args.bfp8_mode is not None:
+        ctx.set_bfp8_mode(args.bfp8_mode)
     T = ttnn.Tensor
     wl = args.workload
     dev = torch.device("cuda", local)
@@ -430,6 +432,8 @@ def main():
     ap.add_argument("--eltwise-mode", default="auto", choices=["auto", "generic", "specialised"])
     ap.add_argument("--gemm-variant", type=int, default=1, choices=[0, 1, 2],
                     help="tensor-core GEMM kernel: 0 one CTA per 128x256 tile, 1 two-CTA clusters per 256x256 tile for large outputs, 2 two-CTA always")
+    ap.add_argument("--bfp8-mode", type=int, default=None, choices=[0, 1, 2],
+                    help="bfp8 weights: 0 unpack kernel + GEMM, 1 unpack inside the GEMM mainloop for large outputs, 2 always inside")
     ap.add_argument("--gather", default="auto", choices=["auto", "p2p", "multicast", "fused", "nccl"],
                     help="sharded workloads: how output shards reach the other ranks (auto = p2p: peer-to-peer copies overlapped with "
                          "compute; multicast: one multimem.st kernel after the compute; fused: multimem.st from the GEMM "

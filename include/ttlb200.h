@@ -306,6 +306,14 @@ TTLB_EXPORT int ttlb_multimem_bcast(ttlb_ctx *ctx, const void *src, int64_t src_
  *   2  the two-CTA kernel for every shape (testing) */
 TTLB_EXPORT int ttlb_set_gemm_variant(ttlb_ctx *ctx, int variant);
 
+/* How ttlb_matmul_bfp8w expands the block-float weights:
+ *   0  a separate unpack kernel writes bf16 into scratch owned by the context, then the bf16 GEMM
+ *   1  inside the GEMM mainloop (packed tiles are staged in shared memory and expanded in registers
+ *      into the tensor-core operand; no scratch, no bf16 copy in HBM) when the output has at least
+ *      one 256x256 tile per SM pair, mode 0 otherwise
+ *   2  inside the mainloop for every shape (testing) */
+TTLB_EXPORT int ttlb_set_bfp8_mode(ttlb_ctx *ctx, int mode);
+
 /* Kernels that wait on hardware barriers (matmul, attention) bound every wait; when
  * one runs out the kernel unwinds normally and records which role gave up.
  * ttlb_check_status synchronises `stream`, returns TTLB_ERR_TIMEOUT if that happened

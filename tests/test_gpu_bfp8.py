@@ -21,6 +21,11 @@ def test_device_unpack_is_bit_exact(k, n, col0, cols):
     from ttl_b200 import bfp8, capi
     w = cases.gen((k, n), "normal*0.02", 1, torch.float32)
     w[0, :16] = torch.tensor([1e-30] * 8 + [3e-39] * 8)[: 16]   # a block with a tiny exponent
+    w[1, :16] = torch.tensor([3e-38, -1.5e-38] + [2e-39] * 14)      # results that are bf16 denormals
+    w[2, :16] = torch.tensor([-3e38, 1e38, 2.5e37, -7.0] + [1e30] * 12)   # the largest exponents
+    w[3, :16] = torch.tensor([1.0, -1.0, 1.5, 1.9921875, -0.0078125, 0.0] + [0.33] * 10)   # exponent 127 / 128 boundary
+    w[4, :16] = torch.tensor([2.0, -3.99, 2.5] + [1.0] * 13)
+    w[5, :16] = 0.0                                             # an all-zero block (exponent 0)
     tiles = bfp8.pack_bfp8_b(w)
     want = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))[:, col0:col0 + cols]
     out = torch.full((k, cols + 8), 9.0, dtype=torch.bfloat16, device="cuda")
@@ -33,8 +38,17 @@ def test_device_unpack_is_bit_exact(k, n, col0, cols):
     assert (got[:, cols:] == 9.0).all(), "unpack wrote outside its window"
 
 
-@pytest.mark.parametrize("m,k,n", [(64, 128, 96), (256, 512, 1024), (160, 2048, 608)])
-def test_c_abi_matmul_bfp8w(m, k, n):
+@pytest.fixture(params=[0, 1, 2], ids=["unpack_kernel", "auto", "in_mainloop"])
+def bfp8_mode(request):
+    """Run with the separate unpack kernel, the default choice, and the unpack fused into the GEMM mainloop."""
+    from ttl_b200 import capi
+    capi.context().set_bfp8_mode(request.param)
+    yield request.param
+    capi.context().set_bfp8_mode(capi.BFP8_MODE_DEFAULT)
+
+
+@pytest.mark.parametrize("m,k,n", [(64, 128, 96), (256, 512, 1024), (160, 2048, 608), (300, 96, 416), (1280, 1056, 2336)])
+def test_c_abi_matmul_bfp8w(m, k, n, bfp8_mode):
     from ttl_b200 import capi, ops, ttnn
     x = cases.gen((m, k), "normal", 0)
     w = cases.gen((k, n), "normal*0.02", 1, torch.float32)
@@ -53,7 +67,7 @@ def test_c_abi_matmul_bfp8w(m, k, n):
         assert (got2[:, :32] == 0).all() and (got2[:, 96:] == 0).all()
 
 
-def test_matmul_program_with_bfloat8_b_weights(backend):
+def test_matmul_program_with_bfloat8_b_weights(backend, bfp8_mode):
     """The multicore matmul tile program, unchanged, with B given as a bfloat8_b tensor."""
     _, mods = backend
     import ttnn
@@ -71,7 +85,7 @@ def test_matmul_program_with_bfloat8_b_weights(backend):
     assert rel_err(ttnn.to_torch(out), tile_oracle.matmul_tiles(x.float(), wq, "f32")) <= 1e-2
 
 
-def test_config4_shard_slab():
+def test_config4_shard_slab(bfp8_mode):
     """configs[3] shapes on one 2048-column stripe (what one of 14 column blocks looks like) with 256
     activation rows checked against the oracle, plus the full 4096 rows for the exact-scaling property."""
     from ttl_b200 import capi, ops, ttnn

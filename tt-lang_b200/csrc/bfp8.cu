@@ -22,12 +22,15 @@
 #include <cmath>
 #include <cstring>
 
+#include "bfp8_unpack.cuh"
 #include "ctx.h"
 
 int ttlb_launch_gemm_bf16(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
                           int64_t m, int64_t n, int64_t k, cudaStream_t stream);
 int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
                              int64_t m, int64_t n, int64_t k, bool multicast, cudaStream_t stream);
+
+int ttlb_launch_gemm_bfp8w_fused(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, cudaStream_t stream);
 
 namespace {
 
@@ -54,38 +57,6 @@ inline uint8_t quantise(uint32_t bits, int E) {
   }
   if (m > 127u) m = 127u;
   return (uint8_t)(((bits >> 31) << 7) | m);
-}
-
-// 16 magnitudes/signs (one block) -> 16 bf16, exact.  Fast path on packed bf16 pairs: the byte is
-// spliced under the exponent byte of 128.0 (0x43), giving bf16(128 + m) exactly; one fused
-// multiply-add (128 + m) * 2^(E-133) - 128 * 2^(E-133) leaves m * 2^(E-133) with no rounding, and
-// the sign bit is moved into place.  Five instructions per pair of values.
-__device__ __forceinline__ void unpack_block(const uint4 v, const int E, uint32_t (&o)[8]) {
-  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-  if (E >= 7 && E <= 250) {
-    const uint32_t sc = (uint32_t)(E - 6) << 7, nb = 0x8000u | ((uint32_t)(E + 1) << 7);
-    const uint32_t sc2 = sc | (sc << 16), nb2 = nb | (nb << 16);
-    const __nv_bfloat162 scale = *reinterpret_cast<const __nv_bfloat162 *>(&sc2);
-    const __nv_bfloat162 nbias = *reinterpret_cast<const __nv_bfloat162 *>(&nb2);
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const uint32_t pr = __byte_perm(w[q >> 1], 0x43434343u, (q & 1) ? 0x4342u : 0x4140u);  // [b, 0x43, b', 0x43]
-      const uint32_t xb = pr & 0xff7fff7fu;
-      const __nv_bfloat162 y = __hfma2(*reinterpret_cast<const __nv_bfloat162 *>(&xb), scale, nbias);
-      o[q] = *reinterpret_cast<const uint32_t *>(&y) ^ ((pr << 8) & 0x80008000u);
-    }
-  } else {  // exponents at the edge of the range (denormal results / overflowing bias): fp32 route
-    const float scale = ldexpf(1.0f, E - 133);
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const uint32_t b0 = (w[q >> 1] >> ((q & 1) * 16)) & 0xffu, b1 = (w[q >> 1] >> ((q & 1) * 16 + 8)) & 0xffu;
-      float x0 = (float)(b0 & 0x7fu) * scale, x1 = (float)(b1 & 0x7fu) * scale;
-      x0 = (b0 & 0x80u) ? -x0 : x0;
-      x1 = (b1 & 0x80u) ? -x1 : x1;
-      __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
-      o[q] = *reinterpret_cast<uint32_t *>(&h);
-    }
-  }
 }
 
 // One thread per block of 16 values; a 256-thread CTA expands 4 consecutive tiles of one tile row
@@ -199,7 +170,19 @@ static int matmul_bfp8w_impl(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, bool m
   ttlb_device_guard g(ctx->device);
   if (!g.ok) return ttlb_fail(ctx, TTLB_ERR_CUDA, "matmul_bfp8w: cannot select device %d", ctx->device);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  // expand the weight window to bf16 in scratch memory owned by the context, then run the bf16 GEMM
+  // Unpack inside the GEMM mainloop (no scratch) when selected and the output fills the SM pairs.
+  const bool fused_ok = !multicast && d->m > 0 && d->m <= 0x7fffffff && d->n <= 0x7fffffff && d->k <= 0x7fffffff;
+  if (fused_ok && (ctx->bfp8_mode == 2 ||
+                   (ctx->bfp8_mode == 1 && ((d->m + 255) / 256) * ((d->n + 255) / 256) >= ctx->sm_count / 2))) {
+    if (!d->a || !d->c) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null operand");
+    if ((d->lda % 8) || (d->ldc % 8) || ((uintptr_t)d->a % 16) || ((uintptr_t)d->c % 16))
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG,
+                       "matmul: pointers must be 16-byte aligned and K, N and the row pitches multiples of 8");
+    if (d->lda < d->k || d->ldc < d->n)
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: row pitch smaller than the row");
+    return ttlb_launch_gemm_bfp8w_fused(ctx, d, s);
+  }
+  // otherwise expand the weight window to bf16 in scratch memory owned by the context, then run the bf16 GEMM
   const size_t need = (size_t)d->k * (size_t)d->n * 2;
   if (ctx->scratch_bytes < need) {
     if (ctx->scratch) {
@@ -215,6 +198,12 @@ static int matmul_bfp8w_impl(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, bool m
                      d->n / 32, ctx->scratch, d->n, s);
   if (rc) return rc;
   return ttlb_launch_gemm_bf16_ex(ctx, d->a, d->lda, ctx->scratch, d->n, d->c, d->ldc, d->m, d->n, d->k, multicast, s);
+}
+
+extern "C" int ttlb_set_bfp8_mode(ttlb_ctx *ctx, int mode) {
+  if (!ctx || mode < 0 || mode > 2) return TTLB_ERR_INVALID_ARG;
+  ctx->bfp8_mode = mode;
+  return TTLB_OK;
 }
 
 extern "C" int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, void *stream) {

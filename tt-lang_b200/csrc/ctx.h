@@ -31,6 +31,8 @@ struct ttlb_ctx {
   bool gemm_attr_set = false;
   bool gemm2_attr_set = false;
   int gemm_variant = 1;  // 0: always one-CTA 128x256 tiles; 1: two-CTA (cta_group::2) 256x256 tiles for large outputs
+  bool gemm_fused_attr_set = false;
+  int bfp8_mode = 0;  // 0: unpack kernel + bf16 GEMM; 1: unpack inside the GEMM mainloop for large outputs; 2: always inside
   bool attn_attr_set = false;
   long long wait_limit_cycles = 4000000000LL;  // ~2 s at 1.9 GHz
   // Scratch in HBM owned by the context (bf16 expansion of bfloat8_b weights); grows on demand.

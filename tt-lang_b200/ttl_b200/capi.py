@@ -77,6 +77,9 @@ def eltwise_source(desc: "EltwiseDesc") -> str:
     return buf.value.decode()
 
 
+BFP8_MODE_DEFAULT = 0
+
+
 class BackendError(RuntimeError):
     """A C-ABI call returned a negative status."""
 
@@ -146,6 +149,8 @@ def lib() -> C.CDLL:
     l.ttlb_selftest_wait_timeout.restype = C.c_int
     l.ttlb_set_gemm_variant.argtypes = [C.c_void_p, C.c_int]
     l.ttlb_set_gemm_variant.restype = C.c_int
+    l.ttlb_set_bfp8_mode.argtypes = [C.c_void_p, C.c_int]
+    l.ttlb_set_bfp8_mode.restype = C.c_int
     l.ttlb_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
     l.ttlb_set_wait_limit.restype = C.c_int
     _LIB = l
@@ -214,6 +219,10 @@ class Context:
     def set_gemm_variant(self, variant: int) -> None:
         """0: one-CTA 128x256 tiles; 1 (default): two-CTA 256x256 tiles for large outputs; 2: two-CTA always."""
         self.check(self._lib.ttlb_set_gemm_variant(self.handle, variant))
+
+    def set_bfp8_mode(self, mode: int) -> None:
+        """0: unpack kernel + GEMM; 1: unpack inside the GEMM mainloop for large outputs; 2: always inside."""
+        self.check(self._lib.ttlb_set_bfp8_mode(self.handle, mode))
 
     def set_wait_limit(self, cycles: int) -> None:
         self.check(self._lib.ttlb_set_wait_limit(self.handle, cycles))
