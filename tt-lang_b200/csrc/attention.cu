@@ -9,14 +9,20 @@
 //   warp 0      TMA producer: Q tile once; K and V blocks (128 keys) through 2-stage rings
 //   warp 1      UMMA issuer: S_j = Q K_j^T (128x128x128) into one of two TMEM score buffers,
 //               then PV_{j-1} = P_{j-1} V_{j-1} into one of two TMEM output buffers, so the
-//               tensor pipe computes the next scores while the softmax warps work
+//               tensor pipe computes the next scores while the softmax warps work.  P is read
+//               from TENSOR MEMORY (the A operand of the second UMMA), not from shared memory.
 //   warps 2..17 softmax: thread (row, one of four 32-column parts) reads its 32 scores with
 //               tcgen05.ld, exchanges the row max with the three partner warps through shared
-//               memory, writes P (bf16) into shared memory in the swizzled K-major layout the
-//               next UMMA reads, and folds the finished P V product into its 32 fp32 output
-//               accumulators (O = O * alpha + PV), which live in registers - no TMEM
+//               memory, writes P (bf16 pairs) with tcgen05.st over the first 64 columns of the
+//               score buffer it came from, and folds the finished P V product into its 32 fp32
+//               output accumulators (O = O * alpha + PV), which live in registers - no TMEM
 //               read-modify-write, no correction pass.  Four softmax warps per scheduler hide
 //               each other's barrier and TMEM-load latency.
+// The shared-memory data path is the scarce resource (a 128x128x128 UMMA reads 512 wavefronts of
+// 128 bytes in its 512 cycles when both operands are in shared memory); keeping P out of shared
+// memory removes a quarter of the kernel's traffic on it.
+// UMMAs of one thread execute in issue order, which is what frees the buffers: S_{j+2} is issued
+// after P_j V_j and so cannot overwrite the P_j that aliases S_j's buffer.
 // Heavy (late) query tiles are scheduled first.  All waits are bounded.
 #include <cuda_bf16.h>
 
@@ -35,7 +41,7 @@ constexpr int NPART = 4;                      // column parts per row: softmax t
 constexpr int PCOLS = 128 / NPART;            // score / output columns per softmax thread
 constexpr int ATT_THREADS = 64 + 128 * NPART;
 constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = OFF_K + KV_STAGES * TILE_BYTES,
-              OFF_P = OFF_V + KV_STAGES * TILE_BYTES, OFF_X = OFF_P + TILE_BYTES;  // X: row-max exchange
+              OFF_X = OFF_V + KV_STAGES * TILE_BYTES;  // X: row-max exchange
 constexpr int XCH_BYTES = 2 * NPART * 128 * 4;   // [parity][part][row] floats
 constexpr int OFF_BAR = OFF_X + XCH_BYTES;
 constexpr int ATT_SMEM = OFF_BAR + 512 + 1024;
@@ -57,13 +63,11 @@ enum {
   B_VFULL = 5,    // [2]
   B_VEMPTY = 7,   // [2]
   B_SFULL = 9,    // [2]
-  B_SEMPTY = 11,  // [2]  count 4*NPART (one arrival per softmax warp)
-  B_PFULL = 13,   //      count 4*NPART
-  B_PEMPTY = 14,
-  B_OFULL = 15,   // [2]
-  B_OEMPTY = 17,  // [2]  count 4*NPART
-  B_XCH = 19,     // [4]  count 32*NPART (all threads that share a TMEM lane quarter)
-  B_COUNT = 23
+  B_PFULL = 11,   // [2]  count 4*NPART (one arrival per softmax warp)
+  B_OFULL = 13,   // [2]
+  B_OEMPTY = 15,  // [2]  count 4*NPART
+  B_XCH = 17,     // [4]  count 32*NPART (all threads that share a TMEM lane quarter)
+  B_COUNT = 21
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -94,7 +98,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     *abort_flag = 0;
     for (int i = 0; i < B_COUNT; ++i) {
       uint32_t count = 1;
-      if (i == B_SEMPTY || i == B_SEMPTY + 1 || i == B_PFULL || i == B_OEMPTY || i == B_OEMPTY + 1) count = 4 * NPART;
+      if (i == B_PFULL || i == B_PFULL + 1 || i == B_OEMPTY || i == B_OEMPTY + 1) count = 4 * NPART;
       if (i >= B_XCH) count = 32 * NPART;
       mbar_init(bar(i), count);
     }
@@ -135,32 +139,30 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);  // Q (K-major) x K^T (K-major)
-      constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // P (K-major) x V (N-major)
+      constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // P (tensor memory) x V (N-major)
       if (!mbar_wait(bar(B_QFULL), 0, abort_flag, p.wait_limit)) fail = 2;
       auto issue_pv = [&](int j) -> bool {  // PV_j = P_j V_j
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1u;
-        if (!mbar_wait(bar(B_PFULL), (uint32_t)(j & 1), abort_flag, p.wait_limit)) return false;
+        if (!mbar_wait(bar(B_PFULL + s), ph, abort_flag, p.wait_limit)) return false;
         if (!mbar_wait(bar(B_VFULL + s), ph, abort_flag, p.wait_limit)) return false;
         if (!mbar_wait(bar(B_OEMPTY + s), ph ^ 1u, abort_flag, p.wait_limit)) return false;
         tc_fence_after();
         const uint32_t sv = base + OFF_V + s * TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
-          const uint64_t da = desc_kmajor_sw128(base + OFF_P + (kk >> 2) * CHUNK_BYTES) + (uint64_t)((kk & 3) * 2);
+          // P_j: 16 keys = 8 columns (two bf16 per column) of score buffer s
           const uint64_t db = desc_mnmajor_sw128(sv, CHUNK_BYTES) + (uint64_t)(kk * 128);
-          umma_f16(tm_o + s * HD, da, db, idesc_o, kk != 0);
+          umma_f16_ts(tm_o + s * HD, tm_s + s * BKV + kk * 8, db, idesc_o, kk != 0);
         }
         umma_commit(bar(B_OFULL + s));
         umma_commit(bar(B_VEMPTY + s));
-        umma_commit(bar(B_PEMPTY));
         return true;
       };
       for (int j = 0; j < nblk && !fail; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1u;
-        if (!mbar_wait(bar(B_KFULL + s), ph, abort_flag, p.wait_limit) ||
-            !mbar_wait(bar(B_SEMPTY + s), ph ^ 1u, abort_flag, p.wait_limit)) { fail = 2; break; }
+        if (!mbar_wait(bar(B_KFULL + s), ph, abort_flag, p.wait_limit)) { fail = 2; break; }
         tc_fence_after();
         const uint32_t sk = base + OFF_K + s * TILE_BYTES;
 #pragma unroll
@@ -210,9 +212,6 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       uint32_t sr[32];
       tmem_ld_32x32(tm_s + lane_addr + s * BKV + part * PCOLS, sr);
       tmem_ld_wait_dep(sr);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_SEMPTY + s));
 
       const int key0 = j * BKV + part * PCOLS;
       if ((p.causal && j == qt) || (j + 1) * BKV > p.seq) {
@@ -251,19 +250,13 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
       l_run = l_run * alpha + (rs0 + rs1);
       m_run = m_new;
-      // P buffer is free once PV_{j-1} has been consumed by the tensor core
-      if (j > 0 && !mbar_wait(bar(B_PEMPTY), (uint32_t)((j - 1) & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
-      {
-        // this thread's 32 bf16 = four 16-byte units of the row's 128-byte swizzle span
-        uint8_t *prow = gen + OFF_P + (part >> 1) * CHUNK_BYTES + row * 128;
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          *reinterpret_cast<uint4 *>(prow + ((((part & 1) * 4 + u) ^ (row & 7)) << 4)) =
-              make_uint4(pk[4 * u], pk[4 * u + 1], pk[4 * u + 2], pk[4 * u + 3]);
-      }
-      fence_proxy_async();
+      // P_j over the first 64 columns of score buffer s: every thread of this lane quarter has read
+      // its scores (it arrived on the exchange barrier after its load completed)
+      tmem_st_32x16(tm_s + lane_addr + s * BKV + part * (PCOLS / 2), pk);
+      tmem_st_wait();
+      tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PFULL));
+      if (lane == 0) mbar_arrive(bar(B_PFULL + s));
       if (j > 0 && !fold(j - 1, alpha_prev)) { fail = 4; break; }
       alpha_prev = alpha;
     }
