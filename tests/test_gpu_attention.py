@@ -26,7 +26,7 @@ def qkv(shape, seeds=(0, 1, 2)):
 
 @pytest.mark.parametrize("shape,causal", [((1, 1, 128, 128), True), ((1, 2, 256, 128), True), ((2, 3, 512, 128), True),
                                           ((1, 2, 384, 128), False), ((1, 1, 200, 128), True), ((1, 2, 72, 128), False),
-                                          ((1, 1, 1000, 128), True)])
+                                          ((1, 1, 1000, 128), True), ((1, 2, 640, 128), True), ((1, 1, 128 * 7, 128), False)])
 def test_attention_matches_oracle(shape, causal):
     """One tile, several KV blocks, several heads, non-causal, and sequence lengths that are not
     multiples of the 128-row tile (ragged last tile: out-of-range keys masked, rows not stored)."""
@@ -37,6 +37,23 @@ def test_attention_matches_oracle(shape, causal):
     ops.attention(ttnn.from_torch(q), ttnn.from_torch(k), ttnn.from_torch(v), causal=causal, scale=scale, out=out)
     capi.context().check_status(capi.current_stream())
     got = ttnn.to_torch(out)
+    assert torch.isfinite(got.float()).all()
+    assert rel_err(got, attention_oracle.attention_tiles(q, k, v, causal, scale)) <= TOL
+    assert rel_err(got, attention_oracle.attention_plain(q, k, v, causal, scale)) <= TOL
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_attention_with_growing_scores(causal):
+    """Keys whose magnitude grows along the sequence: the row max keeps jumping by far more than the
+    kernel's lazy-rescaling threshold, so the output accumulators are corrected in place many times."""
+    from ttl_b200 import capi, ops, ttnn
+    shape = (1, 2, 1152, 128)
+    q, k, v = qkv(shape, seeds=(3, 4, 5))
+    ramp = torch.linspace(0.25, 6.0, shape[2]).reshape(1, 1, -1, 1)
+    k = (k.float() * ramp).to(torch.bfloat16)
+    scale = shape[-1] ** -0.5
+    got = ttnn.to_torch(ops.attention(ttnn.from_torch(q), ttnn.from_torch(k), ttnn.from_torch(v), causal=causal, scale=scale))
+    capi.context().check_status(capi.current_stream())
     assert torch.isfinite(got.float()).all()
     assert rel_err(got, attention_oracle.attention_tiles(q, k, v, causal, scale)) <= TOL
     assert rel_err(got, attention_oracle.attention_plain(q, k, v, causal, scale)) <= TOL

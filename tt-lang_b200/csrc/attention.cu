@@ -8,16 +8,19 @@
 // One CTA per (batch*head, 128-query tile), 576 threads:
 //   warp 0      TMA producer: Q tile once; K and V blocks (128 keys) through 2-stage rings
 //   warp 1      UMMA issuer: S_j = Q K_j^T (128x128x128) into one of two TMEM score buffers,
-//               then PV_{j-1} = P_{j-1} V_{j-1} into one of two TMEM output buffers, so the
-//               tensor pipe computes the next scores while the softmax warps work.  P is read
-//               from TENSOR MEMORY (the A operand of the second UMMA), not from shared memory.
+//               then O += P_{j-1} V_{j-1} accumulated in TMEM, so the tensor pipe computes the
+//               next scores while the softmax warps work.  P is read from TENSOR MEMORY (the A
+//               operand of the second UMMA), not from shared memory.
 //   warps 2..17 softmax: thread (row, one of four 32-column parts) reads its 32 scores with
 //               tcgen05.ld, exchanges the row max with the three partner warps through shared
 //               memory, writes P (bf16 pairs) with tcgen05.st over the first 64 columns of the
-//               score buffer it came from, and folds the finished P V product into its 32 fp32
-//               output accumulators (O = O * alpha + PV), which live in registers - no TMEM
-//               read-modify-write, no correction pass.  Four softmax warps per scheduler hide
-//               each other's barrier and TMEM-load latency.
+//               score buffer it came from, and keeps only the running max and sum.  O is
+//               rescaled LAZILY: the max used for the exponentials is raised only when the true
+//               max has grown by more than 2^8 (P stays below 256, exact enough in bf16 / fp32);
+//               when it is, the threads wait for the last PV UMMA and multiply their 32 columns
+//               of O in tensor memory by the correction.  At the end they read O once, divide by
+//               the row sum and store bf16.  Four softmax warps per scheduler hide each other's
+//               barrier and TMEM latency.
 // The shared-memory data path is the scarce resource (a 128x128x128 UMMA reads 512 wavefronts of
 // 128 bytes in its 512 cycles when both operands are in shared memory); keeping P out of shared
 // memory removes a quarter of the kernel's traffic on it.
@@ -45,6 +48,7 @@ constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = OFF_K + KV_STAGES * TILE_BY
 constexpr int XCH_BYTES = 2 * NPART * 128 * 4;   // [parity][part][row] floats
 constexpr int OFF_BAR = OFF_X + XCH_BYTES;
 constexpr int ATT_SMEM = OFF_BAR + 512 + 1024;
+constexpr float RESCALE_THRESHOLD = 8.0f;   // in log2 units
 
 struct AttnParams {
   __nv_bfloat16 *o;
@@ -64,10 +68,10 @@ enum {
   B_VEMPTY = 7,   // [2]
   B_SFULL = 9,    // [2]
   B_PFULL = 11,   // [2]  count 4*NPART (one arrival per softmax warp)
-  B_OFULL = 13,   // [2]
-  B_OEMPTY = 15,  // [2]  count 4*NPART
-  B_XCH = 17,     // [4]  count 32*NPART (all threads that share a TMEM lane quarter)
-  B_COUNT = 21
+  B_ODONE = 13,   //      a PV UMMA has completed (waited on only by a rescale, see there)
+  B_OFINAL = 14,  //      the last PV UMMA has completed
+  B_XCH = 15,     // [4]  count 32*NPART (all threads that share a TMEM lane quarter)
+  B_COUNT = 19
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -98,7 +102,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     *abort_flag = 0;
     for (int i = 0; i < B_COUNT; ++i) {
       uint32_t count = 1;
-      if (i == B_PFULL || i == B_PFULL + 1 || i == B_OEMPTY || i == B_OEMPTY + 1) count = 4 * NPART;
+      if (i == B_PFULL || i == B_PFULL + 1) count = 4 * NPART;
       if (i >= B_XCH) count = 32 * NPART;
       mbar_init(bar(i), count);
     }
@@ -115,7 +119,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_s = tmem_base, tm_o = tmem_base + 256;  // S[2] at columns 0/128, PV[2] at 256/384
+  const uint32_t tm_s = tmem_base, tm_o = tmem_base + 256;  // S[2] at columns 0 / 128, O at 256
 
   int fail = 0;
   if (warp == 0) {
@@ -146,16 +150,15 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         const uint32_t ph = (j >> 1) & 1u;
         if (!mbar_wait(bar(B_PFULL + s), ph, abort_flag, p.wait_limit)) return false;
         if (!mbar_wait(bar(B_VFULL + s), ph, abort_flag, p.wait_limit)) return false;
-        if (!mbar_wait(bar(B_OEMPTY + s), ph ^ 1u, abort_flag, p.wait_limit)) return false;
         tc_fence_after();
         const uint32_t sv = base + OFF_V + s * TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
           // P_j: 16 keys = 8 columns (two bf16 per column) of score buffer s
           const uint64_t db = desc_mnmajor_sw128(sv, CHUNK_BYTES) + (uint64_t)(kk * 128);
-          umma_f16_ts(tm_o + s * HD, tm_s + s * BKV + kk * 8, db, idesc_o, kk != 0);
+          umma_f16_ts(tm_o, tm_s + s * BKV + kk * 8, db, idesc_o, (j | kk) != 0);
         }
-        umma_commit(bar(B_OFULL + s));
+        umma_commit(bar(B_ODONE));
         umma_commit(bar(B_VEMPTY + s));
         return true;
       };
@@ -176,6 +179,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (j > 0 && !issue_pv(j - 1)) { fail = 2; break; }
       }
       if (!fail && !issue_pv(nblk - 1)) fail = 2;
+      if (!fail) umma_commit(bar(B_OFINAL));
     }
   } else {
     // ---- softmax warps: thread = (query row, one of NPART column parts) -------------------
@@ -185,25 +189,8 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int q_idx = qt * BQ + row;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const float sl2e = p.scale_log2e;
-    float o[PCOLS];
-#pragma unroll
-    for (int c = 0; c < PCOLS; ++c) o[c] = 0.f;
-    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
-
-    auto fold = [&](int jj, float a) -> bool {  // O = O * a + PV_jj (this thread's PCOLS output columns)
-      const int s = jj & 1;
-      if (!mbar_wait(bar(B_OFULL + s), (uint32_t)((jj >> 1) & 1), abort_flag, p.wait_limit)) return false;
-      tc_fence_after();
-      uint32_t r[32];
-      tmem_ld_32x32(tm_o + lane_addr + s * HD + part * PCOLS, r);
-      tmem_ld_wait_dep(r);
-#pragma unroll
-      for (int c = 0; c < 32; ++c) o[c] = fmaf(o[c], a, __uint_as_float(r[c]));
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_OEMPTY + s));
-      return true;
-    };
+    const uint32_t my_o = tm_o + lane_addr + part * PCOLS;
+    float m_used = -INFINITY, l_run = 0.f;
 
     for (int j = 0; j < nblk; ++j) {
       const int s = j & 1;
@@ -233,11 +220,32 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       xrow[part * 128] = mx;
       mbar_arrive(bar(B_XCH + q));
       if (!mbar_wait(bar(B_XCH + q), (uint32_t)(j & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
-      float m_new = fmaxf(m_run, mx);
+      float m_new = fmaxf(m_used, mx);
 #pragma unroll
       for (int k = 1; k < NPART; ++k) m_new = fmaxf(m_new, xrow[((part + k) & (NPART - 1)) * 128]);
-      const float alpha = fast_exp2((m_run - m_new) * sl2e);
-      const float neg = -m_new * sl2e;
+      // raise the max used for the exponentials only when the true max has moved far; all threads
+      // of a row take the same decision from the same numbers
+      float alpha = 1.0f;
+      const bool raise = (m_new - m_used) * sl2e > RESCALE_THRESHOLD;
+      if (raise) {
+        alpha = fast_exp2((m_used - m_new) * sl2e);   // 0 on the first block
+        m_used = m_new;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
+        // O *= alpha, after PV_{j-1} has landed and before PV_j is released.  The parity test is
+        // unambiguous: S_j, which this thread has read, was issued after PV_{j-2}, and UMMAs complete
+        // in order, so the barrier is in phase j-1 or later.
+        if (!mbar_wait(bar(B_ODONE), (uint32_t)((j - 1) & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
+        tc_fence_after();
+        uint32_t r[32];
+        tmem_ld_32x32(my_o, r);
+        tmem_ld_wait_dep(r);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+        tmem_st_32x32(my_o, r);
+        tmem_st_wait();
+      }
+      const float neg = -m_used * sl2e;
       float rs0 = 0.f, rs1 = 0.f;
       uint32_t pk[16];
 #pragma unroll
@@ -249,7 +257,6 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         pk[c >> 1] = pack_bf16x2(p0, p1);
       }
       l_run = l_run * alpha + (rs0 + rs1);
-      m_run = m_new;
       // P_j over the first 64 columns of score buffer s: every thread of this lane quarter has read
       // its scores (it arrived on the exchange barrier after its load completed)
       tmem_st_32x16(tm_s + lane_addr + s * BKV + part * (PCOLS / 2), pk);
@@ -257,16 +264,21 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_PFULL + s));
-      if (j > 0 && !fold(j - 1, alpha_prev)) { fail = 4; break; }
-      alpha_prev = alpha;
     }
-    if (!fail && !fold(nblk - 1, alpha_prev)) fail = 4;
     if (!fail) {
       const int slot = nblk & 1;
       float *xrow = xch + slot * NPART * 128 + row;
       xrow[part * 128] = l_run;
       mbar_arrive(bar(B_XCH + q));
-      if (!mbar_wait(bar(B_XCH + q), (uint32_t)slot, abort_flag, p.wait_limit)) fail = 4;
+      if (!mbar_wait(bar(B_XCH + q), (uint32_t)slot, abort_flag, p.wait_limit) ||
+          !mbar_wait(bar(B_OFINAL), 0, abort_flag, p.wait_limit))
+        fail = 4;
+      uint32_t o[32];
+      if (!fail) {
+        tc_fence_after();
+        tmem_ld_32x32(my_o, o);
+        tmem_ld_wait_dep(o);
+      }
       if (!fail && q_idx < p.seq) {
         float l_tot = l_run;
 #pragma unroll
@@ -276,10 +288,10 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 #pragma unroll
         for (int u = 0; u < PCOLS / 8; ++u) {
           uint4 v;
-          v.x = pack_bf16x2(o[8 * u + 0] * inv, o[8 * u + 1] * inv);
-          v.y = pack_bf16x2(o[8 * u + 2] * inv, o[8 * u + 3] * inv);
-          v.z = pack_bf16x2(o[8 * u + 4] * inv, o[8 * u + 5] * inv);
-          v.w = pack_bf16x2(o[8 * u + 6] * inv, o[8 * u + 7] * inv);
+          v.x = pack_bf16x2(__uint_as_float(o[8 * u + 0]) * inv, __uint_as_float(o[8 * u + 1]) * inv);
+          v.y = pack_bf16x2(__uint_as_float(o[8 * u + 2]) * inv, __uint_as_float(o[8 * u + 3]) * inv);
+          v.z = pack_bf16x2(__uint_as_float(o[8 * u + 4]) * inv, __uint_as_float(o[8 * u + 5]) * inv);
+          v.w = pack_bf16x2(__uint_as_float(o[8 * u + 6]) * inv, __uint_as_float(o[8 * u + 7]) * inv);
           *reinterpret_cast<uint4 *>(dst + 8 * u) = v;
         }
       }
@@ -287,6 +299,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   }
 
   if (fail) atomicCAS(p.status, 0, fail);
+  tc_fence_before();
   __syncthreads();
   if (*abort_flag) {
     const long long t0 = clock64();
