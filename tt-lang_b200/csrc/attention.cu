@@ -5,27 +5,27 @@
 // in the tree); this is the tile program "for each KV block: S = Q @ K^T; online-softmax update;
 // O += P @ V" written directly as a B200 kernel.
 //
-// One CTA per (batch*head, 128-query tile), 576 threads:
-//   warp 0      TMA producer: Q tile once; K and V blocks (128 keys) through 2-stage rings
-//   warp 1      UMMA issuer: S_j = Q K_j^T (128x128x128) into one of two TMEM score buffers,
-//               then O += P_{j-1} V_{j-1} accumulated in TMEM, so the tensor pipe computes the
-//               next scores while the softmax warps work.  P is read from TENSOR MEMORY (the A
-//               operand of the second UMMA), not from shared memory.
-//   warps 2..17 softmax: thread (row, one of four 32-column parts) reads its 32 scores with
-//               tcgen05.ld, exchanges the row max with the three partner warps through shared
-//               memory, writes P (bf16 pairs) with tcgen05.st over the first 64 columns of the
-//               score buffer it came from, and keeps only the running max and sum.  O is
-//               rescaled LAZILY: the max used for the exponentials is raised only when the true
-//               max has grown by more than 2^8 (P stays below 256, exact enough in bf16 / fp32);
-//               when it is, the threads wait for the last PV UMMA and multiply their 32 columns
-//               of O in tensor memory by the correction.  At the end they read O once, divide by
-//               the row sum and store bf16.  Four softmax warps per scheduler hide each other's
-//               barrier and TMEM latency.
-// The shared-memory data path is the scarce resource (a 128x128x128 UMMA reads 512 wavefronts of
-// 128 bytes in its 512 cycles when both operands are in shared memory); keeping P out of shared
-// memory removes a quarter of the kernel's traffic on it.
-// UMMAs of one thread execute in issue order, which is what frees the buffers: S_{j+2} is issued
-// after P_j V_j and so cannot overwrite the P_j that aliases S_j's buffer.
+// One CTA per (batch*head, PAIR of 128-query tiles), 576 threads.  The two query tiles A and B
+// share every K / V block (loaded once) and take turns on the tensor pipe, so the softmax of one
+// tile runs under the UMMAs of the other:
+//   warp 0      TMA producer: Q_A, Q_B once; K and V blocks (128 keys) through 2-stage rings
+//   warp 1      UMMA issuer.  Per KV block j and tile T: S_T = Q_T K_j^T (128x128x128) into T's
+//               score buffer in tensor memory, and O_T += P_T V_j with P_T read FROM TENSOR MEMORY
+//               (A operand) and O_T accumulated in tensor memory.  Issue order
+//               ... PV_A(j), S_A(j+1), PV_B(j), S_B(j+1) ...; UMMAs execute in issue order, which is
+//               what makes S_T(j+1) safe to overwrite the P_T(j) that aliases its buffer.
+//   warps 2..17 softmax, 8 warps per tile: thread (row, half) reads its 64 scores with tcgen05.ld,
+//               exchanges the row max with its partner through shared memory, writes P (bf16 pairs)
+//               with tcgen05.st over the first 64 columns of the score buffer, and keeps only the
+//               running max and sum.  O is rescaled LAZILY: the max used for the exponentials is
+//               raised only when the true max has grown by more than 2^8 (P stays below 256, exact
+//               enough in bf16 and fp32); when it is, the threads wait for the last PV UMMA of
+//               their tile and multiply their 64 columns of O in tensor memory by the correction.
+//               At the end they read O once, divide by the row sum and store bf16.
+// Tensor memory: S_A, S_B, O_A, O_B, 128 columns each.  Shared memory: Q_A, Q_B, K[2], V[2] of 32 KB.
+// The shared-memory data path is the scarce resource (a 128x128x128 UMMA with both operands in
+// shared memory reads 512 wavefronts of 128 bytes in its 512 cycles): P and O never touch it, and
+// each K / V block written by the TMA serves two query tiles.
 // Heavy (late) query tiles are scheduled first.  All waits are bounded.
 #include <cuda_bf16.h>
 
@@ -37,22 +37,23 @@ using namespace sm100;
 namespace {
 
 constexpr int BQ = 128, BKV = 128, HD = 128;
-constexpr int TILE_BYTES = 128 * 128 * 2;    // 32 KB: a 128 x 128 bf16 tile (Q, K block, V block, P)
+constexpr int TILE_BYTES = 128 * 128 * 2;    // 32 KB: a 128 x 128 bf16 tile (Q tile, K block, V block)
 constexpr int CHUNK_BYTES = 128 * 64 * 2;    // 16 KB: 128 rows x 64 elements (one 128-byte swizzle span)
 constexpr int KV_STAGES = 2;
-constexpr int NPART = 4;                      // column parts per row: softmax thread = (row, part)
+constexpr int NT = 2;                         // query tiles per CTA
+constexpr int NPART = 2;                      // column halves per row: softmax thread = (tile, row, half)
 constexpr int PCOLS = 128 / NPART;            // score / output columns per softmax thread
-constexpr int ATT_THREADS = 64 + 128 * NPART;
-constexpr int OFF_Q = 0, OFF_K = TILE_BYTES, OFF_V = OFF_K + KV_STAGES * TILE_BYTES,
-              OFF_X = OFF_V + KV_STAGES * TILE_BYTES;  // X: row-max exchange
-constexpr int XCH_BYTES = 2 * NPART * 128 * 4;   // [parity][part][row] floats
+constexpr int ATT_THREADS = 64 + NT * NPART * 128;
+constexpr int OFF_Q = 0, OFF_K = NT * TILE_BYTES, OFF_V = OFF_K + KV_STAGES * TILE_BYTES,
+              OFF_X = OFF_V + KV_STAGES * TILE_BYTES;  // X: row max / row sum exchange
+constexpr int XCH_BYTES = NT * 2 * NPART * 128 * 4;    // [tile][parity][half][row] floats
 constexpr int OFF_BAR = OFF_X + XCH_BYTES;
 constexpr int ATT_SMEM = OFF_BAR + 512 + 1024;
-constexpr float RESCALE_THRESHOLD = 8.0f;   // in log2 units
+constexpr float RESCALE_THRESHOLD = 8.0f;    // in log2 units
 
 struct AttnParams {
   __nv_bfloat16 *o;
-  int seq, bh, q_tiles;
+  int seq, bh, q_tiles, q_pairs;
   int causal;
   float scale_log2e;
   int *status;
@@ -66,12 +67,11 @@ enum {
   B_KEMPTY = 3,   // [2]
   B_VFULL = 5,    // [2]
   B_VEMPTY = 7,   // [2]
-  B_SFULL = 9,    // [2]
-  B_PFULL = 11,   // [2]  count 4*NPART (one arrival per softmax warp)
-  B_ODONE = 13,   //      a PV UMMA has completed (waited on only by a rescale, see there)
-  B_OFINAL = 14,  //      the last PV UMMA has completed
-  B_XCH = 15,     // [4]  count 32*NPART (all threads that share a TMEM lane quarter)
-  B_COUNT = 19
+  B_SFULL = 9,    // [NT]
+  B_PFULL = 11,   // [NT]  count 4*NPART (one arrival per softmax warp of the tile)
+  B_ODONE = 13,   // [NT]  a PV UMMA of the tile has completed
+  B_XCH = 15,     // [NT*4]  count 32*NPART (the threads of one tile that share a TMEM lane quarter)
+  B_COUNT = 23
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -92,17 +92,24 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   float *xch = reinterpret_cast<float *>(gen + OFF_X);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // heavy tiles first: with a causal mask the last query tile has the most KV blocks
-  const int qt = p.q_tiles - 1 - (int)(blockIdx.x % p.q_tiles);
-  const int bh = (int)(blockIdx.x / p.q_tiles);
+  // heavy pairs first: with a causal mask the last query tiles have the most KV blocks
+  const int pr = p.q_pairs - 1 - (int)(blockIdx.x % p.q_pairs);
+  const int bh = (int)(blockIdx.x / p.q_pairs);
   const int kv_total = (p.seq + BKV - 1) / BKV;
-  const int nblk = p.causal ? min(qt + 1, kv_total) : kv_total;
+  // KV blocks of tile T (0 when the tile does not exist)
+  auto blocks_of = [&](int t) {
+    const int qt = 2 * pr + t;
+    if (qt >= p.q_tiles) return 0;
+    return p.causal ? min(qt + 1, kv_total) : kv_total;
+  };
+  const int n_a = blocks_of(0), n_b = blocks_of(1);
+  const int nblk = max(n_a, n_b);
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < B_COUNT; ++i) {
       uint32_t count = 1;
-      if (i == B_PFULL || i == B_PFULL + 1) count = 4 * NPART;
+      if (i >= B_PFULL && i < B_PFULL + NT) count = 4 * NPART;
       if (i >= B_XCH) count = 32 * NPART;
       mbar_init(bar(i), count);
     }
@@ -119,14 +126,17 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tm_s = tmem_base, tm_o = tmem_base + 256;  // S[2] at columns 0 / 128, O at 256
+  const uint32_t tm_s = tmem_base, tm_o = tmem_base + NT * BKV;  // S_A, S_B at columns 0 / 128; O_A, O_B at 256 / 384
 
   int fail = 0;
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(bar(B_QFULL), TILE_BYTES);
-      tma_load_3d(base + OFF_Q, &map_q, 0, qt * BQ, bh, bar(B_QFULL));
-      tma_load_3d(base + OFF_Q + CHUNK_BYTES, &map_q, 64, qt * BQ, bh, bar(B_QFULL));
+      mbar_expect_tx(bar(B_QFULL), (n_b > 0 ? 2 : 1) * TILE_BYTES);
+      for (int t = 0; t < NT; ++t) {
+        if (t == 1 && n_b == 0) break;
+        tma_load_3d(base + OFF_Q + t * TILE_BYTES, &map_q, 0, (2 * pr + t) * BQ, bh, bar(B_QFULL));
+        tma_load_3d(base + OFF_Q + t * TILE_BYTES + CHUNK_BYTES, &map_q, 64, (2 * pr + t) * BQ, bh, bar(B_QFULL));
+      }
       for (int j = 0; j < nblk; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1u;
@@ -144,87 +154,106 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);  // Q (K-major) x K^T (K-major)
       constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // P (tensor memory) x V (N-major)
-      if (!mbar_wait(bar(B_QFULL), 0, abort_flag, p.wait_limit)) fail = 2;
-      auto issue_pv = [&](int j) -> bool {  // PV_j = P_j V_j
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1u;
-        if (!mbar_wait(bar(B_PFULL + s), ph, abort_flag, p.wait_limit)) return false;
-        if (!mbar_wait(bar(B_VFULL + s), ph, abort_flag, p.wait_limit)) return false;
-        tc_fence_after();
-        const uint32_t sv = base + OFF_V + s * TILE_BYTES;
-#pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          // P_j: 16 keys = 8 columns (two bf16 per column) of score buffer s
-          const uint64_t db = desc_mnmajor_sw128(sv, CHUNK_BYTES) + (uint64_t)(kk * 128);
-          umma_f16_ts(tm_o, tm_s + s * BKV + kk * 8, db, idesc_o, (j | kk) != 0);
-        }
-        umma_commit(bar(B_ODONE));
-        umma_commit(bar(B_VEMPTY + s));
-        return true;
-      };
-      for (int j = 0; j < nblk && !fail; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1u;
-        if (!mbar_wait(bar(B_KFULL + s), ph, abort_flag, p.wait_limit)) { fail = 2; break; }
-        tc_fence_after();
-        const uint32_t sk = base + OFF_K + s * TILE_BYTES;
+      const int n_of[NT] = {n_a, n_b};
+      auto issue_s = [&](int t, int j) {  // S_t = Q_t K_j^T; the caller has waited for K_j
+        const uint32_t sk = base + OFF_K + (j & 1) * TILE_BYTES, sq = base + OFF_Q + t * TILE_BYTES;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
-          const uint64_t da = desc_kmajor_sw128(base + OFF_Q + (kk >> 2) * CHUNK_BYTES) + (uint64_t)((kk & 3) * 2);
+          const uint64_t da = desc_kmajor_sw128(sq + (kk >> 2) * CHUNK_BYTES) + (uint64_t)((kk & 3) * 2);
           const uint64_t db = desc_kmajor_sw128(sk + (kk >> 2) * CHUNK_BYTES) + (uint64_t)((kk & 3) * 2);
-          umma_f16(tm_s + s * BKV, da, db, idesc_s, kk != 0);
+          umma_f16(tm_s + t * BKV, da, db, idesc_s, kk != 0);
         }
-        umma_commit(bar(B_SFULL + s));
-        umma_commit(bar(B_KEMPTY + s));
-        if (j > 0 && !issue_pv(j - 1)) { fail = 2; break; }
+        umma_commit(bar(B_SFULL + t));
+      };
+      auto issue_pv = [&](int t, int j) -> bool {  // O_t (+)= P_t V_j; the caller has waited for V_j
+        if (!mbar_wait(bar(B_PFULL + t), (uint32_t)(j & 1), abort_flag, p.wait_limit)) return false;
+        tc_fence_after();
+        const uint32_t sv = base + OFF_V + (j & 1) * TILE_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk) {
+          // P: 16 keys = 8 columns (two bf16 per column) at the start of the tile's score buffer
+          const uint64_t db = desc_mnmajor_sw128(sv, CHUNK_BYTES) + (uint64_t)(kk * 128);
+          umma_f16_ts(tm_o + t * HD, tm_s + t * BKV + kk * 8, db, idesc_o, (j | kk) != 0);
+        }
+        umma_commit(bar(B_ODONE + t));
+        return true;
+      };
+      if (!mbar_wait(bar(B_QFULL), 0, abort_flag, p.wait_limit) ||
+          !mbar_wait(bar(B_KFULL), 0, abort_flag, p.wait_limit)) fail = 2;
+      if (!fail) {
+        tc_fence_after();
+        for (int t = 0; t < NT; ++t)
+          if (n_of[t] > 0) issue_s(t, 0);
+        umma_commit(bar(B_KEMPTY));
       }
-      if (!fail && !issue_pv(nblk - 1)) fail = 2;
-      if (!fail) umma_commit(bar(B_OFINAL));
+      for (int j = 0; j < nblk && !fail; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(bar(B_VFULL + s), (uint32_t)((j >> 1) & 1), abort_flag, p.wait_limit)) { fail = 2; break; }
+        const bool more = j + 1 < nblk;
+        bool k_ready = false;
+        for (int t = 0; t < NT && !fail; ++t) {
+          if (j < n_of[t] && !issue_pv(t, j)) { fail = 2; break; }
+          if (t == NT - 1) umma_commit(bar(B_VEMPTY + s));
+          if (j + 1 < n_of[t]) {
+            if (!k_ready) {
+              if (!mbar_wait(bar(B_KFULL + (s ^ 1)), (uint32_t)(((j + 1) >> 1) & 1), abort_flag, p.wait_limit)) { fail = 2; break; }
+              tc_fence_after();
+              k_ready = true;
+            }
+            issue_s(t, j + 1);
+          }
+        }
+        if (!fail && more) umma_commit(bar(B_KEMPTY + (s ^ 1)));
+      }
     }
   } else {
-    // ---- softmax warps: thread = (query row, one of NPART column parts) -------------------
-    const int q = warp & 3;               // TMEM lane quarter this warp may access
-    const int part = (warp - 2) >> 2;     // which PCOLS-wide slice of the key / head-dim columns
-    const int row = q * 32 + lane;        // row inside the query tile
+    // ---- softmax warps: thread = (tile, query row, column half) ------------------------------
+    const int t = (warp - 2) >> 3;          // query tile of the pair
+    const int q = warp & 3;                 // TMEM lane quarter this warp may access
+    const int part = ((warp - 2) & 7) >> 2; // which 64-wide half of the key / head-dim columns
+    const int row = q * 32 + lane;          // row inside the query tile
+    const int qt = 2 * pr + t;
     const int q_idx = qt * BQ + row;
+    const int n_t = t == 0 ? n_a : n_b;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t my_s = tm_s + lane_addr + t * BKV, my_o = tm_o + lane_addr + t * HD + part * PCOLS;
     const float sl2e = p.scale_log2e;
-    const uint32_t my_o = tm_o + lane_addr + part * PCOLS;
+    float *xbase = xch + t * (2 * NPART * 128) + row;   // + parity * NPART * 128 + part * 128
+    const uint32_t xbar = bar(B_XCH + t * 4 + q);
     float m_used = -INFINITY, l_run = 0.f;
 
-    for (int j = 0; j < nblk; ++j) {
-      const int s = j & 1;
-      if (!mbar_wait(bar(B_SFULL + s), (uint32_t)((j >> 1) & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
+    for (int j = 0; j < n_t; ++j) {
+      if (!mbar_wait(bar(B_SFULL + t), (uint32_t)(j & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
       tc_fence_after();
-      uint32_t sr[32];
-      tmem_ld_32x32(tm_s + lane_addr + s * BKV + part * PCOLS, sr);
-      tmem_ld_wait_dep(sr);
+      uint32_t s0[32], s1[32];
+      tmem_ld_32x32(my_s + part * PCOLS, s0);
+      tmem_ld_32x32(my_s + part * PCOLS + 32, s1);
+      tmem_ld_wait_dep(s0);
+      tmem_ld_wait_dep(s1);
 
       const int key0 = j * BKV + part * PCOLS;
-      if ((p.causal && j == qt) || (j + 1) * BKV > p.seq) {
+      if ((p.causal && j >= qt) || (j + 1) * BKV > p.seq) {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const int key = key0 + c;
-          if ((p.causal && key > q_idx) || key >= p.seq) sr[c] = 0xff800000u;  // -inf
+          if ((p.causal && key0 + c > q_idx) || key0 + c >= p.seq) s0[c] = 0xff800000u;  // -inf
+          if ((p.causal && key0 + 32 + c > q_idx) || key0 + 32 + c >= p.seq) s1[c] = 0xff800000u;
         }
       }
       float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 32; c += 4) {
-        mx0 = max3(mx0, __uint_as_float(sr[c]), __uint_as_float(sr[c + 1]));
-        mx1 = max3(mx1, __uint_as_float(sr[c + 2]), __uint_as_float(sr[c + 3]));
+      for (int c = 0; c < 32; c += 2) {
+        mx0 = max3(mx0, __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
+        mx1 = max3(mx1, __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
       }
       const float mx = fmaxf(mx0, mx1);
-      // exchange the row max with the partner warps (the other column parts of the same rows)
-      float *xrow = xch + (j & 1) * NPART * 128 + row;
+      // exchange the block's row max with the partner warp (the other half of the same rows)
+      float *xrow = xbase + (j & 1) * NPART * 128;
       xrow[part * 128] = mx;
-      mbar_arrive(bar(B_XCH + q));
-      if (!mbar_wait(bar(B_XCH + q), (uint32_t)(j & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
-      float m_new = fmaxf(m_used, mx);
-#pragma unroll
-      for (int k = 1; k < NPART; ++k) m_new = fmaxf(m_new, xrow[((part + k) & (NPART - 1)) * 128]);
-      // raise the max used for the exponentials only when the true max has moved far; all threads
-      // of a row take the same decision from the same numbers
+      mbar_arrive(xbar);
+      if (!mbar_wait(xbar, (uint32_t)(j & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
+      const float m_new = fmaxf(m_used, fmaxf(mx, xrow[(part ^ 1) * 128]));
+      // raise the max used for the exponentials only when the true max has moved far; both
+      // threads of a row take the same decision from the same numbers
       float alpha = 1.0f;
       const bool raise = (m_new - m_used) * sl2e > RESCALE_THRESHOLD;
       if (raise) {
@@ -232,67 +261,79 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         m_used = m_new;
       }
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
-        // O *= alpha, after PV_{j-1} has landed and before PV_j is released.  The parity test is
-        // unambiguous: S_j, which this thread has read, was issued after PV_{j-2}, and UMMAs complete
-        // in order, so the barrier is in phase j-1 or later.
-        if (!mbar_wait(bar(B_ODONE), (uint32_t)((j - 1) & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
+        // O_t *= alpha, after the last PV UMMA of this tile has landed and before the next is released
+        if (!mbar_wait(bar(B_ODONE + t), (uint32_t)((j - 1) & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
         tc_fence_after();
-        uint32_t r[32];
-        tmem_ld_32x32(my_o, r);
-        tmem_ld_wait_dep(r);
+#pragma unroll 1
+        for (int h = 0; h < PCOLS / 16; ++h) {   // 16 columns at a time: this path must not cost registers
+          uint32_t r[16];
+          tmem_ld_32x16_sync(my_o + h * 16, r);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-        tmem_st_32x32(my_o, r);
+          for (int c = 0; c < 16; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+          tmem_st_32x16(my_o + h * 16, r);
+        }
         tmem_st_wait();
       }
       const float neg = -m_used * sl2e;
       float rs0 = 0.f, rs1 = 0.f;
-      uint32_t pk[16];
+      {
+        uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 32; c += 2) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c]), sl2e, neg));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c + 1]), sl2e, neg));
-        rs0 += p0;
-        rs1 += p1;
-        pk[c >> 1] = pack_bf16x2(p0, p1);
+        for (int c = 0; c < 32; c += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s0[c]), sl2e, neg));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s0[c + 1]), sl2e, neg));
+          rs0 += p0;
+          rs1 += p1;
+          pk[c >> 1] = pack_bf16x2(p0, p1);
+        }
+        // P over the first 64 columns of the tile's score buffer: every thread of this lane quarter
+        // has read its scores (it arrived on the exchange barrier after its loads completed)
+        tmem_st_32x16(my_s + part * (PCOLS / 2), pk);
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(s1[c]), sl2e, neg));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(s1[c + 1]), sl2e, neg));
+          rs0 += p0;
+          rs1 += p1;
+          pk[c >> 1] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x16(my_s + part * (PCOLS / 2) + 16, pk);
       }
       l_run = l_run * alpha + (rs0 + rs1);
-      // P_j over the first 64 columns of score buffer s: every thread of this lane quarter has read
-      // its scores (it arrived on the exchange barrier after its load completed)
-      tmem_st_32x16(tm_s + lane_addr + s * BKV + part * (PCOLS / 2), pk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PFULL + s));
+      if (lane == 0) mbar_arrive(bar(B_PFULL + t));
     }
-    if (!fail) {
-      const int slot = nblk & 1;
-      float *xrow = xch + slot * NPART * 128 + row;
+    if (!fail && n_t > 0) {
+      // the row sum of the other half, then O / l -> bf16
+      const int slot = n_t & 1;
+      float *xrow = xbase + slot * NPART * 128;
       xrow[part * 128] = l_run;
-      mbar_arrive(bar(B_XCH + q));
-      if (!mbar_wait(bar(B_XCH + q), (uint32_t)slot, abort_flag, p.wait_limit) ||
-          !mbar_wait(bar(B_OFINAL), 0, abort_flag, p.wait_limit))
+      mbar_arrive(xbar);
+      if (!mbar_wait(xbar, (uint32_t)slot, abort_flag, p.wait_limit) ||
+          !mbar_wait(bar(B_ODONE + t), (uint32_t)((n_t - 1) & 1), abort_flag, p.wait_limit))
         fail = 4;
-      uint32_t o[32];
       if (!fail) {
         tc_fence_after();
-        tmem_ld_32x32(my_o, o);
-        tmem_ld_wait_dep(o);
-      }
-      if (!fail && q_idx < p.seq) {
-        float l_tot = l_run;
-#pragma unroll
-        for (int k = 1; k < NPART; ++k) l_tot += xrow[((part + k) & (NPART - 1)) * 128];
-        const float inv = 1.0f / l_tot;
+        const float inv = 1.0f / (l_run + xrow[(part ^ 1) * 128]);
         __nv_bfloat16 *dst = p.o + ((long long)bh * p.seq + q_idx) * HD + part * PCOLS;
+#pragma unroll 1
+        for (int h = 0; h < PCOLS / 32; ++h) {
+          uint32_t r[32];
+          tmem_ld_32x32(my_o + h * 32, r);
+          tmem_ld_wait_dep(r);
+          if (q_idx < p.seq) {
 #pragma unroll
-        for (int u = 0; u < PCOLS / 8; ++u) {
-          uint4 v;
-          v.x = pack_bf16x2(__uint_as_float(o[8 * u + 0]) * inv, __uint_as_float(o[8 * u + 1]) * inv);
-          v.y = pack_bf16x2(__uint_as_float(o[8 * u + 2]) * inv, __uint_as_float(o[8 * u + 3]) * inv);
-          v.z = pack_bf16x2(__uint_as_float(o[8 * u + 4]) * inv, __uint_as_float(o[8 * u + 5]) * inv);
-          v.w = pack_bf16x2(__uint_as_float(o[8 * u + 6]) * inv, __uint_as_float(o[8 * u + 7]) * inv);
-          *reinterpret_cast<uint4 *>(dst + 8 * u) = v;
+            for (int u = 0; u < 4; ++u) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]) * inv, __uint_as_float(r[8 * u + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]) * inv, __uint_as_float(r[8 * u + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]) * inv, __uint_as_float(r[8 * u + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]) * inv, __uint_as_float(r[8 * u + 7]) * inv);
+              *reinterpret_cast<uint4 *>(dst + h * 32 + 8 * u) = v;
+            }
+          }
         }
       }
     }
@@ -355,11 +396,12 @@ extern "C" int ttlb_attention(ttlb_ctx *ctx, const ttlb_attn_desc *d, void *stre
   p.seq = (int)d->seq;
   p.bh = (int)d->batch_heads;
   p.q_tiles = (int)((d->seq + BQ - 1) / BQ);
+  p.q_pairs = (p.q_tiles + NT - 1) / NT;
   p.causal = d->causal ? 1 : 0;
   p.scale_log2e = d->scale * 1.4426950408889634f;
   p.status = ctx->d_status;
   p.wait_limit = ctx->wait_limit_cycles;
-  const long long grid = (long long)p.q_tiles * p.bh;
+  const long long grid = (long long)p.q_pairs * p.bh;
   if (grid > 0x7fffffffLL) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "attention: too many tiles");
   ttlb_attention_kernel<<<(unsigned)grid, ATT_THREADS, ATT_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
   TTLB_CUDA_CHECK(ctx, cudaGetLastError());
