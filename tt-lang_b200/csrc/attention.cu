@@ -68,10 +68,10 @@ enum {
   B_VFULL = 5,    // [2]
   B_VEMPTY = 7,   // [2]
   B_SFULL = 9,    // [NT]
-  B_PFULL = 11,   // [NT]  count 4*NPART (one arrival per softmax warp of the tile)
-  B_ODONE = 13,   // [NT]  a PV UMMA of the tile has completed
-  B_XCH = 15,     // [NT*4]  count 32*NPART (the threads of one tile that share a TMEM lane quarter)
-  B_COUNT = 23
+  B_PFULL = 11,   // [NT][2]  count 4*NPART: the first / second 32 keys of each column half of P are written
+  B_ODONE = 15,   // [NT]  a PV UMMA of the tile has completed
+  B_XCH = 17,     // [NT*4]  count 32*NPART (the threads of one tile that share a TMEM lane quarter)
+  B_COUNT = 25
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -109,7 +109,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     *abort_flag = 0;
     for (int i = 0; i < B_COUNT; ++i) {
       uint32_t count = 1;
-      if (i >= B_PFULL && i < B_PFULL + NT) count = 4 * NPART;
+      if (i >= B_PFULL && i < B_PFULL + 2 * NT) count = 4 * NPART;
       if (i >= B_XCH) count = 32 * NPART;
       mbar_init(bar(i), count);
     }
@@ -166,14 +166,19 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         umma_commit(bar(B_SFULL + t));
       };
       auto issue_pv = [&](int t, int j) -> bool {  // O_t (+)= P_t V_j; the caller has waited for V_j
-        if (!mbar_wait(bar(B_PFULL + t), (uint32_t)(j & 1), abort_flag, p.wait_limit)) return false;
-        tc_fence_after();
         const uint32_t sv = base + OFF_V + (j & 1) * TILE_BYTES;
+        // P arrives in two steps: keys [0,32) + [64,96) first, then [32,64) + [96,128); the first half
+        // of the product runs under the second half of the exponentials
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk) {
-          // P: 16 keys = 8 columns (two bf16 per column) at the start of the tile's score buffer
-          const uint64_t db = desc_mnmajor_sw128(sv, CHUNK_BYTES) + (uint64_t)(kk * 128);
-          umma_f16_ts(tm_o + t * HD, tm_s + t * BKV + kk * 8, db, idesc_o, (j | kk) != 0);
+        for (int h = 0; h < 2; ++h) {
+          if (!mbar_wait(bar(B_PFULL + t * 2 + h), (uint32_t)(j & 1), abort_flag, p.wait_limit)) return false;
+          tc_fence_after();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int kk = (i >> 1) * 4 + h * 2 + (i & 1);   // 16 keys = 8 columns (two bf16 per column) of P
+            const uint64_t db = desc_mnmajor_sw128(sv, CHUNK_BYTES) + (uint64_t)(kk * 128);
+            umma_f16_ts(tm_o + t * HD, tm_s + t * BKV + kk * 8, db, idesc_o, (j | h | i) != 0);
+          }
         }
         umma_commit(bar(B_ODONE + t));
         return true;
@@ -289,6 +294,10 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         // P over the first 64 columns of the tile's score buffer: every thread of this lane quarter
         // has read its scores (it arrived on the exchange barrier after its loads completed)
         tmem_st_32x16(my_s + part * (PCOLS / 2), pk);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_PFULL + t * 2));
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
           const float p0 = fast_exp2(fmaf(__uint_as_float(s1[c]), sl2e, neg));
@@ -303,7 +312,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PFULL + t));
+      if (lane == 0) mbar_arrive(bar(B_PFULL + t * 2 + 1));
     }
     if (!fail && n_t > 0) {
       // the row sum of the other half, then O / l -> bf16
