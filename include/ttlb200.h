@@ -298,6 +298,13 @@ TTLB_EXPORT int ttlb_matmul_bfp8w_multicast(ttlb_ctx *ctx, const ttlb_gemm_bfp8_
 TTLB_EXPORT int ttlb_multimem_bcast(ttlb_ctx *ctx, const void *src, int64_t src_ld_bytes, void *mc_dst,
                                     int64_t dst_ld_bytes, int64_t rows, int64_t row_bytes, void *stream);
 
+/* C = A x B + bias: `bias` is a bf16 [m, n] matrix (row pitch ldbias elements, 16-byte aligned, pitch a
+ * multiple of 8), added to the fp32 product before the single rounding to bf16.  The tile program is the
+ * specification's "matmul with bias" (docs/sphinx/specs/TTLangSpecification.md:232-324):
+ * y_blk.store(c_blk, acc=True) followed by y_blk.store(a_blk @ b_blk, acc=True) over the K tiles. */
+TTLB_EXPORT int ttlb_matmul_bf16_bias(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, const void *bias, int64_t ldbias,
+                                      void *stream);
+
 /* Which tensor-core GEMM kernel the bf16 / bfp8-weight matmuls use:
  *   0  always one CTA per 128x256 output tile (tcgen05 cta_group::1)
  *   1  (default) a cluster of two CTAs per 256x256 tile (cta_group::2: each CTA stages half of the

@@ -17,6 +17,8 @@ from __future__ import annotations
 
 from typing import Callable, Dict, List, Sequence, Tuple
 
+from typing import Optional
+
 import torch
 
 TILE = 32
@@ -74,17 +76,19 @@ def eval_expression(expr: Sequence, inputs: Sequence[torch.Tensor], out_shape: T
     return ev(expr).to(dt).contiguous()
 
 
-def matmul_tiles(a: torch.Tensor, b: torch.Tensor, mode: str) -> torch.Tensor:
+def matmul_tiles(a: torch.Tensor, b: torch.Tensor, mode: str, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`for k: out_blk.store(a_blk @ b_blk, acc=True)` for every output tile
     (examples/singlecore_matmul.py:36-45; accumulate rule python/sim/block.py:856-864):
     the first K tile assigns, later ones add, every partial product and every running sum held
     in the tensor dtype ("native") or in fp32 with one final rounding ("f32").  All output tiles
-    of one K step are computed at once as a slab product."""
+    of one K step are computed at once as a slab product.  With `bias` the accumulation starts from
+    `out_blk.store(c_blk, acc=True)` (docs/sphinx/specs/TTLangSpecification.md:290-312)."""
     dt = a.dtype
     if mode == "f32":
         a, b = a.to(torch.float32), b.to(torch.float32)
+        bias = None if bias is None else bias.to(torch.float32)
     kt = -(-a.shape[1] // TILE)   # a ragged last K slab (C-ABI callers may pass K % 32 != 0) is one more step
-    acc = None
+    acc = None if bias is None else bias.clone()
     for k in range(kt):
         p = a[:, k * TILE:(k + 1) * TILE] @ b[k * TILE:(k + 1) * TILE, :]
         acc = p if acc is None else acc + p

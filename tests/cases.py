@@ -112,6 +112,10 @@ MATMUL_CASES: List[Case] = [
          (256, 256), "f32", None, "rel1e-2", factory_args=(2, 4)),
     Case("mm_multi_native_128", "matmul", "multicore_matmul", [((128, 128), "normal*0.09", 6), ((128, 128), "normal*0.09", 7)],
          (128, 128), "native", None, "rel1e-2"),
+    # the specification's matmul with bias (third input = C)
+    Case("mm_bias_96x160x128", "matmul", "matmul_bias", [((96, 160), "normal*0.08", 8), ((160, 128), "normal*0.08", 9),
+                                                         ((96, 128), "normal", 10)],
+         (96, 128), "f32", None, "rel1e-2"),
 ]
 
 

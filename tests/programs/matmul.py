@@ -139,3 +139,47 @@ def make_blocked_matmul(bm, bn, grid=(4, 4)):
                     tx.wait()
 
     return blocked_matmul
+
+
+@ttl.kernel(grid=(1, 1))
+def matmul_bias(a, b, c, out):
+    """Y = A @ B + C as in the specification's matmul example (2-D operands):
+    `y_blk.store(c_blk, acc=True)` and then `y_blk.store(a_blk @ b_blk, acc=True)` over the K tiles."""
+    Mt, Kt, Nt = a.shape[0] // ttnn.TILE_SIZE, a.shape[1] // ttnn.TILE_SIZE, b.shape[1] // ttnn.TILE_SIZE
+    a_cb = ttl.make_circular_buffer_like(a, shape=(1, 1), buffer_factor=2)
+    b_cb = ttl.make_circular_buffer_like(b, shape=(1, 1), buffer_factor=2)
+    c_cb = ttl.make_circular_buffer_like(c, shape=(1, 1), buffer_factor=2)
+    y_cb = ttl.make_circular_buffer_like(out, shape=(1, 1), buffer_factor=2)
+
+    @ttl.compute()
+    def mm_compute():
+        for _ in range(Mt):
+            for _ in range(Nt):
+                with y_cb.reserve() as y_blk:
+                    with c_cb.wait() as c_blk:
+                        y_blk.store(c_blk, acc=True)
+                    for _ in range(Kt):
+                        with a_cb.wait() as a_blk, b_cb.wait() as b_blk:
+                            y_blk.store(a_blk @ b_blk, acc=True)
+
+    @ttl.datamovement()
+    def mm_reader():
+        for m in range(Mt):
+            for n in range(Nt):
+                with c_cb.reserve() as c_blk:
+                    c_xf = ttl.copy(c[m, n], c_blk)
+                    c_xf.wait()
+                for k in range(Kt):
+                    with a_cb.reserve() as a_blk, b_cb.reserve() as b_blk:
+                        a_xf = ttl.copy(a[m, k], a_blk)
+                        b_xf = ttl.copy(b[k, n], b_blk)
+                        a_xf.wait()
+                        b_xf.wait()
+
+    @ttl.datamovement()
+    def mm_writer():
+        for m in range(Mt):
+            for n in range(Nt):
+                with y_cb.wait() as y_blk:
+                    y_xf = ttl.copy(y_blk, out[m, n])
+                    y_xf.wait()

@@ -25,14 +25,16 @@ def test_matmul_program_matches_simulator_and_oracle(case, backend):
     from ttl_b200 import capi
     _, mods = backend
     import ttnn
-    a, b = case.make_inputs()
+    ins = case.make_inputs()
+    a, b = ins[0], ins[1]
+    bias = ins[2] if len(ins) > 2 else None
     out = ttnn.from_torch(torch.zeros(case.out_shape, dtype=torch.bfloat16))
     n0 = capi.context().launch_count()
-    case.get_program(mods)(ttnn.from_torch(a), ttnn.from_torch(b), out)
+    case.get_program(mods)(*[ttnn.from_torch(t) for t in ins], out)
     capi.context().check_status(capi.current_stream())
     assert capi.context().launch_count() == n0 + 1
     got = ttnn.to_torch(out)
-    assert rel_err(got, tile_oracle.matmul_tiles(a, b, "f32")) <= TOL
+    assert rel_err(got, tile_oracle.matmul_tiles(a, b, "f32", bias=bias)) <= TOL
     assert rel_err(got, golden_tensor(load_golden(case.name)["out"], torch.bfloat16)) <= TOL
 
 
@@ -66,6 +68,37 @@ def test_c_abi_matmul_shapes_with_ragged_tiles(m, n, k, variant):
     frame = got.clone()
     frame[32:32 + m, 32:32 + n] = 3.0
     assert (frame == 3.0).all(), "matmul wrote outside its output rectangle"
+
+
+@pytest.mark.parametrize("variant", [0, 2], ids=["one_cta", "two_cta"])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 264, 136), (2304, 4352, 512)])
+def test_c_abi_matmul_with_bias(m, n, k, variant):
+    """C = A B + bias through the C ABI with both tensor-core kernels, ragged tiles included; the bias is
+    added in fp32 before the single rounding (checked exactly against a torch fp32 reference of the op)."""
+    from ttl_b200 import capi
+    g = torch.Generator().manual_seed(m + 2 * n + 3 * k)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    b = torch.randn(k, n, generator=g).to(torch.bfloat16)
+    bias = (4 * torch.randn(m, n, generator=g)).to(torch.bfloat16)
+    A, B, Cb = a.cuda(), b.cuda(), bias.cuda()
+    out = torch.zeros(m, n, dtype=torch.bfloat16, device="cuda")
+    d = capi.GemmDesc()
+    d.a, d.lda, d.b, d.ldb, d.c, d.ldc = A.data_ptr(), k, B.data_ptr(), n, out.data_ptr(), n
+    d.m, d.n, d.k = m, n, k
+    ctx = capi.context()
+    ctx.set_gemm_variant(variant)
+    try:
+        ctx.matmul_bf16_bias(d, Cb.data_ptr(), n, capi.current_stream())
+        ctx.check_status(capi.current_stream())
+    finally:
+        ctx.set_gemm_variant(1)
+    want = tile_oracle.matmul_tiles(a, b, "f32", bias=bias)
+    assert rel_err(out.cpu(), want) <= TOL
+    # the bias is not rounded away: with a zero product the output is the bias itself
+    out.zero_()
+    d.a = torch.zeros_like(A).data_ptr()
+    ctx.matmul_bf16_bias(d, Cb.data_ptr(), n, capi.current_stream())
+    assert torch.equal(out.cpu(), bias)
 
 
 def test_c_abi_matmul_rejects_bad_descriptors():

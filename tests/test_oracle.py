@@ -17,7 +17,7 @@ REFERENCE = Path("/root/reference")
 def oracle_output(case):
     ins = case.make_inputs()
     if case.module == "matmul":
-        return tile_oracle.matmul_tiles(ins[0], ins[1], case.mode)
+        return tile_oracle.matmul_tiles(ins[0], ins[1], case.mode, bias=ins[2] if len(ins) > 2 else None)
     out = tile_oracle.eval_expression(case.expr, ins, case.out_shape, case.mode)
     if case.name == "eltwise_pipe":  # only the pipe's four cores compute: tile columns 0..3
         full = torch.zeros(case.out_shape, dtype=case.dtype)

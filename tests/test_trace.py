@@ -67,6 +67,17 @@ def test_matmul_recognised(backend, tt, name):
     assert d == [{"kind": "matmul_bf16", "a": 0, "b": 1, "out": 2, "rect_tiles": (0, 8, 0, 4), "k_tiles": 6}]
 
 
+def test_matmul_with_bias_recognised(backend, tt):
+    """The specification's matmul with bias (a store of the C block before the K loop) becomes one GEMM
+    launch with the bias operand; a bias block that is not the output tile's block is refused."""
+    _, mods = backend
+    ttl, ttnn = tt
+    a, b = _t(ttnn, (64, 96)), _t(ttnn, (96, 128))
+    c, o = _t(ttnn, (64, 128)), _t(ttnn, (64, 128))
+    d = mods["matmul"].matmul_bias.plan(a, b, c, o).describe()
+    assert d == [{"kind": "matmul_bf16", "a": 0, "b": 1, "out": 3, "rect_tiles": (0, 2, 0, 4), "k_tiles": 3, "bias": 2}]
+
+
 def test_blocked_matmul_recognised_and_tilewise_product_rejected(backend, tt):
     from ttl_b200 import Unsupported
     _, mods = backend

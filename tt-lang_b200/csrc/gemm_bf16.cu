@@ -61,6 +61,8 @@ struct GemmParams {
   int *status;
   long long wait_limit;
   int multicast;  // 1: `c` is an NVLink multicast address; the epilogue stores with multimem.st
+  const __nv_bfloat16 *bias = nullptr;  // optional [m, n] matrix added to the product before rounding
+  long long ldbias = 0;
 };
 
 // 16-byte store to a multicast address: the switch replicates it to every GPU of the group.
@@ -199,6 +201,7 @@ ttlb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       tc_fence_after();
       const int row = tm * BM + q * 32 + lane;
       __nv_bfloat16 *crow = p.c + (long long)row * p.ldc + (long long)tn * BN;
+      const __nv_bfloat16 *brow = p.bias ? p.bias + (long long)row * p.ldbias + (long long)tn * BN : nullptr;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -207,6 +210,7 @@ ttlb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int col0 = tn * BN + c * 32;
         if (row < p.m && col0 < p.n) {
           if (col0 + 32 <= p.n) {
+            if (brow) add_bias32(r, brow + c * 32);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 o;
@@ -222,7 +226,8 @@ ttlb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e)
-              if (col0 + e < p.n) crow[c * 32 + e] = __float2bfloat16_rn(__uint_as_float(r[e]));
+              if (col0 + e < p.n)
+                crow[c * 32 + e] = __float2bfloat16_rn(__uint_as_float(r[e]) + (brow ? __bfloat162float(brow[c * 32 + e]) : 0.f));
           }
         }
       }
@@ -269,7 +274,10 @@ int ttlb_make_map_bf16_2d(ttlb_ctx *ctx, CUtensorMap *map, const void *ptr, uint
   return make_map(ctx, map, ptr, inner, outer, pitch_bytes, box_inner, box_outer);
 }
 int ttlb_launch_gemm_bf16_2cta(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
-                               int64_t m, int64_t n, int64_t k, cudaStream_t stream);
+                               int64_t m, int64_t n, int64_t k, const void *bias, int64_t ldbias, cudaStream_t stream);
+int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
+                               int64_t m, int64_t n, int64_t k, bool multicast, const void *bias, int64_t ldbias,
+                               cudaStream_t stream);
 
 // Shared with the bfp8-weight path, which first expands the weights to bf16.
 int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
@@ -280,10 +288,19 @@ int ttlb_launch_gemm_bf16(ttlb_ctx *ctx, const void *a, int64_t lda, const void 
   return ttlb_launch_gemm_bf16_ex(ctx, a, lda, b, ldb, c, ldc, m, n, k, false, stream);
 }
 
-// multicast: `c` is a multicast address (the output is published to every GPU of the group); needs n % 32 == 0
 int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
                              int64_t m, int64_t n, int64_t k, bool multicast, cudaStream_t stream) {
+  return ttlb_launch_gemm_bf16_full(ctx, a, lda, b, ldb, c, ldc, m, n, k, multicast, nullptr, 0, stream);
+}
+
+// multicast: `c` is a multicast address (the output is published to every GPU of the group); needs n % 32 == 0.
+// bias: optional bf16 [m, n] matrix (row pitch ldbias) added to the fp32 product before the rounding to bf16.
+int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
+                               int64_t m, int64_t n, int64_t k, bool multicast, const void *bias, int64_t ldbias,
+                               cudaStream_t stream) {
   if (m == 0 || n == 0) return TTLB_OK;
+  if (bias && (((uintptr_t)bias % 16) || (ldbias % 8) || ldbias < n))
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: bias must be 16-byte aligned with a row pitch >= N that is a multiple of 8");
   if (multicast && (n % 32))
     return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: a multicast output needs N to be a multiple of 32");
   if (!a || !b || !c) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null operand");
@@ -302,7 +319,7 @@ int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const vo
   // spread better as 128x256 tiles.
   if (!multicast && (ctx->gemm_variant == 2 ||
                      (ctx->gemm_variant == 1 && ((m + 255) / 256) * ((n + 255) / 256) >= ctx->sm_count / 2)))
-    return ttlb_launch_gemm_bf16_2cta(ctx, a, lda, b, ldb, c, ldc, m, n, k, stream);
+    return ttlb_launch_gemm_bf16_2cta(ctx, a, lda, b, ldb, c, ldc, m, n, k, bias, ldbias, stream);
 
   CUtensorMap map_a, map_b;
   int rc = make_map(ctx, &map_a, a, (uint64_t)k, (uint64_t)m, (uint64_t)lda * 2, BK, BM);
@@ -328,6 +345,8 @@ int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const vo
   p.status = ctx->d_status;
   p.wait_limit = ctx->wait_limit_cycles;
   p.multicast = multicast ? 1 : 0;
+  p.bias = reinterpret_cast<const __nv_bfloat16 *>(bias);
+  p.ldbias = ldbias;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
   ttlb_gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
@@ -341,6 +360,14 @@ extern "C" int ttlb_matmul_bf16(ttlb_ctx *ctx, const ttlb_gemm_desc *d, void *st
   if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null descriptor");
   return ttlb_launch_gemm_bf16(ctx, d->a, d->lda, d->b, d->ldb, d->c, d->ldc, d->m, d->n, d->k,
                                reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ttlb_matmul_bf16_bias(ttlb_ctx *ctx, const ttlb_gemm_desc *d, const void *bias, int64_t ldbias, void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null descriptor");
+  if (!bias) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null bias");
+  return ttlb_launch_gemm_bf16_full(ctx, d->a, d->lda, d->b, d->ldb, d->c, d->ldc, d->m, d->n, d->k, false, bias, ldbias,
+                                    reinterpret_cast<cudaStream_t>(stream));
 }
 
 extern "C" int ttlb_matmul_bf16_multicast(ttlb_ctx *ctx, const ttlb_gemm_desc *d, void *stream) {

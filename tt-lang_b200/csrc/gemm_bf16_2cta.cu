@@ -39,6 +39,8 @@ struct Gemm2Params {
   int tiles_m, tiles_n;  // in 256x256 tiles
   int *status;
   long long wait_limit;
+  const __nv_bfloat16 *bias = nullptr;  // optional [m, n] matrix added to the product before rounding
+  long long ldbias = 0;
 };
 
 template <int GROUP_M2>
@@ -157,6 +159,7 @@ ttlb_gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
       tc_fence_after();
       const int row = tm * BM2 + (int)rank * 128 + q * 32 + lane;
       __nv_bfloat16 *crow = p.c + (long long)row * p.ldc + (long long)tn * BN2;
+      const __nv_bfloat16 *brow = p.bias ? p.bias + (long long)row * p.ldbias + (long long)tn * BN2 : nullptr;
 #pragma unroll 1
       for (int c = 0; c < BN2 / 32; ++c) {
         uint32_t r[32];
@@ -165,6 +168,7 @@ ttlb_gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         const int col0 = tn * BN2 + c * 32;
         if (row < p.m && col0 < p.n) {
           if (col0 + 32 <= p.n) {
+            if (brow) add_bias32(r, brow + c * 32);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 o;
@@ -177,7 +181,8 @@ ttlb_gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e)
-              if (col0 + e < p.n) crow[c * 32 + e] = __float2bfloat16_rn(__uint_as_float(r[e]));
+              if (col0 + e < p.n)
+                crow[c * 32 + e] = __float2bfloat16_rn(__uint_as_float(r[e]) + (brow ? __bfloat162float(brow[c * 32 + e]) : 0.f));
           }
         }
       }
@@ -209,7 +214,7 @@ int ttlb_make_map_bf16_2d(ttlb_ctx *ctx, CUtensorMap *map, const void *ptr, uint
 
 // Two-CTA launch; arguments are validated by the caller (ttlb_launch_gemm_bf16_ex).
 int ttlb_launch_gemm_bf16_2cta(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
-                               int64_t m, int64_t n, int64_t k, cudaStream_t stream) {
+                               int64_t m, int64_t n, int64_t k, const void *bias, int64_t ldbias, cudaStream_t stream) {
   CUtensorMap map_a, map_b;
   int rc = ttlb_make_map_bf16_2d(ctx, &map_a, a, (uint64_t)k, (uint64_t)m, (uint64_t)lda * 2, BK2, 128);
   if (rc) return rc;
@@ -230,6 +235,8 @@ int ttlb_launch_gemm_bf16_2cta(ttlb_ctx *ctx, const void *a, int64_t lda, const 
   p.tiles_n = (int)((n + BN2 - 1) / BN2);
   p.status = ctx->d_status;
   p.wait_limit = ctx->wait_limit_cycles;
+  p.bias = reinterpret_cast<const __nv_bfloat16 *>(bias);
+  p.ldbias = ldbias;
   const int tiles = p.tiles_m * p.tiles_n;
   int clusters = ctx->sm_count / 2;
   if (clusters > tiles) clusters = tiles;

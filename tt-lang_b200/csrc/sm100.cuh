@@ -205,6 +205,21 @@ __host__ __device__ constexpr uint32_t idesc_bf16(uint32_t m, uint32_t n, bool a
          ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// fp32 accumulators r[0..31] += 32 consecutive bf16 of a bias row (16-byte aligned)
+__device__ __forceinline__ void add_bias32(uint32_t (&r)[32], const __nv_bfloat16 *bias) {
+  const uint4 *bp = reinterpret_cast<const uint4 *>(bias);
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const uint4 b = bp[v];
+    const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      r[8 * v + 2 * e] = __float_as_uint(__uint_as_float(r[8 * v + 2 * e]) + __uint_as_float(w[e] << 16));
+      r[8 * v + 2 * e + 1] = __float_as_uint(__uint_as_float(r[8 * v + 2 * e + 1]) + __uint_as_float(w[e] & 0xffff0000u));
+    }
+  }
+}
+
 // ---- two-CTA (cta_group::2) forms: a cluster of two CTAs drives one UMMA ------------
 // None of the loads below is multicast: each CTA loads its own part of the operands; only the
 // completion signal (mbarrier) may live in the peer CTA.

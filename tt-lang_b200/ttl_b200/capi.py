@@ -121,6 +121,8 @@ def lib() -> C.CDLL:
     l.ttlb_eltwise_source.restype = C.c_int64
     l.ttlb_matmul_bf16.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]
     l.ttlb_matmul_bf16.restype = C.c_int
+    l.ttlb_matmul_bf16_bias.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_int64, C.c_void_p]
+    l.ttlb_matmul_bf16_bias.restype = C.c_int
     l.ttlb_pack_bfp8_b.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
     l.ttlb_pack_bfp8_b.restype = C.c_int
     l.ttlb_unpack_bfp8_b.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
@@ -182,6 +184,11 @@ class Context:
 
     def matmul_bf16(self, desc: "GemmDesc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_bf16(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def matmul_bf16_bias(self, desc: "GemmDesc", bias_ptr: int, ldbias: int, stream: int) -> None:
+        """C = A @ B + bias (bias: bf16 [m, n], added in fp32 before the rounding)."""
+        self.check(self._lib.ttlb_matmul_bf16_bias(self.handle, C.byref(desc), C.c_void_p(bias_ptr), ldbias,
+                                                   C.c_void_p(stream)))
 
     def matmul_f32(self, desc: "GemmDesc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_f32(self.handle, C.byref(desc), C.c_void_p(stream)))

@@ -23,11 +23,14 @@ def _dev2d(t: "_ttnn.Tensor", what: str) -> torch.Tensor:
 
 
 def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_ttnn.Tensor",
-                rect: Tuple[int, int, int, int], stream: int, multicast_ptr: Optional[int] = None) -> None:
-    """out[r0:r1, c0:c1] = a[r0:r1, :] @ b[:, c0:c1] (element coordinates).  With `multicast_ptr` (the
-    NVLink multicast address of out's element (0, 0)) the result is stored through the switch to every GPU
-    of the multicast group instead of through out's own mapping."""
+                rect: Tuple[int, int, int, int], stream: int, multicast_ptr: Optional[int] = None,
+                bias: Optional["_ttnn.Tensor"] = None) -> None:
+    """out[r0:r1, c0:c1] = a[r0:r1, :] @ b[:, c0:c1] (+ bias[r0:r1, c0:c1]) (element coordinates).  With
+    `multicast_ptr` (the NVLink multicast address of out's element (0, 0)) the result is stored through the
+    switch to every GPU of the multicast group instead of through out's own mapping."""
     r0, r1, c0, c1 = rect
+    if bias is not None and (b._packed is not None or multicast_ptr is not None or a._tensor.dtype != torch.bfloat16):
+        raise Unsupported("matmul with bias: bfloat16 A, B, bias and output, own-memory output only")
     if b._packed is not None:
         xa, xo = _dev2d(a, "A"), _dev2d(out, "out")
         if xa.dtype != torch.bfloat16 or xo.dtype != torch.bfloat16:
@@ -64,6 +67,11 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
         ctx.matmul_f32(d, stream)
     elif multicast_ptr is not None:
         ctx.matmul_bf16_multicast(d, stream)
+    elif bias is not None:
+        xc = _dev2d(bias, "bias")
+        if xc.dtype != torch.bfloat16 or tuple(xc.shape) != tuple(xo.shape):
+            raise Unsupported("matmul with bias: the bias must be a bfloat16 tensor of the output's shape")
+        ctx.matmul_bf16_bias(d, xc.data_ptr() + (r0 * xc.stride(0) + c0) * 2, xc.stride(0), stream)
     else:
         ctx.matmul_bf16(d, stream)
 

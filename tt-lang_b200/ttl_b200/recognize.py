@@ -295,21 +295,25 @@ class EltwiseLaunch:
 
 class GemmLaunch:
     def __init__(self, a_index: int, b_index: int, out_index: int, rect: Tuple[int, int, int, int], k_tiles: int,
-                 b_is_bfp8: bool):
+                 b_is_bfp8: bool, bias_index: Optional[int] = None):
         self.a_index, self.b_index, self.out_index, self.rect = a_index, b_index, out_index, rect
-        self.k_tiles, self.b_is_bfp8 = k_tiles, b_is_bfp8
+        self.k_tiles, self.b_is_bfp8, self.bias_index = k_tiles, b_is_bfp8, bias_index
         self.kind = "matmul_bf16"   # set to "matmul_f32" by the recogniser for float32 programs
 
     def describe(self) -> Dict[str, Any]:
-        return {"kind": "matmul_bfp8w" if self.b_is_bfp8 else self.kind, "a": self.a_index, "b": self.b_index,
-                "out": self.out_index, "rect_tiles": self.rect, "k_tiles": self.k_tiles}
+        d = {"kind": "matmul_bfp8w" if self.b_is_bfp8 else self.kind, "a": self.a_index, "b": self.b_index,
+             "out": self.out_index, "rect_tiles": self.rect, "k_tiles": self.k_tiles}
+        if self.bias_index is not None:
+            d["bias"] = self.bias_index
+        return d
 
     def run(self, ctx: capi.Context, tensors: Sequence[_ttnn.Tensor], stream: int) -> None:
         from . import ops
 
         r0, r1, c0, c1 = self.rect
         ops.launch_gemm(ctx, tensors[self.a_index], tensors[self.b_index], tensors[self.out_index],
-                        (r0 * TILE, r1 * TILE, c0 * TILE, c1 * TILE), stream)
+                        (r0 * TILE, r1 * TILE, c0 * TILE, c1 * TILE), stream,
+                        bias=None if self.bias_index is None else tensors[self.bias_index])
 
 
 class Plan:
@@ -345,11 +349,17 @@ class Plan:
 # --------------------------------------------------------------------------- #
 # plan construction
 # --------------------------------------------------------------------------- #
-def _matmul_terms(w: Write) -> Optional[List[Bin]]:
+def _matmul_terms(w: Write) -> Optional[Tuple[List[Bin], Optional[Leaf]]]:
+    """The write as a block matmul: its `a @ b` terms and, for the specification's matmul with bias
+    (`y.store(c, acc=True)` before the K loop, docs/sphinx/specs/TTLangSpecification.md:290-312), the
+    block the accumulation starts from."""
     e = w.expr
-    terms = e.terms if isinstance(e, Acc) else [e]
-    if all(isinstance(t, Bin) and t.op == "matmul" for t in terms):
-        return terms  # type: ignore[return-value]
+    terms = list(e.terms) if isinstance(e, Acc) else [e]
+    bias = None
+    if len(terms) > 1 and isinstance(terms[0], Leaf):
+        bias, terms = terms[0], terms[1:]
+    if terms and all(isinstance(t, Bin) and t.op == "matmul" for t in terms):
+        return terms, bias  # type: ignore[return-value]
     return None
 
 
@@ -371,9 +381,10 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
         if not (0 <= w.r0 < w.r1 <= tr and 0 <= w.c0 < w.c1 <= tc):
             raise ValueError(f"write region [{w.r0}:{w.r1}, {w.c0}:{w.c1}] is outside the {tr}x{tc}-tile tensor")
         region = (w.r0, w.r1, w.c0, w.c1)
-        terms = _matmul_terms(w)
-        if terms is not None:
-            key = ("mm",) + tuple(_recognise_matmul(w, terms, table, oi))
+        mm = _matmul_terms(w)
+        if mm is not None:
+            terms, bias = mm
+            key = ("mm",) + tuple(_recognise_matmul(w, terms, table, oi)) + (_recognise_bias(w, bias, table),)
         else:
             if _contains_matmul(w.expr):
                 raise Unsupported("matmul mixed with element-wise ops in one store is not supported yet")
@@ -413,14 +424,27 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
             launches.append(EltwiseLaunch(oi, rect, list(inputs), list(ops), odt,
                                           round_each_op=not fp32_intermediates, out_degenerate=degen))
     for key, rects in mm_groups.items():
-        _, ai, bi, oi, kt, b8 = key
+        _, ai, bi, oi, kt, b8, ci = key
         f32 = out_tensors[oi].dtype == torch.float32
+        if ci is not None and (f32 or b8):
+            raise Unsupported("matmul with bias: bfloat16 A, B, bias and output only")
         for rect in merge_rects(rects):
-            gl = GemmLaunch(ai, bi, oi, rect, kt, b8)
+            gl = GemmLaunch(ai, bi, oi, rect, kt, b8, ci)
             if f32:
                 gl.kind = "matmul_f32"
             launches.append(gl)
     return Plan(launches, table.extras, len(table.args))
+
+
+def _recognise_bias(w: Write, bias: Optional[Leaf], table: _TensorTable) -> Optional[int]:
+    if bias is None:
+        return None
+    t = bias.tensor
+    if tuple(t.shape) != tuple(w.tensor.shape) or t.dtype != w.tensor.dtype:
+        raise Unsupported("matmul with bias: the bias tensor must have the output's shape and element type")
+    if (bias.r0, bias.r1, bias.c0, bias.c1) != (w.r0, w.r1, w.c0, w.c1):
+        raise Unsupported("matmul with bias: the bias block is not the block of the output tile being computed")
+    return table.index(t)
 
 
 def _recognise_matmul(w: Write, terms: List[Bin], table: _TensorTable, oi: int) -> Any:
