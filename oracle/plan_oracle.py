@@ -1,0 +1,80 @@
+"""CPU evaluation of a launch plan (test infrastructure only - never on the product path).
+
+A plan is what the recogniser turns a tt-lang kernel call into: element-wise launches (operand
+index modes + a small stack program, include/ttlb200.h) and matmul launches.  Evaluating the plan
+on the host with torch shows that the front half (tracer + recogniser) preserved the program's
+meaning, without a GPU: the reference's own hardware tests (test/python/*.py) are run this way.
+Numerics follow the reference simulator: ops on bf16 tensors round after every op unless the
+kernel asked for fp32 intermediates (python/sim/block.py:856-864)."""
+
+from typing import Any, List, Sequence
+
+import torch
+
+from . import tile_oracle
+
+TILE = 32
+_SAME, _ZERO, _TILE = 0, 1, 2
+
+_UNARY = {
+    "exp": torch.exp, "log": torch.log, "sqrt": torch.sqrt, "rsqrt": torch.rsqrt, "tanh": torch.tanh,
+    "sigmoid": torch.sigmoid, "neg": torch.neg, "abs": torch.abs, "relu": torch.relu,
+}
+_BINARY = {
+    "add": lambda a, b: a + b, "sub": lambda a, b: a - b, "rsub": lambda a, b: b - a, "mul": lambda a, b: a * b,
+    "div": lambda a, b: a / b, "rdiv": lambda a, b: b / a, "max": torch.maximum, "min": torch.minimum,
+}
+
+
+def _index(mode: int, off: int, idx: torch.Tensor) -> torch.Tensor:
+    if mode == _SAME:
+        return idx + off
+    if mode == _ZERO:
+        return torch.zeros_like(idx)
+    return off + idx % TILE
+
+
+def run_eltwise(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
+    """Evaluate one element-wise launch into tensors[launch.out_index] (host tensors)."""
+    out = tensors[launch.out_index]
+    r0, r1, c0, c1 = launch.rect
+    rows = torch.arange(0, 1) if launch.out_degenerate[0] else torch.arange(r0 * TILE, r1 * TILE)
+    cols = torch.arange(0, 1) if launch.out_degenerate[1] else torch.arange(c0 * TILE, c1 * TILE)
+    bf16 = out.dtype == torch.bfloat16
+    rnd = bf16 and launch.round_each_op
+
+    def operand(k: int) -> torch.Tensor:
+        ti, rm, ro, cm, co = launch.inputs[k]
+        x = tensors[ti]
+        if x.dim() == 1:
+            x = x.reshape(1, -1)
+        return x[_index(rm, ro, rows)][:, _index(cm, co, cols)].to(torch.float32)
+
+    acc = torch.zeros(len(rows), len(cols))
+    stack: List[torch.Tensor] = []
+    for op, arg in launch.ops:
+        if op == "push":
+            stack.insert(0, acc)
+            continue
+        if op == "load" or op in _BINARY:
+            x = operand(arg) if arg >= 0 else stack.pop(0)
+            acc = x if op == "load" else _BINARY[op](acc, x)
+        else:
+            acc = _UNARY[op](acc)
+        if rnd and op != "load":
+            acc = acc.to(torch.bfloat16).to(torch.float32)
+    view = out if out.dim() == 2 else out.reshape(1, -1)
+    view[rows[0]:rows[-1] + 1, cols[0]:cols[-1] + 1] = acc.to(out.dtype)
+
+
+def run_gemm(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
+    a, b, out = tensors[launch.a_index], tensors[launch.b_index], tensors[launch.out_index]
+    r0, r1, c0, c1 = (x * TILE for x in launch.rect)
+    bias = None if launch.bias_index is None else tensors[launch.bias_index][r0:r1, c0:c1]
+    mode = "native" if out.dtype == torch.float32 else "f32"
+    out[r0:r1, c0:c1] = tile_oracle.matmul_tiles(a[r0:r1], b[:, c0:c1], mode, bias=bias).to(out.dtype)
+
+
+def run_plan(plan: Any, tensors: Sequence[torch.Tensor]) -> None:
+    for launch in plan.launches:
+        (run_eltwise if hasattr(launch, "ops") else run_gemm)(launch, tensors)

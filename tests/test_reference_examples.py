@@ -52,3 +52,19 @@ def test_reference_example_is_traced_and_recognised(rel, backend, monkeypatch):
     assert plans, "the program never reached a kernel launch"
     kinds = {l["kind"] for p in plans for l in p}
     assert kinds == EXPECTED[rel]
+
+
+@pytest.mark.parametrize("rel,exc,text", [
+    ("examples/copy_lock_error.py", RuntimeError, "copy lock error"),
+    ("examples/eltwise_add_error.py", ValueError, "does not match Block shape"),
+])
+def test_reference_error_examples_fail_the_same_way(rel, exc, text, backend, monkeypatch):
+    """The reference's intentionally wrong programs are refused while tracing, with the simulator's
+    diagnosis (python/sim/block.py:839-843, python/sim/copyhandlers.py:299-310)."""
+    monkeypatch.setattr(sys, "argv", [rel])
+    path = REFERENCE / rel
+    monkeypatch.syspath_prepend(str(path.parent))
+    monkeypatch.syspath_prepend(str(REFERENCE / "python"))
+    with pytest.raises(exc, match=text):
+        with contextlib.redirect_stdout(io.StringIO()):
+            runpy.run_path(str(path), run_name="__main__")

@@ -128,12 +128,18 @@ def current_core() -> int:
 def current_grid() -> Tuple[int, ...]:
     g = getattr(_tls, "grid", None)
     if g is None:
+        # after a kernel has run the compiler keeps its grid in a module global
+        # (python/ttl/operators.py:36), which programs read back with ttl.grid_size()
+        g = getattr(_tls, "last_grid", None)
+    if g is None:
         raise RuntimeError("grid not available - function must be called within a kernel context")
     return g
 
 
 def set_grid(grid: Optional[Tuple[int, ...]]) -> None:
     _tls.grid = grid
+    if grid is not None:
+        _tls.last_grid = grid
 
 
 class DeadlockError(RuntimeError):
@@ -297,7 +303,9 @@ class Block:
     # -- writing ---------------------------------------------------------
     def store(self, items: Any, acc: bool = False) -> None:
         src = _as_block(items)
-        if not isinstance(src, Block):
+        # the simulator also takes a sequence of tile tensors and checks length, then write access
+        # (python/sim/block.py:839-843); the same order here, so that programs get the same error
+        if not isinstance(src, (Block, list, tuple)):
             raise TypeError("store() takes a block or a block expression")
         if len(src) != len(self):
             raise ValueError("Length mismatch in store()")
@@ -309,6 +317,8 @@ class Block:
             raise RuntimeError("Cannot write to Block: Block has no access (OS state). Current state: OS")
         if not self.temporary and self.kind == "wait":
             raise RuntimeError("Cannot write to Block: a waited block is read-only in a compute thread")
+        if not isinstance(src, Block):
+            raise TypeError("store() of a sequence of tile tensors is not supported on the GPU: store a block or a block expression")
         v = src.value()
         if acc:
             if self.state == "MW":  # first accumulating store assigns

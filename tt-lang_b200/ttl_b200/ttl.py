@@ -23,6 +23,13 @@ Size = int
 Shape = tuple
 CopyTransferHandler = CopyTransaction
 
+# the compiler package also exports the element-wise functions at top level
+# (python/ttl/__init__.py:22-24) and itself as `ttl.ttl` (`from ttl import ttl`, python/ttl/ttl.py)
+from .math import abs, exp, log, max, min, neg, relu, rsqrt, sigmoid, sqrt, tanh  # noqa: E402,F401,A004
+import sys as _sys  # noqa: E402
+
+ttl = _sys.modules[__name__]
+
 
 def signpost(name: str) -> None:
     """Profiling marker (python/ttl/__init__.py); a no-op on this backend."""

@@ -151,6 +151,10 @@ class Tensor:
     def __repr__(self) -> str:
         return f"Tensor(shape={self.shape}, dtype={self.dtype})"
 
+    def memory_config(self) -> Any:
+        """Everything lives in HBM; the L1 / DRAM distinction of the reference has no counterpart."""
+        return DRAM_MEMORY_CONFIG
+
     def to_torch(self) -> torch.Tensor:
         return to_torch(self)
 
