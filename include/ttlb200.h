@@ -116,13 +116,19 @@ enum ttlb_opcode {
 
 /* How an input is indexed from an output element (i, j):
  *  SAME  index = i + off                 (same-shape operand, optionally shifted)
- *  ZERO  index = 0                       (degenerate tensor dim: [1,N] row vector,
- *                                         [N,1] column, [1,1] scalar;
- *                                         python/sim/copyhandlers.py:103-131)
+ *  ZERO  index = off                     (one fixed row / column: a degenerate tensor dim -
+ *                                         [1,N] row vector, [N,1] column, [1,1] scalar,
+ *                                         python/sim/copyhandlers.py:103-131 - or the first
+ *                                         row / column of one fixed tile)
  *  TILE  index = off + (i mod 32)        (one fixed tile repeated over the tile
  *                                         grid: the simulator's tile-grid
- *                                         broadcast, python/sim/ttnnsim.py:67-109) */
-enum ttlb_index_mode { TTLB_IDX_SAME = 0, TTLB_IDX_ZERO = 1, TTLB_IDX_TILE = 2 };
+ *                                         broadcast, python/sim/ttnnsim.py:67-109)
+ *  FIRST index = off + (i - i mod 32)    (element 0 of the tile that i falls in: the hardware
+ *                                         broadcast convention, a FULL source tile whose first
+ *                                         row / column / element carries the data, ttl.bcast
+ *                                         Row / Col / Scalar, TTLOps.td:570-597,
+ *                                         test/python/test_bcast_ops.py:31-55) */
+enum ttlb_index_mode { TTLB_IDX_SAME = 0, TTLB_IDX_ZERO = 1, TTLB_IDX_TILE = 2, TTLB_IDX_FIRST = 3 };
 
 typedef struct {
   const void *ptr; /* element (0,0) of the tensor */

@@ -14,7 +14,7 @@ import torch
 from . import tile_oracle
 
 TILE = 32
-_SAME, _ZERO, _TILE = 0, 1, 2
+_SAME, _ZERO, _TILE, _FIRST = 0, 1, 2, 3
 
 _UNARY = {
     "exp": torch.exp, "log": torch.log, "sqrt": torch.sqrt, "rsqrt": torch.rsqrt, "tanh": torch.tanh,
@@ -30,7 +30,9 @@ def _index(mode: int, off: int, idx: torch.Tensor) -> torch.Tensor:
     if mode == _SAME:
         return idx + off
     if mode == _ZERO:
-        return torch.zeros_like(idx)
+        return torch.full_like(idx, off)
+    if mode == _FIRST:
+        return off + idx - idx % TILE
     return off + idx % TILE
 
 

@@ -400,3 +400,37 @@ def intermediate_cb(a, b, y):
             with y_cb.wait() as y_blk:
                 tx = ttl.copy(y_blk, y[r:r + 1, 0:ct])
                 tx.wait()
+
+
+def make_hw_broadcast(dims, in_block, out_block):
+    """Compiler-style broadcast of FULL tiles (test/python/test_bcast_ops.py:60-84): the first row
+    (dims=[0]) / first column (dims=[1]) / element [0,0] (dims=[0,1]) of every source tile is spread
+    over the tile; a source block of one tile along a dim expands to the output block.  Computes
+    out = x * 2 + broadcast(b) on one block.  Only meaningful with the hardware broadcast switch on."""
+
+    @ttl.kernel(grid=(1, 1))
+    def hw_broadcast(x, b, out):
+        x_cb = ttl.make_circular_buffer_like(x, shape=out_block, buffer_factor=2)
+        b_cb = ttl.make_circular_buffer_like(b, shape=in_block, buffer_factor=2)
+        o_cb = ttl.make_circular_buffer_like(out, shape=out_block, buffer_factor=2)
+
+        @ttl.compute()
+        def compute():
+            with x_cb.wait() as xb, b_cb.wait() as bb, o_cb.reserve() as ob:
+                ob.store(xb + xb + ttl.math.broadcast(bb, ob, dims=dims))
+
+        @ttl.datamovement()
+        def reader():
+            with x_cb.reserve() as xb, b_cb.reserve() as bb:
+                tx = ttl.copy(x[0:out_block[0], 0:out_block[1]], xb)
+                tb = ttl.copy(b[0:in_block[0], 0:in_block[1]], bb)
+                tx.wait()
+                tb.wait()
+
+        @ttl.datamovement()
+        def writer():
+            with o_cb.wait() as ob:
+                tx = ttl.copy(ob, out[0:out_block[0], 0:out_block[1]])
+                tx.wait()
+
+    return hw_broadcast

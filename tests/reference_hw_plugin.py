@@ -18,6 +18,7 @@ os.environ["TTLANG_HAS_DEVICE"] = "1"   # the reference's helper module decides 
 import ttl_b200  # noqa: E402
 
 ttl_b200.install()
+ttl_b200.set_hardware_broadcast(True)   # these tests are written against the compiler's broadcast (full source tiles)
 for _name in ("ttl", "ttnn"):
     if getattr(sys.modules[_name], "__spec__", None) is None:
         sys.modules[_name].__spec__ = importlib.machinery.ModuleSpec(_name, None)

@@ -181,3 +181,32 @@ def test_c_abi_sub_rectangle_and_offsets_leave_the_rest_untouched():
     want = torch.full((96, 128), 7.0, dtype=torch.bfloat16)
     want[32:64, 32:96] = xc[32:64, 32:96] * yc[64:96, 0:64]
     assert torch.equal(o.cpu(), want)
+
+
+@pytest.mark.parametrize("dims,in_block,out_block", [([0], (2, 2), (2, 2)), ([1], (2, 2), (2, 2)), ([0, 1], (2, 2), (2, 2)),
+                                                      ([0], (1, 2), (2, 2)), ([1], (2, 1), (2, 3)), ([0, 1], (1, 1), (3, 2))])
+def test_hardware_broadcast_of_full_tiles(dims, in_block, out_block, backend, eltwise_path):
+    """The compiler's broadcast convention (first row / column / element of every FULL source tile,
+    test/python/test_bcast_ops.py:31-55), selected with set_hardware_broadcast: index modes FIRST and
+    ZERO-with-offset in both GPU kernels, against a torch restatement."""
+    import ttl_b200
+    _, mods = backend
+    import ttnn
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(out_block[0] * 32, out_block[1] * 32, generator=g).to(torch.bfloat16)
+    b = torch.randn(in_block[0] * 32, in_block[1] * 32, generator=g).to(torch.bfloat16)
+    src = b.float().reshape(in_block[0], 32, in_block[1], 32)
+    if 0 in dims:
+        src = src[:, :1].expand(-1, 32, -1, -1)
+    if 1 in dims:
+        src = src[:, :, :, :1].expand(-1, -1, -1, 32)
+    src = src.expand(out_block[0] if in_block[0] == 1 else -1, -1, out_block[1] if in_block[1] == 1 else -1, -1)
+    xf = x.float()
+    want = ((xf + xf).to(torch.bfloat16).float() + src.reshape(out_block[0] * 32, out_block[1] * 32)).to(torch.bfloat16)
+    out = ttnn.from_torch(torch.zeros_like(x))
+    ttl_b200.set_hardware_broadcast(True)
+    try:
+        mods["eltwise"].make_hw_broadcast(dims, in_block, out_block)(ttnn.from_torch(x), ttnn.from_torch(b), out)
+    finally:
+        ttl_b200.set_hardware_broadcast(False)
+    assert torch.equal(ttnn.to_torch(out), want)

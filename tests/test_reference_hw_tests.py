@@ -21,6 +21,8 @@ EXPECTED = {
     "test_adversarial_multicore.py": 1,
     "test_axby.py": 1,
     "test_bcast_multicore.py": 1,
+    "test_bcast_ops.py": 15,
+    "test_bcast_shape_expansion.py": 6,
     "test_comprehensive_multicore.py": 1,
     "test_dst_multi_consumer.py": 5,
     "test_elementwise_ops.py": 13,

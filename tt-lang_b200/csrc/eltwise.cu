@@ -44,17 +44,19 @@ struct Elem<false> {
 template <bool BF16>
 __device__ __forceinline__ uint4 load_operand(const ttlb_operand &o, long long gi, long long gj) {
   using T = typename Elem<BF16>::T;
-  long long r = o.row_mode == TTLB_IDX_SAME   ? gi + o.row_off
-                : o.row_mode == TTLB_IDX_ZERO ? 0
-                                              : o.row_off + (gi & 31);
+  long long r = o.row_mode == TTLB_IDX_SAME    ? gi + o.row_off
+                : o.row_mode == TTLB_IDX_ZERO  ? o.row_off
+                : o.row_mode == TTLB_IDX_FIRST ? o.row_off + (gi & ~31LL)
+                                               : o.row_off + (gi & 31);
   const T *rowp = reinterpret_cast<const T *>(o.ptr) + r * o.ld;
-  if (o.col_mode == TTLB_IDX_ZERO) {
+  if (o.col_mode == TTLB_IDX_ZERO || o.col_mode == TTLB_IDX_FIRST) {   // one element for the whole vector
+    const T *ep = rowp + (o.col_mode == TTLB_IDX_ZERO ? o.col_off : o.col_off + (gj & ~31LL));
     if constexpr (BF16) {
-      unsigned h = *reinterpret_cast<const unsigned short *>(rowp);
+      unsigned h = *reinterpret_cast<const unsigned short *>(ep);
       unsigned hh = h | (h << 16);
       return make_uint4(hh, hh, hh, hh);
     } else {
-      unsigned w = *reinterpret_cast<const unsigned *>(rowp);
+      unsigned w = *reinterpret_cast<const unsigned *>(ep);
       return make_uint4(w, w, w, w);
     }
   }
@@ -220,9 +222,9 @@ static int validate_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d) {
   for (int k = 0; k < d->n_in; ++k) {
     const ttlb_operand &o = d->in[k];
     if (!o.ptr) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: input %d is null", k);
-    if (o.row_mode < 0 || o.row_mode > 2 || o.col_mode < 0 || o.col_mode > 2)
+    if (o.row_mode < 0 || o.row_mode > 3 || o.col_mode < 0 || o.col_mode > 3)
       return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: input %d has a bad index mode", k);
-    if (o.col_mode != TTLB_IDX_ZERO) {
+    if (o.col_mode == TTLB_IDX_SAME || o.col_mode == TTLB_IDX_TILE) {
       if ((o.ld % vec) || (o.col_off % vec) || ((uintptr_t)o.ptr % 16))
         return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: input %d is not 16-byte aligned", k);
     } else if ((uintptr_t)o.ptr % esz) {
@@ -232,8 +234,11 @@ static int validate_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d) {
       return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: input %d row offset underflows", k);
     if (o.col_mode == TTLB_IDX_SAME && d->col0 + o.col_off < 0)
       return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: input %d col offset underflows", k);
-    if ((o.row_mode == TTLB_IDX_TILE && o.row_off < 0) || (o.col_mode == TTLB_IDX_TILE && o.col_off < 0))
+    if ((o.row_mode == TTLB_IDX_TILE && o.row_off < 0) || (o.col_mode == TTLB_IDX_TILE && o.col_off < 0) ||
+        (o.row_mode == TTLB_IDX_ZERO && o.row_off < 0) || (o.col_mode == TTLB_IDX_ZERO && o.col_off < 0))
       return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: input %d tile offset is negative", k);
+    if ((o.row_mode == TTLB_IDX_FIRST && d->row0 + o.row_off < 0) || (o.col_mode == TTLB_IDX_FIRST && d->col0 + o.col_off < 0))
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: input %d tile offset underflows", k);
   }
   // Walk the program once: operand indices in range, stack never under/overflows,
   // first instruction defines the accumulator.

@@ -139,12 +139,16 @@ void emit_load(std::ostringstream &s, const ttlb_eltwise_desc *d, int k, bool bf
                const std::string &var, const std::string &gi) {
   const ttlb_operand &o = d->in[k];
   const int esz = bf16 ? 2 : 4;
-  std::string row = o.row_mode == TTLB_IDX_SAME   ? "(" + gi + " + p.roff[" + std::to_string(k) + "])"
-                    : o.row_mode == TTLB_IDX_ZERO ? std::string("0")
-                                                  : "(p.roff[" + std::to_string(k) + "] + (" + gi + " & 31))";
+  const std::string ks = std::to_string(k);
+  std::string row = o.row_mode == TTLB_IDX_SAME    ? "(" + gi + " + p.roff[" + ks + "])"
+                    : o.row_mode == TTLB_IDX_ZERO  ? "p.roff[" + ks + "]"
+                    : o.row_mode == TTLB_IDX_FIRST ? "(p.roff[" + ks + "] + (" + gi + " & ~31LL))"
+                                                   : "(p.roff[" + ks + "] + (" + gi + " & 31))";
   s << indent << "{ const char* rp = (const char*)p.in[" << k << "] + " << row << " * p.ld[" << k << "] * " << esz
     << ";\n";
-  if (o.col_mode == TTLB_IDX_ZERO) {
+  if (o.col_mode == TTLB_IDX_ZERO || o.col_mode == TTLB_IDX_FIRST) {   // one element for the whole vector
+    const std::string ec = o.col_mode == TTLB_IDX_ZERO ? "p.coff[" + ks + "]" : "(p.coff[" + ks + "] + (gj & ~31LL))";
+    s << indent << "  rp += " << ec << " * " << esz << ";\n";
     if (bf16)
       s << indent << "  u32 h = *(const unsigned short*)rp; h |= h << 16; " << var << " = make_uint4(h, h, h, h); }\n";
     else

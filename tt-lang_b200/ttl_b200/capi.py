@@ -21,7 +21,7 @@ TTLB_ERR_NCCL = -5
 
 TTLB_BF16, TTLB_F32, TTLB_BFP8_B = 0, 1, 2
 TTLB_MAX_IN, TTLB_MAX_OPS, TTLB_ARG_STACK = 6, 32, -1
-IDX_SAME, IDX_ZERO, IDX_TILE = 0, 1, 2
+IDX_SAME, IDX_ZERO, IDX_TILE, IDX_FIRST = 0, 1, 2, 3
 
 OPCODES = {
     "load": 0, "add": 1, "sub": 2, "rsub": 3, "mul": 4, "div": 5, "rdiv": 6, "max": 7, "min": 8,

@@ -12,24 +12,55 @@ from __future__ import annotations
 
 from typing import Any, List, Optional
 
-from .trace import Block, _as_block
+from .trace import Block, Leaf, _as_block
 
 
-def broadcast(block: Any, _unused_arg: Optional[Any] = None, dims: Optional[List[int]] = None) -> Block:
+# Which meaning `broadcast` has on FULL (non-degenerate) tiles.  The two reference front ends disagree:
+# the simulator returns the block unchanged and lets the consuming op repeat the whole tile over the
+# tile grid (python/sim/math.py:62-80); the compiler lowers to ttl.bcast, which spreads the tile's first
+# row / column / element over the tile (TTLOps.td:570-597, test/python/test_bcast_ops.py:31-55).
+# The simulator is the oracle, so its meaning is the default; on degenerate tensors ([1,N], [N,1],
+# [1,1]) the two agree.
+_hardware_broadcast = False
+
+
+def set_hardware_broadcast(enabled: bool) -> None:
+    """Give `ttl.math.broadcast` the compiler's (hardware) meaning on full tiles instead of the simulator's."""
+    global _hardware_broadcast
+    _hardware_broadcast = bool(enabled)
+
+
+def broadcast(block: Any, out_block: Optional[Any] = None, dims: Optional[List[int]] = None) -> Block:
     if dims is None:
         raise ValueError("dims parameter is required for broadcast()")
     b = _as_block(block)
     shape = b.shape
+    v = b.value()
     for dim in dims:
         if dim >= len(shape):
             raise ValueError(
                 f"Cannot broadcast along dimension {dim}: block has shape {shape} "
                 f"with only {len(shape)} dimensions")
+    if _hardware_broadcast and isinstance(v, Leaf) and any(v.tensor.shape[dim] != 1 for dim in dims):
+        # hardware convention (compiler form `broadcast(inp, out_blk, dims=[..])`, ttl.bcast Row / Col / Scalar,
+        # python/ttl/operators.py:332-360, test/python/test_bcast_ops.py:31-55): FULL tiles whose first row
+        # (dims=[0]) / first column (dims=[1]) / element [0,0] carries the data; every tile of the block is
+        # broadcast within itself, and a block dim of one tile expands to the output block's
+        first = (0 in dims and v.tensor.shape[0] != 1, 1 in dims and v.tensor.shape[1] != 1)
+        out_shape = shape
+        if out_block is not None:
+            out_shape = _as_block(out_block).shape
+            for d in (0, 1):
+                if shape[d] != out_shape[d] and shape[d] != 1:
+                    raise ValueError(f"Cannot broadcast block of shape {shape} to output block of shape {out_shape}")
+        leaf = Leaf(v.tensor, v.r0, v.r1, v.c0, v.c1, first)
+        return Block(out_shape, b.dtype, leaf, "FULL", "temp", temporary=True)
+    for dim in dims:
         if shape[dim] != 1:
             raise ValueError(
                 f"Cannot broadcast along dimension {dim}: dimension must have size 1, "
                 f"but has size {shape[dim]}")
-    return Block(shape, b.dtype, b.value(), "FULL", "temp", temporary=True)
+    return Block(shape, b.dtype, v, "FULL", "temp", temporary=True)
 
 
 def _unary(name: str):

@@ -108,15 +108,16 @@ def _classify(leaf: Leaf, w: Write) -> Tuple[int, int, int, int]:
     trows, tcols = t.shape
     tt = t.tile_shape()
     res = []
-    for (lo, hi, wlo, whi, n_elem, n_tiles) in (
-            (leaf.r0, leaf.r1, w.r0, w.r1, trows, tt[0]),
-            (leaf.c0, leaf.c1, w.c0, w.c1, tcols, tt[1])):
+    for (lo, hi, wlo, whi, n_elem, n_tiles, first) in (
+            (leaf.r0, leaf.r1, w.r0, w.r1, trows, tt[0], leaf.first[0]),
+            (leaf.c0, leaf.c1, w.c0, w.c1, tcols, tt[1], leaf.first[1])):
         if n_elem == 1:
             res += [capi.IDX_ZERO, 0]
         elif n_tiles == 1 or (hi - lo == 1 and whi - wlo > 1):
-            res += [capi.IDX_TILE, lo * TILE]
+            # one tile repeated over the region; with `first`, its row / column 0 only
+            res += [capi.IDX_ZERO if first else capi.IDX_TILE, lo * TILE]
         elif hi - lo == whi - wlo:
-            res += [capi.IDX_SAME, (lo - wlo) * TILE]
+            res += [capi.IDX_FIRST if first else capi.IDX_SAME, (lo - wlo) * TILE]
         else:
             raise Unsupported(f"operand region {hi - lo} tiles does not line up with output region {whi - wlo} tiles")
     return res[0], res[1], res[2], res[3]

@@ -47,12 +47,15 @@ class Expr:
 
 
 class Leaf(Expr):
-    """Tile region [r0:r1, c0:c1] (tile coordinates) of input tensor `tensor`."""
+    """Tile region [r0:r1, c0:c1] (tile coordinates) of input tensor `tensor`.  `first[d]` set: along
+    dim d every element reads element 0 of its tile (the hardware broadcast of a full tile whose first
+    row / column carries the data, `ttl.math.broadcast` on non-degenerate tiles)."""
 
-    __slots__ = ("tensor", "r0", "r1", "c0", "c1")
+    __slots__ = ("tensor", "r0", "r1", "c0", "c1", "first")
 
-    def __init__(self, tensor: "_ttnn.Tensor", r0: int, r1: int, c0: int, c1: int):
-        self.tensor, self.r0, self.r1, self.c0, self.c1 = tensor, r0, r1, c0, c1
+    def __init__(self, tensor: "_ttnn.Tensor", r0: int, r1: int, c0: int, c1: int,
+                 first: Tuple[bool, bool] = (False, False)):
+        self.tensor, self.r0, self.r1, self.c0, self.c1, self.first = tensor, r0, r1, c0, c1, first
         self.shape = (r1 - r0, c1 - c0)
 
 
