@@ -419,6 +419,91 @@ def run_sharded(args):
         dist.destroy_process_group()
 
 
+def run_add_1024(args) -> None:
+    """configs[0]: C = A + B on bf16 [1024, 1024] (the reference's own CPU-runnable case), one GPU.
+    6.3 MB of traffic: the launch is latency-bound, so the line reports time and GB/s without a
+    roofline claim.  The operands fit in L2, so a buffer larger than L2 is written between iterations
+    and each iteration is timed on its own."""
+    import importlib.util
+
+    import torch
+
+    import ttl_b200
+
+    ttl_b200.install()
+    import ttnn
+
+    from ttl_b200 import capi
+
+    torch.cuda.set_device(0)
+    spec = importlib.util.spec_from_file_location("bench_programs_eltwise", ROOT / "tests" / "programs" / "eltwise.py")
+    programs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(programs)
+    n = 1024
+    host = [torch.randn(n, n, generator=torch.Generator().manual_seed(s)).to(torch.bfloat16).pin_memory() for s in (0, 1)]
+    dev = [ttnn.from_torch(t) for t in host]
+    out = ttnn.empty((n, n), dtype=ttnn.bfloat16)
+    plan = programs.eltwise_add.plan(*dev, out)
+    assert len(plan.launches) == 1, plan.describe()
+    desc = plan.launches[0].desc(dev + [out])
+    ctx = capi.context(0)
+    stream = capi.current_stream()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    algo = 3 * n * n * 2
+    for _ in range(args.warmup):
+        ctx.eltwise(desc, stream)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    sampler.start()
+    l0 = ctx.launch_count()
+    times = []
+    for _ in range(args.steps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ctx.eltwise(desc, stream)
+        e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1))
+    launches = ctx.launch_count() - l0
+    clocks = sampler.stop()
+    ms = sorted(times)[len(times) // 2]
+    assert torch.equal(ttnn.to_torch(out), host[0] + host[1]), "C = A + B is not bit-exact"
+    host_out = torch.empty((n, n), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        tensors = [ttnn.from_torch(t) for t in host]
+        y = ttnn.empty((n, n), dtype=ttnn.bfloat16)
+        programs.eltwise_add(*tensors, y)
+        ttnn.to_torch(y, out=host_out)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    f1.record()
+    torch.cuda.synchronize()
+    e2e_ms = f0.elapsed_time(f1) / args.e2e_steps
+    peak, peak_src = measured_peak_hbm()
+    gbs = algo / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "eltwise HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "eltwise_add_1024: C = A + B, bf16 [1024,1024], N(0,1) seeds 0/1, bf16 rounding, bit-exact "
+                               "result checked in this run",
+                   "l2": "256 MB written between iterations (operands fit in L2); median of per-iteration CUDA-event times",
+                   "algorithmic_bytes_per_step": algo},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                     "peak_source": peak_src, "kernel": "ttlb_eltwise_jit",
+                     "note": "6.3 MB per launch: launch-latency bound, no bandwidth claim"},
+        "e2e": {"value": algo / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 2 * n * n * 2,
+                "d2h_bytes_per_step": n * n * 2, "ms_per_step": e2e_ms, "steps": args.e2e_steps},
+        "gpu_launches": launches, "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -449,6 +534,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: the backend has no CPU fallback")
+    if args.workload == "eltwise_add_1024":
+        run_add_1024(args)
+        return
     if args.workload != "fused_eltwise_bcast_8192":
         run_sharded(args)
         return
