@@ -285,32 +285,52 @@ def run_sharded(args):
                 # compute into the local copy, then one kernel re-sends the shard through the switch
                 # (multimem.st, coalesced): 1x outgoing traffic instead of (world-1)x
                 esz = 2
+                # run_chunk(x, u0, u1) computes units [u0, u1) of this rank's shard (rows / heads) in place
                 if wl == "matmul_bf16_8192":
                     ml = n // world
                     a_contig = a[rank * ml:(rank + 1) * ml].contiguous().to(dev)
                     mine_view = so.buf[rank * ml:(rank + 1) * ml]
-                    run_local = lambda x: ops.matmul(T(a_contig), T(x[1]), out=T(mine_view))  # noqa: E731
+                    units = ml
+                    run_chunk = lambda x, u0, u1: ops.matmul(T(a_contig[u0:u1]), T(x[1]), out=T(mine_view[u0:u1]))  # noqa: E731
                 elif wl == "matmul_bfp8w":
                     nl = c0 * 32
                     mine_view = so.buf[:, rank * nl:(rank + 1) * nl]
-                    run_local = lambda xs: ops.launch_gemm(ctx, T(xs[0]), W, T(mine_view), (0, m, 0, nl),  # noqa: E731
-                                                           capi.current_stream())
+                    units = m
+                    run_chunk = lambda xs, u0, u1: ops.launch_gemm(ctx, T(xs[0]), W, T(mine_view), (u0, u1, 0, nl),  # noqa: E731
+                                                                   capi.current_stream())
                 else:
                     ul = (B * H) // world
                     mine_view = so.buf[rank * ul:(rank + 1) * ul]
                     host_in = [cases.gen((ul * S, D), "normal", sd + 10 * rank).reshape(ul, S, D).pin_memory() for sd in (0, 1, 2)]
                     dev_in = [t.to(dev) for t in host_in]
-                    run_local = lambda x: ops.attention(T(x[0]), T(x[1]), T(x[2]), causal=True, scale=D ** -0.5,  # noqa: E731
-                                                        out=T(mine_view))
+                    units = ul
+                    run_chunk = lambda x, u0, u1: ops.attention(T(x[0][u0:u1]), T(x[1][u0:u1]), T(x[2][u0:u1]),  # noqa: E731
+                                                                causal=True, scale=D ** -0.5, out=T(mine_view[u0:u1]))
                 v2 = mine_view if mine_view.dim() == 2 else mine_view.reshape(mine_view.shape[0], -1)
-                rows_, row_bytes_, ld_bytes_ = v2.shape[0], v2.shape[1] * esz, v2.stride(0) * esz
+                row_bytes_, ld_bytes_ = v2.shape[1] * esz, v2.stride(0) * esz
+                rounds = max(1, min(args.mc_rounds, units // 256 if wl != "attention" else units))
+                while units % rounds:
+                    rounds -= 1
+                side = torch.cuda.Stream()
 
                 def step(x):
-                    run_local(x)
-                    ctx.multimem_bcast(mine_view.data_ptr(), ld_bytes_, so.multicast_ptr_of(mine_view), ld_bytes_, rows_,
-                                       row_bytes_, capi.current_stream())
+                    # the re-send of round r (a light kernel next to the persistent compute CTAs) runs on a side
+                    # stream under the compute of round r + 1
+                    main = torch.cuda.current_stream()
+                    per = units // rounds
+                    for r in range(rounds):
+                        u0, u1 = r * per, (r + 1) * per
+                        run_chunk(x, u0, u1)
+                        ev = torch.cuda.Event()
+                        ev.record(main)
+                        side.wait_event(ev)
+                        with torch.cuda.stream(side):
+                            ctx.multimem_bcast(v2[u0:u1].data_ptr(), ld_bytes_, so.multicast_ptr_of(v2[u0:u1]), ld_bytes_,
+                                               u1 - u0, row_bytes_, capi.current_stream())
+                    main.wait_stream(side)
                     return so.barrier()
-                gather = "local compute, then the shard is re-sent once through the NVSwitch (multimem.st kernel), barrier"
+                gather = (f"local compute in {rounds} round(s); each round's part of the shard is re-sent once through the "
+                          "NVSwitch (multimem.st kernel) under the next round's compute; barrier")
             elif args.gather == "fused" and so.has_multicast and wl != "attention":
                 # publication fused into the GEMM epilogue: every tile is stored once with multimem.st and
                 # the NVSwitch delivers it to all ranks; one launch per rank, then a cross-rank barrier
@@ -517,6 +537,8 @@ def main():
     ap.add_argument("--eltwise-mode", default="auto", choices=["auto", "generic", "specialised"])
     ap.add_argument("--gemm-variant", type=int, default=1, choices=[0, 1, 2],
                     help="tensor-core GEMM kernel: 0 one CTA per 128x256 tile, 1 two-CTA clusters per 256x256 tile for large outputs, 2 two-CTA always")
+    ap.add_argument("--mc-rounds", type=int, default=2,
+                    help="multicast gather: rounds the local shard is computed and re-sent in")
     ap.add_argument("--bfp8-mode", type=int, default=None, choices=[0, 1, 2],
                     help="bfp8 weights: 0 unpack kernel + GEMM, 1 unpack inside the GEMM mainloop for large outputs, 2 always inside")
     ap.add_argument("--gather", default="auto", choices=["auto", "p2p", "multicast", "fused", "nccl"],
