@@ -208,6 +208,8 @@ def run_sharded(args):
     ctx.set_gemm_variant(args.gemm_variant)
     if args.bfp8_mode is not None:
         ctx.set_bfp8_mode(args.bfp8_mode)
+    if args.bfp8_chunks is not None:
+        ctx.set_bfp8_chunks(args.bfp8_chunks)
     T = ttnn.Tensor
     wl = args.workload
     dev = torch.device("cuda", local)
@@ -537,6 +539,8 @@ def main():
     ap.add_argument("--eltwise-mode", default="auto", choices=["auto", "generic", "specialised"])
     ap.add_argument("--gemm-variant", type=int, default=1, choices=[0, 1, 2],
                     help="tensor-core GEMM kernel: 0 one CTA per 128x256 tile, 1 two-CTA clusters per 256x256 tile for large outputs, 2 two-CTA always")
+    ap.add_argument("--bfp8-chunks", type=int, default=None, choices=[1, 2, 3, 4],
+                    help="bfp8 weights, two-step path: column chunks whose expansion overlaps the previous chunk's GEMM")
     ap.add_argument("--mc-rounds", type=int, default=1,
                     help="multicast gather: rounds the local shard is computed and re-sent in (2 rounds measured on 2 GPUs: "
                          "matmul 0.527 vs 0.541 ms, attention 0.994 vs 1.010 ms, bfp8 matmul 1.110 vs 1.052 ms)")

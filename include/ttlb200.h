@@ -326,6 +326,12 @@ TTLB_EXPORT int ttlb_set_gemm_variant(ttlb_ctx *ctx, int variant);
  *      one 256x256 tile per SM pair, mode 0 otherwise
  *   2  inside the mainloop for every shape (testing) */
 TTLB_EXPORT int ttlb_set_bfp8_mode(ttlb_ctx *ctx, int mode);
+/* Mode 0 can work in up to `chunks` (1..4) column chunks: the expansion of chunk i+1 runs on a stream owned
+ * by the context under the GEMM of chunk i; both are ordered against `stream` by events and the side stream
+ * has joined again when ttlb_matmul_bfp8w returns.  Default 1 (expand everything, then one GEMM): on
+ * 4096x8192x28672 the overlap measured 1.395 ms with 2 or 4 chunks against 1.365 ms with 1 - the GEMM runs
+ * at the power cap, so work moved under it is not free, and smaller GEMMs have longer tails. */
+TTLB_EXPORT int ttlb_set_bfp8_chunks(ttlb_ctx *ctx, int chunks);
 
 /* Kernels that wait on hardware barriers (matmul, attention) bound every wait; when
  * one runs out the kernel unwinds normally and records which role gave up.

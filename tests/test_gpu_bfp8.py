@@ -99,3 +99,31 @@ def test_config4_shard_slab(bfp8_mode):
     assert rel_err(got[:256], tile_oracle.matmul_tiles(x[:256].float(), wq, "f32")) <= 1e-2
     got2 = ttnn.to_torch(ops.matmul(ttnn.from_torch(x * 2), W))
     assert torch.equal(got2, got * 2)
+
+
+def test_chunked_expansion_overlapping_the_gemm_gives_the_same_bits():
+    """The two-step path can expand the weights in column chunks on a side stream under the GEMM of the
+    previous chunk (ttlb_set_bfp8_chunks).  Same kernels, so the result must equal the unchunked one bit for bit - also on a second
+    call that reuses the scratch buffer while the first may still be running, and with a different matrix."""
+    from ttl_b200 import capi, ops, ttnn
+    m, k, n = 4096, 256, 8192
+    x = cases.gen((m, k), "normal", 20)
+    ctx = capi.context()
+    ctx.set_bfp8_mode(0)
+    outs = {}
+    for seed in (21, 22):
+        w = cases.gen((k, n), "normal*0.02", seed, torch.float32)
+        W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+        X = ttnn.from_torch(x)
+        for chunks in (4, 1):
+            ctx.set_bfp8_chunks(chunks)
+            a = ops.matmul(X, W)
+            b = ops.matmul(X, W)          # back to back on the same stream
+            outs[(seed, chunks)] = (ttnn.to_torch(a), ttnn.to_torch(b))
+        ctx.set_bfp8_chunks(1)
+        capi.context().check_status(capi.current_stream())
+        assert torch.equal(outs[(seed, 4)][0], outs[(seed, 1)][0])
+        assert torch.equal(outs[(seed, 4)][1], outs[(seed, 1)][0])
+        wq = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))
+        assert rel_err(outs[(seed, 4)][0][:256], tile_oracle.matmul_tiles(x[:256].float(), wq, "f32")) <= 1e-2
+    assert not torch.equal(outs[(21, 4)][0], outs[(22, 4)][0])

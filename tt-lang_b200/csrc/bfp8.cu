@@ -194,10 +194,54 @@ static int matmul_bfp8w_impl(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, bool m
     TTLB_CUDA_CHECK(ctx, cudaMalloc(&ctx->scratch, need));
     ctx->scratch_bytes = need;
   }
-  rc = launch_unpack(ctx, reinterpret_cast<const uint8_t *>(d->b_tiles), d->b_tile_cols, d->b_tile_col0, d->k / 32,
-                     d->n / 32, ctx->scratch, d->n, s);
-  if (rc) return rc;
-  return ttlb_launch_gemm_bf16_ex(ctx, d->a, d->lda, ctx->scratch, d->n, d->c, d->ldc, d->m, d->n, d->k, multicast, s);
+  // Column chunks: the expansion of chunk i+1 (HBM-bound, on a side stream) runs under the GEMM of chunk i
+  // (tensor-bound, on the caller's stream).  Events order them: fork from the caller's stream, one event per
+  // expanded chunk, every side-stream kernel is waited for by a GEMM, so the side stream has joined again when
+  // the call returns.  Chunks are multiples of 256 columns and large enough to keep the two-CTA GEMM.
+  int chunks = 1;
+  if (!multicast && ctx->bfp8_chunks > 1) {
+    for (int c = ctx->bfp8_chunks > 4 ? 4 : ctx->bfp8_chunks; c > 1; --c)
+      if (d->n % (256 * c) == 0 && ((d->m + 255) / 256) * (d->n / c / 256) >= ctx->sm_count / 2) {
+        chunks = c;
+        break;
+      }
+  }
+  const uint8_t *tiles = reinterpret_cast<const uint8_t *>(d->b_tiles);
+  if (chunks == 1) {
+    rc = launch_unpack(ctx, tiles, d->b_tile_cols, d->b_tile_col0, d->k / 32, d->n / 32, ctx->scratch, d->n, s);
+    if (rc) return rc;
+    return ttlb_launch_gemm_bf16_ex(ctx, d->a, d->lda, ctx->scratch, d->n, d->c, d->ldc, d->m, d->n, d->k, multicast, s);
+  }
+  if (!ctx->side_stream) {
+    TTLB_CUDA_CHECK(ctx, cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking));
+    TTLB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming));
+    for (cudaEvent_t &e : ctx->ev_chunk) TTLB_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  }
+  const int64_t nc = d->n / chunks;   // columns per chunk
+  __nv_bfloat16 *wb = reinterpret_cast<__nv_bfloat16 *>(ctx->scratch);
+  // the side stream starts after everything already queued on the caller's stream (earlier users of the
+  // scratch buffer included)
+  TTLB_CUDA_CHECK(ctx, cudaEventRecord(ctx->ev_fork, s));
+  TTLB_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->ev_fork, 0));
+  for (int i = 0; i < chunks; ++i) {
+    rc = launch_unpack(ctx, tiles, d->b_tile_cols, d->b_tile_col0 + i * (nc / 32), d->k / 32, nc / 32, wb + i * nc, d->n,
+                       ctx->side_stream);
+    if (rc) return rc;
+    TTLB_CUDA_CHECK(ctx, cudaEventRecord(ctx->ev_chunk[i], ctx->side_stream));
+  }
+  for (int i = 0; i < chunks; ++i) {
+    TTLB_CUDA_CHECK(ctx, cudaStreamWaitEvent(s, ctx->ev_chunk[i], 0));
+    rc = ttlb_launch_gemm_bf16_ex(ctx, d->a, d->lda, wb + i * nc, d->n,
+                                  reinterpret_cast<__nv_bfloat16 *>(d->c) + i * nc, d->ldc, d->m, nc, d->k, false, s);
+    if (rc) return rc;
+  }
+  return TTLB_OK;
+}
+
+extern "C" int ttlb_set_bfp8_chunks(ttlb_ctx *ctx, int chunks) {
+  if (!ctx || chunks < 1 || chunks > 4) return TTLB_ERR_INVALID_ARG;
+  ctx->bfp8_chunks = chunks;
+  return TTLB_OK;
 }
 
 extern "C" int ttlb_set_bfp8_mode(ttlb_ctx *ctx, int mode) {

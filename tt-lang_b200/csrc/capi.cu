@@ -41,6 +41,10 @@ void ttlb_destroy(ttlb_ctx *ctx) {
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
+    if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
+    for (cudaEvent_t e : ctx->ev_chunk)
+      if (e) cudaEventDestroy(e);
     ttlb_jit_cache_destroy(ctx->jit);
   }
   delete ctx;

@@ -38,6 +38,11 @@ struct ttlb_ctx {
   // Scratch in HBM owned by the context (bf16 expansion of bfloat8_b weights); grows on demand.
   void *scratch = nullptr;
   size_t scratch_bytes = 0;
+  // bfp8-weight matmul: the weight expansion of column chunk i+1 runs on this stream under the GEMM of chunk i
+  cudaStream_t side_stream = nullptr;
+  cudaEvent_t ev_fork = nullptr;
+  cudaEvent_t ev_chunk[4] = {nullptr, nullptr, nullptr, nullptr};
+  int bfp8_chunks = 1;  // column chunks of the two-step bfp8 path (1: no overlap; measured: overlap gains nothing)
 };
 
 inline int ttlb_fail(ttlb_ctx *ctx, int code, const char *fmt, ...) {

@@ -151,6 +151,8 @@ def lib() -> C.CDLL:
     l.ttlb_selftest_wait_timeout.restype = C.c_int
     l.ttlb_set_gemm_variant.argtypes = [C.c_void_p, C.c_int]
     l.ttlb_set_gemm_variant.restype = C.c_int
+    l.ttlb_set_bfp8_chunks.argtypes = [C.c_void_p, C.c_int]
+    l.ttlb_set_bfp8_chunks.restype = C.c_int
     l.ttlb_set_bfp8_mode.argtypes = [C.c_void_p, C.c_int]
     l.ttlb_set_bfp8_mode.restype = C.c_int
     l.ttlb_set_wait_limit.argtypes = [C.c_void_p, C.c_int64]
@@ -226,6 +228,10 @@ class Context:
     def set_gemm_variant(self, variant: int) -> None:
         """0: one-CTA 128x256 tiles; 1 (default): two-CTA 256x256 tiles for large outputs; 2: two-CTA always."""
         self.check(self._lib.ttlb_set_gemm_variant(self.handle, variant))
+
+    def set_bfp8_chunks(self, chunks: int) -> None:
+        """Column chunks (1..4) of the two-step bfp8 matmul: expansion of chunk i+1 under the GEMM of chunk i."""
+        self.check(self._lib.ttlb_set_bfp8_chunks(self.handle, chunks))
 
     def set_bfp8_mode(self, mode: int) -> None:
         """0: unpack kernel + GEMM; 1: unpack inside the GEMM mainloop for large outputs; 2: always inside."""
