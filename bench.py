@@ -526,6 +526,94 @@ def run_add_1024(args) -> None:
         "gpu_launches": launches, "clocks": clocks}))
 
 
+def run_reduce_8192(args) -> None:
+    """`ttl.math.reduce_sum / reduce_max` over a bf16 [8192, 8192] tensor (--workload reduce_<sum|max>_<rows|cols|all>_8192),
+    one GPU.  HBM-bound: 134 MB read per launch; two input tensors are used in turn so that no launch finds
+    its input in L2.  The result is checked against a float64 reduction in the same run."""
+    import importlib.util
+
+    import torch
+
+    import ttl_b200
+
+    ttl_b200.install()
+    import ttnn
+
+    from ttl_b200 import capi
+
+    _, op, which, _n = args.workload.split("_")
+    dims = {"rows": [0], "cols": [1], "all": [0, 1]}[which]
+    torch.cuda.set_device(0)
+    spec = importlib.util.spec_from_file_location("bench_programs_reduce", ROOT / "tests" / "programs" / "reduce.py")
+    programs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(programs)
+    n = 8192
+    host = [torch.randn(n, n, generator=torch.Generator().manual_seed(s)).to(torch.bfloat16).pin_memory() for s in (0, 1)]
+    dev = [ttnn.from_torch(t) for t in host]
+    scaler = ttnn.from_torch(torch.ones(32, 32, dtype=torch.bfloat16))
+    out_shape = (1 if 0 in dims else n, 1 if 1 in dims else n)
+    out = ttnn.empty(out_shape, dtype=ttnn.bfloat16)
+    prog = programs.make_reduce(op, dims)
+    plan = prog.plan(dev[0], scaler, out)
+    assert len(plan.launches) == 1, plan.describe()
+    descs = [plan.launches[0].desc([d, scaler, out]) for d in dev]
+    ctx = capi.context(0)
+    stream = capi.current_stream()
+    algo = n * n * 2 + out_shape[0] * out_shape[1] * 2
+    for i in range(args.warmup):
+        ctx.reduce(descs[i % 2], stream)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    sampler.start()
+    l0 = ctx.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        ctx.reduce(descs[i % 2], stream)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = ctx.launch_count() - l0
+    clocks = sampler.stop()
+    last = host[(args.steps - 1) % 2].double()
+    ref = last.sum(dim=dims, keepdim=True) if op == "sum" else last.amax(dim=dims, keepdim=True)
+    got = ttnn.to_torch(out).double()
+    tol = 2.0 ** -8 * ref.abs().max().item() + (0.0 if op == "max" else 1e-3 * n)
+    assert (got - ref).abs().max().item() <= tol, "reduction result is wrong"
+    host_out = torch.empty(out_shape, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(i):
+        x = ttnn.from_torch(host[i % 2])
+        y = ttnn.empty(out_shape, dtype=ttnn.bfloat16)
+        prog(x, scaler, y)
+        ttnn.to_torch(y, out=host_out)
+
+    e2e_step(0)
+    torch.cuda.synchronize()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for i in range(args.e2e_steps):
+        e2e_step(i)
+    f1.record()
+    torch.cuda.synchronize()
+    e2e_ms = f0.elapsed_time(f1) / args.e2e_steps
+    peak, peak_src = measured_peak_hbm()
+    gbs = algo / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "eltwise HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"{args.workload}: reduce_{op}(A, s, dims={dims}), A bf16 [8192,8192] N(0,1), fp32 combine, "
+                               "one bf16 rounding; result checked against a float64 reduction in this run",
+                   "l2": "two 134 MB inputs used in turn (each larger than L2)", "algorithmic_bytes_per_step": algo},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                     "peak_source": peak_src, "kernel": "ttlb_reduce_jit",
+                     "note": "peak is a copy (read + write); this kernel only reads"},
+        "e2e": {"value": algo / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": n * n * 2,
+                "d2h_bytes_per_step": out_shape[0] * out_shape[1] * 2, "ms_per_step": e2e_ms, "steps": args.e2e_steps},
+        "gpu_launches": launches, "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -561,6 +649,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: the backend has no CPU fallback")
+    if args.workload.startswith("reduce_"):
+        run_reduce_8192(args)
+        return
     if args.workload == "eltwise_add_1024":
         run_add_1024(args)
         return

@@ -181,6 +181,46 @@ TTLB_EXPORT int ttlb_eltwise_last_path(ttlb_ctx *ctx);
 TTLB_EXPORT int64_t ttlb_eltwise_source(const ttlb_eltwise_desc *desc, char *buf, size_t len);
 
 /* ------------------------------------------------------------------------ *
+ * Reductions: `ttl.math.reduce_sum(expr, scaler, dims)` / `ttl.math.reduce_max(...)`.
+ *
+ * The functions are specified (docs/sphinx/specs/TTLangSpecification.md:750-755: "scaled sum /
+ * maximum reduction over specified dimensions", dims=[0] over rows, dims=[0,1] over rows and
+ * columns) but implemented by neither the reference compiler nor its simulator.  Meaning used
+ * here: the values of the element-wise program `src` over the rectangle
+ * [src.row0, +src.rows) x [src.col0, +src.cols) are combined in fp32 along the reduced
+ * dimension(s), the result is multiplied by the scaler and rounded once to `src.dtype`.
+ *   dims = ROWS          result[j]   = s * reduce_i value(i, j)   -> out[0 .. fill_rows) x [0 .. cols)
+ *   dims = COLS          result[i]   = s * reduce_j value(i, j)   -> out[0 .. rows) x [0 .. fill_cols)
+ *   dims = ROWS | COLS   result      = s * reduce_ij value(i, j)  -> out[0 .. fill_rows) x [0 .. fill_cols)
+ * Along a reduced dimension the result is written at index 0 and indices 1 .. fill-1 are set to
+ * zero: fill = 1 for a degenerate output ([1,N] row vector, [N,1] column, [1,1] scalar), fill = 32
+ * for an output of full tiles, which then has the layout ttl.math.broadcast expects of its source
+ * on hardware (data in the first row / column / element, test/python/test_bcast_ops.py:31-55).
+ * Sums are formed in a fixed order (the same inputs give the same bits on every launch).
+ * `src.out`, `src.out_ld` are ignored.  Partial results of a reduction over rows pass through
+ * scratch memory owned by the context (allocated on first use).
+ * ------------------------------------------------------------------------ */
+#define TTLB_REDUCE_SUM 0
+#define TTLB_REDUCE_MAX 1
+#define TTLB_REDUCE_ROWS 1 /* `dims` contains 0 */
+#define TTLB_REDUCE_COLS 2 /* `dims` contains 1 */
+
+typedef struct {
+  ttlb_eltwise_desc src; /* the values to reduce; cols and col0 multiples of 8 (bf16) or 4 (fp32) */
+  int32_t op;            /* TTLB_REDUCE_SUM / TTLB_REDUCE_MAX */
+  int32_t dims;          /* TTLB_REDUCE_ROWS, TTLB_REDUCE_COLS or both */
+  const void *scaler;    /* one element of src.dtype in device memory; NULL = 1.0 */
+  void *out;             /* where result element (0, 0) goes; src.dtype */
+  int64_t out_ld;        /* row pitch of the output in elements */
+  int32_t fill_rows, fill_cols; /* 1..32, see above (ignored along a dimension that is kept) */
+} ttlb_reduce_desc;
+
+TTLB_EXPORT int ttlb_reduce(ttlb_ctx *ctx, const ttlb_reduce_desc *desc, void *stream);
+/* CUDA source of the kernel specialised for `desc` (no GPU needed); same contract as
+ * ttlb_eltwise_source. */
+TTLB_EXPORT int64_t ttlb_reduce_source(const ttlb_reduce_desc *desc, char *buf, size_t len);
+
+/* ------------------------------------------------------------------------ *
  * Matmul tile programs: C[M,N] = A[M,K] x B[K,N], bf16 in, fp32 accumulate,
  * bf16 out, all row-major.
  *

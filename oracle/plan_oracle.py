@@ -36,17 +36,12 @@ def _index(mode: int, off: int, idx: torch.Tensor) -> torch.Tensor:
     return off + idx % TILE
 
 
-def run_eltwise(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
-    """Evaluate one element-wise launch into tensors[launch.out_index] (host tensors)."""
-    out = tensors[launch.out_index]
-    r0, r1, c0, c1 = launch.rect
-    rows = torch.arange(0, 1) if launch.out_degenerate[0] else torch.arange(r0 * TILE, r1 * TILE)
-    cols = torch.arange(0, 1) if launch.out_degenerate[1] else torch.arange(c0 * TILE, c1 * TILE)
-    bf16 = out.dtype == torch.bfloat16
-    rnd = bf16 and launch.round_each_op
+def _evaluate(inputs: Any, ops: Any, tensors: Sequence[torch.Tensor], rows: torch.Tensor, cols: torch.Tensor,
+              rnd: bool) -> torch.Tensor:
+    """The stack program of a launch on the index ranges `rows` x `cols`, as an fp32 matrix."""
 
     def operand(k: int) -> torch.Tensor:
-        ti, rm, ro, cm, co = launch.inputs[k]
+        ti, rm, ro, cm, co = inputs[k]
         x = tensors[ti]
         if x.dim() == 1:
             x = x.reshape(1, -1)
@@ -54,7 +49,7 @@ def run_eltwise(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
 
     acc = torch.zeros(len(rows), len(cols))
     stack: List[torch.Tensor] = []
-    for op, arg in launch.ops:
+    for op, arg in ops:
         if op == "push":
             stack.insert(0, acc)
             continue
@@ -65,8 +60,42 @@ def run_eltwise(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
             acc = _UNARY[op](acc)
         if rnd and op != "load":
             acc = acc.to(torch.bfloat16).to(torch.float32)
+    return acc
+
+
+def run_eltwise(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
+    """Evaluate one element-wise launch into tensors[launch.out_index] (host tensors)."""
+    out = tensors[launch.out_index]
+    r0, r1, c0, c1 = launch.rect
+    rows = torch.arange(0, 1) if launch.out_degenerate[0] else torch.arange(r0 * TILE, r1 * TILE)
+    cols = torch.arange(0, 1) if launch.out_degenerate[1] else torch.arange(c0 * TILE, c1 * TILE)
+    rnd = out.dtype == torch.bfloat16 and launch.round_each_op
+    acc = _evaluate(launch.inputs, launch.ops, tensors, rows, cols, rnd)
     view = out if out.dim() == 2 else out.reshape(1, -1)
     view[rows[0]:rows[-1] + 1, cols[0]:cols[-1] + 1] = acc.to(out.dtype)
+
+
+def run_reduce(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
+    """Evaluate one reduction launch (include/ttlb200.h, ttlb_reduce): values in fp32, combined along the
+    reduced dims, times the scaler, one rounding; the result sits at index 0 of a reduced dim and the rest
+    of a full result tile is zero."""
+    out = tensors[launch.out_index]
+    row0, nrows, col0, ncols = launch.region()
+    rnd = out.dtype == torch.bfloat16 and launch.round_each_op
+    vals = _evaluate(launch.inputs, launch.ops, tensors, torch.arange(row0, row0 + nrows),
+                     torch.arange(col0, col0 + ncols), rnd)
+    dims = list(launch.dims)
+    res = vals.sum(dim=dims, keepdim=True) if launch.op == "sum" else vals.amax(dim=dims, keepdim=True)
+    if launch.scaler is not None:
+        si, srow, scol = launch.scaler
+        res = res * tensors[si][srow, scol].to(torch.float32)
+    orow = 0 if out.shape[0] == 1 else launch.rect[0] * TILE
+    ocol = 0 if out.shape[1] == 1 else launch.rect[2] * TILE
+    fill_r = (1 if out.shape[0] == 1 else TILE) if 0 in dims else nrows
+    fill_c = (1 if out.shape[1] == 1 else TILE) if 1 in dims else ncols
+    block = torch.zeros(fill_r, fill_c)
+    block[:res.shape[0], :res.shape[1]] = res
+    out[orow:orow + fill_r, ocol:ocol + fill_c] = block.to(out.dtype)
 
 
 def run_gemm(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
@@ -79,4 +108,7 @@ def run_gemm(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
 
 def run_plan(plan: Any, tensors: Sequence[torch.Tensor]) -> None:
     for launch in plan.launches:
-        (run_eltwise if hasattr(launch, "ops") else run_gemm)(launch, tensors)
+        if hasattr(launch, "extent"):
+            run_reduce(launch, tensors)
+        else:
+            (run_eltwise if hasattr(launch, "ops") else run_gemm)(launch, tensors)

@@ -76,6 +76,31 @@ def eval_expression(expr: Sequence, inputs: Sequence[torch.Tensor], out_shape: T
     return ev(expr).to(dt).contiguous()
 
 
+def reduce_expression(expr: Sequence, inputs: Sequence[torch.Tensor], in_shape: Tuple[int, int], mode: str,
+                      op: str, dims: Sequence[int], scaler: Optional[torch.Tensor]) -> torch.Tensor:
+    """`reduce_sum / reduce_max(expr, scaler, dims)` (docs/sphinx/specs/TTLangSpecification.md:750-755; no
+    reference implementation - this is the meaning the build gives it, see oracle/sim_addons.py): the
+    expression's values (evaluated as `eval_expression` does, in `mode`) are combined in fp32 along `dims`,
+    multiplied by the scaler's element [0, 0], and rounded once to the inputs' dtype.  Reduced dims keep
+    length 1."""
+    dt = inputs[0].dtype
+    work = [t.to(torch.float32) if mode == "f32" else t for t in inputs]
+
+    def ev(e):
+        if isinstance(e, int):
+            return expand_operand(work[e], in_shape)
+        if e[0] in UNARY:
+            return UNARY[e[0]](ev(e[1]))
+        return BINARY[e[0]](ev(e[1]), ev(e[2]))
+
+    vals = ev(expr).to(torch.float32)
+    ds = sorted(set(dims))
+    res = vals.sum(dim=ds, keepdim=True) if op == "sum" else vals.amax(dim=ds, keepdim=True)
+    if scaler is not None:
+        res = res * scaler[0, 0].to(torch.float32)
+    return res.to(dt).contiguous()
+
+
 def matmul_tiles(a: torch.Tensor, b: torch.Tensor, mode: str, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`for k: out_blk.store(a_blk @ b_blk, acc=True)` for every output tile
     (examples/singlecore_matmul.py:36-45; accumulate rule python/sim/block.py:856-864):

@@ -32,7 +32,8 @@ def gen(shape: Tuple[int, int], dist: str, seed: int, dtype: torch.dtype = torch
 class Case:
     def __init__(self, name: str, module: str, program: str, inputs: List[Tuple[Tuple[int, int], str, int]],
                  out_shape: Tuple[int, int], mode: str, expr: Any, check: str, factory_args: Tuple = (),
-                 dtype: torch.dtype = torch.bfloat16, store: str = "full"):
+                 dtype: torch.dtype = torch.bfloat16, store: str = "full", reduce: Any = None):
+        self.reduce = reduce   # (op, dims, index of the scaler input, shape of the reduced values) for reductions
         self.name, self.module, self.program, self.inputs, self.out_shape = name, module, program, inputs, out_shape
         self.mode, self.expr, self.check, self.factory_args, self.dtype, self.store = (
             mode, expr, check, factory_args, dtype, store)
@@ -44,7 +45,7 @@ class Case:
         obj = getattr(modules[self.module], self.program)
         if self.factory_args or self.program.startswith("make_"):
             args = self.factory_args
-            if self.program == "make_unary_chain":
+            if self.program == "make_unary_chain" or self.module == "reduce":
                 return obj(*args, fp32_dest_acc_en=f32acc)
             return obj(*args)
         if f32acc and hasattr(modules[self.module], self.program + "_f32acc"):
@@ -119,8 +120,38 @@ MATMUL_CASES: List[Case] = [
 ]
 
 
+# reductions (ttl.math.reduce_sum / reduce_max): the last-but-one input of the single-operand programs is the
+# scaler tile; "native" = one block per result (fp32 combine, one rounding), "f32" = fp32 intermediates
+def _red(name, program, args, in_shape, out_shape, op, dims, mode, check, dtype=torch.bfloat16, dist="normal", scaler="const:0.5"):
+    return Case(name, "reduce", program, [(in_shape, dist, 80), ((32, 32), scaler, 0)], out_shape, mode, 0, check,
+                factory_args=args, dtype=dtype, reduce=(op, dims, 1, in_shape))
+
+
+REDUCE_CASES: List[Case] = [
+    _red("red_sum_rows_256x160", "make_reduce", ("sum", [0]), (256, 160), (1, 160), "sum", [0], "native", "ulp1"),
+    _red("red_sum_cols_160x256", "make_reduce", ("sum", [1]), (160, 256), (160, 1), "sum", [1], "native", "ulp1"),
+    _red("red_sum_all_96x128", "make_reduce", ("sum", [0, 1]), (96, 128), (1, 1), "sum", [0, 1], "native", "ulp1"),
+    _red("red_max_rows_256x160", "make_reduce", ("max", [0]), (256, 160), (1, 160), "max", [0], "native", "exact"),
+    _red("red_max_cols_160x256", "make_reduce", ("max", [1]), (160, 256), (160, 1), "max", [1], "native", "exact"),
+    _red("red_max_all_96x128", "make_reduce", ("max", [0, 1]), (96, 128), (1, 1), "max", [0, 1], "native", "exact",
+         scaler="const:2.0"),
+    _red("red_sum_rows_f32_128x96", "make_reduce", ("sum", [0]), (128, 96), (1, 96), "sum", [0], "native", "rel1e-5",
+         dtype=torch.float32),
+    _red("red_max_cols_f32_128x96", "make_reduce", ("max", [1]), (128, 96), (128, 1), "max", [1], "native", "exact",
+         dtype=torch.float32),
+    # accumulated over blocks of 2 row tiles with store(acc=True): fp32 partial sums
+    _red("red_colsum_acc_256x96", "make_colsum_acc", (2,), (256, 96), (1, 96), "sum", [0], "f32", "ulp1"),
+    _red("red_colsum_acc_f32_256x96", "make_colsum_acc", (2,), (256, 96), (1, 96), "sum", [0], "native", "rel1e-5",
+         dtype=torch.float32),
+    # element-wise chain + broadcast row vector reduced over columns: sum_j exp(a_ij) * b_j
+    Case("red_rowsum_exp_128x256", "reduce", "make_rowsum_exp",
+         [((128, 256), "uniform", 81), ((1, 256), "uniform", 82), ((32, 32), "const:0.25", 0)], (128, 1), "f32",
+         ("mul", ("exp", 0), 1), "ulp1", factory_args=(), reduce=("sum", [1], 2, (128, 256))),
+]
+
+
 def by_name(name: str) -> Case:
-    for c in CASES + MATMUL_CASES:
+    for c in CASES + MATMUL_CASES + REDUCE_CASES:
         if c.name == name:
             return c
     raise KeyError(name)

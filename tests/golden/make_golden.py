@@ -41,7 +41,7 @@ def load_sim(reference: Path):
 
 def load_programs(tag: str):
     mods = {}
-    for name in ("eltwise", "matmul"):
+    for name in ("eltwise", "matmul", "reduce"):
         spec = importlib.util.spec_from_file_location(f"programs_{tag}_{name}", TESTS / "programs" / f"{name}.py")
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
@@ -80,7 +80,10 @@ def main() -> None:
     import cases
 
     mods = load_programs("sim")
-    for case in cases.CASES + cases.MATMUL_CASES:
+    only = set(sys.argv[2:])   # optional: names of the fixtures to (re)generate
+    for case in cases.CASES + cases.MATMUL_CASES + cases.REDUCE_CASES:
+        if only and case.name not in only:
+            continue
         t0 = time.time()
         out = run_case_on_sim(case, mods, ttnn)
         rec = {"input_digest": np.array(digest(case.make_inputs())), "mode": np.array(case.mode),

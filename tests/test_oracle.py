@@ -18,6 +18,10 @@ def oracle_output(case):
     ins = case.make_inputs()
     if case.module == "matmul":
         return tile_oracle.matmul_tiles(ins[0], ins[1], case.mode, bias=ins[2] if len(ins) > 2 else None)
+    if case.reduce is not None:
+        op, dims, si, in_shape = case.reduce
+        data = [t for k, t in enumerate(ins) if k != si]
+        return tile_oracle.reduce_expression(case.expr, data, in_shape, case.mode, op, dims, ins[si])
     out = tile_oracle.eval_expression(case.expr, ins, case.out_shape, case.mode)
     if case.name == "eltwise_pipe":  # only the pipe's four cores compute: tile columns 0..3
         full = torch.zeros(case.out_shape, dtype=case.dtype)

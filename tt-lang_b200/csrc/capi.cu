@@ -41,6 +41,7 @@ void ttlb_destroy(ttlb_ctx *ctx) {
     if (ctx->d_status) cudaFree(ctx->d_status);
     if (ctx->h_status) cudaFreeHost(ctx->h_status);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->reduce_scratch) cudaFree(ctx->reduce_scratch);
     if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
     if (ctx->ev_fork) cudaEventDestroy(ctx->ev_fork);
     for (cudaEvent_t e : ctx->ev_chunk)

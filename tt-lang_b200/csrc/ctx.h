@@ -38,6 +38,8 @@ struct ttlb_ctx {
   // Scratch in HBM owned by the context (bf16 expansion of bfloat8_b weights); grows on demand.
   void *scratch = nullptr;
   size_t scratch_bytes = 0;
+  // Reductions over rows: partial rows, per-column-group partials and arrival counters (one allocation).
+  void *reduce_scratch = nullptr;
   // bfp8-weight matmul: the weight expansion of column chunk i+1 runs on this stream under the GEMM of chunk i
   cudaStream_t side_stream = nullptr;
   cudaEvent_t ev_fork = nullptr;

@@ -200,7 +200,7 @@ bool is_unary(int op) { return op >= TTLB_OP_EXP && op <= TTLB_OP_RELU; }
 }  // namespace
 
 // Host-side validation shared by every execution path.  Returns 1 for "valid but empty".
-static int validate_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d) {
+static int validate_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, bool need_out = true) {
   if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: null descriptor");
   if (d->dtype != TTLB_BF16 && d->dtype != TTLB_F32)
     return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "eltwise: dtype %d (bf16 and f32 only)", d->dtype);
@@ -213,12 +213,16 @@ static int validate_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d) {
                      TTLB_MAX_OPS);
   if (d->rows < 0 || d->cols < 0 || d->row0 < 0 || d->col0 < 0)
     return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: negative rectangle");
-  if (!d->out) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: null output");
-  if ((d->cols % vec) || (d->col0 % vec) || (d->out_ld % vec) || ((uintptr_t)d->out % 16))
-    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG,
-                     "eltwise: output must be 16-byte aligned (col0, cols, ld multiples of %d)", vec);
-  if (d->out_ld < d->col0 + d->cols)
-    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: rectangle exceeds the output pitch");
+  if (need_out) {
+    if (!d->out) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: null output");
+    if ((d->cols % vec) || (d->col0 % vec) || (d->out_ld % vec) || ((uintptr_t)d->out % 16))
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG,
+                       "eltwise: output must be 16-byte aligned (col0, cols, ld multiples of %d)", vec);
+    if (d->out_ld < d->col0 + d->cols)
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: rectangle exceeds the output pitch");
+  } else if ((d->cols % vec) || (d->col0 % vec)) {
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: col0 and cols must be multiples of %d", vec);
+  }
   for (int k = 0; k < d->n_in; ++k) {
     const ttlb_operand &o = d->in[k];
     if (!o.ptr) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: input %d is null", k);
@@ -339,4 +343,89 @@ extern "C" int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, void *str
   ctx->launches += 1;
   ctx->eltwise_last_path = TTLB_ELTWISE_GENERIC;
   return TTLB_OK;
+}
+
+// --------------------------------------------------------------------------- //
+// Reductions
+// --------------------------------------------------------------------------- //
+namespace {
+constexpr size_t kReducePartialFloats = 4u << 20;  // 16 MiB of partial rows
+constexpr unsigned kReduceMaxGroups = 8192;        // column groups of 256 vectors
+}  // namespace
+
+static int validate_reduce(ttlb_ctx *ctx, const ttlb_reduce_desc *r) {
+  if (!r) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: null descriptor");
+  const int rc = validate_eltwise(ctx, &r->src, false);
+  if (rc < 0) return rc;
+  const ttlb_eltwise_desc *d = &r->src;
+  const int vec = d->dtype == TTLB_BF16 ? 8 : 4;
+  const int esz = d->dtype == TTLB_BF16 ? 2 : 4;
+  if (r->op != TTLB_REDUCE_SUM && r->op != TTLB_REDUCE_MAX)
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: unknown op %d", r->op);
+  if (r->dims < 1 || r->dims > 3) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: dims=%d (1: rows, 2: columns, 3: both)", r->dims);
+  if (!r->out) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: null output");
+  if (r->scaler && ((uintptr_t)r->scaler % esz)) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: scaler is misaligned");
+  if ((r->dims & TTLB_REDUCE_ROWS) && (r->fill_rows < 1 || r->fill_rows > 32))
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: fill_rows=%d outside [1,32]", r->fill_rows);
+  if ((r->dims & TTLB_REDUCE_COLS) && (r->fill_cols < 1 || r->fill_cols > 32))
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: fill_cols=%d outside [1,32]", r->fill_cols);
+  if (r->dims == TTLB_REDUCE_ROWS) {
+    // the result row is stored as 16-byte vectors
+    if (((uintptr_t)r->out % 16) || (r->fill_rows > 1 && (r->out_ld % vec)))
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: output must be 16-byte aligned (ld a multiple of %d)", vec);
+    if (r->fill_rows > 1 && r->out_ld < d->cols) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: result exceeds the output pitch");
+  } else {
+    if ((uintptr_t)r->out % esz) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: output is misaligned");
+    if ((d->rows > 1 || r->fill_rows > 1) && r->out_ld < r->fill_cols)
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: result exceeds the output pitch");
+  }
+  if (d->rows > 0xffffffffll || d->cols / vec > 0xffffffffll) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "reduce: region too large");
+  if (rc == 1) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "reduce: empty region");
+  return TTLB_OK;
+}
+
+extern "C" int64_t ttlb_reduce_source(const ttlb_reduce_desc *r, char *buf, size_t len) {
+  if (!r) return TTLB_ERR_INVALID_ARG;
+  ttlb_reduce_desc c = *r;
+  if (!c.out) c.out = reinterpret_cast<void *>(16);  // source generation needs no buffers
+  for (int k = 0; k < c.src.n_in && k < TTLB_MAX_IN; ++k)
+    if (!c.src.in[k].ptr) c.src.in[k].ptr = reinterpret_cast<const void *>(16);
+  const int rc = validate_reduce(nullptr, &c);
+  if (rc < 0) return rc;
+  const std::string src = ttlb_reduce_jit_source(&c);
+  if (buf && len) {
+    const size_t n = src.size() < len - 1 ? src.size() : len - 1;
+    memcpy(buf, src.data(), n);
+    buf[n] = 0;
+  }
+  return (int64_t)src.size() + 1;
+}
+
+extern "C" int ttlb_reduce(ttlb_ctx *ctx, const ttlb_reduce_desc *r, void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  {
+    const int rc = validate_reduce(ctx, r);
+    if (rc < 0) return rc;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  ttlb_device_guard g(ctx->device);
+  if (!g.ok) return ttlb_fail(ctx, TTLB_ERR_CUDA, "reduce: cannot select device %d", ctx->device);
+  const size_t counter_bytes = (kReduceMaxGroups + 64) * sizeof(unsigned);
+  const size_t partial2_bytes = kReduceMaxGroups * sizeof(float);
+  if ((r->dims & TTLB_REDUCE_ROWS) && !ctx->reduce_scratch) {
+    void *p = nullptr;
+    TTLB_CUDA_CHECK(ctx, cudaMalloc(&p, counter_bytes + partial2_bytes + kReducePartialFloats * sizeof(float)));
+    cudaError_t e = cudaMemset(p, 0, counter_bytes);  // arrival counters start at zero; kernels leave them zero
+    if (e != cudaSuccess) {
+      cudaFree(p);
+      return ttlb_fail(ctx, TTLB_ERR_CUDA, "reduce: cudaMemset failed: %s", cudaGetErrorString(e));
+    }
+    ctx->reduce_scratch = p;
+  }
+  char *base = static_cast<char *>(ctx->reduce_scratch);
+  const int rc = ttlb_reduce_jit_launch(ctx, &ctx->jit, r, reinterpret_cast<float *>(base + counter_bytes + partial2_bytes),
+                                        kReducePartialFloats, reinterpret_cast<float *>(base + counter_bytes),
+                                        reinterpret_cast<unsigned *>(base), kReduceMaxGroups, s);
+  if (rc == TTLB_OK) ctx->launches += 1;
+  return rc;
 }

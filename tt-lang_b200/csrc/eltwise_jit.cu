@@ -136,7 +136,7 @@ const char *unary_expr(int op) {
 
 // `var` is the register the 16-byte vector lands in, `gi` the name of the row index.
 void emit_load(std::ostringstream &s, const ttlb_eltwise_desc *d, int k, bool bf16, const char *indent,
-               const std::string &var, const std::string &gi) {
+               const std::string &var, const std::string &gi, const std::string &gj = "gj") {
   const ttlb_operand &o = d->in[k];
   const int esz = bf16 ? 2 : 4;
   const std::string ks = std::to_string(k);
@@ -147,7 +147,7 @@ void emit_load(std::ostringstream &s, const ttlb_eltwise_desc *d, int k, bool bf
   s << indent << "{ const char* rp = (const char*)p.in[" << k << "] + " << row << " * p.ld[" << k << "] * " << esz
     << ";\n";
   if (o.col_mode == TTLB_IDX_ZERO || o.col_mode == TTLB_IDX_FIRST) {   // one element for the whole vector
-    const std::string ec = o.col_mode == TTLB_IDX_ZERO ? "p.coff[" + ks + "]" : "(p.coff[" + ks + "] + (gj & ~31LL))";
+    const std::string ec = o.col_mode == TTLB_IDX_ZERO ? "p.coff[" + ks + "]" : "(p.coff[" + ks + "] + (" + gj + " & ~31LL))";
     s << indent << "  rp += " << ec << " * " << esz << ";\n";
     if (bf16)
       s << indent << "  u32 h = *(const unsigned short*)rp; h |= h << 16; " << var << " = make_uint4(h, h, h, h); }\n";
@@ -155,8 +155,8 @@ void emit_load(std::ostringstream &s, const ttlb_eltwise_desc *d, int k, bool bf
       s << indent << "  u32 w = *(const u32*)rp; " << var << " = make_uint4(w, w, w, w); }\n";
     return;
   }
-  std::string col = o.col_mode == TTLB_IDX_SAME ? "(gj + p.coff[" + std::to_string(k) + "])"
-                                                : "(p.coff[" + std::to_string(k) + "] + (gj & 31))";
+  std::string col = o.col_mode == TTLB_IDX_SAME ? "(" + gj + " + p.coff[" + ks + "])"
+                                                : "(p.coff[" + ks + "] + (" + gj + " & 31))";
   const bool stream = o.row_mode == TTLB_IDX_SAME && o.col_mode == TTLB_IDX_SAME;
   s << indent << "  " << var << " = " << (stream ? "ld_stream" : "ld_cached") << "(rp + " << col << " * " << esz
     << "); }\n";
@@ -171,6 +171,42 @@ void emit_unpack(std::ostringstream &s, const std::string &var, const char *dst,
     } else {
       s << "        " << dst << "[" << q << "] = __uint_as_float(" << var << "." << comp[q] << ");\n";
     }
+  }
+}
+
+// The op sequence of the program as straight-line code: leaves the value of the V elements of one
+// 16-byte vector in `acc[V]`.  `var(k)` names the register holding operand k's vector.
+template <class VarFn>
+void emit_ops(std::ostringstream &s, const ttlb_eltwise_desc *d, VarFn var, bool bf16, bool rnd) {
+  s << "      float acc[V], x[V], stk0[V], stk1[V];\n"
+       "      (void)x; (void)stk0; (void)stk1;\n";
+  int depth = 0;
+  for (int pc = 0; pc < d->n_ops; ++pc) {
+    const int op = d->ops[pc].opcode, arg = d->ops[pc].arg;
+    s << "      {  // op " << pc << "\n";
+    if (op == TTLB_OP_LOAD) {
+      emit_unpack(s, var(arg), "acc", bf16);
+    } else if (op == TTLB_OP_PUSH) {
+      s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) stk" << depth << "[e] = acc[e];\n";
+      ++depth;
+    } else if (const char *be = binary_expr(op)) {
+      if (arg >= 0) {
+        emit_unpack(s, var(arg), "x", bf16);
+      } else {
+        --depth;
+        s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) x[e] = stk" << depth << "[e];\n";
+      }
+      s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { const float a = acc[e], b = x[e]; acc[e] = "
+        << be << "; }\n";
+    } else if (const char *ue = unary_expr(op)) {
+      s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { const float a = acc[e]; acc[e] = " << ue
+        << "; }\n";
+    }
+    if (rnd && op != TTLB_OP_LOAD && op != TTLB_OP_PUSH) {
+      s << "        _Pragma(\"unroll\") for (int e = 0; e < V; e += 2) { const u32 w = pack_bf16x2(acc[e], acc[e + 1]); "
+           "acc[e] = __uint_as_float(w << 16); acc[e + 1] = __uint_as_float(w & 0xffff0000u); }\n";
+    }
+    s << "      }\n";
   }
 }
 
@@ -233,36 +269,7 @@ std::string ttlb_eltwise_jit_source(const ttlb_eltwise_desc *d) {
       }
   for (int u = 0; u < U; ++u) {
     s << "    " << (u ? "if (ok" + std::to_string(u) + ") " : "") << "{  // row " << u << "\n";
-    s << "      float acc[V], x[V], stk0[V], stk1[V];\n"
-         "      (void)x; (void)stk0; (void)stk1;\n";
-    int depth = 0;
-    for (int pc = 0; pc < d->n_ops; ++pc) {
-      const int op = d->ops[pc].opcode, arg = d->ops[pc].arg;
-      s << "      {  // op " << pc << "\n";
-      if (op == TTLB_OP_LOAD) {
-        emit_unpack(s, var(arg, u), "acc", bf16);
-      } else if (op == TTLB_OP_PUSH) {
-        s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) stk" << depth << "[e] = acc[e];\n";
-        ++depth;
-      } else if (const char *be = binary_expr(op)) {
-        if (arg >= 0) {
-          emit_unpack(s, var(arg, u), "x", bf16);
-        } else {
-          --depth;
-          s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) x[e] = stk" << depth << "[e];\n";
-        }
-        s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { const float a = acc[e], b = x[e]; acc[e] = "
-          << be << "; }\n";
-      } else if (const char *ue = unary_expr(op)) {
-        s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { const float a = acc[e]; acc[e] = " << ue
-          << "; }\n";
-      }
-      if (rnd && op != TTLB_OP_LOAD && op != TTLB_OP_PUSH) {
-        s << "        _Pragma(\"unroll\") for (int e = 0; e < V; e += 2) { const u32 w = pack_bf16x2(acc[e], acc[e + 1]); "
-             "acc[e] = __uint_as_float(w << 16); acc[e + 1] = __uint_as_float(w & 0xffff0000u); }\n";
-      }
-      s << "      }\n";
-    }
+    emit_ops(s, d, [&](int k) { return var(k, u); }, bf16, rnd);
     s << "      uint4 o;\n";
     if (bf16) {
       s << "      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);\n"
@@ -296,55 +303,67 @@ void ttlb_jit_cache_destroy(ttlb_jit_cache *c) {
   delete c;
 }
 
-// Returns TTLB_OK and launches, or an error (the caller may then use the interpreter).
-int ttlb_eltwise_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_eltwise_desc *d, cudaStream_t stream) {
+// Compiles `src` (entry point `name`) for sm_100a unless `key` is already in the cache.
+static int get_kernel(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const std::string &key, const std::string &src,
+                      const char *name, JitKernel *out) {
   Nvrtc &n = nvrtc();
-  if (!n.ok) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "eltwise: NVRTC (libnvrtc.so.12) is not available");
+  if (!n.ok) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "%s: NVRTC (libnvrtc.so.12) is not available", name);
   if (!*cachep) *cachep = new ttlb_jit_cache();
   ttlb_jit_cache *cache = *cachep;
-  const std::string key = ttlb_eltwise_jit_key(d);
   auto it = cache->kernels.find(key);
-  JitKernel jk;
-  if (it == cache->kernels.end()) {
-    cudaKernel_t kern;
-    const std::string src = ttlb_eltwise_jit_source(d);
-    nvrtcProgram prog;
-    if (n.CreateProgram(&prog, src.c_str(), "ttlb_eltwise_jit.cu", 0, nullptr, nullptr) != 0)
-      return ttlb_fail(ctx, TTLB_ERR_CUDA, "eltwise: nvrtcCreateProgram failed");
-    const char *opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "-lineinfo", "--std=c++17"};
-    const int rc = n.CompileProgram(prog, 4, opts);
-    if (rc != 0) {
-      size_t ls = 0;
-      n.GetProgramLogSize(prog, &ls);
-      std::string log(ls, '\0');
-      if (ls) n.GetProgramLog(prog, log.data());
-      n.DestroyProgram(&prog);
-      return ttlb_fail(ctx, TTLB_ERR_CUDA, "eltwise: NVRTC compile failed: %.400s", log.c_str());
-    }
-    size_t cs = 0;
-    n.GetCUBINSize(prog, &cs);
-    std::vector<char> cubin(cs);
-    n.GetCUBIN(prog, cubin.data());
+  if (it != cache->kernels.end()) {
+    *out = it->second;
+    return TTLB_OK;
+  }
+  nvrtcProgram prog;
+  if (n.CreateProgram(&prog, src.c_str(), "ttlb_jit.cu", 0, nullptr, nullptr) != 0)
+    return ttlb_fail(ctx, TTLB_ERR_CUDA, "%s: nvrtcCreateProgram failed", name);
+  const char *opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "-lineinfo", "--std=c++17"};
+  const int rc = n.CompileProgram(prog, 4, opts);
+  if (rc != 0) {
+    size_t ls = 0;
+    n.GetProgramLogSize(prog, &ls);
+    std::string log(ls, '\0');
+    if (ls) n.GetProgramLog(prog, log.data());
     n.DestroyProgram(&prog);
-    cudaLibrary_t lib;
-    TTLB_CUDA_CHECK(ctx, cudaLibraryLoadData(&lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
-    cudaError_t e = cudaLibraryGetKernel(&kern, lib, "ttlb_eltwise_jit");
-    if (e != cudaSuccess) {
-      cudaLibraryUnload(lib);
-      return ttlb_fail(ctx, TTLB_ERR_CUDA, "eltwise: cudaLibraryGetKernel failed: %s", cudaGetErrorString(e));
-    }
-    cache->libs.push_back(lib);
-    jk.kern = kern;
-    jk.blocks_per_sm = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&jk.blocks_per_sm, reinterpret_cast<const void *>(kern), 256, 0) !=
-            cudaSuccess ||
-        jk.blocks_per_sm < 1) {
-      cudaGetLastError();
-      jk.blocks_per_sm = 4;
-    }
-    cache->kernels[key] = jk;
-  } else {
-    jk = it->second;
+    return ttlb_fail(ctx, TTLB_ERR_CUDA, "%s: NVRTC compile failed: %.400s", name, log.c_str());
+  }
+  size_t cs = 0;
+  n.GetCUBINSize(prog, &cs);
+  std::vector<char> cubin(cs);
+  n.GetCUBIN(prog, cubin.data());
+  n.DestroyProgram(&prog);
+  cudaLibrary_t lib;
+  TTLB_CUDA_CHECK(ctx, cudaLibraryLoadData(&lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+  cudaKernel_t kern;
+  cudaError_t e = cudaLibraryGetKernel(&kern, lib, name);
+  if (e != cudaSuccess) {
+    cudaLibraryUnload(lib);
+    return ttlb_fail(ctx, TTLB_ERR_CUDA, "%s: cudaLibraryGetKernel failed: %s", name, cudaGetErrorString(e));
+  }
+  cache->libs.push_back(lib);
+  JitKernel jk;
+  jk.kern = kern;
+  jk.blocks_per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&jk.blocks_per_sm, reinterpret_cast<const void *>(kern), 256, 0) !=
+          cudaSuccess ||
+      jk.blocks_per_sm < 1) {
+    cudaGetLastError();
+    jk.blocks_per_sm = 4;
+  }
+  cache->kernels[key] = jk;
+  *out = jk;
+  return TTLB_OK;
+}
+
+// Returns TTLB_OK and launches, or an error (the caller may then use the interpreter).
+int ttlb_eltwise_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_eltwise_desc *d, cudaStream_t stream) {
+  JitKernel jk;
+  {
+    const std::string key = ttlb_eltwise_jit_key(d);
+    const bool cached = *cachep && (*cachep)->kernels.count(key);
+    const int rc = get_kernel(ctx, cachep, key, cached ? std::string() : ttlb_eltwise_jit_source(d), "ttlb_eltwise_jit", &jk);
+    if (rc != TTLB_OK) return rc;
   }
 
   const int vec = d->dtype == TTLB_BF16 ? 8 : 4;
@@ -373,6 +392,281 @@ int ttlb_eltwise_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_e
   if (gy > row_blocks) gy = row_blocks;
   if (gy > 65535u) gy = 65535u;
   void *args[] = {&p};
+  TTLB_CUDA_CHECK(ctx, cudaLaunchKernel(reinterpret_cast<const void *>(jk.kern), dim3(gx, gy, 1), dim3(256, 1, 1), args, 0,
+                                        stream));
+  return TTLB_OK;
+}
+
+// --------------------------------------------------------------------------- //
+// Reductions (ttlb_reduce): the same per-program specialisation, with the store
+// replaced by a running sum / maximum.
+//
+// Over rows (ROWS, ROWS|COLS): the element-wise geometry - a thread owns one 16-byte
+// column vector and walks rows - with V running values per thread.  A CTA combines its
+// threads' values through shared memory, writes one partial row to scratch, and the
+// last CTA of a column group to finish (a counter in scratch) combines the partial rows
+// in index order, scales, rounds and stores: one launch, fixed summation order.
+// Over columns only (COLS): one warp per row, lanes stride over the row's 16-byte
+// vectors with several loads in flight, then a butterfly of shuffles.
+// --------------------------------------------------------------------------- //
+namespace {
+
+struct RedParams {
+  JitParams p;
+  const void *scaler;
+  void *out;
+  long long out_ld;
+  float *partial;     // [gridDim.y][ncols]
+  float *partial2;    // [gridDim.x]
+  unsigned *counter;  // [gridDim.x] arrivals per column group, zero between launches
+  unsigned *counter2; // arrivals of column groups (ROWS|COLS), zero between launches
+  unsigned fill_rows, fill_cols, ncols, pad;
+};
+
+const char *kRedPrelude = R"SRC(
+struct RedParams {
+  JitParams p; const void* scaler; void* out; i64 out_ld;
+  float* partial; float* partial2; u32* counter; u32* counter2;
+  u32 fill_rows, fill_cols, ncols, pad;
+};
+)SRC";
+
+int cols_in_flight(const ttlb_eltwise_desc *d) {
+  int streaming = 0;
+  for (int k = 0; k < d->n_in; ++k)
+    if (d->in[k].col_mode == TTLB_IDX_SAME || d->in[k].col_mode == TTLB_IDX_TILE) ++streaming;
+  int u = 8 / (streaming > 0 ? streaming : 1);
+  return u < 1 ? 1 : u > 4 ? 4 : u;
+}
+
+}  // namespace
+
+std::string ttlb_reduce_jit_key(const ttlb_reduce_desc *r) {
+  std::ostringstream k;
+  k << "red" << r->op << '/' << r->dims << ':' << ttlb_eltwise_jit_key(&r->src);
+  return k.str();
+}
+
+std::string ttlb_reduce_jit_source(const ttlb_reduce_desc *r) {
+  const ttlb_eltwise_desc *d = &r->src;
+  const bool bf16 = d->dtype == TTLB_BF16;
+  const int V = bf16 ? 8 : 4;
+  const bool rnd = bf16 && d->round_each_op;
+  const bool is_max = r->op == TTLB_REDUCE_MAX;
+  const char *init = is_max ? "__uint_as_float(0xff800000u)" : "0.0f";
+  std::ostringstream s;
+  s << kPrelude << kRedPrelude;
+  s << "#define V " << V << "\n#define ESZ " << (bf16 ? 2 : 4) << "\n";
+  s << "#define COMB(a, b) " << (is_max ? "nan_max((a), (b))" : "((a) + (b))") << "\n";
+  if (bf16)
+    s << "__device__ __forceinline__ float ld_elem(const void* q) { return __uint_as_float(((u32)*(const unsigned short*)q) << 16); }\n"
+         "__device__ __forceinline__ void st_elem(void* base, i64 idx, float x) { ((unsigned short*)base)[idx] = "
+         "(unsigned short)(pack_bf16x2(x, 0.0f) & 0xffffu); }\n";
+  else
+    s << "__device__ __forceinline__ float ld_elem(const void* q) { return *(const float*)q; }\n"
+         "__device__ __forceinline__ void st_elem(void* base, i64 idx, float x) { ((float*)base)[idx] = x; }\n";
+  s << "extern \"C\" __global__ void __launch_bounds__(256) ttlb_reduce_jit(const __grid_constant__ RedParams q) {\n"
+       "  const JitParams& p = q.p;\n"
+       "  const float sc = q.scaler ? ld_elem(q.scaler) : 1.0f;\n";
+
+  if (r->dims == TTLB_REDUCE_COLS) {
+    const int U = cols_in_flight(d);
+    auto var = [&](int k, int u) { return "v" + std::to_string(k) + "_" + std::to_string(u); };
+    s << "  const u32 lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;\n"
+         "  for (u32 r = blockIdx.x * 8u + warp; r < p.rows; r += gridDim.x * 8u) {\n"
+         "    const i64 gi = p.row0 + (i64)r;\n"
+         "    float racc = " << init << ";\n"
+         "    for (u32 c = lane; c < p.vpr; c += 32u * " << U << ") {\n";
+    for (int u = 0; u < U; ++u) {
+      s << "      const i64 gj" << u << " = p.col0 + (i64)(c + 32u * " << u << ") * V;\n";
+      if (u) s << "      const bool ok" << u << " = c + 32u * " << u << " < p.vpr;\n";
+    }
+    for (int u = 0; u < U; ++u)
+      for (int k = 0; k < d->n_in; ++k) {
+        s << "      uint4 " << var(k, u) << " = make_uint4(0, 0, 0, 0);\n";
+        if (u) s << "      if (ok" << u << ")\n";
+        emit_load(s, d, k, bf16, "      ", var(k, u), "gi", "gj" + std::to_string(u));
+      }
+    for (int u = 0; u < U; ++u) {
+      s << "      " << (u ? "if (ok" + std::to_string(u) + ") " : "") << "{\n";
+      emit_ops(s, d, [&](int k) { return var(k, u); }, bf16, rnd);
+      s << "      _Pragma(\"unroll\") for (int e = 0; e < V; ++e) racc = COMB(racc, acc[e]);\n"
+           "      }\n";
+    }
+    s << "    }\n"
+         "    _Pragma(\"unroll\") for (int o = 16; o; o >>= 1) { const float y = __shfl_xor_sync(0xffffffffu, racc, o); "
+         "racc = COMB(racc, y); }\n"
+         "    if (lane < q.fill_cols) st_elem(q.out, (i64)r * q.out_ld + lane, lane == 0 ? racc * sc : 0.0f);\n"
+         "  }\n}\n";
+    return s.str();
+  }
+
+  // ---- over rows (and optionally columns) --------------------------------
+  const int U = rows_per_iteration(d);
+  auto var = [&](int k, int u) {
+    return d->in[k].row_mode == TTLB_IDX_ZERO ? "v" + std::to_string(k) : "v" + std::to_string(k) + "_" + std::to_string(u);
+  };
+  s << "  __shared__ float sm[256 * V];\n"
+       "  __shared__ u32 s_last;\n"
+       "  const u32 bx = 1u << p.bx_log2, tx = threadIdx.x & (bx - 1u), ty = threadIdx.x >> p.bx_log2;\n"
+       "  const u32 by = 256u >> p.bx_log2;\n"
+       "  const u32 cv = (blockIdx.x << p.bx_log2) + tx;\n"
+       "  const bool colok = cv < p.vpr;\n"
+       "  const i64 gj = p.col0 + (i64)cv * V;\n"
+       "  float racc[V];\n"
+       "  _Pragma(\"unroll\") for (int e = 0; e < V; ++e) racc[e] = " << init << ";\n"
+       "  if (colok) {\n";
+  for (int k = 0; k < d->n_in; ++k)
+    if (d->in[k].row_mode == TTLB_IDX_ZERO) {
+      s << "  uint4 v" << k << ";\n";
+      emit_load(s, d, k, bf16, "  ", "v" + std::to_string(k), "0");
+    }
+  s << "  const u32 rstride = gridDim.y * by;\n"
+       "  for (u32 r = blockIdx.y * by + ty; r < p.rows; r += rstride * " << U << ") {\n";
+  for (int u = 0; u < U; ++u) {
+    s << "    const i64 gi" << u << " = p.row0 + (i64)r + (i64)rstride * " << u << ";\n";
+    if (u) s << "    const bool ok" << u << " = r + rstride * " << u << " < p.rows;\n";
+  }
+  for (int u = 0; u < U; ++u)
+    for (int k = 0; k < d->n_in; ++k)
+      if (d->in[k].row_mode != TTLB_IDX_ZERO) {
+        s << "    uint4 " << var(k, u) << " = make_uint4(0, 0, 0, 0);\n";
+        if (u) s << "    if (ok" << u << ")\n";
+        emit_load(s, d, k, bf16, "    ", var(k, u), "gi" + std::to_string(u));
+      }
+  for (int u = 0; u < U; ++u) {
+    s << "    " << (u ? "if (ok" + std::to_string(u) + ") " : "") << "{  // row " << u << "\n";
+    emit_ops(s, d, [&](int k) { return var(k, u); }, bf16, rnd);
+    s << "      _Pragma(\"unroll\") for (int e = 0; e < V; ++e) racc[e] = COMB(racc[e], acc[e]);\n"
+         "    }\n";
+  }
+  s << "  }\n  }\n";
+  // CTA-level combine over ty (in index order), one partial row per CTA
+  s << "  _Pragma(\"unroll\") for (int e = 0; e < V; ++e) sm[(ty * bx + tx) * V + e] = racc[e];\n"
+       "  __syncthreads();\n"
+       "  if (ty == 0) {\n"
+       "    for (u32 t = 1; t < by; ++t)\n"
+       "      _Pragma(\"unroll\") for (int e = 0; e < V; ++e) racc[e] = COMB(racc[e], sm[(t * bx + tx) * V + e]);\n"
+       "    if (colok) {\n"
+       "      float4* dst = (float4*)(q.partial + (size_t)blockIdx.y * q.ncols + (size_t)cv * V);\n"
+       "      _Pragma(\"unroll\") for (int e = 0; e < V; e += 4) dst[e >> 2] = make_float4(racc[e], racc[e + 1], racc[e + 2], racc[e + 3]);\n"
+       "    }\n"
+       "  }\n"
+       "  __threadfence();\n"
+       "  __syncthreads();\n"
+       "  if (threadIdx.x == 0) s_last = (atomicAdd(&q.counter[blockIdx.x], 1u) == gridDim.y - 1u) ? 1u : 0u;\n"
+       "  __syncthreads();\n"
+       "  if (!s_last) return;\n"
+       "  __threadfence();\n"
+       "  float tot[V];\n"
+       "  _Pragma(\"unroll\") for (int e = 0; e < V; ++e) tot[e] = " << init << ";\n"
+       "  if (ty == 0 && colok) {\n"
+       "    for (u32 g = 0; g < gridDim.y; ++g) {\n"
+       "      const float4* src = (const float4*)(q.partial + (size_t)g * q.ncols + (size_t)cv * V);\n"
+       "      _Pragma(\"unroll\") for (int e = 0; e < V; e += 4) { const float4 f = __ldcg(src + (e >> 2)); "
+       "tot[e] = COMB(tot[e], f.x); tot[e + 1] = COMB(tot[e + 1], f.y); tot[e + 2] = COMB(tot[e + 2], f.z); "
+       "tot[e + 3] = COMB(tot[e + 3], f.w); }\n"
+       "    }\n"
+       "  }\n";
+  if (r->dims == TTLB_REDUCE_ROWS) {
+    s << "  if (ty == 0 && colok) {\n"
+         "    uint4 o, z = make_uint4(0, 0, 0, 0);\n"
+         "    _Pragma(\"unroll\") for (int e = 0; e < V; ++e) tot[e] = tot[e] * sc;\n";
+    if (bf16)
+      s << "    o.x = pack_bf16x2(tot[0], tot[1]); o.y = pack_bf16x2(tot[2], tot[3]);\n"
+           "    o.z = pack_bf16x2(tot[4], tot[5]); o.w = pack_bf16x2(tot[6], tot[7]);\n";
+    else
+      s << "    o.x = __float_as_uint(tot[0]); o.y = __float_as_uint(tot[1]);\n"
+           "    o.z = __float_as_uint(tot[2]); o.w = __float_as_uint(tot[3]);\n";
+    s << "    *(uint4*)((char*)q.out + (i64)cv * V * ESZ) = o;\n"
+         "    for (u32 rr = 1; rr < q.fill_rows; ++rr) *(uint4*)((char*)q.out + ((i64)rr * q.out_ld + (i64)cv * V) * ESZ) = z;\n"
+         "  }\n"
+         "  if (threadIdx.x == 0) q.counter[blockIdx.x] = 0u;\n"
+         "}\n";
+    return s.str();
+  }
+  // ROWS | COLS: fold the column group, then the column groups
+  s << "  float t = " << init << ";\n"
+       "  if (ty == 0 && colok) { _Pragma(\"unroll\") for (int e = 0; e < V; ++e) t = COMB(t, tot[e]); }\n"
+       "  __syncthreads();\n"
+       "  if (ty == 0) sm[tx] = t;\n"
+       "  __syncthreads();\n"
+       "  if (threadIdx.x == 0) {\n"
+       "    float c = sm[0];\n"
+       "    for (u32 i = 1; i < bx; ++i) c = COMB(c, sm[i]);\n"
+       "    q.partial2[blockIdx.x] = c;\n"
+       "    q.counter[blockIdx.x] = 0u;\n"
+       "    __threadfence();\n"
+       "    if (atomicAdd(q.counter2, 1u) == gridDim.x - 1u) {\n"
+       "      __threadfence();\n"
+       "      float res = " << init << ";\n"
+       "      for (u32 g = 0; g < gridDim.x; ++g) res = COMB(res, __ldcg(q.partial2 + g));\n"
+       "      for (u32 rr = 0; rr < q.fill_rows; ++rr)\n"
+       "        for (u32 cc = 0; cc < q.fill_cols; ++cc) st_elem(q.out, (i64)rr * q.out_ld + cc, (rr | cc) ? 0.0f : res * sc);\n"
+       "      *q.counter2 = 0u;\n"
+       "    }\n"
+       "  }\n"
+       "}\n";
+  return s.str();
+}
+
+int ttlb_reduce_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_reduce_desc *r, float *partial,
+                           size_t partial_floats, float *partial2, unsigned *counters, unsigned max_groups,
+                           cudaStream_t stream) {
+  const ttlb_eltwise_desc *d = &r->src;
+  JitKernel jk;
+  {
+    const std::string key = ttlb_reduce_jit_key(r);
+    const bool cached = *cachep && (*cachep)->kernels.count(key);
+    const int rc = get_kernel(ctx, cachep, key, cached ? std::string() : ttlb_reduce_jit_source(r), "ttlb_reduce_jit", &jk);
+    if (rc != TTLB_OK) return rc;
+  }
+  const int vec = d->dtype == TTLB_BF16 ? 8 : 4;
+  RedParams q{};
+  JitParams &p = q.p;
+  for (int k = 0; k < d->n_in; ++k) {
+    p.in[k] = d->in[k].ptr;
+    p.ld[k] = d->in[k].ld;
+    p.roff[k] = d->in[k].row_off;
+    p.coff[k] = d->in[k].col_off;
+  }
+  p.row0 = d->row0;
+  p.col0 = d->col0;
+  p.vpr = (unsigned)(d->cols / vec);
+  p.rows = (unsigned)d->rows;
+  q.scaler = r->scaler;
+  q.out = r->out;
+  q.out_ld = r->out_ld;
+  q.fill_rows = (unsigned)r->fill_rows;
+  q.fill_cols = (unsigned)r->fill_cols;
+  q.ncols = (unsigned)d->cols;
+  const unsigned resident = (unsigned)(ctx->sm_count * jk.blocks_per_sm);
+  void *args[] = {&q};
+  if (r->dims == TTLB_REDUCE_COLS) {
+    unsigned gx = (p.rows + 7u) / 8u;
+    if (gx > resident) gx = resident;
+    TTLB_CUDA_CHECK(ctx, cudaLaunchKernel(reinterpret_cast<const void *>(jk.kern), dim3(gx, 1, 1), dim3(256, 1, 1), args,
+                                          0, stream));
+    return TTLB_OK;
+  }
+  unsigned bx_log2 = 0;
+  while (bx_log2 < 8 && (1u << bx_log2) < p.vpr) ++bx_log2;
+  p.bx_log2 = bx_log2;
+  const unsigned bx = 1u << bx_log2, by = 256u / bx;
+  const unsigned gx = (p.vpr + bx - 1) / bx;
+  if (gx > max_groups) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "reduce: %lld columns are too many", (long long)d->cols);
+  const unsigned row_blocks = (p.rows + by - 1) / by;
+  unsigned gy = resident / gx;
+  const size_t fit = partial_floats / (size_t)d->cols;  // partial rows the scratch holds
+  if (fit < 1) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "reduce: %lld columns are too many", (long long)d->cols);
+  if (gy > fit) gy = (unsigned)fit;
+  if (gy > row_blocks) gy = row_blocks;
+  if (gy < 1) gy = 1;
+  if (gy > 65535u) gy = 65535u;
+  q.partial = partial;
+  q.partial2 = partial2;
+  q.counter = counters;
+  q.counter2 = counters + max_groups;
   TTLB_CUDA_CHECK(ctx, cudaLaunchKernel(reinterpret_cast<const void *>(jk.kern), dim3(gx, gy, 1), dim3(256, 1, 1), args, 0,
                                         stream));
   return TTLB_OK;

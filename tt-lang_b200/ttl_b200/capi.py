@@ -46,6 +46,15 @@ class EltwiseDesc(C.Structure):
                 ("row0", C.c_int64), ("col0", C.c_int64), ("rows", C.c_int64), ("cols", C.c_int64)]
 
 
+REDUCE_SUM, REDUCE_MAX = 0, 1
+REDUCE_ROWS, REDUCE_COLS = 1, 2
+
+
+class ReduceDesc(C.Structure):
+    _fields_ = [("src", EltwiseDesc), ("op", C.c_int32), ("dims", C.c_int32), ("scaler", C.c_void_p),
+                ("out", C.c_void_p), ("out_ld", C.c_int64), ("fill_rows", C.c_int32), ("fill_cols", C.c_int32)]
+
+
 class GemmDesc(C.Structure):
     _fields_ = [("a", C.c_void_p), ("lda", C.c_int64), ("b", C.c_void_p), ("ldb", C.c_int64),
                 ("c", C.c_void_p), ("ldc", C.c_int64), ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64)]
@@ -74,6 +83,17 @@ def eltwise_source(desc: "EltwiseDesc") -> str:
         raise BackendError(int(n), "invalid element-wise descriptor")
     buf = C.create_string_buffer(int(n))
     l.ttlb_eltwise_source(C.byref(desc), buf, int(n))
+    return buf.value.decode()
+
+
+def reduce_source(desc: "ReduceDesc") -> str:
+    """CUDA source of the reduction kernel specialised for `desc` (works without a GPU)."""
+    l = lib()
+    n = l.ttlb_reduce_source(C.byref(desc), None, 0)
+    if n < 0:
+        raise BackendError(int(n), "invalid reduction descriptor")
+    buf = C.create_string_buffer(int(n))
+    l.ttlb_reduce_source(C.byref(desc), buf, int(n))
     return buf.value.decode()
 
 
@@ -119,6 +139,10 @@ def lib() -> C.CDLL:
     l.ttlb_eltwise_last_path.restype = C.c_int
     l.ttlb_eltwise_source.argtypes = [C.POINTER(EltwiseDesc), C.c_char_p, C.c_size_t]
     l.ttlb_eltwise_source.restype = C.c_int64
+    l.ttlb_reduce.argtypes = [C.c_void_p, C.POINTER(ReduceDesc), C.c_void_p]
+    l.ttlb_reduce.restype = C.c_int
+    l.ttlb_reduce_source.argtypes = [C.POINTER(ReduceDesc), C.c_char_p, C.c_size_t]
+    l.ttlb_reduce_source.restype = C.c_int64
     l.ttlb_matmul_bf16.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]
     l.ttlb_matmul_bf16.restype = C.c_int
     l.ttlb_matmul_bf16_bias.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_int64, C.c_void_p]
@@ -183,6 +207,9 @@ class Context:
 
     def eltwise(self, desc: EltwiseDesc, stream: int) -> None:
         self.check(self._lib.ttlb_eltwise(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def reduce(self, desc: "ReduceDesc", stream: int) -> None:
+        self.check(self._lib.ttlb_reduce(self.handle, C.byref(desc), C.c_void_p(stream)))
 
     def matmul_bf16(self, desc: "GemmDesc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_bf16(self.handle, C.byref(desc), C.c_void_p(stream)))

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 from typing import Any, List, Optional
 
-from .trace import Block, Leaf, _as_block
+from .trace import Block, Leaf, Red, _as_block
 
 
 # Which meaning `broadcast` has on FULL (non-degenerate) tiles.  The two reference front ends disagree:
@@ -88,3 +88,38 @@ def max(a: Any, b: Any) -> Block:  # noqa: A001 - reference spelling
 
 def min(a: Any, b: Any) -> Block:  # noqa: A001
     return _as_block(a)._binary(b, "min")
+
+
+def _reduce(op: str, block: Any, scaler: Any, dims: Optional[List[int]]) -> Block:
+    if dims is None:
+        raise ValueError(f"dims parameter is required for reduce_{op}()")
+    b = _as_block(block)
+    if not isinstance(b, Block):
+        raise TypeError(f"reduce_{op}() takes a block or a block expression")
+    ds = tuple(sorted(set(int(d) for d in dims)))
+    if not ds or any(d not in (0, 1) for d in ds):
+        raise ValueError(f"reduce_{op}(): dims must name block dimensions 0 and/or 1, got {list(dims)}")
+    sc = None
+    if scaler is not None:
+        sb = _as_block(scaler)
+        if not isinstance(sb, Block):
+            raise TypeError(f"reduce_{op}(): the scaler must be a block")
+        if sb.shape != (1, 1):
+            raise ValueError(f"reduce_{op}(): the scaler must be a block of one tile, got shape {sb.shape}")
+        sc = sb.value()
+    e = Red(op, b.value(), sc, ds)
+    return Block(e.shape, b.dtype, e, "FULL", "temp", temporary=True)
+
+
+def reduce_sum(block: Any, scaler: Any = None, dims: Optional[List[int]] = None) -> Block:
+    """Scaled sum over block dims (docs/sphinx/specs/TTLangSpecification.md:754): dims=[0] sums over rows
+    (a block of (R, C) tiles gives (1, C) tiles), dims=[1] over columns, dims=[0, 1] over both.  The sum of
+    the elements, formed in fp32, is multiplied by element [0, 0] of the one-tile `scaler` block and rounded
+    once to the block's element type."""
+    return _reduce("sum", block, scaler, dims)
+
+
+def reduce_max(block: Any, scaler: Any = None, dims: Optional[List[int]] = None) -> Block:
+    """Scaled maximum over block dims (docs/sphinx/specs/TTLangSpecification.md:755); same conventions as
+    `reduce_sum`."""
+    return _reduce("max", block, scaler, dims)

@@ -25,7 +25,7 @@ import torch
 
 from . import capi
 from . import ttnn as _ttnn
-from .trace import Acc, Bin, Expr, Leaf, Trace, Un, Write, Zero
+from .trace import Acc, Bin, Expr, Leaf, Red, Trace, Un, Write, Zero
 
 TILE = 32
 
@@ -294,6 +294,65 @@ class EltwiseLaunch:
         ctx.eltwise(self.desc(tensors), stream)
 
 
+class ReduceLaunch:
+    """One `ttlb_reduce` launch: `inputs`/`ops` produce the values (offsets along a reduced dim are absolute,
+    along a kept dim relative to the output rectangle), `extent` is the number of tiles reduced per dim."""
+
+    def __init__(self, out_index: int, rect: Tuple[int, int, int, int], op: str, dims: Tuple[int, ...],
+                 extent: Tuple[int, int], inputs: List[Tuple[int, int, int, int, int]], ops: List[Tuple[str, int]],
+                 scaler: Optional[Tuple[int, int, int]], dtype: Any, round_each_op: bool):
+        self.out_index, self.rect, self.op, self.dims, self.extent = out_index, rect, op, dims, extent
+        self.inputs, self.ops, self.scaler, self.dtype, self.round_each_op = inputs, ops, scaler, dtype, round_each_op
+
+    def describe(self) -> Dict[str, Any]:
+        return {"kind": "reduce_" + self.op, "dims": list(self.dims), "out": self.out_index, "rect_tiles": self.rect,
+                "reduced_tiles": self.extent, "inputs": self.inputs, "ops": self.ops, "scaler": self.scaler,
+                "round_each_op": self.round_each_op}
+
+    def region(self) -> Tuple[int, int, int, int]:
+        """(row0, rows, col0, cols) of the values reduced, in elements of the program's index space."""
+        r0, r1, c0, c1 = self.rect
+        rows = (0, self.extent[0] * TILE) if 0 in self.dims else (r0 * TILE, (r1 - r0) * TILE)
+        cols = (0, self.extent[1] * TILE) if 1 in self.dims else (c0 * TILE, (c1 - c0) * TILE)
+        return rows[0], rows[1], cols[0], cols[1]
+
+    def desc(self, tensors: Sequence[_ttnn.Tensor], with_pointers: bool = True) -> capi.ReduceDesc:
+        r = capi.ReduceDesc()
+        d = r.src
+        d.dtype = _dtype_code(self.dtype)
+        d.round_each_op = 1 if self.round_each_op else 0
+        d.n_in, d.n_ops = len(self.inputs), len(self.ops)
+        for k, (ti, rm, ro, cm, co) in enumerate(self.inputs):
+            x = _torch_of(tensors[ti]) if with_pointers else tensors[ti]._tensor
+            if with_pointers:
+                d.inp[k].ptr = x.data_ptr()
+            d.inp[k].ld = x.stride(0) if x.shape[0] > 1 else x.shape[1]
+            d.inp[k].row_mode, d.inp[k].row_off = rm, ro
+            d.inp[k].col_mode, d.inp[k].col_off = cm, co
+        for k, (op, arg) in enumerate(self.ops):
+            d.ops[k].opcode, d.ops[k].arg = capi.OPCODES[op], arg
+        d.row0, d.rows, d.col0, d.cols = self.region()
+        r.op = capi.REDUCE_SUM if self.op == "sum" else capi.REDUCE_MAX
+        r.dims = (capi.REDUCE_ROWS if 0 in self.dims else 0) | (capi.REDUCE_COLS if 1 in self.dims else 0)
+        o = _torch_of(tensors[self.out_index]) if with_pointers else tensors[self.out_index]._tensor
+        esz = o.element_size()
+        r.out_ld = o.stride(0) if o.shape[0] > 1 else o.shape[1]
+        orow = 0 if o.shape[0] == 1 else self.rect[0] * TILE
+        ocol = 0 if o.shape[1] == 1 else self.rect[2] * TILE
+        r.fill_rows = 1 if o.shape[0] == 1 else TILE
+        r.fill_cols = 1 if o.shape[1] == 1 else TILE
+        if with_pointers:
+            r.out = o.data_ptr() + (orow * r.out_ld + ocol) * esz
+            if self.scaler is not None:
+                si, srow, scol = self.scaler
+                st = _torch_of(tensors[si])
+                r.scaler = st.data_ptr() + (srow * (st.stride(0) if st.shape[0] > 1 else 0) + scol) * esz
+        return r
+
+    def run(self, ctx: capi.Context, tensors: Sequence[_ttnn.Tensor], stream: int) -> None:
+        ctx.reduce(self.desc(tensors), stream)
+
+
 class GemmLaunch:
     def __init__(self, a_index: int, b_index: int, out_index: int, rect: Tuple[int, int, int, int], k_tiles: int,
                  b_is_bfp8: bool, bias_index: Optional[int] = None):
@@ -364,6 +423,125 @@ def _matmul_terms(w: Write) -> Optional[Tuple[List[Bin], Optional[Leaf]]]:
     return None
 
 
+def _reduce_terms(w: Write) -> Optional[List[Red]]:
+    e = _unwrap(w.expr)
+    terms = list(e.terms) if isinstance(e, Acc) else [e]
+    terms = [_unwrap(t) for t in terms]
+    if terms and all(isinstance(t, Red) for t in terms):
+        return terms  # type: ignore[return-value]
+    return None
+
+
+class _Region:
+    """Stand-in for a Write when operands are classified against a region that is not an output region."""
+
+    def __init__(self, r0: int, r1: int, c0: int, c1: int):
+        self.r0, self.r1, self.c0, self.c1 = r0, r1, c0, c1
+
+
+def _recognise_reduce(w: Write, terms: List[Red], table: _TensorTable, oi: int, fp32_intermediates: bool) -> Any:
+    """Key of a write `out_blk <- reduce(x)` or `out_blk <- sum_k reduce_sum(x_k)` (accumulating stores over
+    blocks that tile the reduced extent).  Offsets along a reduced dim are absolute (the region starts at tile
+    0), along a kept dim relative to the write region, so that neighbouring writes share a key and merge."""
+    t0 = terms[0]
+    op, dims = t0.op, t0.dims
+    odt = w.tensor.dtype
+    if (w.r1 - w.r0, w.c1 - w.c0) != t0.shape:
+        raise Unsupported(f"reduction result of {t0.shape} tiles stored into a block of {(w.r1 - w.r0, w.c1 - w.c0)} tiles")
+    for d in (0, 1):
+        if d not in dims and w.tensor.shape[d] == 1:
+            raise Unsupported("a reduction keeps a dimension in which the output tensor is degenerate")
+    if len(terms) > 1:
+        if op != "sum":
+            raise Unsupported("store(acc=True) adds: only reduce_sum results can be accumulated over blocks")
+        if odt != torch.float32 and not fp32_intermediates:
+            raise Unsupported("accumulating reduce_sum over blocks of a bfloat16 tensor rounds every partial sum in "
+                              "the simulator; run the kernel with fp32_dest_acc_en=True (fp32 partial sums, one rounding)")
+    sc_key = None
+    per_term = []
+    for t in terms:
+        if t.op != op or t.dims != dims or t.x.shape != t0.x.shape:
+            raise Unsupported("accumulated reductions must be the same reduction of equal-shape blocks")
+        if _contains_matmul(t.x) or _contains_red(t.x):
+            raise Unsupported("a reduction of a matmul or of another reduction in one expression is not supported yet")
+        k = None
+        if t.scaler is not None:
+            sl = _unwrap(t.scaler)
+            if not isinstance(sl, Leaf):
+                raise Unsupported("the scaler of a reduction must come straight from a circular buffer")
+            st = sl.tensor
+            if st.dtype != odt:
+                raise Unsupported(f"mixed element types ({st.dtype} scaler, {odt} output)")
+            k = (table.index(st), 0 if st.shape[0] == 1 else sl.r0 * TILE, 0 if st.shape[1] == 1 else sl.c0 * TILE)
+        if t is t0:
+            sc_key = k
+        elif k != sc_key:
+            raise Unsupported("accumulated reductions must use the same scaler")
+        rr = (0, t.x.shape[0]) if 0 in dims else (w.r0, w.r1)
+        cc = (0, t.x.shape[1]) if 1 in dims else (w.c0, w.c1)
+        lin = _Lin(_Region(rr[0], rr[1], cc[0], cc[1]), table)  # type: ignore[arg-type]
+        lin.emit(t.x)
+        per_term.append(lin)
+    base = per_term[0]
+    if len(base.inputs) > capi.TTLB_MAX_IN or len(base.ops) > capi.TTLB_MAX_OPS or _stack_depth(base.ops) > 2:
+        raise Unsupported("the reduced expression is too large (operands, ops or temporaries)")
+    for (ti, rm, _ro, cm, _co) in base.inputs:
+        t = table.args[ti] if ti < len(table.args) else table.extras[ti - len(table.args)]
+        if t.dtype != odt:
+            raise Unsupported(f"mixed element types ({t.dtype} operand, {odt} output)")
+    for d, name in ((0, "row"), (1, "column")):
+        if d in dims and not any((inp[1] if d == 0 else inp[3]) == capi.IDX_SAME for inp in base.inputs):
+            raise Unsupported(f"a reduction over {name}s needs an operand that varies along them")
+    # the blocks of the terms must tile a rectangle of the reduced dims
+    deltas = []
+    for lin in per_term:
+        if lin.ops != base.ops or len(lin.inputs) != len(base.inputs):
+            raise Unsupported("accumulated reductions must reduce the same expression")
+        dr = dc = None
+        for a, b in zip(lin.inputs, base.inputs):
+            if (a[0], a[1], a[3]) != (b[0], b[1], b[3]):
+                raise Unsupported("accumulated reductions must reduce the same expression")
+            for mode, oa, ob, which in ((a[1], a[2], b[2], 0), (a[3], a[4], b[4], 1)):
+                if mode == capi.IDX_SAME:
+                    cur = dr if which == 0 else dc
+                    if cur is not None and cur != oa - ob:
+                        raise Unsupported("operands of an accumulated reduction move by different steps")
+                    if which == 0:
+                        dr = oa - ob
+                    else:
+                        dc = oa - ob
+                elif oa != ob:
+                    raise Unsupported("a broadcast operand of an accumulated reduction changes between blocks")
+        deltas.append((dr or 0, dc or 0))
+    hr, hc = t0.x.shape[0] * TILE, t0.x.shape[1] * TILE
+    mr, mc = min(d[0] for d in deltas), min(d[1] for d in deltas)
+    cells = sorted(((d[0] - mr) // hr, (d[1] - mc) // hc) for d in deltas)
+    nr, nc = cells[-1][0] + 1, cells[-1][1] + 1
+    ok = all((d[0] - mr) % hr == 0 and (d[1] - mc) % hc == 0 for d in deltas)
+    if not ok or cells != [(i, j) for i in range(nr) for j in range(nc)] or (nr > 1 and 0 not in dims) or (nc > 1 and 1 not in dims):
+        raise Unsupported("the blocks of an accumulated reduction do not tile a rectangle exactly once")
+    inputs = tuple((ti, rm, ro + (mr if rm == capi.IDX_SAME else 0), cm, co + (mc if cm == capi.IDX_SAME else 0))
+                   for (ti, rm, ro, cm, co) in base.inputs)
+    extent = (t0.x.shape[0] * nr if 0 in dims else 0, t0.x.shape[1] * nc if 1 in dims else 0)
+    anchor = (w.r0 if 0 in dims else -1, w.c0 if 1 in dims else -1)
+    return (oi, op, dims, extent, inputs, tuple(base.ops), sc_key, anchor)
+
+
+def _contains_red(e: Expr) -> bool:
+    stack = [e]
+    while stack:
+        x = stack.pop()
+        if isinstance(x, Red):
+            return True
+        if isinstance(x, Bin):
+            stack += [x.a, x.b]
+        elif isinstance(x, Un):
+            stack.append(x.x)
+        elif isinstance(x, Acc):
+            stack.extend(x.terms)
+    return False
+
+
 def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermediates: bool = False) -> Plan:
     table = _TensorTable(arg_tensors)
     # 1. every write gets a key (what is computed, from where); 2. writes must not overlap, except that
@@ -375,6 +553,7 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
     elt_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
     elt_meta: Dict[Any, Any] = {}
     mm_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
+    red_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
     for w in trace.writes:
         oi = table.index(w.tensor)
         out_tensors[oi] = w.tensor
@@ -383,12 +562,18 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
             raise ValueError(f"write region [{w.r0}:{w.r1}, {w.c0}:{w.c1}] is outside the {tr}x{tc}-tile tensor")
         region = (w.r0, w.r1, w.c0, w.c1)
         mm = _matmul_terms(w)
-        if mm is not None:
+        red = _reduce_terms(w)
+        if red is not None:
+            key = ("red",) + _recognise_reduce(w, red, table, oi, fp32_intermediates)
+        elif mm is not None:
             terms, bias = mm
             key = ("mm",) + tuple(_recognise_matmul(w, terms, table, oi)) + (_recognise_bias(w, bias, table),)
         else:
             if _contains_matmul(w.expr):
                 raise Unsupported("matmul mixed with element-wise ops in one store is not supported yet")
+            if _contains_red(w.expr):
+                raise Unsupported("a reduction inside a larger expression is not supported yet: store the "
+                                  "reduction into its own output tensor")
             lin = _Lin(w, table)
             lin.emit(w.expr)
             if len(lin.inputs) > capi.TTLB_MAX_IN:
@@ -415,7 +600,7 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
             raise Unsupported(f"output tiles [{w.r0}:{w.r1}, {w.c0}:{w.c1}] are written more than once")
         covered[...] = True
         seen[(oi, region)] = key
-        (mm_groups if key[0] == "mm" else elt_groups).setdefault(key, []).append(region)
+        {"mm": mm_groups, "elt": elt_groups, "red": red_groups}[key[0]].setdefault(key, []).append(region)
 
     launches: List[Any] = []
     for key, rects in elt_groups.items():
@@ -424,6 +609,11 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
         for rect in merge_rects(rects):
             launches.append(EltwiseLaunch(oi, rect, list(inputs), list(ops), odt,
                                           round_each_op=not fp32_intermediates, out_degenerate=degen))
+    for key, rects in red_groups.items():
+        _, oi, op, dims, extent, inputs, ops, sc_key, _anchor = key
+        for rect in merge_rects(rects):
+            launches.append(ReduceLaunch(oi, rect, op, dims, extent, list(inputs), list(ops), sc_key,
+                                         out_tensors[oi].dtype, round_each_op=not fp32_intermediates))
     for key, rects in mm_groups.items():
         _, ai, bi, oi, kt, b8, ci = key
         f32 = out_tensors[oi].dtype == torch.float32

@@ -92,6 +92,18 @@ class Acc(Expr):
         self.terms, self.shape = terms, shape
 
 
+class Red(Expr):
+    """`ttl.math.reduce_sum / reduce_max(x, scaler, dims)`: the elements of block `x` combined along the
+    block dims in `dims` (0: rows, 1: columns), times the scaler.  The reduced dims of the result are one
+    tile long; the value sits in the tile's first row / column / element."""
+
+    __slots__ = ("op", "x", "scaler", "dims")
+
+    def __init__(self, op: str, x: Expr, scaler: Optional[Expr], dims: Tuple[int, ...]):
+        self.op, self.x, self.scaler, self.dims = op, x, scaler, dims
+        self.shape = (1 if 0 in dims else x.shape[0], 1 if 1 in dims else x.shape[1])
+
+
 class Write:
     """`tensor[r0:r1, c0:c1] <- expr` (tile coordinates)."""
 
