@@ -614,6 +614,90 @@ def run_reduce_8192(args) -> None:
         "gpu_launches": launches, "clocks": clocks}))
 
 
+def run_softmax_8192(args) -> None:
+    """Row softmax of a bf16 [8192, 8192] tensor written as a tile program (tests/programs/reduce.py,
+    make_softmax): the plan is three launches - row maximum, row sum of exp(x - max) fused into the
+    reduction, exp(x - max) / sum - so x is read three times and y written once.  Algorithmic bytes: one
+    read and one write of the tensor (what a kernel holding a whole row on chip would move)."""
+    import importlib.util
+
+    import torch
+
+    import ttl_b200
+
+    ttl_b200.install()
+    import ttnn
+
+    from ttl_b200 import capi
+
+    torch.cuda.set_device(0)
+    spec = importlib.util.spec_from_file_location("bench_programs_reduce", ROOT / "tests" / "programs" / "reduce.py")
+    programs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(programs)
+    n = 8192
+    host = torch.randn(n, n, generator=torch.Generator().manual_seed(0)).to(torch.bfloat16).pin_memory()
+    x = ttnn.from_torch(host)
+    scaler = ttnn.from_torch(torch.ones(32, 32, dtype=torch.bfloat16))
+    y = ttnn.empty((n, n), dtype=ttnn.bfloat16)
+    prog = programs.make_softmax(fp32_dest_acc_en=True)
+    plan = prog.plan(x, scaler, y)
+    kinds = [d["kind"] for d in plan.describe()]
+    assert kinds == ["reduce_max", "reduce_sum", "eltwise"], kinds
+    ctx = capi.context(0)
+    algo = 2 * n * n * 2
+    for _ in range(args.warmup):
+        plan.run([x, scaler, y])
+    torch.cuda.synchronize()
+    sampler = ClockSampler(physical_gpu_index(0))
+    sampler.start()
+    l0 = ctx.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        plan.run([x, scaler, y])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = ctx.launch_count() - l0
+    clocks = sampler.stop()
+    got = ttnn.to_torch(y).double()
+    want = torch.softmax(host.double(), dim=1)
+    assert ((got - want).abs() <= 2.0 ** -6 * want + 1e-7).all(), "softmax result is wrong"
+    host_out = torch.empty((n, n), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        xx = ttnn.from_torch(host)
+        yy = ttnn.empty((n, n), dtype=ttnn.bfloat16)
+        prog(xx, scaler, yy)
+        ttnn.to_torch(yy, out=host_out)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.e2e_steps):
+        e2e_step()
+    f1.record()
+    torch.cuda.synchronize()
+    e2e_ms = f0.elapsed_time(f1) / args.e2e_steps
+    peak, peak_src = measured_peak_hbm()
+    gbs = algo / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "eltwise HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "softmax_8192: row softmax as a tile program (reduce_max, reduce_sum, exp, broadcast), "
+                               "bf16 [8192,8192] N(0,1), fp32 intermediates; checked against a float64 softmax in this run",
+                   "l2": "input and output are 134 MB each (larger than L2)", "algorithmic_bytes_per_step": algo,
+                   "bytes_moved_per_step": 4 * n * n * 2, "launches_per_step": 3},
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak, "traffic": None,
+                     "peak_source": peak_src, "kernel": "ttlb_reduce_jit x2 + ttlb_eltwise_jit",
+                     "note": "three passes over x: at most half of the peak is reachable with this plan"},
+        "e2e": {"value": algo / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": n * n * 2,
+                "d2h_bytes_per_step": n * n * 2, "ms_per_step": e2e_ms, "steps": args.e2e_steps},
+        "gpu_launches": launches, "clocks": clocks}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -649,6 +733,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200: the backend has no CPU fallback")
+    if args.workload == "softmax_8192":
+        run_softmax_8192(args)
+        return
     if args.workload.startswith("reduce_"):
         run_reduce_8192(args)
         return

@@ -106,7 +106,22 @@ def run_gemm(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
     out[r0:r1, c0:c1] = tile_oracle.matmul_tiles(a[r0:r1], b[:, c0:c1], mode, bias=bias).to(out.dtype)
 
 
+class _WithTemps:
+    """The call's tensors plus the plan's temporaries (indices from 1000 on name temporaries)."""
+
+    def __init__(self, tensors: Sequence[torch.Tensor], temps: Sequence[torch.Tensor]):
+        self.tensors, self.temps = list(tensors), list(temps)
+
+    def __getitem__(self, i: int) -> torch.Tensor:
+        return self.temps[i - 1000] if i >= 1000 else self.tensors[i]
+
+
 def run_plan(plan: Any, tensors: Sequence[torch.Tensor]) -> None:
+    """Evaluate the launches in order.  `tensors`: the call's arguments followed by the plan's extras, as
+    host torch tensors; temporaries of the plan are replaced by host tensors of the same shape."""
+    temps = getattr(plan, "temps", None)
+    if temps:
+        tensors = _WithTemps(tensors, [torch.zeros(t._tensor.shape, dtype=t._tensor.dtype) for t in temps])  # type: ignore[assignment]
     for launch in plan.launches:
         if hasattr(launch, "extent"):
             run_reduce(launch, tensors)

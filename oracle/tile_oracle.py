@@ -71,6 +71,13 @@ def eval_expression(expr: Sequence, inputs: Sequence[torch.Tensor], out_shape: T
         op = e[0]
         if op in UNARY:
             return UNARY[op](ev(e[1]))
+        if op in ("reduce_sum", "reduce_max"):
+            # ("reduce_sum", expr, index of the scaler input, dims): fp32 combine, times scaler[0, 0], one
+            # rounding to the working dtype; reduced dims keep length 1 and broadcast in the ops that follow
+            x = ev(e[1])
+            v = x.to(torch.float32)
+            r = v.sum(dim=list(e[3]), keepdim=True) if op == "reduce_sum" else v.amax(dim=list(e[3]), keepdim=True)
+            return (r * work[e[2]][0, 0].to(torch.float32)).to(x.dtype)
         return BINARY[op](ev(e[1]), ev(e[2]))
 
     return ev(expr).to(dt).contiguous()

@@ -150,8 +150,25 @@ REDUCE_CASES: List[Case] = [
 ]
 
 
+# tile programs whose reductions feed further element-wise ops (results pass through circular buffers)
+_SM_E = ("exp", ("sub", 0, ("reduce_max", 0, 1, [1])))
+_SOFTMAX = ("div", _SM_E, ("reduce_sum", _SM_E, 1, [1]))
+_ST_C = ("sub", 0, ("reduce_sum", 0, 1, [1]))
+_STANDARDIZE = ("mul", _ST_C, ("rsqrt", ("reduce_sum", ("mul", _ST_C, _ST_C), 1, [1])))
+COMPOSITE_CASES: List[Case] = [
+    Case("softmax_128x256", "reduce", "make_softmax", [((128, 256), "normal", 85), ((32, 32), "const:1.0", 0)],
+         (128, 256), "native", _SOFTMAX, "ulp2", factory_args=()),
+    Case("softmax_f32_96x160", "reduce", "make_softmax", [((96, 160), "normal", 86), ((32, 32), "const:1.0", 0)],
+         (96, 160), "native", _SOFTMAX, "rel1e-5", factory_args=(), dtype=torch.float32),
+    Case("standardize_128x256", "reduce", "make_standardize", [((128, 256), "normal", 87), ((32, 32), "const:0.00390625", 0)],
+         (128, 256), "native", _STANDARDIZE, "ulp2", factory_args=()),
+    Case("standardize_f32_96x128", "reduce", "make_standardize", [((96, 128), "normal", 88), ((32, 32), "const:0.0078125", 0)],
+         (96, 128), "native", _STANDARDIZE, "rel1e-5", factory_args=(), dtype=torch.float32),
+]
+
+
 def by_name(name: str) -> Case:
-    for c in CASES + MATMUL_CASES + REDUCE_CASES:
+    for c in CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES:
         if c.name == name:
             return c
     raise KeyError(name)

@@ -178,3 +178,104 @@ def make_rowsum_exp(fp32_dest_acc_en=False):
                     tx.wait()
 
     return rowsum_exp
+
+
+def make_softmax(fp32_dest_acc_en=False):
+    """Row softmax as a tile program: y = exp(x - max_j x) / sum_j exp(x - max_j x), one row strip of
+    tiles per step; the row maximum and the row sum travel through circular buffers of (1,1) blocks
+    and are broadcast over the columns."""
+
+    @_kernel((2, 2), fp32_dest_acc_en)
+    def softmax(x, s, y):
+        rt, ct = x.shape[0] // 32, x.shape[1] // 32
+        per_core = math.ceil(rt / N_CORES)
+        x_cb = ttl.make_circular_buffer_like(x, shape=(1, ct), buffer_factor=2)
+        s_cb = ttl.make_circular_buffer_like(s, shape=(1, 1), buffer_factor=2)
+        m_cb = ttl.make_circular_buffer_like(x, shape=(1, 1), buffer_factor=2)
+        e_cb = ttl.make_circular_buffer_like(x, shape=(1, ct), buffer_factor=2)
+        d_cb = ttl.make_circular_buffer_like(x, shape=(1, 1), buffer_factor=2)
+        y_cb = ttl.make_circular_buffer_like(y, shape=(1, ct), buffer_factor=2)
+
+        def my_rows():
+            core = ttl.core(dims=1)
+            return range(core * per_core, min((core + 1) * per_core, rt))
+
+        @ttl.compute()
+        def compute():
+            for _r in my_rows():
+                with x_cb.wait() as xb, s_cb.wait() as sb:
+                    with m_cb.reserve() as mb:
+                        mb.store(ttl.math.reduce_max(xb, sb, dims=[1]))
+                    with m_cb.wait() as mb, e_cb.reserve() as eb:
+                        eb.store(ttl.math.exp(xb - ttl.math.broadcast(mb, dims=[1])))
+                    with e_cb.wait() as eb:
+                        with d_cb.reserve() as db:
+                            db.store(ttl.math.reduce_sum(eb, sb, dims=[1]))
+                        with d_cb.wait() as db, y_cb.reserve() as yb:
+                            yb.store(eb / ttl.math.broadcast(db, dims=[1]))
+
+        @ttl.datamovement()
+        def dm0():
+            for r in my_rows():
+                with x_cb.reserve() as xb:
+                    tx = ttl.copy(x[r:r + 1, 0:ct], xb)
+                    tx.wait()
+                with s_cb.reserve() as sb:
+                    tx = ttl.copy(s[0:1, 0:1], sb)
+                    tx.wait()
+
+        @ttl.datamovement()
+        def dm1():
+            for r in my_rows():
+                with y_cb.wait() as yb:
+                    tx = ttl.copy(yb, y[r:r + 1, 0:ct])
+                    tx.wait()
+
+    return softmax
+
+
+def make_standardize(fp32_dest_acc_en=False):
+    """Row standardisation (the core of layer norm): c = x - mean_j x, y = c * rsqrt(mean_j c*c), with the
+    scaler tile holding 1/N.  Two reductions, the second over an expression that reads the first."""
+
+    @_kernel((2, 2), fp32_dest_acc_en)
+    def standardize(x, s, y):
+        rt, ct = x.shape[0] // 32, x.shape[1] // 32
+        per_core = math.ceil(rt / N_CORES)
+        x_cb = ttl.make_circular_buffer_like(x, shape=(1, ct), buffer_factor=2)
+        s_cb = ttl.make_circular_buffer_like(s, shape=(1, 1), buffer_factor=2)
+        c_cb = ttl.make_circular_buffer_like(x, shape=(1, ct), buffer_factor=2)
+        y_cb = ttl.make_circular_buffer_like(y, shape=(1, ct), buffer_factor=2)
+
+        def my_rows():
+            core = ttl.core(dims=1)
+            return range(core * per_core, min((core + 1) * per_core, rt))
+
+        @ttl.compute()
+        def compute():
+            for _r in my_rows():
+                with x_cb.wait() as xb, s_cb.wait() as sb:
+                    with c_cb.reserve() as cb:
+                        cb.store(xb - ttl.math.broadcast(ttl.math.reduce_sum(xb, sb, dims=[1]), dims=[1]))
+                    with c_cb.wait() as cb, y_cb.reserve() as yb:
+                        var = ttl.math.reduce_sum(cb * cb, sb, dims=[1])
+                        yb.store(cb * ttl.math.broadcast(ttl.math.rsqrt(var), dims=[1]))
+
+        @ttl.datamovement()
+        def dm0():
+            for r in my_rows():
+                with x_cb.reserve() as xb:
+                    tx = ttl.copy(x[r:r + 1, 0:ct], xb)
+                    tx.wait()
+                with s_cb.reserve() as sb:
+                    tx = ttl.copy(s[0:1, 0:1], sb)
+                    tx.wait()
+
+        @ttl.datamovement()
+        def dm1():
+            for r in my_rows():
+                with y_cb.wait() as yb:
+                    tx = ttl.copy(yb, y[r:r + 1, 0:ct])
+                    tx.wait()
+
+    return standardize

@@ -34,6 +34,45 @@ def test_program_matches_simulator_and_oracle(case, backend):
     close(got, golden_tensor(load_golden(case.name)["out"], case.dtype), case.check, "vs simulator golden")
 
 
+@pytest.mark.parametrize("case", cases.COMPOSITE_CASES, ids=lambda c: c.name)
+def test_reductions_inside_expressions(case, backend):
+    """Softmax / row standardisation as tile programs: three launches (two reductions into temporaries, one
+    element-wise), against the simulator fixture and the oracle; a second call reuses plan and temporaries."""
+    _, mods = backend
+    import ttnn
+    prog = case.get_program(mods)
+    want = golden_tensor(load_golden(case.name)["out"], case.dtype)
+    for _ in range(2):
+        ins = [ttnn.from_torch(t) for t in case.make_inputs()]
+        out = ttnn.from_torch(torch.zeros(case.out_shape, dtype=case.dtype))
+        before = _launches()
+        prog(*ins, out)
+        assert _launches() == before + 3
+        got = ttnn.to_torch(out)
+        close(got, oracle_output(case), case.check, "vs oracle")
+        close(got, want, case.check, "vs simulator golden")
+
+
+def test_softmax_full_size(backend):
+    """Row softmax of a bf16 [8192, 8192] tensor as a tile program, fp32 tensors' worth of checks: rows sum
+    to one, results within bf16 rounding of a float64 softmax."""
+    _, mods = backend
+    import ttnn
+    n = 8192
+    x = cases.gen((n, n), "normal", 93)
+    s = ttnn.from_torch(torch.ones(32, 32, dtype=torch.bfloat16))
+    out = ttnn.from_torch(torch.zeros((n, n), dtype=torch.bfloat16))
+    before = _launches()
+    mods["reduce"].make_softmax()(ttnn.from_torch(x), s, out)
+    assert _launches() == before + 3
+    got = ttnn.to_torch(out).double()
+    want = torch.softmax(x.double(), dim=1)
+    # every op rounds to bf16: x - max (up to 2^-9 * 10 absolute, so 2 % in the exponential), exp, the row
+    # sum, the quotient
+    assert ((got - want).abs() <= 2.0 ** -5 * want + 1e-7).all()
+    assert (got.sum(dim=1) - 1).abs().max() < 2e-2
+
+
 def test_full_tile_output_and_repeat_calls(backend):
     """Output of full tiles: value in row 0 of the tile, zeros below.  The scratch (partial rows, arrival
     counters) is shared by all calls of a context: a second and third call must give the same bits."""

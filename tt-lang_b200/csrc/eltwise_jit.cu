@@ -560,14 +560,19 @@ std::string ttlb_reduce_jit_source(const ttlb_reduce_desc *r) {
        "  __threadfence();\n"
        "  float tot[V];\n"
        "  _Pragma(\"unroll\") for (int e = 0; e < V; ++e) tot[e] = " << init << ";\n"
-       "  if (ty == 0 && colok) {\n"
-       "    for (u32 g = 0; g < gridDim.y; ++g) {\n"
+       "  if (colok) {\n"   // the CTA's `by` thread rows share the partial rows, then combine in thread-row order
+       "    for (u32 g = ty; g < gridDim.y; g += by) {\n"
        "      const float4* src = (const float4*)(q.partial + (size_t)g * q.ncols + (size_t)cv * V);\n"
        "      _Pragma(\"unroll\") for (int e = 0; e < V; e += 4) { const float4 f = __ldcg(src + (e >> 2)); "
        "tot[e] = COMB(tot[e], f.x); tot[e + 1] = COMB(tot[e + 1], f.y); tot[e + 2] = COMB(tot[e + 2], f.z); "
        "tot[e + 3] = COMB(tot[e + 3], f.w); }\n"
        "    }\n"
-       "  }\n";
+       "  }\n"
+       "  _Pragma(\"unroll\") for (int e = 0; e < V; ++e) sm[(ty * bx + tx) * V + e] = tot[e];\n"
+       "  __syncthreads();\n"
+       "  if (ty == 0)\n"
+       "    for (u32 t = 1; t < by; ++t)\n"
+       "      _Pragma(\"unroll\") for (int e = 0; e < V; ++e) tot[e] = COMB(tot[e], sm[(t * bx + tx) * V + e]);\n";
   if (r->dims == TTLB_REDUCE_ROWS) {
     s << "  if (ty == 0 && colok) {\n"
          "    uint4 o, z = make_uint4(0, 0, 0, 0);\n"
@@ -649,8 +654,11 @@ int ttlb_reduce_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_re
                                           0, stream));
     return TTLB_OK;
   }
+  // One warp wide (32 vectors = 512 contiguous bytes per row), 8 thread rows: the CTA folds 8 rows in
+  // shared memory before it writes a partial row, and a column group is 256 columns, so that there are
+  // few partial rows and many groups to finish them in parallel.
   unsigned bx_log2 = 0;
-  while (bx_log2 < 8 && (1u << bx_log2) < p.vpr) ++bx_log2;
+  while (bx_log2 < 5 && (1u << bx_log2) < p.vpr) ++bx_log2;
   p.bx_log2 = bx_log2;
   const unsigned bx = 1u << bx_log2, by = 256u / bx;
   const unsigned gx = (p.vpr + bx - 1) / bx;

@@ -81,14 +81,44 @@ def _contains_matmul(e: Expr) -> bool:
     return False
 
 
+TEMP_BASE = 1000   # tensor indices from here on name temporaries owned by the plan
+
+
+class _Indexed:
+    """Kernel arguments (+ tensors derived in the kernel body) and the plan's temporaries under one index space."""
+
+    def __init__(self, tensors: Sequence[Any], temps: Sequence[Any]):
+        self.tensors, self.temps = list(tensors), list(temps)
+
+    def __getitem__(self, i: int) -> Any:
+        return self.temps[i - TEMP_BASE] if i >= TEMP_BASE else self.tensors[i]
+
+    def __len__(self) -> int:
+        return len(self.tensors)
+
+
 class _TensorTable:
     """Maps tensor objects of a trace to kernel-argument positions."""
 
     def __init__(self, args: Sequence[_ttnn.Tensor]):
         self.args = list(args)
         self.extras: List[_ttnn.Tensor] = []
+        self.temps: List[_ttnn.Tensor] = []
+
+    def tensor(self, i: int) -> _ttnn.Tensor:
+        if i >= TEMP_BASE:
+            return self.temps[i - TEMP_BASE]
+        return self.args[i] if i < len(self.args) else self.extras[i - len(self.args)]
+
+    def new_temp(self, shape: Tuple[int, int], like: _ttnn.Tensor) -> _ttnn.Tensor:
+        t = _ttnn.Tensor(torch.zeros(shape, dtype=like._tensor.dtype, device=like._tensor.device))
+        self.temps.append(t)
+        return t
 
     def index(self, t: _ttnn.Tensor) -> int:
+        for i, a in enumerate(self.temps):
+            if a is t:
+                return TEMP_BASE + i
         for i, a in enumerate(self.args):
             if a is t:
                 return i
@@ -379,8 +409,16 @@ class GemmLaunch:
 class Plan:
     """The launches one kernel call turns into."""
 
-    def __init__(self, launches: List[Any], extras: List[_ttnn.Tensor], n_args: int):
+    def __init__(self, launches: List[Any], extras: List[_ttnn.Tensor], n_args: int,
+                 temps: Optional[List[_ttnn.Tensor]] = None):
         self.launches, self.extras, self.n_args = launches, extras, n_args
+        # results of reductions used inside larger expressions: small tensors owned by the plan
+        self.temps: List[_ttnn.Tensor] = temps or []
+
+    def indexed(self, tensors: Sequence[_ttnn.Tensor]) -> _Indexed:
+        """The tensors a launch may name by index: the call's arguments, tensors derived in the kernel
+        body, and the plan's temporaries."""
+        return _Indexed(list(tensors) + self.extras, self.temps)
 
     @property
     def cacheable(self) -> bool:
@@ -402,8 +440,12 @@ class Plan:
                 break
         ctx = capi.context(dev)
         stream = capi.current_stream()
+        for t in self.temps:
+            if not t._tensor.is_cuda or t._tensor.device.index != dev:
+                t._tensor = torch.zeros(t._tensor.shape, dtype=t._tensor.dtype, device=torch.device("cuda", dev))
+        ix = _Indexed(allt, self.temps)
         for l in self.launches:
-            l.run(ctx, allt, stream)
+            l.run(ctx, ix, stream)
 
 
 # --------------------------------------------------------------------------- #
@@ -486,7 +528,7 @@ def _recognise_reduce(w: Write, terms: List[Red], table: _TensorTable, oi: int, 
     if len(base.inputs) > capi.TTLB_MAX_IN or len(base.ops) > capi.TTLB_MAX_OPS or _stack_depth(base.ops) > 2:
         raise Unsupported("the reduced expression is too large (operands, ops or temporaries)")
     for (ti, rm, _ro, cm, _co) in base.inputs:
-        t = table.args[ti] if ti < len(table.args) else table.extras[ti - len(table.args)]
+        t = table.tensor(ti)
         if t.dtype != odt:
             raise Unsupported(f"mixed element types ({t.dtype} operand, {odt} output)")
     for d, name in ((0, "row"), (1, "column")):
@@ -542,6 +584,61 @@ def _contains_red(e: Expr) -> bool:
     return False
 
 
+def _lower_reductions(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tensor],
+                      out: List[Tuple[Write, int]]) -> Tuple[Expr, int]:
+    """Replace every reduction inside the expression of write `w` by a read of a temporary and append the
+    write that fills the temporary to `out`, innermost first.  A reduction over columns of a block that
+    spans the write's rows leaves one value per row: it goes to a [rows, 1] temporary indexed like the
+    output's rows (and likewise [1, cols] for a reduction over rows), so the writes of neighbouring blocks
+    fill neighbouring parts of one temporary and merge into one launch.  This is what a tile program does
+    when it passes a reduction result on through a circular buffer: the value is held in a tile of the
+    tensor's element type.  Returns the rewritten expression and its level (1 + the deepest temporary read)."""
+    memo: Dict[int, Tuple[Expr, int]] = {}
+    slot = [0]
+    oi = table.index(w.tensor)
+
+    def go(e: Expr) -> Tuple[Expr, int]:
+        if isinstance(e, (Leaf, Zero)):
+            return e, 0
+        hit = memo.get(id(e))
+        if hit is not None:
+            return hit
+        if isinstance(e, Un):
+            x, l = go(e.x)
+            res: Tuple[Expr, int] = (e if x is e.x else Un(e.op, x), l)
+        elif isinstance(e, Bin):
+            a, la = go(e.a)
+            b, lb = go(e.b)
+            res = (e if (a is e.a and b is e.b) else Bin(e.op, a, b, e.shape), max(la, lb))
+        elif isinstance(e, Acc):
+            parts = [go(t) for t in e.terms]
+            res = (Acc([p[0] for p in parts], e.shape), max(p[1] for p in parts))
+        elif isinstance(e, Red):
+            if len(e.dims) != 1:
+                raise Unsupported("a reduction over both dimensions inside a larger expression is not supported: "
+                                  "store it into its own output tensor")
+            x, l = go(e.x)
+            kept = 1 - e.dims[0]
+            span = (w.r1 - w.r0, w.c1 - w.c0)[kept]
+            if e.shape[kept] != span or w.tensor.shape[kept] == 1:
+                raise Unsupported("a reduction inside an expression must keep the extent of the block it is stored into")
+            key = (oi, slot[0], e.op, e.dims)
+            slot[0] += 1
+            t = temps.get(key)
+            if t is None:
+                shape = (w.tensor.shape[0], 1) if kept == 0 else (1, w.tensor.shape[1])
+                t = temps[key] = table.new_temp(shape, w.tensor)
+            region = (w.r0, w.r1, 0, 1) if kept == 0 else (0, 1, w.c0, w.c1)
+            out.append((Write(t, region[0], region[1], region[2], region[3], Red(e.op, x, e.scaler, e.dims), w.core), l))
+            res = (Leaf(t, *region), l + 1)
+        else:
+            raise Unsupported(f"cannot lower {type(e).__name__}")
+        memo[id(e)] = res
+        return res
+
+    return go(w.expr)
+
+
 def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermediates: bool = False) -> Plan:
     table = _TensorTable(arg_tensors)
     # 1. every write gets a key (what is computed, from where); 2. writes must not overlap, except that
@@ -554,7 +651,17 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
     elt_meta: Dict[Any, Any] = {}
     mm_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
     red_groups: Dict[Any, List[Tuple[int, int, int, int]]] = {}
+    # reductions inside larger expressions first become writes of their own into temporaries
+    temps: Dict[Any, _ttnn.Tensor] = {}
+    writes: List[Tuple[Write, int]] = []
     for w in trace.writes:
+        if _reduce_terms(w) is None and _matmul_terms(w) is None and not _contains_matmul(w.expr) and _contains_red(w.expr):
+            expr, level = _lower_reductions(w, table, temps, writes)
+            writes.append((Write(w.tensor, w.r0, w.r1, w.c0, w.c1, expr, w.core), level))
+        else:
+            writes.append((w, 0))
+    level_of: Dict[Any, int] = {}
+    for w, level in writes:
         oi = table.index(w.tensor)
         out_tensors[oi] = w.tensor
         tr, tc = w.tensor.tile_shape()
@@ -571,9 +678,6 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
         else:
             if _contains_matmul(w.expr):
                 raise Unsupported("matmul mixed with element-wise ops in one store is not supported yet")
-            if _contains_red(w.expr):
-                raise Unsupported("a reduction inside a larger expression is not supported yet: store the "
-                                  "reduction into its own output tensor")
             lin = _Lin(w, table)
             lin.emit(w.expr)
             if len(lin.inputs) > capi.TTLB_MAX_IN:
@@ -584,7 +688,7 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
                 raise Unsupported("expression needs more than two temporaries")
             odt = w.tensor.dtype
             for (ti, *_rest) in lin.inputs:
-                t = table.args[ti] if ti < len(table.args) else table.extras[ti - len(table.args)]
+                t = table.tensor(ti)
                 if t.dtype != odt:
                     raise Unsupported(f"mixed element types ({t.dtype} operand, {odt} output)")
                 for dim in (0, 1):
@@ -601,19 +705,20 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
         covered[...] = True
         seen[(oi, region)] = key
         {"mm": mm_groups, "elt": elt_groups, "red": red_groups}[key[0]].setdefault(key, []).append(region)
+        level_of[key] = max(level_of.get(key, 0), level)
 
-    launches: List[Any] = []
+    launches: List[Tuple[int, Any]] = []
     for key, rects in elt_groups.items():
         _, oi, inputs, ops = key
         odt, degen = elt_meta[key]
         for rect in merge_rects(rects):
-            launches.append(EltwiseLaunch(oi, rect, list(inputs), list(ops), odt,
-                                          round_each_op=not fp32_intermediates, out_degenerate=degen))
+            launches.append((level_of[key], EltwiseLaunch(oi, rect, list(inputs), list(ops), odt,
+                                                          round_each_op=not fp32_intermediates, out_degenerate=degen)))
     for key, rects in red_groups.items():
         _, oi, op, dims, extent, inputs, ops, sc_key, _anchor = key
         for rect in merge_rects(rects):
-            launches.append(ReduceLaunch(oi, rect, op, dims, extent, list(inputs), list(ops), sc_key,
-                                         out_tensors[oi].dtype, round_each_op=not fp32_intermediates))
+            launches.append((level_of[key], ReduceLaunch(oi, rect, op, dims, extent, list(inputs), list(ops), sc_key,
+                                                         out_tensors[oi].dtype, round_each_op=not fp32_intermediates)))
     for key, rects in mm_groups.items():
         _, ai, bi, oi, kt, b8, ci = key
         f32 = out_tensors[oi].dtype == torch.float32
@@ -623,8 +728,10 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
             gl = GemmLaunch(ai, bi, oi, rect, kt, b8, ci)
             if f32:
                 gl.kind = "matmul_f32"
-            launches.append(gl)
-    return Plan(launches, table.extras, len(table.args))
+            launches.append((level_of[key], gl))
+    # a launch that reads a temporary runs after the launch that fills it
+    ordered = [l for _, l in sorted(launches, key=lambda p: p[0])]
+    return Plan(ordered, table.extras, len(table.args), table.temps)
 
 
 def _recognise_bias(w: Write, bias: Optional[Leaf], table: _TensorTable) -> Optional[int]:
