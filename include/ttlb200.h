@@ -111,8 +111,40 @@ enum ttlb_opcode {
   TTLB_OP_NEG = 22,
   TTLB_OP_ABS = 23,
   TTLB_OP_RELU = 24,
-  TTLB_OP_PUSH = 32 /* push acc on the stack */
+  TTLB_OP_PUSH = 32, /* push acc on the stack */
+  /* Unary math functions of the specification's Appendix B
+   * (docs/sphinx/specs/TTLangSpecification.md:700-748) beyond the compiler's op table; executed by the
+   * specialised kernel only.  `arg` is unused. */
+  TTLB_OP_EXP2 = 40,
+  TTLB_OP_EXPM1 = 41,
+  TTLB_OP_LOGP1 = 42, /* log(1 + x) */
+  TTLB_OP_SQUARE = 43,
+  TTLB_OP_RECIP = 44,
+  TTLB_OP_TAN = 45,
+  TTLB_OP_ATAN = 46,
+  TTLB_OP_ATANH = 47,
+  TTLB_OP_SIN = 48,
+  TTLB_OP_ASIN = 49,
+  TTLB_OP_ASINH = 50,
+  TTLB_OP_COS = 51,
+  TTLB_OP_ACOS = 52,
+  TTLB_OP_ACOSH = 53,
+  TTLB_OP_GELU = 54,        /* 0.5 x (1 + erf(x / sqrt 2)) */
+  TTLB_OP_SILU = 55,        /* x / (1 + exp(-x)) */
+  TTLB_OP_SOFTSIGN = 56,    /* x / (1 + |x|) */
+  TTLB_OP_HARDSIGMOID = 57, /* clamp(x / 6 + 1/2, 0, 1) */
+  /* Functions with scalar parameters: `arg` is the index of the first parameter in `imm`. */
+  TTLB_OP_RSUB_IMM = 64,   /* p0 - x */
+  TTLB_OP_RELU_MAX = 65,   /* relu(min(x, p0)) */
+  TTLB_OP_RELU_MIN = 66,   /* relu(max(x, p0)) */
+  TTLB_OP_LEAKY_RELU = 67, /* x >= 0 ? x : p0 x (also prelu) */
+  TTLB_OP_ELU = 68,        /* x > 0 ? x : p0 (exp(x) - 1) */
+  TTLB_OP_CELU = 69,       /* max(0, x) + min(0, p0 (exp(x p1) - 1)), p1 = 1 / p0 */
+  TTLB_OP_SOFTPLUS = 70,   /* x p0 > p2 ? x : log(1 + exp(x p0)) p1, p1 = 1 / p0 */
+  TTLB_OP_HARDTANH = 71,   /* min(max(x, p0), p1) */
+  TTLB_OP_SELU = 72        /* p0 (x > 0 ? x : p1 (exp(x) - 1)) */
 };
+#define TTLB_MAX_IMM 8
 
 /* How an input is indexed from an output element (i, j):
  *  SAME  index = i + off                 (same-shape operand, optionally shifted)
@@ -154,6 +186,7 @@ typedef struct {
   int64_t out_ld; /* row pitch in elements */
   int64_t row0, col0, rows, cols; /* rectangle of the output to compute, in elements;
                                      col0 and cols must be multiples of 8 */
+  float imm[TTLB_MAX_IMM];        /* scalar parameters of the TTLB_OP_*_IMM-style functions */
 } ttlb_eltwise_desc;
 
 TTLB_EXPORT int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *desc, void *stream);

@@ -16,10 +16,10 @@ from . import tile_oracle
 TILE = 32
 _SAME, _ZERO, _TILE, _FIRST = 0, 1, 2, 3
 
-_UNARY = {
-    "exp": torch.exp, "log": torch.log, "sqrt": torch.sqrt, "rsqrt": torch.rsqrt, "tanh": torch.tanh,
-    "sigmoid": torch.sigmoid, "neg": torch.neg, "abs": torch.abs, "relu": torch.relu,
-}
+_UNARY = dict(tile_oracle.UNARY)
+_PARAM_UNARY = tile_oracle.PARAM_UNARY
+_N_PARAMS = {"rsub_imm": 1, "relu_max": 1, "relu_min": 1, "leaky_relu": 1, "elu": 1, "celu": 2, "softplus": 3,
+             "hardtanh": 2, "selu": 2}
 _BINARY = {
     "add": lambda a, b: a + b, "sub": lambda a, b: a - b, "rsub": lambda a, b: b - a, "mul": lambda a, b: a * b,
     "div": lambda a, b: a / b, "rdiv": lambda a, b: b / a, "max": torch.maximum, "min": torch.minimum,
@@ -37,7 +37,7 @@ def _index(mode: int, off: int, idx: torch.Tensor) -> torch.Tensor:
 
 
 def _evaluate(inputs: Any, ops: Any, tensors: Sequence[torch.Tensor], rows: torch.Tensor, cols: torch.Tensor,
-              rnd: bool) -> torch.Tensor:
+              rnd: bool, imms: Sequence[float] = ()) -> torch.Tensor:
     """The stack program of a launch on the index ranges `rows` x `cols`, as an fp32 matrix."""
 
     def operand(k: int) -> torch.Tensor:
@@ -56,6 +56,8 @@ def _evaluate(inputs: Any, ops: Any, tensors: Sequence[torch.Tensor], rows: torc
         if op == "load" or op in _BINARY:
             x = operand(arg) if arg >= 0 else stack.pop(0)
             acc = x if op == "load" else _BINARY[op](acc, x)
+        elif op in _PARAM_UNARY:
+            acc = _PARAM_UNARY[op](acc, *imms[arg:arg + _N_PARAMS[op]])
         else:
             acc = _UNARY[op](acc)
         if rnd and op != "load":
@@ -70,7 +72,7 @@ def run_eltwise(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
     rows = torch.arange(0, 1) if launch.out_degenerate[0] else torch.arange(r0 * TILE, r1 * TILE)
     cols = torch.arange(0, 1) if launch.out_degenerate[1] else torch.arange(c0 * TILE, c1 * TILE)
     rnd = out.dtype == torch.bfloat16 and launch.round_each_op
-    acc = _evaluate(launch.inputs, launch.ops, tensors, rows, cols, rnd)
+    acc = _evaluate(launch.inputs, launch.ops, tensors, rows, cols, rnd, getattr(launch, "imms", ()))
     view = out if out.dim() == 2 else out.reshape(1, -1)
     view[rows[0]:rows[-1] + 1, cols[0]:cols[-1] + 1] = acc.to(out.dtype)
 
@@ -83,7 +85,7 @@ def run_reduce(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
     row0, nrows, col0, ncols = launch.region()
     rnd = out.dtype == torch.bfloat16 and launch.round_each_op
     vals = _evaluate(launch.inputs, launch.ops, tensors, torch.arange(row0, row0 + nrows),
-                     torch.arange(col0, col0 + ncols), rnd)
+                     torch.arange(col0, col0 + ncols), rnd, getattr(launch, "imms", ()))
     dims = list(launch.dims)
     res = vals.sum(dim=dims, keepdim=True) if launch.op == "sum" else vals.amax(dim=dims, keepdim=True)
     if launch.scaler is not None:

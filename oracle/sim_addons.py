@@ -37,6 +37,13 @@ UNARY_GOLDEN = {
 BINARY_GOLDEN = {"max": torch.maximum, "min": torch.minimum}
 
 
+def _appendix_b() -> Any:
+    """The other functions of the specification's Appendix B, as the oracle defines them (one block op each)."""
+    from . import tile_oracle
+    extra = {k: v for k, v in tile_oracle.UNARY.items() if k not in UNARY_GOLDEN}
+    return extra, tile_oracle.PARAM_UNARY, tile_oracle.MATH_NAMES
+
+
 def install(sim_module: Any) -> None:
     """Add the functions to `sim_module.ttl.math` (sim_module is the imported `sim` package)."""
     from sim.block import Block, BlockAcquisition, ThreadType  # type: ignore
@@ -99,7 +106,19 @@ def install(sim_module: Any) -> None:
             return result
         return op
 
+    def make_param_unary(fn: Callable[..., torch.Tensor]) -> Callable[..., Any]:
+        def op(block: Any, *params: float) -> Any:
+            return make_unary(lambda t: fn(t, *params))(block)
+        return op
+
     m = sim_module.ttl.math
+    extra_unary, param_unary, spellings = _appendix_b()
+    for name, fn in extra_unary.items():
+        setattr(m, name, make_unary(fn))
+    for name, fn in param_unary.items():
+        setattr(m, name, make_param_unary(fn))
+    for spelling, name in spellings.items():
+        setattr(m, spelling, make_param_unary(param_unary[name]))
     m.reduce_sum = make_reduce("sum")
     m.reduce_max = make_reduce("max")
     for name, fn in UNARY_GOLDEN.items():

@@ -28,6 +28,38 @@ UNARY: Dict[str, Callable[[torch.Tensor], torch.Tensor]] = {
     "exp": torch.exp, "log": torch.log, "sqrt": torch.sqrt, "rsqrt": torch.rsqrt, "tanh": torch.tanh,
     "sigmoid": torch.sigmoid, "neg": torch.neg, "abs": torch.abs, "relu": torch.relu,
 }
+
+
+def _in_f32(fn: Callable[..., torch.Tensor]) -> Callable[..., torch.Tensor]:
+    """A function of the specification's Appendix B is ONE block op: evaluated in fp32, rounded once."""
+    def wrapped(x: torch.Tensor, *params: float) -> torch.Tensor:
+        return fn(x.to(torch.float32), *params).to(x.dtype)
+    return wrapped
+
+
+_F = torch.nn.functional
+# The rest of the specification's Appendix B (docs/sphinx/specs/TTLangSpecification.md:700-748), paired with the
+# torch functions the specification links to.  No reference implementation exists: parity unpinned.
+UNARY.update({name: _in_f32(fn) for name, fn in {
+    "exp2": torch.exp2, "expm1": torch.expm1, "logp1": torch.log1p, "square": torch.square, "recip": torch.reciprocal,
+    "tan": torch.tan, "atan": torch.atan, "atanh": torch.atanh, "sin": torch.sin, "asin": torch.asin,
+    "asinh": torch.asinh, "cos": torch.cos, "acos": torch.acos, "acosh": torch.acosh, "gelu": _F.gelu,
+    "silu": _F.silu, "softsign": _F.softsign, "hardsigmoid": _F.hardsigmoid}.items()})
+# functions with scalar parameters: name -> fn(x, *params)
+PARAM_UNARY: Dict[str, Callable[..., torch.Tensor]] = {name: _in_f32(fn) for name, fn in {
+    "rsub_imm": lambda x, b: b - x,
+    "relu_max": lambda x, hi: torch.relu(torch.clamp(x, max=hi)),
+    "relu_min": lambda x, lo: torch.relu(torch.clamp(x, min=lo)),
+    "leaky_relu": lambda x, slope: _F.leaky_relu(x, slope),
+    "elu": lambda x, alpha: _F.elu(x, alpha),
+    "celu": lambda x, alpha, _alpha_recip: _F.celu(x, alpha),
+    "softplus": lambda x, beta, _beta_recip, threshold: _F.softplus(x, beta, threshold),
+    "hardtanh": lambda x, lo, hi: _F.hardtanh(x, lo, hi),
+    "selu": lambda x, scale, alpha: scale * torch.where(x > 0, x, alpha * torch.expm1(x)),
+}.items()}
+# spelling in ttl.math -> op name
+MATH_NAMES = {"rsub": "rsub_imm", "prelu": "leaky_relu"}
+
 BINARY: Dict[str, Callable[[torch.Tensor, torch.Tensor], torch.Tensor]] = {
     "add": torch.add, "sub": torch.sub, "mul": torch.mul, "div": torch.div,
     "max": torch.maximum, "min": torch.minimum,
@@ -69,6 +101,8 @@ def eval_expression(expr: Sequence, inputs: Sequence[torch.Tensor], out_shape: T
         if isinstance(e, int):
             return expand_operand(work[e], out_shape)
         op = e[0]
+        if isinstance(op, (tuple, list)):   # ((name, p0, ...), operand): a function with scalar parameters
+            return PARAM_UNARY[MATH_NAMES.get(op[0], op[0])](ev(e[1]), *op[1:])
         if op in UNARY:
             return UNARY[op](ev(e[1]))
         if op in ("reduce_sum", "reduce_max"):

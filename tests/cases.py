@@ -20,6 +20,8 @@ def gen(shape: Tuple[int, int], dist: str, seed: int, dtype: torch.dtype = torch
         t = torch.rand(shape, generator=g, dtype=torch.float32) * 2 - 1
     elif dist == "positive":          # U(0.01, 10): log / sqrt / rsqrt domain (test/me2e/ops/__init__.py:44-48)
         t = torch.rand(shape, generator=g, dtype=torch.float32) * 9.99 + 0.01
+    elif dist == "ge1":               # U(1, 10): acosh domain
+        t = torch.rand(shape, generator=g, dtype=torch.float32) * 9 + 1
     elif dist.startswith("const:"):
         t = torch.full(shape, float(dist.split(":")[1]), dtype=torch.float32)
     elif dist.startswith("normal*"):  # N(0, sigma)
@@ -103,6 +105,23 @@ for _i, (_op, _dist, _check) in enumerate([
     CASES.append(Case(f"unary_{_op}", "eltwise", "make_unary_chain", [((64, 64), _dist, 50 + _i), ((64, 64), "uniform", 70 + _i)],
                       (64, 64), "native", ("add", (_op, 0), 1), _check, factory_args=([_op],)))
 
+# the rest of the specification's Appendix B: one case per function, Y = f(A) + B (run by the specialised kernel only)
+MATH_CASES: List[Case] = []
+for _i, (_op, _dist, _check) in enumerate([
+        ("exp2", "uniform", "ulp1"), ("expm1", "uniform", "ulp1"), ("logp1", "positive", "ulp1"),
+        ("square", "normal", "exact"), ("recip", "positive", "exact"), ("tan", "uniform", "ulp1"),
+        ("atan", "normal", "ulp1"), ("atanh", "uniform", "ulp1"), ("sin", "normal", "ulp1"), ("asin", "uniform", "ulp1"),
+        ("asinh", "normal", "ulp1"), ("cos", "normal", "ulp1"), ("acos", "uniform", "ulp1"), ("acosh", "ge1", "ulp1"),
+        ("gelu", "normal", "ulp1"), ("silu", "normal", "ulp1"), ("softsign", "normal", "exact"),
+        ("hardsigmoid", "normal*3", "ulp1"),
+        (("rsub", 2), "normal", "exact"), (("relu_max", 1), "normal", "exact"), (("relu_min", 1), "normal", "exact"),
+        (("leaky_relu", 0.25), "normal", "exact"), (("prelu", 0.125), "normal", "exact"), (("elu", 1.5), "normal", "ulp1"),
+        (("celu", 2, 0.5), "normal", "ulp1"), (("softplus", 2, 0.5, 4), "normal*3", "ulp1"),
+        (("hardtanh", -0.5, 0.75), "normal", "exact"), (("selu", 1.0507, 1.67326), "normal", "ulp1")]):
+    _name = _op if isinstance(_op, str) else _op[0]
+    MATH_CASES.append(Case(f"math_{_name}", "eltwise", "make_unary_chain", [((64, 96), _dist, 100 + _i), ((64, 96), "uniform", 140 + _i)],
+                           (64, 96), "native", ("add", (_op, 0), 1), _check, factory_args=([_op],)))
+
 MATMUL_CASES: List[Case] = [
     # the reference's own simulator test sizes (examples/metal_examples/*/ttlang: 256^3) and smaller
     Case("mm_single_128x256x64", "matmul", "singlecore_matmul", [((128, 256), "normal*0.0625", 0), ((256, 64), "normal*0.0625", 1)],
@@ -168,7 +187,7 @@ COMPOSITE_CASES: List[Case] = [
 
 
 def by_name(name: str) -> Case:
-    for c in CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES:
+    for c in CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES + MATH_CASES:
         if c.name == name:
             return c
     raise KeyError(name)

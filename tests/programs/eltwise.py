@@ -208,7 +208,8 @@ def mul_add_bcast(a, b, c, y):
 
 
 def make_unary_chain(op_names, fp32_dest_acc_en=False):
-    """Y = opN(...op1(A)...) + B on 1x1-tile blocks, single core; op names from ttl.math."""
+    """Y = opN(...op1(A)...) + B on 1x1-tile blocks, single core; op names from ttl.math, or
+    (name, scalar parameters...) for functions such as leaky_relu(x, slope)."""
     @_kernel((1, 1), fp32_dest_acc_en)
     def unary_chain(a, b, y):
         rt, ct = a.shape[0] // 32, a.shape[1] // 32
@@ -222,7 +223,10 @@ def make_unary_chain(op_names, fp32_dest_acc_en=False):
                 with a_cb.wait() as a_blk, b_cb.wait() as b_blk, y_cb.reserve() as y_blk:
                     v = a_blk
                     for name in op_names:
-                        v = getattr(ttl.math, name)(v)
+                        if isinstance(name, (tuple, list)):
+                            v = getattr(ttl.math, name[0])(v, *name[1:])
+                        else:
+                            v = getattr(ttl.math, name)(v)
                     y_blk.store(v + b_blk)
 
         @ttl.datamovement()

@@ -33,7 +33,7 @@ def test_descriptor_layout_matches_header():
     # ttlb_operand: ptr, ld, 2 x int32, 2 x int64; ttlb_instr: 2 x int16
     assert ctypes.sizeof(capi.Operand) == 40
     assert ctypes.sizeof(capi.Instr) == 4
-    assert ctypes.sizeof(capi.EltwiseDesc) == 16 + 6 * 40 + 32 * 4 + 8 + 8 + 32
+    assert ctypes.sizeof(capi.EltwiseDesc) == 16 + 6 * 40 + 32 * 4 + 8 + 8 + 32 + 8 * 4   # ... + imm[8]
 
 
 def test_init_without_gpu_returns_error():

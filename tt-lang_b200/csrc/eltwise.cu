@@ -195,7 +195,21 @@ __global__ void __launch_bounds__(256, 4) ttlb_eltwise_kernel(const __grid_const
 }
 
 bool is_binary(int op) { return op >= TTLB_OP_ADD && op <= TTLB_OP_MIN; }
-bool is_unary(int op) { return op >= TTLB_OP_EXP && op <= TTLB_OP_RELU; }
+bool is_unary(int op) {
+  return (op >= TTLB_OP_EXP && op <= TTLB_OP_RELU) || (op >= TTLB_OP_EXP2 && op <= TTLB_OP_HARDSIGMOID);
+}
+// Functions with scalar parameters: how many entries of `imm` they read (0: not such a function).
+int imm_params(int op) {
+  switch (op) {
+    case TTLB_OP_RSUB_IMM: case TTLB_OP_RELU_MAX: case TTLB_OP_RELU_MIN: case TTLB_OP_LEAKY_RELU: case TTLB_OP_ELU:
+      return 1;
+    case TTLB_OP_CELU: case TTLB_OP_HARDTANH: case TTLB_OP_SELU:
+      return 2;
+    case TTLB_OP_SOFTPLUS:
+      return 3;
+  }
+  return 0;
+}
 
 }  // namespace
 
@@ -263,6 +277,10 @@ static int validate_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, bool need
     } else if (op == TTLB_OP_PUSH) {
       if (++depth > 2)
         return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "eltwise: expression needs a stack deeper than 2");
+    } else if (const int np = imm_params(op)) {
+      if (arg < 0 || arg + np > TTLB_MAX_IMM)
+        return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: op %d reads parameters %d..%d of %d", pc, arg, arg + np - 1,
+                         TTLB_MAX_IMM);
     } else if (!is_unary(op)) {
       return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "eltwise: unknown opcode %d at %d", op, pc);
     }
@@ -316,6 +334,10 @@ extern "C" int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, void *str
     // AUTO falls back to the generic GPU kernel only when the run-time compiler is absent
     if (ctx->eltwise_mode == TTLB_ELTWISE_SPECIALISED || ttlb_eltwise_jit_available()) return rc;
   }
+  for (int pc = 0; pc < d->n_ops; ++pc)
+    if (d->ops[pc].opcode >= TTLB_OP_EXP2)
+      return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED,
+                       "eltwise: opcode %d is implemented by the specialised kernel only (NVRTC is needed)", d->ops[pc].opcode);
   const unsigned long long vpr = (unsigned long long)(d->cols / vec);
   if (vpr > 0xffffffffull) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "eltwise: row too long");
   EltParams p;

@@ -78,6 +78,7 @@ struct JitParams {
   void *out;
   long long out_ld, row0, col0;
   unsigned vpr, rows, bx_log2, pad;
+  float imm[TTLB_MAX_IMM];
 };
 
 const char *kPrelude = R"SRC(
@@ -85,7 +86,7 @@ typedef unsigned int u32;
 typedef long long i64;
 struct JitParams {
   const void* in[6]; i64 ld[6]; i64 roff[6]; i64 coff[6];
-  void* out; i64 out_ld, row0, col0; u32 vpr, rows, bx_log2, pad;
+  void* out; i64 out_ld, row0, col0; u32 vpr, rows, bx_log2, pad; float imm[8];
 };
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
   uint4 v; asm volatile("ld.global.cs.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
@@ -130,6 +131,34 @@ const char *unary_expr(int op) {
     case TTLB_OP_NEG: return "-a";
     case TTLB_OP_ABS: return "fabsf(a)";
     case TTLB_OP_RELU: return "(a < 0.f ? 0.f : a)";
+    case TTLB_OP_EXP2: return "exp2f(a)";
+    case TTLB_OP_EXPM1: return "expm1f(a)";
+    case TTLB_OP_LOGP1: return "log1pf(a)";
+    case TTLB_OP_SQUARE: return "a * a";
+    case TTLB_OP_RECIP: return "1.0f / a";
+    case TTLB_OP_TAN: return "tanf(a)";
+    case TTLB_OP_ATAN: return "atanf(a)";
+    case TTLB_OP_ATANH: return "atanhf(a)";
+    case TTLB_OP_SIN: return "sinf(a)";
+    case TTLB_OP_ASIN: return "asinf(a)";
+    case TTLB_OP_ASINH: return "asinhf(a)";
+    case TTLB_OP_COS: return "cosf(a)";
+    case TTLB_OP_ACOS: return "acosf(a)";
+    case TTLB_OP_ACOSH: return "acoshf(a)";
+    case TTLB_OP_GELU: return "0.5f * a * (1.0f + erff(a * 0.70710678118654752f))";
+    case TTLB_OP_SILU: return "a / (1.0f + expf(-a))";
+    case TTLB_OP_SOFTSIGN: return "a / (1.0f + fabsf(a))";
+    case TTLB_OP_HARDSIGMOID: return "fminf(fmaxf(a * (1.0f / 6.0f) + 0.5f, 0.0f), 1.0f)";
+    // with scalar parameters P0.. (entries of p.imm starting at the instruction's arg)
+    case TTLB_OP_RSUB_IMM: return "P0 - a";
+    case TTLB_OP_RELU_MAX: return "fmaxf(nan_min(a, P0), 0.0f)";
+    case TTLB_OP_RELU_MIN: return "fmaxf(nan_max(a, P0), 0.0f)";
+    case TTLB_OP_LEAKY_RELU: return "(a >= 0.0f ? a : a * P0)";
+    case TTLB_OP_ELU: return "(a > 0.0f ? a : P0 * expm1f(a))";
+    case TTLB_OP_CELU: return "(fmaxf(a, 0.0f) + fminf(0.0f, P0 * expm1f(a * P1)))";
+    case TTLB_OP_SOFTPLUS: return "(a * P0 > P2 ? a : log1pf(expf(a * P0)) * P1)";
+    case TTLB_OP_HARDTANH: return "fminf(fmaxf(a, P0), P1)";
+    case TTLB_OP_SELU: return "P0 * (a > 0.0f ? a : P1 * expm1f(a))";
   }
   return nullptr;
 }
@@ -199,6 +228,9 @@ void emit_ops(std::ostringstream &s, const ttlb_eltwise_desc *d, VarFn var, bool
       s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { const float a = acc[e], b = x[e]; acc[e] = "
         << be << "; }\n";
     } else if (const char *ue = unary_expr(op)) {
+      if (op >= TTLB_OP_RSUB_IMM)
+        s << "        const float P0 = p.imm[" << arg << "], P1 = p.imm[" << (arg + 1 < TTLB_MAX_IMM ? arg + 1 : arg)
+          << "], P2 = p.imm[" << (arg + 2 < TTLB_MAX_IMM ? arg + 2 : arg) << "]; (void)P1; (void)P2;\n";
       s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { const float a = acc[e]; acc[e] = " << ue
         << "; }\n";
     }
@@ -380,6 +412,7 @@ int ttlb_eltwise_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_e
   p.col0 = d->col0;
   p.vpr = (unsigned)(d->cols / vec);
   p.rows = (unsigned)d->rows;
+  for (int k = 0; k < TTLB_MAX_IMM; ++k) p.imm[k] = d->imm[k];
   unsigned bx_log2 = 0;
   while (bx_log2 < 8 && (1u << bx_log2) < p.vpr) ++bx_log2;
   p.bx_log2 = bx_log2;
@@ -639,6 +672,7 @@ int ttlb_reduce_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_re
   p.col0 = d->col0;
   p.vpr = (unsigned)(d->cols / vec);
   p.rows = (unsigned)d->rows;
+  for (int k = 0; k < TTLB_MAX_IMM; ++k) p.imm[k] = d->imm[k];
   q.scaler = r->scaler;
   q.out = r->out;
   q.out_ld = r->out_ld;

@@ -20,14 +20,24 @@ TTLB_ERR_TIMEOUT = -4
 TTLB_ERR_NCCL = -5
 
 TTLB_BF16, TTLB_F32, TTLB_BFP8_B = 0, 1, 2
-TTLB_MAX_IN, TTLB_MAX_OPS, TTLB_ARG_STACK = 6, 32, -1
+TTLB_MAX_IN, TTLB_MAX_OPS, TTLB_ARG_STACK, TTLB_MAX_IMM = 6, 32, -1, 8
 IDX_SAME, IDX_ZERO, IDX_TILE, IDX_FIRST = 0, 1, 2, 3
 
 OPCODES = {
     "load": 0, "add": 1, "sub": 2, "rsub": 3, "mul": 4, "div": 5, "rdiv": 6, "max": 7, "min": 8,
     "exp": 16, "log": 17, "sqrt": 18, "rsqrt": 19, "tanh": 20, "sigmoid": 21, "neg": 22, "abs": 23, "relu": 24,
     "push": 32,
+    # the specification's Appendix B beyond the compiler's op table (specialised kernel only)
+    "exp2": 40, "expm1": 41, "logp1": 42, "square": 43, "recip": 44, "tan": 45, "atan": 46, "atanh": 47, "sin": 48,
+    "asin": 49, "asinh": 50, "cos": 51, "acos": 52, "acosh": 53, "gelu": 54, "silu": 55, "softsign": 56,
+    "hardsigmoid": 57,
+    # with scalar parameters (arg = index of the first one in EltwiseDesc.imm)
+    "rsub_imm": 64, "relu_max": 65, "relu_min": 66, "leaky_relu": 67, "elu": 68, "celu": 69, "softplus": 70,
+    "hardtanh": 71, "selu": 72,
 }
+# number of scalar parameters of the parametrised functions
+IMM_PARAMS = {"rsub_imm": 1, "relu_max": 1, "relu_min": 1, "leaky_relu": 1, "elu": 1, "celu": 2, "softplus": 3,
+              "hardtanh": 2, "selu": 2}
 
 
 class Operand(C.Structure):
@@ -43,7 +53,8 @@ class EltwiseDesc(C.Structure):
     _fields_ = [("dtype", C.c_int32), ("round_each_op", C.c_int32), ("n_in", C.c_int32), ("n_ops", C.c_int32),
                 ("inp", Operand * TTLB_MAX_IN), ("ops", Instr * TTLB_MAX_OPS),
                 ("out", C.c_void_p), ("out_ld", C.c_int64),
-                ("row0", C.c_int64), ("col0", C.c_int64), ("rows", C.c_int64), ("cols", C.c_int64)]
+                ("row0", C.c_int64), ("col0", C.c_int64), ("rows", C.c_int64), ("cols", C.c_int64),
+                ("imm", C.c_float * TTLB_MAX_IMM)]
 
 
 REDUCE_SUM, REDUCE_MAX = 0, 1

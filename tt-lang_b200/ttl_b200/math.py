@@ -82,6 +82,79 @@ abs = _unary("abs")  # noqa: A001 - reference spelling
 relu = _unary("relu")
 
 
+# The rest of the specification's Appendix B (docs/sphinx/specs/TTLangSpecification.md:700-748); neither the
+# reference compiler's op table nor its simulator has these yet.
+exp2 = _unary("exp2")
+expm1 = _unary("expm1")
+logp1 = _unary("logp1")
+square = _unary("square")
+recip = _unary("recip")
+tan = _unary("tan")
+atan = _unary("atan")
+atanh = _unary("atanh")
+sin = _unary("sin")
+asin = _unary("asin")
+asinh = _unary("asinh")
+cos = _unary("cos")
+acos = _unary("acos")
+acosh = _unary("acosh")
+gelu = _unary("gelu")
+silu = _unary("silu")
+softsign = _unary("softsign")
+hardsigmoid = _unary("hardsigmoid")
+
+
+def _with_params(name: str, op: str, block: Any, *params: Any) -> Block:
+    for v in params:
+        if isinstance(v, bool) or not isinstance(v, (int, float)):
+            raise TypeError(f"{name}(): scalar parameters must be numbers, got {type(v).__name__}")
+    return _as_block(block)._unary(op, tuple(float(v) for v in params))
+
+
+def rsub(a: Any, b: Any) -> Block:
+    """`b - a` with a scalar `b`."""
+    return _with_params("rsub", "rsub_imm", a, b)
+
+
+def relu_max(expr: Any, upper_limit: Any) -> Block:
+    """relu(min(x, upper_limit))."""
+    return _with_params("relu_max", "relu_max", expr, upper_limit)
+
+
+def relu_min(expr: Any, lower_limit: Any) -> Block:
+    """relu(max(x, lower_limit))."""
+    return _with_params("relu_min", "relu_min", expr, lower_limit)
+
+
+def leaky_relu(expr: Any, slope: Any) -> Block:
+    return _with_params("leaky_relu", "leaky_relu", expr, slope)
+
+
+def prelu(expr: Any, alpha: Any) -> Block:
+    """PReLU with one scalar weight: the same function as leaky_relu."""
+    return _with_params("prelu", "leaky_relu", expr, alpha)
+
+
+def elu(expr: Any, slope: Any) -> Block:
+    return _with_params("elu", "elu", expr, slope)
+
+
+def celu(expr: Any, alpha: Any, alpha_recip: Any) -> Block:
+    return _with_params("celu", "celu", expr, alpha, alpha_recip)
+
+
+def softplus(expr: Any, beta: Any, beta_reciprocal: Any, threshold: Any) -> Block:
+    return _with_params("softplus", "softplus", expr, beta, beta_reciprocal, threshold)
+
+
+def hardtanh(expr: Any, min: Any, max: Any) -> Block:  # noqa: A002 - reference spelling
+    return _with_params("hardtanh", "hardtanh", expr, min, max)
+
+
+def selu(expr: Any, scale: Any, alpha: Any) -> Block:
+    return _with_params("selu", "selu", expr, scale, alpha)
+
+
 def max(a: Any, b: Any) -> Block:  # noqa: A001 - reference spelling
     return _as_block(a)._binary(b, "max")
 

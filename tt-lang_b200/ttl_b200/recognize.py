@@ -35,7 +35,9 @@ class Unsupported(NotImplementedError):
 
 
 _REVERSE = {"add": "add", "mul": "mul", "max": "max", "min": "min", "sub": "rsub", "div": "rdiv"}
-_UNARY = {"exp", "log", "sqrt", "rsqrt", "tanh", "sigmoid", "neg", "abs", "relu"}
+_UNARY = {"exp", "log", "sqrt", "rsqrt", "tanh", "sigmoid", "neg", "abs", "relu",
+          "exp2", "expm1", "logp1", "square", "recip", "tan", "atan", "atanh", "sin", "asin", "asinh", "cos", "acos",
+          "acosh", "gelu", "silu", "softsign", "hardsigmoid"} | set(capi.IMM_PARAMS)
 _BINARY = {"add", "sub", "mul", "div", "max", "min"}
 
 
@@ -173,6 +175,7 @@ class _Lin:
         self.w, self.table = w, table
         self.inputs: List[Tuple[int, int, int, int, int]] = []
         self.ops: List[Tuple[str, int]] = []
+        self.imms: List[float] = []    # scalar parameters of functions such as leaky_relu, in op order
 
     def slot(self, leaf: Leaf) -> int:
         rm, ro, cm, co = _classify(leaf, self.w)
@@ -195,7 +198,15 @@ class _Lin:
             if e.op not in _UNARY:
                 raise Unsupported(f"unary op {e.op}")
             self.emit(e.x)
-            self.ops.append((e.op, 0))
+            if e.op in capi.IMM_PARAMS:
+                if len(e.params) != capi.IMM_PARAMS[e.op]:
+                    raise Unsupported(f"{e.op} takes {capi.IMM_PARAMS[e.op]} scalar parameter(s)")
+                if len(self.imms) + len(e.params) > capi.TTLB_MAX_IMM:
+                    raise Unsupported(f"expression has more than {capi.TTLB_MAX_IMM} scalar parameters")
+                self.ops.append((e.op, len(self.imms)))
+                self.imms.extend(e.params)
+            else:
+                self.ops.append((e.op, 0))
         elif isinstance(e, Bin):
             if e.op not in _BINARY:
                 raise Unsupported(f"binary op {e.op} inside an element-wise expression")
@@ -271,13 +282,18 @@ def _dtype_code(dt: Any) -> int:
 
 class EltwiseLaunch:
     def __init__(self, out_index: int, rect: Tuple[int, int, int, int], inputs: List[Tuple[int, int, int, int, int]],
-                 ops: List[Tuple[str, int]], dtype: Any, round_each_op: bool, out_degenerate: Tuple[bool, bool]):
+                 ops: List[Tuple[str, int]], dtype: Any, round_each_op: bool, out_degenerate: Tuple[bool, bool],
+                 imms: Sequence[float] = ()):
+        self.imms = tuple(imms)
         self.out_index, self.rect, self.inputs, self.ops = out_index, rect, inputs, ops
         self.dtype, self.round_each_op, self.out_degenerate = dtype, round_each_op, out_degenerate
 
     def describe(self) -> Dict[str, Any]:
-        return {"kind": "eltwise", "out": self.out_index, "rect_tiles": self.rect, "inputs": self.inputs,
-                "ops": self.ops, "round_each_op": self.round_each_op}
+        d = {"kind": "eltwise", "out": self.out_index, "rect_tiles": self.rect, "inputs": self.inputs,
+             "ops": self.ops, "round_each_op": self.round_each_op}
+        if self.imms:
+            d["imm"] = list(self.imms)
+        return d
 
     def desc(self, tensors: Sequence[_ttnn.Tensor]) -> capi.EltwiseDesc:
         d = capi.EltwiseDesc()
@@ -292,6 +308,8 @@ class EltwiseLaunch:
             d.inp[k].col_mode, d.inp[k].col_off = cm, co
         for k, (op, arg) in enumerate(self.ops):
             d.ops[k].opcode, d.ops[k].arg = capi.OPCODES[op], arg
+        for k, v in enumerate(self.imms):
+            d.imm[k] = v
         o = _torch_of(tensors[self.out_index])
         d.out = o.data_ptr()
         d.out_ld = o.stride(0) if o.shape[0] > 1 else o.shape[1]
@@ -313,6 +331,8 @@ class EltwiseLaunch:
             d.inp[k].col_mode, d.inp[k].col_off = cm, co
         for k, (op, arg) in enumerate(self.ops):
             d.ops[k].opcode, d.ops[k].arg = capi.OPCODES[op], arg
+        for k, v in enumerate(self.imms):
+            d.imm[k] = v
         o = tensors[self.out_index]._tensor
         d.out_ld = o.stride(0) if o.shape[0] > 1 else o.shape[1]
         r0, r1, c0, c1 = self.rect
@@ -330,14 +350,15 @@ class ReduceLaunch:
 
     def __init__(self, out_index: int, rect: Tuple[int, int, int, int], op: str, dims: Tuple[int, ...],
                  extent: Tuple[int, int], inputs: List[Tuple[int, int, int, int, int]], ops: List[Tuple[str, int]],
-                 scaler: Optional[Tuple[int, int, int]], dtype: Any, round_each_op: bool):
+                 scaler: Optional[Tuple[int, int, int]], dtype: Any, round_each_op: bool, imms: Sequence[float] = ()):
+        self.imms = tuple(imms)
         self.out_index, self.rect, self.op, self.dims, self.extent = out_index, rect, op, dims, extent
         self.inputs, self.ops, self.scaler, self.dtype, self.round_each_op = inputs, ops, scaler, dtype, round_each_op
 
     def describe(self) -> Dict[str, Any]:
         return {"kind": "reduce_" + self.op, "dims": list(self.dims), "out": self.out_index, "rect_tiles": self.rect,
                 "reduced_tiles": self.extent, "inputs": self.inputs, "ops": self.ops, "scaler": self.scaler,
-                "round_each_op": self.round_each_op}
+                "round_each_op": self.round_each_op, "imm": list(self.imms)}
 
     def region(self) -> Tuple[int, int, int, int]:
         """(row0, rows, col0, cols) of the values reduced, in elements of the program's index space."""
@@ -361,6 +382,8 @@ class ReduceLaunch:
             d.inp[k].col_mode, d.inp[k].col_off = cm, co
         for k, (op, arg) in enumerate(self.ops):
             d.ops[k].opcode, d.ops[k].arg = capi.OPCODES[op], arg
+        for k, v in enumerate(self.imms):
+            d.imm[k] = v
         d.row0, d.rows, d.col0, d.cols = self.region()
         r.op = capi.REDUCE_SUM if self.op == "sum" else capi.REDUCE_MAX
         r.dims = (capi.REDUCE_ROWS if 0 in self.dims else 0) | (capi.REDUCE_COLS if 1 in self.dims else 0)
@@ -537,7 +560,7 @@ def _recognise_reduce(w: Write, terms: List[Red], table: _TensorTable, oi: int, 
     # the blocks of the terms must tile a rectangle of the reduced dims
     deltas = []
     for lin in per_term:
-        if lin.ops != base.ops or len(lin.inputs) != len(base.inputs):
+        if lin.ops != base.ops or lin.imms != base.imms or len(lin.inputs) != len(base.inputs):
             raise Unsupported("accumulated reductions must reduce the same expression")
         dr = dc = None
         for a, b in zip(lin.inputs, base.inputs):
@@ -566,7 +589,7 @@ def _recognise_reduce(w: Write, terms: List[Red], table: _TensorTable, oi: int, 
                    for (ti, rm, ro, cm, co) in base.inputs)
     extent = (t0.x.shape[0] * nr if 0 in dims else 0, t0.x.shape[1] * nc if 1 in dims else 0)
     anchor = (w.r0 if 0 in dims else -1, w.c0 if 1 in dims else -1)
-    return (oi, op, dims, extent, inputs, tuple(base.ops), sc_key, anchor)
+    return (oi, op, dims, extent, inputs, tuple(base.ops), sc_key, anchor, tuple(base.imms))
 
 
 def _contains_red(e: Expr) -> bool:
@@ -605,7 +628,7 @@ def _lower_reductions(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tens
             return hit
         if isinstance(e, Un):
             x, l = go(e.x)
-            res: Tuple[Expr, int] = (e if x is e.x else Un(e.op, x), l)
+            res: Tuple[Expr, int] = (e if x is e.x else Un(e.op, x, e.params), l)
         elif isinstance(e, Bin):
             a, la = go(e.a)
             b, lb = go(e.b)
@@ -694,7 +717,7 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
                 for dim in (0, 1):
                     if w.tensor.shape[dim] == 1 and t.shape[dim] != 1:
                         raise Unsupported("a degenerate output dimension needs degenerate operands")
-            key = ("elt", oi, tuple(lin.inputs), tuple(lin.ops))
+            key = ("elt", oi, tuple(lin.inputs), tuple(lin.ops), tuple(lin.imms))
             elt_meta[key] = (odt, (w.tensor.shape[0] == 1, w.tensor.shape[1] == 1))
         grid = cover.setdefault(oi, np.zeros((tr, tc), dtype=bool))
         covered = grid[w.r0:w.r1, w.c0:w.c1]
@@ -709,16 +732,18 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
 
     launches: List[Tuple[int, Any]] = []
     for key, rects in elt_groups.items():
-        _, oi, inputs, ops = key
+        _, oi, inputs, ops, imms = key
         odt, degen = elt_meta[key]
         for rect in merge_rects(rects):
             launches.append((level_of[key], EltwiseLaunch(oi, rect, list(inputs), list(ops), odt,
-                                                          round_each_op=not fp32_intermediates, out_degenerate=degen)))
+                                                          round_each_op=not fp32_intermediates, out_degenerate=degen,
+                                                          imms=imms)))
     for key, rects in red_groups.items():
-        _, oi, op, dims, extent, inputs, ops, sc_key, _anchor = key
+        _, oi, op, dims, extent, inputs, ops, sc_key, _anchor, imms = key
         for rect in merge_rects(rects):
             launches.append((level_of[key], ReduceLaunch(oi, rect, op, dims, extent, list(inputs), list(ops), sc_key,
-                                                         out_tensors[oi].dtype, round_each_op=not fp32_intermediates)))
+                                                         out_tensors[oi].dtype, round_each_op=not fp32_intermediates,
+                                                         imms=imms)))
     for key, rects in mm_groups.items():
         _, ai, bi, oi, kt, b8, ci = key
         f32 = out_tensors[oi].dtype == torch.float32

@@ -69,10 +69,13 @@ class Zero(Expr):
 
 
 class Un(Expr):
-    __slots__ = ("op", "x")
+    """Element-wise function of one block; `params` are the scalar parameters of functions such as
+    leaky_relu(x, slope)."""
 
-    def __init__(self, op: str, x: Expr):
-        self.op, self.x, self.shape = op, x, x.shape
+    __slots__ = ("op", "x", "params")
+
+    def __init__(self, op: str, x: Expr, params: Tuple[float, ...] = ()):
+        self.op, self.x, self.params, self.shape = op, x, params, x.shape
 
 
 class Bin(Expr):
@@ -377,8 +380,8 @@ class Block:
             return Block(self._shape, self.dtype, e, "FULL", "temp", temporary=True)
         raise TypeError("block ** block is not supported by the B200 backend")
 
-    def _unary(self, op: str) -> "Block":
-        return Block(self._shape, self.dtype, Un(op, self.value()), "FULL", "temp", temporary=True)
+    def _unary(self, op: str, params: Tuple[float, ...] = ()) -> "Block":
+        return Block(self._shape, self.dtype, Un(op, self.value(), params), "FULL", "temp", temporary=True)
 
 
 class _BlockContext:
