@@ -186,8 +186,17 @@ COMPOSITE_CASES: List[Case] = [
 ]
 
 
+# matmul whose result is used further: product through an intermediate circular buffer, then bias + activation.
+# `expr` is the epilogue over [product, further inputs...]
+EPILOGUE_CASES: List[Case] = [
+    Case("linear_relu_96x160x128", "matmul", "linear_relu",
+         [((96, 160), "normal*0.08", 11), ((160, 128), "normal*0.08", 12), ((1, 128), "normal", 13)],
+         (96, 128), "native", ("relu", ("add", 0, 1)), "rel1e-2"),
+]
+
+
 def by_name(name: str) -> Case:
-    for c in CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES + MATH_CASES:
+    for c in CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES + MATH_CASES + EPILOGUE_CASES:
         if c.name == name:
             return c
     raise KeyError(name)

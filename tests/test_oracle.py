@@ -16,6 +16,9 @@ REFERENCE = Path("/root/reference")
 
 def oracle_output(case):
     ins = case.make_inputs()
+    if case.module == "matmul" and case.expr is not None:   # product, then an element-wise epilogue
+        prod = tile_oracle.matmul_tiles(ins[0], ins[1], case.mode)
+        return tile_oracle.eval_expression(case.expr, [prod] + ins[2:], case.out_shape, case.mode)
     if case.module == "matmul":
         return tile_oracle.matmul_tiles(ins[0], ins[1], case.mode, bias=ins[2] if len(ins) > 2 else None)
     if case.reduce is not None:

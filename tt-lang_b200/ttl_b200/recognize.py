@@ -528,7 +528,7 @@ def _recognise_reduce(w: Write, terms: List[Red], table: _TensorTable, oi: int, 
         if t.op != op or t.dims != dims or t.x.shape != t0.x.shape:
             raise Unsupported("accumulated reductions must be the same reduction of equal-shape blocks")
         if _contains_matmul(t.x) or _contains_red(t.x):
-            raise Unsupported("a reduction of a matmul or of another reduction in one expression is not supported yet")
+            raise Unsupported("a reduction of a matmul, or accumulated reductions of reductions, are not supported yet")
         k = None
         if t.scaler is not None:
             sl = _unwrap(t.scaler)
@@ -626,6 +626,23 @@ def _lower_reductions(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tens
         hit = memo.get(id(e))
         if hit is not None:
             return hit
+        mm_terms = list(e.terms) if isinstance(e, Acc) else [e]
+        if len(mm_terms) > 1 and isinstance(mm_terms[0], Leaf):
+            mm_terms = mm_terms[1:]     # accumulation that starts from a bias block
+        if mm_terms and all(isinstance(t, Bin) and t.op == "matmul" for t in mm_terms):
+            # a block matmul whose result is used further (bias / activation epilogues): the product goes to a
+            # temporary of the output's shape, in the output's element type like a block in a circular buffer
+            if e.shape != (w.r1 - w.r0, w.c1 - w.c0) or 1 in w.tensor.shape:
+                raise Unsupported("a matmul inside an expression must produce the block it is stored into")
+            key = (oi, slot[0], "mm", ())
+            slot[0] += 1
+            t = temps.get(key)
+            if t is None:
+                t = temps[key] = table.new_temp(tuple(w.tensor.shape), w.tensor)
+            out.append((Write(t, w.r0, w.r1, w.c0, w.c1, e, w.core), 0))
+            res0: Tuple[Expr, int] = (Leaf(t, w.r0, w.r1, w.c0, w.c1), 1)
+            memo[id(e)] = res0
+            return res0
         if isinstance(e, Un):
             x, l = go(e.x)
             res: Tuple[Expr, int] = (e if x is e.x else Un(e.op, x, e.params), l)
@@ -678,7 +695,7 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
     temps: Dict[Any, _ttnn.Tensor] = {}
     writes: List[Tuple[Write, int]] = []
     for w in trace.writes:
-        if _reduce_terms(w) is None and _matmul_terms(w) is None and not _contains_matmul(w.expr) and _contains_red(w.expr):
+        if _reduce_terms(w) is None and _matmul_terms(w) is None and (_contains_matmul(w.expr) or _contains_red(w.expr)):
             expr, level = _lower_reductions(w, table, temps, writes)
             writes.append((Write(w.tensor, w.r0, w.r1, w.c0, w.c1, expr, w.core), level))
         else:
