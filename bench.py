@@ -432,7 +432,10 @@ def run_sharded(args):
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in),
                     "d2h_bytes_per_step": int(result_holder["host"].numel() * 2) if "host" in result_holder else 0,
-                    "ms_per_step": e2e_ms, "steps": args.e2e_steps},
+                    "ms_per_step": e2e_ms, "steps": args.e2e_steps,
+                    "api": (f"ttl_b200.run_streamed(kernel, pinned inputs, pinned output, chunks={args.e2e_chunks}): "
+                            "host->HBM, kernel, HBM->host overlapped per row chunk" if args.e2e_chunks > 1 else
+                            "ttnn.from_torch, kernel call, ttnn.to_torch(out=pinned), one after the other")},
             "gpu_launches": launches,
             "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
         }
@@ -706,6 +709,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="fused_eltwise_bcast_8192")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--e2e-chunks", type=int, default=8,
+                    help="row chunks of the end-to-end leg (1: plain from_torch / call / to_torch, no overlap)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (for profiler runs)")
     ap.add_argument("--eltwise-mode", default="auto", choices=["auto", "generic", "specialised"])
@@ -817,6 +822,9 @@ def main():
     d2h = host_out.numel() * host_out.element_size()
 
     def e2e_step():
+        if args.e2e_chunks > 1:   # row chunks: copy-in, kernel and copy-out overlapped on three streams
+            ttl_b200.run_streamed(program, host, host_out, chunks=args.e2e_chunks)
+            return
         tensors = [ttnn.from_torch(t) for t in host]
         y = ttnn.empty((N, N), dtype=ttnn.bfloat16)
         program(*tensors, y)
