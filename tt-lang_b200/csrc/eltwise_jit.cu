@@ -245,9 +245,11 @@ void emit_ops(std::ostringstream &s, const ttlb_eltwise_desc *d, VarFn var, bool
 // Rows handled per loop iteration: all their loads are issued before any arithmetic, so a
 // thread keeps U x (streaming operands) 16-byte loads in flight.  Bounded by registers.
 int rows_per_iteration(const ttlb_eltwise_desc *d) {
+  // operands that cost a 16-byte load per row; one element per row (a column vector) is a 2- or 4-byte load
   int streaming = 0;
   for (int k = 0; k < d->n_in; ++k)
-    if (d->in[k].row_mode != TTLB_IDX_ZERO) ++streaming;
+    if (d->in[k].row_mode != TTLB_IDX_ZERO && (d->in[k].col_mode == TTLB_IDX_SAME || d->in[k].col_mode == TTLB_IDX_TILE))
+      ++streaming;
   int u = 8 / (streaming > 0 ? streaming : 1);
   return u < 1 ? 1 : u > 4 ? 4 : u;
 }

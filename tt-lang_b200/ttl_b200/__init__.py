@@ -13,7 +13,7 @@ from __future__ import annotations
 
 import sys
 
-from . import ttl, ttnn  # noqa: F401
+from . import profile, ttl, ttnn  # noqa: F401
 from .capi import BackendError  # noqa: F401
 from .math import set_hardware_broadcast  # noqa: F401
 from .recognize import Unsupported  # noqa: F401

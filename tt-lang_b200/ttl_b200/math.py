@@ -12,7 +12,7 @@ from __future__ import annotations
 
 from typing import Any, List, Optional
 
-from .trace import Block, Leaf, Red, _as_block
+from .trace import Block, Leaf, Red, _as_block, _tag
 
 
 # Which meaning `broadcast` has on FULL (non-degenerate) tiles.  The two reference front ends disagree:
@@ -180,7 +180,7 @@ def _reduce(op: str, block: Any, scaler: Any, dims: Optional[List[int]]) -> Bloc
         if sb.shape != (1, 1):
             raise ValueError(f"reduce_{op}(): the scaler must be a block of one tile, got shape {sb.shape}")
         sc = sb.value()
-    e = Red(op, b.value(), sc, ds)
+    e = _tag(Red(op, b.value(), sc, ds))
     return Block(e.shape, b.dtype, e, "FULL", "temp", temporary=True)
 
 

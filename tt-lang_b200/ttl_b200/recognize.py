@@ -25,7 +25,7 @@ import torch
 
 from . import capi
 from . import ttnn as _ttnn
-from .trace import Acc, Bin, Expr, Leaf, Red, Trace, Un, Write, Zero
+from .trace import PROFILE, Acc, Bin, Expr, Leaf, Red, Trace, Un, Write, Zero
 
 TILE = 32
 
@@ -65,6 +65,35 @@ def merge_rects(rects: Sequence[Tuple[int, int, int, int]]) -> List[Tuple[int, i
                 cur.append(r)
         if len(cur) == n:
             return sorted(cur)
+
+
+def _lines_of(w: Write) -> List[Tuple[str, int]]:
+    """Program lines (file, line) that made write `w`: the copy to the output tensor and every op, reduction,
+    accumulating store and copy-in of its expression (recorded while profiling is on)."""
+    seen: Dict[int, None] = {}
+    lines: Dict[Tuple[str, int], None] = {}
+    if w.line is not None:
+        lines[w.line] = None
+    stack = [w.expr]
+    while stack:
+        x = stack.pop()
+        if id(x) in seen:
+            continue
+        seen[id(x)] = None
+        ln = getattr(x, "line", None)
+        if ln is not None:
+            lines[ln] = None
+        if isinstance(x, Bin):
+            stack += [x.a, x.b]
+        elif isinstance(x, Un):
+            stack.append(x.x)
+        elif isinstance(x, Acc):
+            stack.extend(x.terms)
+        elif isinstance(x, Red):
+            stack.append(x.x)
+            if x.scaler is not None:
+                stack.append(x.scaler)
+    return list(lines)
 
 
 def _contains_matmul(e: Expr) -> bool:
@@ -467,6 +496,10 @@ class Plan:
             if not t._tensor.is_cuda or t._tensor.device.index != dev:
                 t._tensor = torch.zeros(t._tensor.shape, dtype=t._tensor.dtype, device=torch.device("cuda", dev))
         ix = _Indexed(allt, self.temps)
+        if PROFILE.enabled:
+            from . import profile
+            profile.run_timed(self, ctx, ix, stream)
+            return
         for l in self.launches:
             l.run(ctx, ix, stream)
 
@@ -620,6 +653,12 @@ def _lower_reductions(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tens
     slot = [0]
     oi = table.index(w.tensor)
 
+    def like(new: Expr, old: Expr) -> Expr:   # a rebuilt node keeps the program line of the node it replaces
+        ln = getattr(old, "line", None)
+        if ln is not None:
+            new.line = ln
+        return new
+
     def go(e: Expr) -> Tuple[Expr, int]:
         if isinstance(e, (Leaf, Zero)):
             return e, 0
@@ -645,14 +684,14 @@ def _lower_reductions(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tens
             return res0
         if isinstance(e, Un):
             x, l = go(e.x)
-            res: Tuple[Expr, int] = (e if x is e.x else Un(e.op, x, e.params), l)
+            res: Tuple[Expr, int] = (e if x is e.x else like(Un(e.op, x, e.params), e), l)
         elif isinstance(e, Bin):
             a, la = go(e.a)
             b, lb = go(e.b)
-            res = (e if (a is e.a and b is e.b) else Bin(e.op, a, b, e.shape), max(la, lb))
+            res = (e if (a is e.a and b is e.b) else like(Bin(e.op, a, b, e.shape), e), max(la, lb))
         elif isinstance(e, Acc):
             parts = [go(t) for t in e.terms]
-            res = (Acc([p[0] for p in parts], e.shape), max(p[1] for p in parts))
+            res = (like(Acc([p[0] for p in parts], e.shape), e), max(p[1] for p in parts))
         elif isinstance(e, Red):
             if len(e.dims) != 1:
                 raise Unsupported("a reduction over both dimensions inside a larger expression is not supported: "
@@ -669,7 +708,8 @@ def _lower_reductions(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tens
                 shape = (w.tensor.shape[0], 1) if kept == 0 else (1, w.tensor.shape[1])
                 t = temps[key] = table.new_temp(shape, w.tensor)
             region = (w.r0, w.r1, 0, 1) if kept == 0 else (0, 1, w.c0, w.c1)
-            out.append((Write(t, region[0], region[1], region[2], region[3], Red(e.op, x, e.scaler, e.dims), w.core), l))
+            out.append((Write(t, region[0], region[1], region[2], region[3], like(Red(e.op, x, e.scaler, e.dims), e),
+                              w.core), l))
             res = (Leaf(t, *region), l + 1)
         else:
             raise Unsupported(f"cannot lower {type(e).__name__}")
@@ -697,10 +737,11 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
     for w in trace.writes:
         if _reduce_terms(w) is None and _matmul_terms(w) is None and (_contains_matmul(w.expr) or _contains_red(w.expr)):
             expr, level = _lower_reductions(w, table, temps, writes)
-            writes.append((Write(w.tensor, w.r0, w.r1, w.c0, w.c1, expr, w.core), level))
+            writes.append((Write(w.tensor, w.r0, w.r1, w.c0, w.c1, expr, w.core, w.line), level))
         else:
             writes.append((w, 0))
     level_of: Dict[Any, int] = {}
+    lines_of: Dict[Any, Dict[Tuple[str, int], int]] = {}   # per launch key: program line -> writes it took part in
     for w, level in writes:
         oi = table.index(w.tensor)
         out_tensors[oi] = w.tensor
@@ -746,21 +787,28 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
         seen[(oi, region)] = key
         {"mm": mm_groups, "elt": elt_groups, "red": red_groups}[key[0]].setdefault(key, []).append(region)
         level_of[key] = max(level_of.get(key, 0), level)
+        if PROFILE.enabled:
+            per_key = lines_of.setdefault(key, {})
+            for ln in _lines_of(w):
+                per_key[ln] = per_key.get(ln, 0) + 1
 
-    launches: List[Tuple[int, Any]] = []
+    class _Launches(list):   # appending a launch also hands it the program lines of its key
+        def add(self, key: Any, launch: Any) -> None:
+            launch.lines = lines_of.get(key, {})
+            self.append((level_of[key], launch))
+
+    launches = _Launches()
     for key, rects in elt_groups.items():
         _, oi, inputs, ops, imms = key
         odt, degen = elt_meta[key]
         for rect in merge_rects(rects):
-            launches.append((level_of[key], EltwiseLaunch(oi, rect, list(inputs), list(ops), odt,
-                                                          round_each_op=not fp32_intermediates, out_degenerate=degen,
-                                                          imms=imms)))
+            launches.add(key, EltwiseLaunch(oi, rect, list(inputs), list(ops), odt,
+                                            round_each_op=not fp32_intermediates, out_degenerate=degen, imms=imms))
     for key, rects in red_groups.items():
         _, oi, op, dims, extent, inputs, ops, sc_key, _anchor, imms = key
         for rect in merge_rects(rects):
-            launches.append((level_of[key], ReduceLaunch(oi, rect, op, dims, extent, list(inputs), list(ops), sc_key,
-                                                         out_tensors[oi].dtype, round_each_op=not fp32_intermediates,
-                                                         imms=imms)))
+            launches.add(key, ReduceLaunch(oi, rect, op, dims, extent, list(inputs), list(ops), sc_key,
+                                           out_tensors[oi].dtype, round_each_op=not fp32_intermediates, imms=imms))
     for key, rects in mm_groups.items():
         _, ai, bi, oi, kt, b8, ci = key
         f32 = out_tensors[oi].dtype == torch.float32
@@ -770,7 +818,7 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
             gl = GemmLaunch(ai, bi, oi, rect, kt, b8, ci)
             if f32:
                 gl.kind = "matmul_f32"
-            launches.append((level_of[key], gl))
+            launches.add(key, gl)
     # a launch that reads a temporary runs after the launch that fills it
     ordered = [l for _, l in sorted(launches, key=lambda p: p[0])]
     return Plan(ordered, table.extras, len(table.args), table.temps)

@@ -27,6 +27,8 @@ Semantics kept from the simulator:
 from __future__ import annotations
 
 import copy as _copy
+import os
+import sys
 import threading
 import types
 from collections import deque
@@ -42,8 +44,34 @@ MAX_CBS = 32
 # Expression IR (block level: every node stands for a grid of tiles)
 # --------------------------------------------------------------------------- #
 class Expr:
-    __slots__ = ("shape",)
+    __slots__ = ("shape", "line")
     shape: Tuple[int, int]
+
+
+class _ProfileSwitch:
+    """While `enabled`, expression nodes and writes remember the program line that created them, so that a
+    launch can be reported against the source lines it implements (profile.py)."""
+    enabled = False
+
+
+PROFILE = _ProfileSwitch()
+_PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+
+
+def _site() -> Optional[Tuple[str, int]]:
+    """(file, line) of the tile-program statement being executed: the innermost frame outside this package."""
+    if not PROFILE.enabled:
+        return None
+    f = sys._getframe(1)
+    while f is not None and os.path.abspath(f.f_code.co_filename).startswith(_PKG_DIR):
+        f = f.f_back
+    return (f.f_code.co_filename, f.f_lineno) if f is not None else None
+
+
+def _tag(e: "Expr") -> "Expr":
+    if PROFILE.enabled:
+        e.line = _site()
+    return e
 
 
 class Leaf(Expr):
@@ -110,10 +138,12 @@ class Red(Expr):
 class Write:
     """`tensor[r0:r1, c0:c1] <- expr` (tile coordinates)."""
 
-    __slots__ = ("tensor", "r0", "r1", "c0", "c1", "expr", "core")
+    __slots__ = ("tensor", "r0", "r1", "c0", "c1", "expr", "core", "line")
 
-    def __init__(self, tensor: "_ttnn.Tensor", r0: int, r1: int, c0: int, c1: int, expr: Expr, core: int):
+    def __init__(self, tensor: "_ttnn.Tensor", r0: int, r1: int, c0: int, c1: int, expr: Expr, core: int,
+                 line: Optional[Tuple[str, int]] = None):
         self.tensor, self.r0, self.r1, self.c0, self.c1, self.expr, self.core = tensor, r0, r1, c0, c1, expr, core
+        self.line = line
 
 
 def infer_broadcast_shape(left: Tuple[int, ...], right: Tuple[int, ...]) -> Tuple[int, int]:
@@ -340,12 +370,12 @@ class Block:
         v = src.value()
         if acc:
             if self.state == "MW":  # first accumulating store assigns
-                self.expr = Acc([v], self._shape)
+                self.expr = _tag(Acc([v], self._shape))
             elif isinstance(self.expr, Acc):
                 self.expr.terms.append(v)
             else:
                 assert self.expr is not None
-                self.expr = Acc([self.expr, v], self._shape)
+                self.expr = _tag(Acc([self.expr, v], self._shape))
             self.state = "ACC"
         else:
             self.expr = v
@@ -361,7 +391,7 @@ class Block:
             shape = self._shape
         else:
             shape = infer_broadcast_shape(self._shape, o._shape)
-        return Block(shape, self.dtype, Bin(op, a, b, shape), "FULL", "temp", temporary=True)
+        return Block(shape, self.dtype, _tag(Bin(op, a, b, shape)), "FULL", "temp", temporary=True)
 
     def __add__(self, o: Any) -> "Block": return self._binary(o, "add")
     def __sub__(self, o: Any) -> "Block": return self._binary(o, "sub")
@@ -376,12 +406,12 @@ class Block:
             v = self.value()
             e: Expr = v
             for _ in range(o - 1):
-                e = Bin("mul", e, v, self._shape)
+                e = _tag(Bin("mul", e, v, self._shape))
             return Block(self._shape, self.dtype, e, "FULL", "temp", temporary=True)
         raise TypeError("block ** block is not supported by the B200 backend")
 
     def _unary(self, op: str, params: Tuple[float, ...] = ()) -> "Block":
-        return Block(self._shape, self.dtype, Un(op, self.value(), params), "FULL", "temp", temporary=True)
+        return Block(self._shape, self.dtype, _tag(Un(op, self.value(), params)), "FULL", "temp", temporary=True)
 
 
 class _BlockContext:
@@ -746,6 +776,7 @@ class CopyTransaction:
     def __init__(self, src: Any, dst: Any):
         self._src, self._dst = src, dst
         self._completed = False
+        self._line = _site()
         s, d = _as_block(src), _as_block(dst)
         s = s.pipe if isinstance(s, (SrcPipeIdentity, DstPipeIdentity)) else s
         d = d.pipe if isinstance(d, (SrcPipeIdentity, DstPipeIdentity)) else d
@@ -811,10 +842,11 @@ class CopyTransaction:
             tr.note_input(base)
             d.expr = Leaf(base, r0, r1, c0, c1)
             d.expr.shape = d.shape
+            d.expr.line = self._line
             d.state = "FULL"
         elif self._mode == "b2t":
             base, r0, r1, c0, c1 = d._origin if d._origin is not None else (d, 0, d.tile_shape()[0], 0, d.tile_shape()[1])
-            tr.writes.append(Write(base, r0, r1, c0, c1, s.value(), current_core()))
+            tr.writes.append(Write(base, r0, r1, c0, c1, s.value(), current_core(), self._line))
         elif self._mode == "b2p":
             tr.pipe_send(d, s.value(), len(_dst_cores(d.dst_core_range, current_grid())))
         else:  # p2b
