@@ -254,6 +254,34 @@ TTLB_EXPORT int ttlb_reduce(ttlb_ctx *ctx, const ttlb_reduce_desc *desc, void *s
 TTLB_EXPORT int64_t ttlb_reduce_source(const ttlb_reduce_desc *desc, char *buf, size_t len);
 
 /* ------------------------------------------------------------------------ *
+ * Row-resident fusion: up to three reductions over columns followed by an element-wise program, all over
+ * the same rows, in ONE kernel that reads every operand once.
+ *
+ * A tile program such as row softmax - m = reduce_max(x), d = reduce_sum(exp(x - m)), y = exp(x - m) / d -
+ * passes m and d on through circular buffers; run launch by launch it reads x three times.  Here one CTA
+ * holds a whole row of every operand in registers, forms the reductions one after the other (each result
+ * scaled and rounded to `dtype` exactly as ttlb_reduce would store it) and then evaluates `final`.  An
+ * operand whose row_mode is TTLB_IDX_PHASE stands for the result of the earlier reduction number row_off
+ * (0-based) of the same call, one value per row, used for every column; its ptr is ignored.
+ * Requirements: every phase has dims = TTLB_REDUCE_COLS and the same dtype and rectangle as `final`
+ * (row0, rows, col0, cols); cols <= 2048 vectors of 16 bytes; phase[].out may be NULL (result not stored)
+ * or receives the result as ttlb_reduce would write it.  Sums have a fixed order.
+ * No counterpart in the reference compiler, which fuses element-wise chains only
+ * (lib/Dialect/TTL/IR/TTLOpsUtils.cpp:9-63).
+ * ------------------------------------------------------------------------ */
+#define TTLB_MAX_PHASES 3
+#define TTLB_IDX_PHASE 4
+
+typedef struct {
+  int32_t n_phases; /* 1..TTLB_MAX_PHASES */
+  ttlb_reduce_desc phase[TTLB_MAX_PHASES];
+  ttlb_eltwise_desc final;
+} ttlb_rowfused_desc;
+
+TTLB_EXPORT int ttlb_rowfused(ttlb_ctx *ctx, const ttlb_rowfused_desc *desc, void *stream);
+TTLB_EXPORT int64_t ttlb_rowfused_source(const ttlb_rowfused_desc *desc, char *buf, size_t len);
+
+/* ------------------------------------------------------------------------ *
  * Matmul tile programs: C[M,N] = A[M,K] x B[K,N], bf16 in, fp32 accumulate,
  * bf16 out, all row-major.
  *

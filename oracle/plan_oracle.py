@@ -125,7 +125,11 @@ def run_plan(plan: Any, tensors: Sequence[torch.Tensor]) -> None:
     if temps:
         tensors = _WithTemps(tensors, [torch.zeros(t._tensor.shape, dtype=t._tensor.dtype) for t in temps])  # type: ignore[assignment]
     for launch in plan.launches:
-        if hasattr(launch, "extent"):
+        if hasattr(launch, "parts"):      # row-fused: the same stages, one after the other
+            for part in launch.parts:
+                run_reduce(part, tensors)
+            run_eltwise(launch.final, tensors)
+        elif hasattr(launch, "extent"):
             run_reduce(launch, tensors)
         else:
             (run_eltwise if hasattr(launch, "ops") else run_gemm)(launch, tensors)

@@ -34,26 +34,36 @@ def test_program_matches_simulator_and_oracle(case, backend):
     close(got, golden_tensor(load_golden(case.name)["out"], case.dtype), case.check, "vs simulator golden")
 
 
+@pytest.fixture(params=[True, False], ids=["row_fused", "launch_by_launch"])
+def row_fusion(request):
+    import ttl_b200
+    ttl_b200.set_row_fusion(request.param)
+    yield request.param
+    ttl_b200.set_row_fusion(True)
+
+
 @pytest.mark.parametrize("case", cases.COMPOSITE_CASES, ids=lambda c: c.name)
-def test_reductions_inside_expressions(case, backend):
-    """Softmax / row standardisation as tile programs: three launches (two reductions into temporaries, one
-    element-wise), against the simulator fixture and the oracle; a second call reuses plan and temporaries."""
+def test_reductions_inside_expressions(case, backend, row_fusion):
+    """Softmax / row standardisation as tile programs: one row-resident launch, or three launches (two
+    reductions into temporaries, one element-wise); against the simulator fixture and the oracle; a second
+    call reuses the plan."""
     _, mods = backend
     import ttnn
     prog = case.get_program(mods)
+    n_launches = 1 if row_fusion else 3
     want = golden_tensor(load_golden(case.name)["out"], case.dtype)
     for _ in range(2):
         ins = [ttnn.from_torch(t) for t in case.make_inputs()]
         out = ttnn.from_torch(torch.zeros(case.out_shape, dtype=case.dtype))
         before = _launches()
         prog(*ins, out)
-        assert _launches() == before + 3
+        assert _launches() == before + n_launches
         got = ttnn.to_torch(out)
         close(got, oracle_output(case), case.check, "vs oracle")
         close(got, want, case.check, "vs simulator golden")
 
 
-def test_softmax_full_size(backend):
+def test_softmax_full_size(backend, row_fusion):
     """Row softmax of a bf16 [8192, 8192] tensor as a tile program, fp32 tensors' worth of checks: rows sum
     to one, results within bf16 rounding of a float64 softmax."""
     _, mods = backend
@@ -64,7 +74,7 @@ def test_softmax_full_size(backend):
     out = ttnn.from_torch(torch.zeros((n, n), dtype=torch.bfloat16))
     before = _launches()
     mods["reduce"].make_softmax()(ttnn.from_torch(x), s, out)
-    assert _launches() == before + 3
+    assert _launches() == before + (1 if row_fusion else 3)
     got = ttnn.to_torch(out).double()
     want = torch.softmax(x.double(), dim=1)
     # every op rounds to bf16: x - max (up to 2^-9 * 10 absolute, so 2 % in the exponential), exp, the row

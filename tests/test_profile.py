@@ -25,8 +25,13 @@ def _source_lines(report, section):
 def test_launches_are_reported_against_the_program_lines_they_implement(profiling, backend):
     _, mods = backend
     import ttnn
+    import ttl_b200
     z = lambda s: ttnn.from_torch(torch.zeros(s, dtype=torch.bfloat16))  # noqa: E731
-    plan = mods["reduce"].make_softmax().plan(z((128, 256)), z((32, 32)), z((128, 256)))
+    ttl_b200.set_row_fusion(False)   # launch by launch: three launches to tell apart
+    try:
+        plan = mods["reduce"].make_softmax().plan(z((128, 256)), z((32, 32)), z((128, 256)))
+    finally:
+        ttl_b200.set_row_fusion(True)
     assert all(l.lines for l in plan.launches)
     report = profiling.summarize([(l, 10.0 * (i + 1)) for _ in range(2) for i, l in enumerate(plan.launches)], 2)
     assert "TTLANG-B200 PROFILE REPORT" in report and "GPU launches: 6" in report and "GPU time: 120.0 us" in report
@@ -65,10 +70,11 @@ def test_gpu_report_has_measured_times(profiling, backend):
         out = ttnn.from_torch(torch.zeros(case.out_shape, dtype=case.dtype))
         prog(*ins, out)
     report = profiling.report()
-    assert "Kernel calls: 3" in report and "GPU launches: 9" in report
+    assert "Kernel calls: 3" in report and "GPU launches: 3" in report and "LAUNCH 1: row_fused" in report
     import re
     totals = [float(x.replace(",", "")) for x in re.findall(r"total=([\d,\.]+) us", report)]
-    assert len(totals) == 3 and all(t > 0 for t in totals)
+    assert len(totals) == 1 and all(t > 0 for t in totals)
+    assert "reduce_max(xb, sb, dims=[1])" in report and "ttl.copy(yb, y[r:r + 1, 0:ct])" in report
     # the result is still right when every launch is bracketed by events
     from conftest import golden_tensor, load_golden
     from test_reduce import close

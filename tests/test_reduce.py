@@ -68,14 +68,43 @@ def test_reductions_inside_expressions(case, backend):
     import ttnn
     ins = [ttnn.from_torch(t) for t in case.make_inputs()]
     out = ttnn.from_torch(torch.zeros(case.out_shape, dtype=case.dtype))
-    plan = case.get_program(mods).plan(*ins, out)
-    kinds = [x["kind"] for x in plan.describe()]
-    assert kinds == (["reduce_max", "reduce_sum", "eltwise"] if "softmax" in case.name else ["reduce_sum", "reduce_sum", "eltwise"])
-    assert len(plan.temps) == 2 and all(t.shape == (case.out_shape[0], 1) for t in plan.temps)
-    plan_oracle.run_plan(plan, [t._tensor for t in ins] + [out._tensor])
-    close(out._tensor, want, case.check, "plan vs simulator")
+    import ttl_b200
+    stages = ["reduce_max", "reduce_sum", "eltwise"] if "softmax" in case.name else ["reduce_sum", "reduce_sum", "eltwise"]
+    for fusion in (False, True):
+        ttl_b200.set_row_fusion(fusion)
+        try:
+            plan = case.get_program(mods).plan(*ins, out)
+        finally:
+            ttl_b200.set_row_fusion(True)
+        d = plan.describe()
+        if fusion:   # the three stages as one row-resident launch
+            assert [x["kind"] for x in d] == ["row_fused"]
+            assert [x["kind"] for x in d[0]["phases"]] + [d[0]["final"]["kind"]] == stages
+        else:
+            assert [x["kind"] for x in d] == stages
+        assert len(plan.temps) == 2 and all(t.shape == (case.out_shape[0], 1) for t in plan.temps)
+        out._tensor.zero_()
+        plan_oracle.run_plan(plan, [t._tensor for t in ins] + [out._tensor])
+        close(out._tensor, want, case.check, "plan vs simulator")
     if "softmax" in case.name:
         assert (out._tensor.float().sum(dim=1) - 1).abs().max() < 2e-2
+
+
+def test_row_fused_source_reads_each_operand_once(backend):
+    from ttl_b200 import capi
+    _, mods = backend
+    import ttnn
+    z = lambda s: ttnn.from_torch(torch.zeros(s, dtype=torch.bfloat16))  # noqa: E731
+    args = [z((8192, 8192)), z((32, 32)), z((8192, 8192))]
+    plan = mods["reduce"].make_softmax(fp32_dest_acc_en=True).plan(*args)
+    src = capi.rowfused_source(plan.launches[0].desc(plan.indexed(args), with_pointers=False))
+    body = src.split("ttlb_rowfused_jit", 1)[1]
+    assert body.count("ld_stream(") == 4, "x: 4 vectors per thread, loaded once for all three stages"
+    assert body.count("__shfl_xor_sync") == 2 and "phv0" in body and "phv1" in body
+    # rows too long to hold on chip are left as separate launches
+    args = [z((32, 32768)), z((32, 32)), z((32, 32768))]
+    kinds = [d["kind"] for d in mods["reduce"].make_softmax().plan(*args).describe()]
+    assert kinds == ["reduce_max", "reduce_sum", "eltwise"]
 
 
 def test_full_tile_output_has_the_value_in_row_zero(backend):

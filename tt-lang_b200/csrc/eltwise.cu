@@ -451,3 +451,81 @@ extern "C" int ttlb_reduce(ttlb_ctx *ctx, const ttlb_reduce_desc *r, void *strea
   if (rc == TTLB_OK) ctx->launches += 1;
   return rc;
 }
+
+// --------------------------------------------------------------------------- //
+// Row-resident fusion
+// --------------------------------------------------------------------------- //
+// Checks a stage's program with the stand-ins for earlier results replaced by an ordinary operand.
+static int validate_stage(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, int stage, bool need_out) {
+  ttlb_eltwise_desc c = *d;
+  for (int k = 0; k < c.n_in && k < TTLB_MAX_IN; ++k) {
+    if (c.in[k].row_mode != TTLB_IDX_PHASE) continue;
+    if (c.in[k].row_off < 0 || c.in[k].row_off >= stage)
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "rowfused: stage %d reads the result of reduction %lld, which is not earlier",
+                       stage, (long long)c.in[k].row_off);
+    c.in[k].ptr = reinterpret_cast<const void *>(16);
+    c.in[k].row_mode = c.in[k].col_mode = TTLB_IDX_ZERO;
+    c.in[k].row_off = c.in[k].col_off = 0;
+  }
+  return validate_eltwise(ctx, &c, need_out);
+}
+
+static int validate_rowfused(ttlb_ctx *ctx, const ttlb_rowfused_desc *f) {
+  if (!f) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "rowfused: null descriptor");
+  if (f->n_phases < 1 || f->n_phases > TTLB_MAX_PHASES)
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "rowfused: n_phases=%d outside [1,%d]", f->n_phases, TTLB_MAX_PHASES);
+  int rc = validate_stage(ctx, &f->final, f->n_phases, true);
+  if (rc < 0) return rc;
+  if (rc == 1) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "rowfused: empty region");
+  const ttlb_eltwise_desc *d = &f->final;
+  const int esz = d->dtype == TTLB_BF16 ? 2 : 4;
+  for (int ph = 0; ph < f->n_phases; ++ph) {
+    const ttlb_reduce_desc &R = f->phase[ph];
+    rc = validate_stage(ctx, &R.src, ph, false);
+    if (rc < 0) return rc;
+    if (R.src.dtype != d->dtype || R.src.row0 != d->row0 || R.src.rows != d->rows || R.src.col0 != d->col0 ||
+        R.src.cols != d->cols)
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "rowfused: reduction %d has another element type or rectangle than the final stage", ph);
+    if (R.dims != TTLB_REDUCE_COLS) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "rowfused: reduction %d is not over columns only", ph);
+    if (R.op != TTLB_REDUCE_SUM && R.op != TTLB_REDUCE_MAX) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "rowfused: unknown op %d", R.op);
+    if (R.scaler && ((uintptr_t)R.scaler % esz)) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "rowfused: scaler is misaligned");
+    if (R.out && (((uintptr_t)R.out % esz) || R.fill_cols < 1 || R.fill_cols > 32 || (d->rows > 1 && R.out_ld < R.fill_cols)))
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "rowfused: bad output of reduction %d", ph);
+  }
+  if (d->rows > 0xffffffffll) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "rowfused: too many rows");
+  if (d->cols / (d->dtype == TTLB_BF16 ? 8 : 4) > 2048)
+    return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "rowfused: rows longer than 2048 16-byte vectors do not fit on chip");
+  return TTLB_OK;
+}
+
+extern "C" int64_t ttlb_rowfused_source(const ttlb_rowfused_desc *f, char *buf, size_t len) {
+  if (!f) return TTLB_ERR_INVALID_ARG;
+  ttlb_rowfused_desc c = *f;
+  if (!c.final.out) c.final.out = reinterpret_cast<void *>(16);  // source generation needs no buffers
+  for (int st = 0; st <= c.n_phases && st <= TTLB_MAX_PHASES; ++st) {
+    ttlb_eltwise_desc *d = st < c.n_phases ? &c.phase[st].src : &c.final;
+    for (int k = 0; k < d->n_in && k < TTLB_MAX_IN; ++k)
+      if (!d->in[k].ptr) d->in[k].ptr = reinterpret_cast<const void *>(16);  // equal geometry = one operand
+  }
+  const int rc = validate_rowfused(nullptr, &c);
+  if (rc < 0) return rc;
+  const std::string src = ttlb_rowfused_jit_source(&c);
+  if (src.empty()) return TTLB_ERR_UNSUPPORTED;
+  if (buf && len) {
+    const size_t n = src.size() < len - 1 ? src.size() : len - 1;
+    memcpy(buf, src.data(), n);
+    buf[n] = 0;
+  }
+  return (int64_t)src.size() + 1;
+}
+
+extern "C" int ttlb_rowfused(ttlb_ctx *ctx, const ttlb_rowfused_desc *f, void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  const int rc = validate_rowfused(ctx, f);
+  if (rc < 0) return rc;
+  ttlb_device_guard g(ctx->device);
+  if (!g.ok) return ttlb_fail(ctx, TTLB_ERR_CUDA, "rowfused: cannot select device %d", ctx->device);
+  const int rl = ttlb_rowfused_jit_launch(ctx, &ctx->jit, f, reinterpret_cast<cudaStream_t>(stream));
+  if (rl == TTLB_OK) ctx->launches += 1;
+  return rl;
+}

@@ -16,6 +16,8 @@
 // --fmad=false keeps `a*b + c` as two roundings, which is what the simulator computes.
 #include <dlfcn.h>
 
+#include <functional>
+
 #include <map>
 #include <mutex>
 #include <sstream>
@@ -206,11 +208,14 @@ void emit_unpack(std::ostringstream &s, const std::string &var, const char *dst,
 // The op sequence of the program as straight-line code: leaves the value of the V elements of one
 // 16-byte vector in `acc[V]`.  `var(k)` names the register holding operand k's vector.
 template <class VarFn>
-void emit_ops(std::ostringstream &s, const ttlb_eltwise_desc *d, VarFn var, bool bf16, bool rnd) {
+void emit_ops(std::ostringstream &s, const ttlb_eltwise_desc *d, VarFn var, bool bf16, bool rnd,
+              const std::string &imm = "p.imm", int start_pc = 0, const std::string &start_from = "") {
   s << "      float acc[V], x[V], stk0[V], stk1[V];\n"
        "      (void)x; (void)stk0; (void)stk1;\n";
+  if (start_pc > 0)   // the first start_pc ops were evaluated by an earlier stage: continue from its values
+    s << "      _Pragma(\"unroll\") for (int e = 0; e < V; ++e) acc[e] = " << start_from << "[e];\n";
   int depth = 0;
-  for (int pc = 0; pc < d->n_ops; ++pc) {
+  for (int pc = start_pc; pc < d->n_ops; ++pc) {
     const int op = d->ops[pc].opcode, arg = d->ops[pc].arg;
     s << "      {  // op " << pc << "\n";
     if (op == TTLB_OP_LOAD) {
@@ -229,8 +234,8 @@ void emit_ops(std::ostringstream &s, const ttlb_eltwise_desc *d, VarFn var, bool
         << be << "; }\n";
     } else if (const char *ue = unary_expr(op)) {
       if (op >= TTLB_OP_RSUB_IMM)
-        s << "        const float P0 = p.imm[" << arg << "], P1 = p.imm[" << (arg + 1 < TTLB_MAX_IMM ? arg + 1 : arg)
-          << "], P2 = p.imm[" << (arg + 2 < TTLB_MAX_IMM ? arg + 2 : arg) << "]; (void)P1; (void)P2;\n";
+        s << "        const float P0 = " << imm << "[" << arg << "], P1 = " << imm << "[" << (arg + 1 < TTLB_MAX_IMM ? arg + 1 : arg)
+          << "], P2 = " << imm << "[" << (arg + 2 < TTLB_MAX_IMM ? arg + 2 : arg) << "]; (void)P1; (void)P2;\n";
       s << "        _Pragma(\"unroll\") for (int e = 0; e < V; ++e) { const float a = acc[e]; acc[e] = " << ue
         << "; }\n";
     }
@@ -712,6 +717,315 @@ int ttlb_reduce_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_re
   q.counter = counters;
   q.counter2 = counters + max_groups;
   TTLB_CUDA_CHECK(ctx, cudaLaunchKernel(reinterpret_cast<const void *>(jk.kern), dim3(gx, gy, 1), dim3(256, 1, 1), args, 0,
+                                        stream));
+  return TTLB_OK;
+}
+
+// --------------------------------------------------------------------------- //
+// Row-resident fusion (ttlb_rowfused): reductions over columns, then an element-wise
+// program, over the same rows in one kernel.  A CTA of 256 threads owns a row at a
+// time: thread t holds the 16-byte vectors t, t+256, ... of every operand in registers
+// (all loads of a row are issued before any arithmetic), each reduction is folded per
+// thread, by shuffles per warp and through shared memory per CTA in a fixed order, its
+// scaled and rounded result is broadcast to the threads as the operand of the next
+// stage, and the final program is evaluated from the same registers and stored.
+// --------------------------------------------------------------------------- //
+namespace {
+
+struct RowParams {
+  JitParams p;  // the distinct memory operands of all stages; out / out_ld: the final output
+  const void *scaler[TTLB_MAX_PHASES];
+  void *red_out[TTLB_MAX_PHASES];
+  long long red_ld[TTLB_MAX_PHASES];
+  unsigned red_fill[TTLB_MAX_PHASES];
+  unsigned pad;
+  float imm[TTLB_MAX_PHASES + 1][TTLB_MAX_IMM];
+};
+
+const char *kRowPrelude = R"SRC(
+struct RowParams {
+  JitParams p; const void* scaler[3]; void* red_out[3]; i64 red_ld[3]; u32 red_fill[3]; u32 pad; float imm[4][8];
+};
+)SRC";
+
+// The distinct memory operands of all stages, and for every (stage, operand) where it lives.
+struct RowLayout {
+  ttlb_eltwise_desc g;                               // g.in[0 .. g.n_in): the distinct operands
+  int where[TTLB_MAX_PHASES + 1][TTLB_MAX_IN];       // >= 0: index into g.in; < 0: result of phase -(v + 1)
+  bool ok = true;
+};
+
+RowLayout row_layout(const ttlb_rowfused_desc *f) {
+  RowLayout L;
+  L.g = f->final;
+  L.g.n_in = 0;
+  for (int st = 0; st <= f->n_phases; ++st) {
+    const ttlb_eltwise_desc *d = st < f->n_phases ? &f->phase[st].src : &f->final;
+    for (int k = 0; k < d->n_in; ++k) {
+      const ttlb_operand &o = d->in[k];
+      if (o.row_mode == TTLB_IDX_PHASE) {
+        L.where[st][k] = -(int)o.row_off - 1;
+        continue;
+      }
+      int found = -1;
+      for (int n = 0; n < L.g.n_in; ++n) {
+        const ttlb_operand &x = L.g.in[n];
+        if (x.ptr == o.ptr && x.ld == o.ld && x.row_mode == o.row_mode && x.col_mode == o.col_mode &&
+            x.row_off == o.row_off && x.col_off == o.col_off)
+          found = n;
+      }
+      if (found < 0) {
+        if (L.g.n_in == TTLB_MAX_IN) {
+          L.ok = false;
+          return L;
+        }
+        found = L.g.n_in++;
+        L.g.in[found] = o;
+      }
+      L.where[st][k] = found;
+    }
+  }
+  return L;
+}
+
+bool per_vector(const ttlb_operand &o) { return o.col_mode != TTLB_IDX_ZERO; }
+
+bool takes_operand(int op) { return op <= TTLB_OP_MIN; }   // LOAD and the binary ops name an input (or the stack)
+int n_imm(int op) {
+  switch (op) {
+    case TTLB_OP_RSUB_IMM: case TTLB_OP_RELU_MAX: case TTLB_OP_RELU_MIN: case TTLB_OP_LEAKY_RELU: case TTLB_OP_ELU: return 1;
+    case TTLB_OP_CELU: case TTLB_OP_HARDTANH: case TTLB_OP_SELU: return 2;
+    case TTLB_OP_SOFTPLUS: return 3;
+  }
+  return 0;
+}
+
+// Stage `st` may continue from the values reduction `a` computed when its program starts with the whole
+// program of `a` (same ops on the same operands with the same parameters and rounding): exp(x - max) of a
+// softmax is then evaluated once.  Returns the reduction to continue from, or -1.
+int continue_from(const ttlb_rowfused_desc *f, const RowLayout &L, int st) {
+  const ttlb_eltwise_desc *d = st < f->n_phases ? &f->phase[st].src : &f->final;
+  int best = -1, best_n = 1;   // continuing from a bare LOAD saves nothing
+  for (int a = 0; a < st && a < f->n_phases; ++a) {
+    const ttlb_eltwise_desc *e = &f->phase[a].src;
+    if (e->n_ops > d->n_ops || e->n_ops <= best_n || (e->round_each_op != 0) != (d->round_each_op != 0)) continue;
+    bool same = true;
+    for (int pc = 0; pc < e->n_ops && same; ++pc) {
+      const int op = e->ops[pc].opcode, arg = e->ops[pc].arg;
+      if (op != d->ops[pc].opcode) same = false;
+      else if (takes_operand(op)) {
+        const int arg2 = d->ops[pc].arg;
+        if ((arg < 0) != (arg2 < 0)) same = false;
+        else if (arg >= 0 && L.where[a][arg] != L.where[st][arg2]) same = false;
+      } else {
+        for (int i = 0; i < n_imm(op) && same; ++i)
+          if (e->imm[arg + i] != d->imm[d->ops[pc].arg + i]) same = false;
+      }
+    }
+    if (same) {
+      best = a;
+      best_n = e->n_ops;
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+std::string ttlb_rowfused_jit_key(const ttlb_rowfused_desc *f, const RowLayout &L, int vpt) {
+  std::ostringstream k;
+  k << "rowf" << vpt << ':' << f->n_phases << ':';
+  for (int n = 0; n < L.g.n_in; ++n) k << L.g.in[n].row_mode << L.g.in[n].col_mode << ',';
+  for (int st = 0; st <= f->n_phases; ++st) {
+    const ttlb_eltwise_desc *d = st < f->n_phases ? &f->phase[st].src : &f->final;
+    k << '|';
+    if (st < f->n_phases) k << f->phase[st].op << (f->phase[st].out ? 'w' : '-') << (f->phase[st].scaler ? 's' : '-');
+    k << d->dtype << (d->round_each_op ? 1 : 0) << 'c' << continue_from(f, L, st) << ':';
+    for (int i = 0; i < d->n_in; ++i) k << L.where[st][i] << ',';
+    k << ':';
+    for (int i = 0; i < d->n_ops; ++i) k << d->ops[i].opcode << '/' << d->ops[i].arg << ',';
+  }
+  return k.str();
+}
+
+static int rowfused_vpt(const ttlb_rowfused_desc *f) {
+  const int vec = f->final.dtype == TTLB_BF16 ? 8 : 4;
+  const long long vpr = f->final.cols / vec;
+  return (int)((vpr + 255) / 256);
+}
+
+std::string ttlb_rowfused_jit_source(const ttlb_rowfused_desc *f) {
+  const RowLayout L = row_layout(f);
+  if (!L.ok) return std::string();
+  const bool bf16 = f->final.dtype == TTLB_BF16;
+  const int V = bf16 ? 8 : 4;
+  const int VPT = rowfused_vpt(f);
+  std::ostringstream s;
+  s << kPrelude << kRowPrelude;
+  s << "#define V " << V << "\n#define ESZ " << (bf16 ? 2 : 4) << "\n";
+  if (bf16)
+    s << "__device__ __forceinline__ float ld_elem(const void* q) { return __uint_as_float(((u32)*(const unsigned short*)q) << 16); }\n"
+         "__device__ __forceinline__ void st_elem(void* base, i64 idx, float x) { ((unsigned short*)base)[idx] = "
+         "(unsigned short)(pack_bf16x2(x, 0.0f) & 0xffffu); }\n";
+  else
+    s << "__device__ __forceinline__ float ld_elem(const void* q) { return *(const float*)q; }\n"
+         "__device__ __forceinline__ void st_elem(void* base, i64 idx, float x) { ((float*)base)[idx] = x; }\n";
+  s << "extern \"C\" __global__ void __launch_bounds__(256) ttlb_rowfused_jit(const __grid_constant__ RowParams q) {\n"
+       "  const JitParams& p = q.p;\n"
+       "  __shared__ float sm[8];\n"
+       "  const u32 lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;\n";
+  for (int j = 0; j < VPT; ++j)
+    s << "  const u32 cv" << j << " = threadIdx.x + 256u * " << j << "; const bool ok" << j << " = cv" << j
+      << " < p.vpr; const i64 gj" << j << " = p.col0 + (i64)cv" << j << " * V;\n";
+  for (int ph = 0; ph < f->n_phases; ++ph)
+    s << "  const float sc" << ph << " = q.scaler[" << ph << "] ? ld_elem(q.scaler[" << ph << "]) : 1.0f;\n";
+  // Registers g*: the row being worked on; h*: the CTA's next row, whose loads are issued before the
+  // arithmetic of the current row starts (a CTA works on one row at a time, so without this its loads and
+  // its arithmetic would take turns).
+  auto loads = [&](const char *pre, const std::string &gi, const std::string &cond) {
+    for (int n = 0; n < L.g.n_in; ++n) {
+      if (!per_vector(L.g.in[n])) {
+        if (!cond.empty()) s << "    if (" << cond << ")\n";
+        emit_load(s, &L.g, n, bf16, "    ", pre + std::to_string(n), gi, "gj0");
+        continue;
+      }
+      for (int j = 0; j < VPT; ++j) {
+        s << "    if (ok" << j << (cond.empty() ? "" : " && " + cond) << ")\n";
+        emit_load(s, &L.g, n, bf16, "    ", pre + std::to_string(n) + "_" + std::to_string(j), gi, "gj" + std::to_string(j));
+      }
+    }
+  };
+  auto each_reg = [&](const std::function<void(const std::string &)> &fn) {
+    for (int n = 0; n < L.g.n_in; ++n) {
+      if (!per_vector(L.g.in[n])) fn(std::to_string(n));
+      else
+        for (int j = 0; j < VPT; ++j) fn(std::to_string(n) + "_" + std::to_string(j));
+    }
+  };
+  each_reg([&](const std::string &r) { s << "  uint4 g" << r << " = make_uint4(0, 0, 0, 0);\n"; });
+  s << "  if (blockIdx.x < p.rows) {\n    const i64 gi0 = p.row0 + (i64)blockIdx.x;\n";
+  loads("g", "gi0", "");
+  s << "  }\n"
+       "  for (u32 r = blockIdx.x; r < p.rows; r += gridDim.x) {\n"
+       "    const i64 gi = p.row0 + (i64)r;\n"
+       "    const bool more = r + gridDim.x < p.rows;\n"
+       "    const i64 gin = gi + (i64)gridDim.x;\n";
+  each_reg([&](const std::string &r) { s << "    uint4 h" << r << " = make_uint4(0, 0, 0, 0);\n"; });
+  loads("h", "gin", "more");
+  auto var = [&](int st, int k, int j) -> std::string {
+    const int w = L.where[st][k];
+    if (w < 0) return "phv" + std::to_string(-w - 1);
+    return per_vector(L.g.in[w]) ? "g" + std::to_string(w) + "_" + std::to_string(j) : "g" + std::to_string(w);
+  };
+  int from[TTLB_MAX_PHASES + 1];
+  bool saved[TTLB_MAX_PHASES] = {false, false, false};
+  for (int st = 0; st <= f->n_phases; ++st) {
+    from[st] = continue_from(f, L, st);
+    if (from[st] >= 0) saved[from[st]] = true;
+  }
+  auto start_pc = [&](int st) { return from[st] >= 0 ? f->phase[from[st]].src.n_ops : 0; };
+  auto start_var = [&](int st, int j) {
+    return from[st] >= 0 ? "sv" + std::to_string(from[st]) + "_" + std::to_string(j) : std::string();
+  };
+  for (int ph = 0; ph < f->n_phases; ++ph) {
+    const ttlb_reduce_desc &R = f->phase[ph];
+    const bool is_max = R.op == TTLB_REDUCE_MAX;
+    const std::string P = std::to_string(ph);
+    if (saved[ph])
+      for (int j = 0; j < VPT; ++j) s << "    float sv" << P << "_" << j << "[V];\n";
+    auto comb = [&](const std::string &a, const std::string &b) {
+      return is_max ? "nan_max(" + a + ", " + b + ")" : "(" + a + " + " + b + ")";
+    };
+    s << "    float racc" << P << " = " << (is_max ? "__uint_as_float(0xff800000u)" : "0.0f") << ";\n";
+    for (int j = 0; j < VPT; ++j) {
+      s << "    if (ok" << j << ") {\n";
+      emit_ops(s, &R.src, [&](int k) { return var(ph, k, j); }, bf16, bf16 && R.src.round_each_op, "q.imm[" + P + "]",
+               start_pc(ph), start_var(ph, j));
+      if (saved[ph]) s << "      _Pragma(\"unroll\") for (int e = 0; e < V; ++e) sv" << P << "_" << j << "[e] = acc[e];\n";
+      s << "      _Pragma(\"unroll\") for (int e = 0; e < V; ++e) racc" << P << " = " << comb("racc" + P, "acc[e]") << ";\n"
+           "    }\n";
+    }
+    s << "    _Pragma(\"unroll\") for (int o = 16; o; o >>= 1) { const float y = __shfl_xor_sync(0xffffffffu, racc" << P
+      << ", o); racc" << P << " = " << comb("racc" + P, "y") << "; }\n"
+         "    if (lane == 0) sm[warp] = racc" << P << ";\n"
+         "    __syncthreads();\n"
+         "    float res" << P << " = sm[0];\n"
+         "    _Pragma(\"unroll\") for (int w = 1; w < 8; ++w) res" << P << " = " << comb("res" + P, "sm[w]") << ";\n"
+         "    __syncthreads();\n"
+         "    res" << P << " = res" << P << " * sc" << P << ";\n";
+    if (bf16)
+      s << "    uint4 phv" << P << "; { u32 h = pack_bf16x2(res" << P << ", 0.0f) & 0xffffu; res" << P
+        << " = __uint_as_float(h << 16); h |= h << 16; phv" << P << " = make_uint4(h, h, h, h); }\n";
+    else
+      s << "    uint4 phv" << P << "; { const u32 w = __float_as_uint(res" << P << "); phv" << P << " = make_uint4(w, w, w, w); }\n";
+    if (R.out)
+      s << "    if (threadIdx.x < q.red_fill[" << P << "]) st_elem(q.red_out[" << P << "], (i64)r * q.red_ld[" << P
+        << "] + threadIdx.x, threadIdx.x == 0 ? res" << P << " : 0.0f);\n";
+  }
+  const std::string FP = std::to_string(f->n_phases);
+  for (int j = 0; j < VPT; ++j) {
+    s << "    if (ok" << j << ") {\n";
+    emit_ops(s, &f->final, [&](int k) { return var(f->n_phases, k, j); }, bf16, bf16 && f->final.round_each_op,
+             "q.imm[" + FP + "]", start_pc(f->n_phases), start_var(f->n_phases, j));
+    s << "      uint4 o;\n";
+    if (bf16)
+      s << "      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);\n"
+           "      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);\n";
+    else
+      s << "      o.x = __float_as_uint(acc[0]); o.y = __float_as_uint(acc[1]);\n"
+           "      o.z = __float_as_uint(acc[2]); o.w = __float_as_uint(acc[3]);\n";
+    s << "      st_stream((char*)p.out + (gi * p.out_ld + gj" << j << ") * ESZ, o);\n"
+         "    }\n";
+  }
+  each_reg([&](const std::string &r) { s << "    g" << r << " = h" << r << ";\n"; });
+  s << "  }\n}\n";
+  return s.str();
+}
+
+int ttlb_rowfused_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_rowfused_desc *f, cudaStream_t stream) {
+  const RowLayout L = row_layout(f);
+  if (!L.ok) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "rowfused: more than %d distinct operands", TTLB_MAX_IN);
+  const int vpt = rowfused_vpt(f);
+  int vectors = 0;
+  for (int n = 0; n < L.g.n_in; ++n) vectors += per_vector(L.g.in[n]) ? vpt : 1;
+  if (vpt > 8 || vectors > 24)
+    return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "rowfused: a row of the operands does not fit in registers (%d vectors per thread)",
+                     vectors);
+  JitKernel jk;
+  {
+    const std::string key = ttlb_rowfused_jit_key(f, L, vpt);
+    const bool cached = *cachep && (*cachep)->kernels.count(key);
+    const int rc = get_kernel(ctx, cachep, key, cached ? std::string() : ttlb_rowfused_jit_source(f), "ttlb_rowfused_jit", &jk);
+    if (rc != TTLB_OK) return rc;
+  }
+  const ttlb_eltwise_desc *d = &f->final;
+  const int vec = d->dtype == TTLB_BF16 ? 8 : 4;
+  RowParams q{};
+  JitParams &p = q.p;
+  for (int n = 0; n < L.g.n_in; ++n) {
+    p.in[n] = L.g.in[n].ptr;
+    p.ld[n] = L.g.in[n].ld;
+    p.roff[n] = L.g.in[n].row_off;
+    p.coff[n] = L.g.in[n].col_off;
+  }
+  p.out = d->out;
+  p.out_ld = d->out_ld;
+  p.row0 = d->row0;
+  p.col0 = d->col0;
+  p.vpr = (unsigned)(d->cols / vec);
+  p.rows = (unsigned)d->rows;
+  for (int ph = 0; ph < f->n_phases; ++ph) {
+    q.scaler[ph] = f->phase[ph].scaler;
+    q.red_out[ph] = f->phase[ph].out;
+    q.red_ld[ph] = f->phase[ph].out_ld;
+    q.red_fill[ph] = (unsigned)f->phase[ph].fill_cols;
+    for (int k = 0; k < TTLB_MAX_IMM; ++k) q.imm[ph][k] = f->phase[ph].src.imm[k];
+  }
+  for (int k = 0; k < TTLB_MAX_IMM; ++k) q.imm[f->n_phases][k] = d->imm[k];
+  unsigned grid = (unsigned)(ctx->sm_count * jk.blocks_per_sm);
+  if (grid > p.rows) grid = p.rows;
+  void *args[] = {&q};
+  TTLB_CUDA_CHECK(ctx, cudaLaunchKernel(reinterpret_cast<const void *>(jk.kern), dim3(grid, 1, 1), dim3(256, 1, 1), args, 0,
                                         stream));
   return TTLB_OK;
 }

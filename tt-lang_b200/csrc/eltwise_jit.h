@@ -23,3 +23,7 @@ std::string ttlb_reduce_jit_source(const ttlb_reduce_desc *r);
 int ttlb_reduce_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cache, const ttlb_reduce_desc *r, float *partial,
                            size_t partial_floats, float *partial2, unsigned *counters, unsigned max_groups,
                            cudaStream_t stream);
+
+// Row-resident fusion (ttlb_rowfused): reductions over columns + a final element-wise program, one kernel.
+std::string ttlb_rowfused_jit_source(const ttlb_rowfused_desc *f);
+int ttlb_rowfused_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cache, const ttlb_rowfused_desc *f, cudaStream_t stream);

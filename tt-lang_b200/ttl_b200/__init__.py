@@ -16,7 +16,7 @@ import sys
 from . import profile, ttl, ttnn  # noqa: F401
 from .capi import BackendError  # noqa: F401
 from .math import set_hardware_broadcast  # noqa: F401
-from .recognize import Unsupported  # noqa: F401
+from .recognize import Unsupported, set_row_fusion  # noqa: F401
 from .stream import run_streamed  # noqa: F401
 
 __version__ = "0.1"

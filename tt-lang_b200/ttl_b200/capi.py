@@ -66,6 +66,13 @@ class ReduceDesc(C.Structure):
                 ("out", C.c_void_p), ("out_ld", C.c_int64), ("fill_rows", C.c_int32), ("fill_cols", C.c_int32)]
 
 
+TTLB_MAX_PHASES, IDX_PHASE = 3, 4
+
+
+class RowFusedDesc(C.Structure):
+    _fields_ = [("n_phases", C.c_int32), ("phase", ReduceDesc * TTLB_MAX_PHASES), ("final", EltwiseDesc)]
+
+
 class GemmDesc(C.Structure):
     _fields_ = [("a", C.c_void_p), ("lda", C.c_int64), ("b", C.c_void_p), ("ldb", C.c_int64),
                 ("c", C.c_void_p), ("ldc", C.c_int64), ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64)]
@@ -105,6 +112,17 @@ def reduce_source(desc: "ReduceDesc") -> str:
         raise BackendError(int(n), "invalid reduction descriptor")
     buf = C.create_string_buffer(int(n))
     l.ttlb_reduce_source(C.byref(desc), buf, int(n))
+    return buf.value.decode()
+
+
+def rowfused_source(desc: "RowFusedDesc") -> str:
+    """CUDA source of the row-resident kernel specialised for `desc` (works without a GPU)."""
+    l = lib()
+    n = l.ttlb_rowfused_source(C.byref(desc), None, 0)
+    if n < 0:
+        raise BackendError(int(n), "invalid or unsupported row-fusion descriptor")
+    buf = C.create_string_buffer(int(n))
+    l.ttlb_rowfused_source(C.byref(desc), buf, int(n))
     return buf.value.decode()
 
 
@@ -154,6 +172,10 @@ def lib() -> C.CDLL:
     l.ttlb_reduce.restype = C.c_int
     l.ttlb_reduce_source.argtypes = [C.POINTER(ReduceDesc), C.c_char_p, C.c_size_t]
     l.ttlb_reduce_source.restype = C.c_int64
+    l.ttlb_rowfused.argtypes = [C.c_void_p, C.POINTER(RowFusedDesc), C.c_void_p]
+    l.ttlb_rowfused.restype = C.c_int
+    l.ttlb_rowfused_source.argtypes = [C.POINTER(RowFusedDesc), C.c_char_p, C.c_size_t]
+    l.ttlb_rowfused_source.restype = C.c_int64
     l.ttlb_matmul_bf16.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p]
     l.ttlb_matmul_bf16.restype = C.c_int
     l.ttlb_matmul_bf16_bias.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_int64, C.c_void_p]
@@ -221,6 +243,9 @@ class Context:
 
     def reduce(self, desc: "ReduceDesc", stream: int) -> None:
         self.check(self._lib.ttlb_reduce(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def rowfused(self, desc: "RowFusedDesc", stream: int) -> None:
+        self.check(self._lib.ttlb_rowfused(self.handle, C.byref(desc), C.c_void_p(stream)))
 
     def matmul_bf16(self, desc: "GemmDesc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_bf16(self.handle, C.byref(desc), C.c_void_p(stream)))

@@ -64,6 +64,8 @@ def _kernel_name(kind: str) -> str:
         return "ttlb_eltwise_jit"
     if kind.startswith("reduce"):
         return "ttlb_reduce_jit"
+    if kind == "row_fused":
+        return "ttlb_rowfused_jit"
     return {"matmul_bf16": "ttlb_gemm_bf16", "matmul_f32": "ttlb_gemm_f32", "matmul_bfp8w": "ttlb_unpack_bfp8 + ttlb_gemm_bf16"}.get(kind, kind)
 
 
@@ -90,6 +92,8 @@ def summarize(records: List[Tuple[Any, float]], calls: int) -> str:
         l = r["launch"]
         d = l.describe()
         what = d["kind"] + (f" dims={d['dims']}" if "dims" in d else "")
+        if "phases" in d:
+            what += " (" + " + ".join([ph["kind"] for ph in d["phases"]] + [d["final"]["kind"]]) + ")"
         out += ["=" * W,
                 f"LAUNCH {idx}: {what} -> {_kernel_name(d['kind'])}   (x{r['n']}, avg={r['us'] / r['n']:,.1f} us, "
                 f"{r['min']:,.1f}-{r['max']:,.1f}, total={r['us']:,.1f} us, {100 * r['us'] / total:.1f}% of total)",

@@ -18,6 +18,7 @@ Anything else raises Unsupported: there is no CPU fallback.
 
 from __future__ import annotations
 
+import os
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -435,6 +436,127 @@ class ReduceLaunch:
         ctx.reduce(self.desc(tensors), stream)
 
 
+ROW_FUSION = os.environ.get("TTLB200_ROW_FUSION", "1") != "0"
+MAX_FUSED_VECTORS_PER_ROW = 2048
+
+
+def set_row_fusion(enabled: bool) -> None:
+    """Whether reductions over columns and the element-wise launch that consumes them are merged into one
+    row-resident kernel (default on).  Affects plans built afterwards."""
+    global ROW_FUSION
+    ROW_FUSION = bool(enabled)
+
+
+class RowFusedLaunch:
+    """Reductions over columns (`parts`) and the element-wise launch (`final`) that reads their results,
+    all over the same rows, as ONE `ttlb_rowfused` launch: every operand row is read once and held on chip;
+    the reduction results never reach memory."""
+
+    lines: Dict[Any, int] = {}
+
+    def __init__(self, parts: List[ReduceLaunch], final: EltwiseLaunch):
+        self.parts, self.final = parts, final
+        self.out_index, self.rect = final.out_index, final.rect
+        self._unfused = False
+
+    def describe(self) -> Dict[str, Any]:
+        return {"kind": "row_fused", "out": self.out_index, "rect_tiles": self.rect,
+                "phases": [p.describe() for p in self.parts], "final": self.final.describe()}
+
+    def _patch(self, d: capi.EltwiseDesc, inputs: Sequence[Tuple[int, int, int, int, int]]) -> None:
+        produced = {p.out_index: i for i, p in enumerate(self.parts)}
+        for k, (ti, *_rest) in enumerate(inputs):
+            if ti in produced:
+                d.inp[k].ptr = None
+                d.inp[k].row_mode, d.inp[k].row_off = capi.IDX_PHASE, produced[ti]
+                d.inp[k].col_mode, d.inp[k].col_off = capi.IDX_ZERO, 0
+
+    def desc(self, tensors: Sequence[_ttnn.Tensor], with_pointers: bool = True) -> capi.RowFusedDesc:
+        f = capi.RowFusedDesc()
+        f.n_phases = len(self.parts)
+        for i, p in enumerate(self.parts):
+            rd = p.desc(tensors, with_pointers)
+            rd.out = None          # the result is consumed on chip; the temporary is not written
+            self._patch(rd.src, p.inputs)
+            f.phase[i] = rd
+        fd = self.final.desc(tensors) if with_pointers else self.final.desc_cpu(tensors)
+        self._patch(fd, self.final.inputs)
+        f.final = fd
+        return f
+
+    def run(self, ctx: capi.Context, tensors: Sequence[_ttnn.Tensor], stream: int) -> None:
+        if not self._unfused:
+            try:
+                ctx.rowfused(self.desc(tensors), stream)
+                return
+            except capi.BackendError as e:
+                if e.code != capi.TTLB_ERR_UNSUPPORTED:
+                    raise
+                self._unfused = True   # e.g. the operand rows do not fit in registers: launch by launch
+        for p in self.parts:
+            p.run(ctx, tensors, stream)
+        self.final.run(ctx, tensors, stream)
+
+
+def _fuse_rows(launches: List[Any]) -> List[Any]:
+    """Merge [reductions over columns into temporaries] + [the element-wise launch that reads them] into
+    RowFusedLaunch where every launch covers the same rows and full row length, and the temporaries have no
+    other reader."""
+    readers: Dict[int, int] = {}
+    for l in launches:
+        for (ti, *_r) in getattr(l, "inputs", []):
+            if ti >= TEMP_BASE:
+                readers[ti] = readers.get(ti, 0) + 1
+        for attr in ("a_index", "b_index", "bias_index"):
+            ti = getattr(l, attr, None)
+            if ti is not None and ti >= TEMP_BASE:
+                readers[ti] = readers.get(ti, 0) + 100   # read by a matmul: never fused away
+    producer = {l.out_index: l for l in launches if isinstance(l, ReduceLaunch) and l.out_index >= TEMP_BASE}
+    gone: Dict[int, None] = {}
+    out: List[Any] = []
+    for l in launches:
+        if not isinstance(l, EltwiseLaunch) or l.out_degenerate != (False, False):
+            out.append(l)
+            continue
+        r0, r1, c0, c1 = l.rect
+        group: List[ReduceLaunch] = []
+        inside: Dict[int, int] = {}
+        ok = True
+
+        def visit(inputs: Sequence[Tuple[int, int, int, int, int]]) -> None:
+            nonlocal ok
+            for (ti, rm, ro, cm, co) in inputs:
+                if ti < TEMP_BASE or not ok:
+                    continue
+                inside[ti] = inside.get(ti, 0) + 1
+                p = producer.get(ti)
+                if (p is None or p.dims != (1,) or p.rect != (r0, r1, 0, 1) or c0 != 0 or p.extent[1] != c1
+                        or (rm, ro, cm, co) != (capi.IDX_SAME, 0, capi.IDX_ZERO, 0) or p.dtype != l.dtype
+                        or p.round_each_op != l.round_each_op):
+                    ok = False
+                    return
+                if p not in group:
+                    visit(p.inputs)
+                    group.append(p)
+
+        visit(l.inputs)
+        vec = 8 if l.dtype == torch.bfloat16 else 4
+        if (not ok or not group or len(group) > capi.TTLB_MAX_PHASES or (c1 - c0) * TILE // vec > MAX_FUSED_VECTORS_PER_ROW
+                or any(readers.get(ti, 0) != n for ti, n in inside.items())):
+            out.append(l)
+            continue
+        for p in group:
+            gone[id(p)] = None
+        fused = RowFusedLaunch(group, l)
+        lines: Dict[Any, int] = {}
+        for part in group + [l]:
+            for ln, n in (getattr(part, "lines", None) or {}).items():
+                lines[ln] = lines.get(ln, 0) + n
+        fused.lines = lines
+        out.append(fused)
+    return [l for l in out if id(l) not in gone]
+
+
 class GemmLaunch:
     def __init__(self, a_index: int, b_index: int, out_index: int, rect: Tuple[int, int, int, int], k_tiles: int,
                  b_is_bfp8: bool, bias_index: Optional[int] = None):
@@ -821,6 +943,8 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
             launches.add(key, gl)
     # a launch that reads a temporary runs after the launch that fills it
     ordered = [l for _, l in sorted(launches, key=lambda p: p[0])]
+    if ROW_FUSION:
+        ordered = _fuse_rows(ordered)
     return Plan(ordered, table.extras, len(table.args), table.temps)
 
 
