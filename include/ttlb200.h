@@ -412,6 +412,21 @@ TTLB_EXPORT int ttlb_multimem_bcast(ttlb_ctx *ctx, const void *src, int64_t src_
 TTLB_EXPORT int ttlb_matmul_bf16_bias(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, const void *bias, int64_t ldbias,
                                       void *stream);
 
+/* C = act(A x B + bias): bias and activation applied to the fp32 accumulators in the GEMM epilogue, one rounding.
+ * bias: NULL, a bf16 [m, n] matrix (ldbias >= n), or with ldbias == 0 one row of n values added to every output
+ * row (the bias vector of a linear layer).  The tile program: the product accumulated over the K tiles into a
+ * block of an intermediate circular buffer, then `y_blk.store(act(p_blk + broadcast(bias_blk, dims=[0])))`, in a
+ * kernel with fp32_dest_acc_en=True (without it every op rounds to bf16 and the program runs as a GEMM into a
+ * temporary plus an element-wise launch). */
+#define TTLB_ACT_NONE 0
+#define TTLB_ACT_RELU 1
+#define TTLB_ACT_GELU 2
+#define TTLB_ACT_SILU 3
+#define TTLB_ACT_SIGMOID 4
+#define TTLB_ACT_TANH 5
+TTLB_EXPORT int ttlb_matmul_bf16_epilogue(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, const void *bias, int64_t ldbias,
+                                          int act, void *stream);
+
 /* Which tensor-core GEMM kernel the bf16 / bfp8-weight matmuls use:
  *   0  always one CTA per 128x256 output tile (tcgen05 cta_group::1)
  *   1  (default) a cluster of two CTAs per 256x256 tile (cta_group::2: each CTA stages half of the

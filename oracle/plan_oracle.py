@@ -103,9 +103,18 @@ def run_reduce(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
 def run_gemm(launch: Any, tensors: Sequence[torch.Tensor]) -> None:
     a, b, out = tensors[launch.a_index], tensors[launch.b_index], tensors[launch.out_index]
     r0, r1, c0, c1 = (x * TILE for x in launch.rect)
-    bias = None if launch.bias_index is None else tensors[launch.bias_index][r0:r1, c0:c1]
-    mode = "native" if out.dtype == torch.float32 else "f32"
-    out[r0:r1, c0:c1] = tile_oracle.matmul_tiles(a[r0:r1], b[:, c0:c1], mode, bias=bias).to(out.dtype)
+    bias = None
+    if launch.bias_index is not None:
+        bt = tensors[launch.bias_index]
+        bias = bt[:, c0:c1] if (bt.shape[0] == 1 and out.shape[0] != 1) else bt[r0:r1, c0:c1]   # one row, or a matrix
+    act = getattr(launch, "act", None)
+    if act is None:
+        mode = "native" if out.dtype == torch.float32 else "f32"
+        out[r0:r1, c0:c1] = tile_oracle.matmul_tiles(a[r0:r1], b[:, c0:c1], mode, bias=bias).to(out.dtype)
+        return
+    # bias and activation in the GEMM epilogue: on the fp32 accumulators, one rounding
+    acc = tile_oracle.matmul_tiles(a[r0:r1].float(), b[:, c0:c1].float(), "native", bias=None if bias is None else bias.float())
+    out[r0:r1, c0:c1] = _UNARY[act](acc).to(out.dtype)
 
 
 class _WithTemps:

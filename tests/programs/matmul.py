@@ -185,6 +185,65 @@ def matmul_bias(a, b, c, out):
                     y_xf.wait()
 
 
+def _kernel(grid, fp32_dest_acc_en=False):
+    if fp32_dest_acc_en:
+        try:
+            return ttl.kernel(grid=grid, fp32_dest_acc_en=True)
+        except TypeError:
+            pass
+    return ttl.kernel(grid=grid)
+
+
+def make_linear(act, fp32_dest_acc_en=False):
+    """Y = act(A @ B + bias) like `linear_relu`, for any unary function of ttl.math; with fp32_dest_acc_en the
+    bias and the activation are applied to the fp32 product (on the B200 backend: inside the GEMM)."""
+    fn = getattr(ttl.math, act)
+
+    @_kernel((1, 1), fp32_dest_acc_en)
+    def linear(a, b, bias, out):
+        Mt, Kt, Nt = a.shape[0] // ttnn.TILE_SIZE, a.shape[1] // ttnn.TILE_SIZE, b.shape[1] // ttnn.TILE_SIZE
+        a_cb = ttl.make_circular_buffer_like(a, shape=(1, 1), buffer_factor=2)
+        b_cb = ttl.make_circular_buffer_like(b, shape=(1, 1), buffer_factor=2)
+        v_cb = ttl.make_circular_buffer_like(bias, shape=(1, 1), buffer_factor=2)
+        p_cb = ttl.make_circular_buffer_like(out, shape=(1, 1), buffer_factor=2)
+        y_cb = ttl.make_circular_buffer_like(out, shape=(1, 1), buffer_factor=2)
+
+        @ttl.compute()
+        def mm_compute():
+            for _ in range(Mt):
+                for _ in range(Nt):
+                    with p_cb.reserve() as p_blk:
+                        for _ in range(Kt):
+                            with a_cb.wait() as a_blk, b_cb.wait() as b_blk:
+                                p_blk.store(a_blk @ b_blk, acc=True)
+                    with p_cb.wait() as p_blk, v_cb.wait() as v_blk, y_cb.reserve() as y_blk:
+                        y_blk.store(fn(p_blk + ttl.math.broadcast(v_blk, dims=[0])))
+
+        @ttl.datamovement()
+        def mm_reader():
+            for m in range(Mt):
+                for n in range(Nt):
+                    for k in range(Kt):
+                        with a_cb.reserve() as a_blk, b_cb.reserve() as b_blk:
+                            a_xf = ttl.copy(a[m, k], a_blk)
+                            b_xf = ttl.copy(b[k, n], b_blk)
+                            a_xf.wait()
+                            b_xf.wait()
+                    with v_cb.reserve() as v_blk:
+                        v_xf = ttl.copy(bias[0, n], v_blk)
+                        v_xf.wait()
+
+        @ttl.datamovement()
+        def mm_writer():
+            for m in range(Mt):
+                for n in range(Nt):
+                    with y_cb.wait() as y_blk:
+                        y_xf = ttl.copy(y_blk, out[m, n])
+                        y_xf.wait()
+
+    return linear
+
+
 @ttl.kernel(grid=(1, 1))
 def linear_relu(a, b, bias, out):
     """Y = relu(A @ B + bias), bias a [1, N] row vector: the product is accumulated over the K tiles into a

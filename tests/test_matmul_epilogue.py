@@ -64,3 +64,47 @@ def test_gpu_linear_relu_1024(backend):
     want = torch.relu(a.cuda().float() @ b.cuda().float() + v.cuda().float())
     got = out._tensor.float()
     assert ((got - want).abs().max() / want.abs().max()).item() <= 1e-2
+
+
+@pytest.mark.parametrize("act", ["relu", "gelu", "silu", "sigmoid", "tanh"])
+def test_fp32_intermediates_fuse_bias_and_activation_into_the_gemm(act, backend):
+    """With fp32_dest_acc_en the element-wise launch disappears: one GEMM launch with the bias row and the
+    activation in its epilogue; its temporary gives its memory back."""
+    _, mods = backend
+    import ttnn
+    a, b, v = cases.gen((96, 160), "normal*0.08", 11), cases.gen((160, 128), "normal*0.08", 12), cases.gen((1, 128), "normal", 13)
+    ins = [ttnn.from_torch(t) for t in (a, b, v)]
+    out = ttnn.from_torch(torch.zeros((96, 128), dtype=torch.bfloat16))
+    plan = mods["matmul"].make_linear(act, fp32_dest_acc_en=True).plan(*ins, out)
+    d = plan.describe()
+    assert len(d) == 1 and d[0]["kind"] == "matmul_bf16" and d[0]["bias"] == 2 and d[0]["act"] == act and d[0]["out"] == 3
+    assert plan.temps[0]._tensor.numel() == 0
+    plan_oracle.run_plan(plan, [t._tensor for t in ins] + [out._tensor])
+    from oracle import tile_oracle
+    want = tile_oracle.UNARY[act](a.float() @ b.float() + v.float())
+    assert _rel(out._tensor, want) <= 1e-2
+    # without fp32 intermediates every op rounds to bf16: two launches
+    kinds = [x["kind"] for x in mods["matmul"].make_linear(act).plan(*ins, out).describe()]
+    assert kinds == ["matmul_bf16", "eltwise"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("act", ["relu", "gelu", "silu", "sigmoid", "tanh"])
+@pytest.mark.parametrize("shape", [(96, 160, 128), (2048, 256, 4096)], ids=["small_one_cta", "large_two_cta"])
+def test_gpu_fused_epilogue(act, shape, backend):
+    """The fused epilogue on both GEMM kernels (the large shape takes the two-CTA kernel) against fp32 torch."""
+    from ttl_b200 import capi
+    from oracle import tile_oracle
+    _, mods = backend
+    import ttnn
+    m, k, n = shape
+    a, b, v = cases.gen((m, k), f"normal*{k ** -0.5}", 21), cases.gen((k, n), "normal", 22), cases.gen((1, n), "normal", 23)
+    out = ttnn.from_torch(torch.zeros((m, n), dtype=torch.bfloat16))
+    prog = mods["matmul"].make_linear(act, fp32_dest_acc_en=True)
+    before = capi.context().launch_count()
+    prog(*(ttnn.from_torch(t) for t in (a, b, v)), out)
+    assert capi.context().launch_count() == before + 1
+    want = tile_oracle.UNARY[act](a.cuda().float() @ b.cuda().float() + v.cuda().float())
+    got = out._tensor.float()
+    assert ((got - want).abs().max() / want.abs().max()).item() <= 1e-2
+    capi.context().check_status()

@@ -62,7 +62,8 @@ struct GemmParams {
   long long wait_limit;
   int multicast;  // 1: `c` is an NVLink multicast address; the epilogue stores with multimem.st
   const __nv_bfloat16 *bias = nullptr;  // optional [m, n] matrix added to the product before rounding
-  long long ldbias = 0;
+  long long ldbias = 0;                 // 0: the bias is one row of n values, added to every output row
+  int act = 0;                          // TTLB_ACT_*: applied to product + bias before the rounding
 };
 
 // 16-byte store to a multicast address: the switch replicates it to every GPU of the group.
@@ -82,6 +83,9 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
   tn = r / rows;
 }
 
+// ACT: the instantiation with the activation epilogue (its transcendental code costs registers; the plain
+// instantiation is the kernel the matmul configurations are measured with)
+template <bool ACT>
 __global__ void __launch_bounds__(THREADS, 1)
 ttlb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
@@ -211,6 +215,7 @@ ttlb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (row < p.m && col0 < p.n) {
           if (col0 + 32 <= p.n) {
             if (brow) add_bias32(r, brow + c * 32);
+            if (ACT) apply_act32(r, p.act);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 o;
@@ -227,7 +232,7 @@ ttlb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
             for (int e = 0; e < 32; ++e)
               if (col0 + e < p.n)
-                crow[c * 32 + e] = __float2bfloat16_rn(__uint_as_float(r[e]) + (brow ? __bfloat162float(brow[c * 32 + e]) : 0.f));
+                crow[c * 32 + e] = __float2bfloat16_rn(act1(__uint_as_float(r[e]) + (brow ? __bfloat162float(brow[c * 32 + e]) : 0.f), ACT ? p.act : 0));
           }
         }
       }
@@ -299,8 +304,9 @@ int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const 
                                int64_t m, int64_t n, int64_t k, bool multicast, const void *bias, int64_t ldbias,
                                cudaStream_t stream) {
   if (m == 0 || n == 0) return TTLB_OK;
-  if (bias && (((uintptr_t)bias % 16) || (ldbias % 8) || ldbias < n))
-    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: bias must be 16-byte aligned with a row pitch >= N that is a multiple of 8");
+  if (bias && (((uintptr_t)bias % 16) || (ldbias % 8) || (ldbias != 0 && ldbias < n)))
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG,
+                     "matmul: bias must be 16-byte aligned with a row pitch >= N that is a multiple of 8 (or 0: one row)");
   if (multicast && (n % 32))
     return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: a multicast output needs N to be a multiple of 32");
   if (!a || !b || !c) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null operand");
@@ -329,7 +335,9 @@ int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const 
 
   // the attribute is per device, and a context is bound to one device
   if (!ctx->gemm_attr_set) {
-    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              SMEM_BYTES));
+    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               SMEM_BYTES));
     ctx->gemm_attr_set = true;
   }
@@ -347,9 +355,13 @@ int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const 
   p.multicast = multicast ? 1 : 0;
   p.bias = reinterpret_cast<const __nv_bfloat16 *>(bias);
   p.ldbias = ldbias;
+  p.act = ctx->gemm_act;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  ttlb_gemm_bf16_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+  if (p.act)
+    ttlb_gemm_bf16_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+  else
+    ttlb_gemm_bf16_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   TTLB_CUDA_CHECK(ctx, cudaGetLastError());
   ctx->launches += 1;
   return TTLB_OK;
@@ -368,6 +380,19 @@ extern "C" int ttlb_matmul_bf16_bias(ttlb_ctx *ctx, const ttlb_gemm_desc *d, con
   if (!bias) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null bias");
   return ttlb_launch_gemm_bf16_full(ctx, d->a, d->lda, d->b, d->ldb, d->c, d->ldc, d->m, d->n, d->k, false, bias, ldbias,
                                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int ttlb_matmul_bf16_epilogue(ttlb_ctx *ctx, const ttlb_gemm_desc *d, const void *bias, int64_t ldbias, int act,
+                                         void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null descriptor");
+  if (act < TTLB_ACT_NONE || act > TTLB_ACT_TANH) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: unknown activation %d", act);
+  if (!bias && ldbias != 0) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: a bias pitch without a bias");
+  ctx->gemm_act = act;
+  const int rc = ttlb_launch_gemm_bf16_full(ctx, d->a, d->lda, d->b, d->ldb, d->c, d->ldc, d->m, d->n, d->k, false, bias,
+                                            ldbias, reinterpret_cast<cudaStream_t>(stream));
+  ctx->gemm_act = 0;
+  return rc;
 }
 
 extern "C" int ttlb_matmul_bf16_multicast(ttlb_ctx *ctx, const ttlb_gemm_desc *d, void *stream) {
@@ -417,7 +442,7 @@ int ttlb_gemm_bf16_launch_raw(const void *a, int64_t lda, const void *b, int64_t
   rc = make_map(nullptr, &map_b, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb * 2, 64, BK);
   if (rc) return rc;
   if (!*attr_set) {
-    if (cudaFuncSetAttribute(ttlb_gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(ttlb_gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
       return TTLB_ERR_CUDA;
     *attr_set = true;
   }
@@ -433,7 +458,7 @@ int ttlb_gemm_bf16_launch_raw(const void *a, int64_t lda, const void *b, int64_t
   p.wait_limit = wait_limit;
   p.multicast = 0;
   const int tiles = p.tiles_m * p.tiles_n;
-  ttlb_gemm_bf16_kernel<<<tiles < sm_count ? tiles : sm_count, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
+  ttlb_gemm_bf16_kernel<false><<<tiles < sm_count ? tiles : sm_count, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   return cudaGetLastError() == cudaSuccess ? TTLB_OK : TTLB_ERR_CUDA;
 }
 

@@ -40,7 +40,8 @@ struct Gemm2Params {
   int *status;
   long long wait_limit;
   const __nv_bfloat16 *bias = nullptr;  // optional [m, n] matrix added to the product before rounding
-  long long ldbias = 0;
+  long long ldbias = 0;                 // 0: the bias is one row of n values, added to every output row
+  int act = 0;                          // TTLB_ACT_*: applied to product + bias before the rounding
 };
 
 template <int GROUP_M2>
@@ -54,7 +55,7 @@ __device__ __forceinline__ void tile_coords2(int t, int tiles_m, int tiles_n, in
   tn = r / rows;
 }
 
-template <int STAGES2, int GROUP_M2>
+template <int STAGES2, int GROUP_M2, bool ACT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS2, 1)
 ttlb_gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                            const Gemm2Params p) {
@@ -169,6 +170,7 @@ ttlb_gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         if (row < p.m && col0 < p.n) {
           if (col0 + 32 <= p.n) {
             if (brow) add_bias32(r, brow + c * 32);
+            if (ACT) apply_act32(r, p.act);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint4 o;
@@ -182,7 +184,7 @@ ttlb_gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
 #pragma unroll
             for (int e = 0; e < 32; ++e)
               if (col0 + e < p.n)
-                crow[c * 32 + e] = __float2bfloat16_rn(__uint_as_float(r[e]) + (brow ? __bfloat162float(brow[c * 32 + e]) : 0.f));
+                crow[c * 32 + e] = __float2bfloat16_rn(act1(__uint_as_float(r[e]) + (brow ? __bfloat162float(brow[c * 32 + e]) : 0.f), ACT ? p.act : 0));
           }
         }
       }
@@ -221,7 +223,9 @@ int ttlb_launch_gemm_bf16_2cta(ttlb_ctx *ctx, const void *a, int64_t lda, const 
   rc = ttlb_make_map_bf16_2d(ctx, &map_b, b, (uint64_t)n, (uint64_t)k, (uint64_t)ldb * 2, 64, BK2);
   if (rc) return rc;
   if (!ctx->gemm2_attr_set) {
-    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bf16_2cta_kernel<STAGES2_DEFAULT, GROUP_M2_DEFAULT>,
+    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bf16_2cta_kernel<STAGES2_DEFAULT, GROUP_M2_DEFAULT, false>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(STAGES2_DEFAULT)));
+    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bf16_2cta_kernel<STAGES2_DEFAULT, GROUP_M2_DEFAULT, true>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(STAGES2_DEFAULT)));
     ctx->gemm2_attr_set = true;
   }
@@ -237,11 +241,16 @@ int ttlb_launch_gemm_bf16_2cta(ttlb_ctx *ctx, const void *a, int64_t lda, const 
   p.wait_limit = ctx->wait_limit_cycles;
   p.bias = reinterpret_cast<const __nv_bfloat16 *>(bias);
   p.ldbias = ldbias;
+  p.act = ctx->gemm_act;
   const int tiles = p.tiles_m * p.tiles_n;
   int clusters = ctx->sm_count / 2;
   if (clusters > tiles) clusters = tiles;
-  ttlb_gemm_bf16_2cta_kernel<STAGES2_DEFAULT, GROUP_M2_DEFAULT>
-      <<<clusters * 2, THREADS2, smem2_bytes(STAGES2_DEFAULT), stream>>>(map_a, map_b, p);
+  if (p.act)
+    ttlb_gemm_bf16_2cta_kernel<STAGES2_DEFAULT, GROUP_M2_DEFAULT, true>
+        <<<clusters * 2, THREADS2, smem2_bytes(STAGES2_DEFAULT), stream>>>(map_a, map_b, p);
+  else
+    ttlb_gemm_bf16_2cta_kernel<STAGES2_DEFAULT, GROUP_M2_DEFAULT, false>
+        <<<clusters * 2, THREADS2, smem2_bytes(STAGES2_DEFAULT), stream>>>(map_a, map_b, p);
   TTLB_CUDA_CHECK(ctx, cudaGetLastError());
   ctx->launches += 1;
   return TTLB_OK;

@@ -207,6 +207,22 @@ __device__ __forceinline__ void add_bias32(uint32_t (&r)[32], const __nv_bfloat1
   }
 }
 
+// Activation applied to the fp32 accumulators in a GEMM epilogue (TTLB_ACT_* of ttlb200.h).
+__device__ __forceinline__ float act1(float x, int act) {
+  switch (act) {
+    case 1: return x < 0.f ? 0.f : x;                                  // relu
+    case 2: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); // gelu
+    case 3: return x / (1.0f + expf(-x));                              // silu
+    case 4: return 1.0f / (1.0f + expf(-x));                           // sigmoid
+    case 5: return tanhf(x);
+  }
+  return x;
+}
+__device__ __forceinline__ void apply_act32(uint32_t (&r)[32], int act) {
+#pragma unroll
+  for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(act1(__uint_as_float(r[e]), act));
+}
+
 // ---- two-CTA (cta_group::2) forms: a cluster of two CTAs drives one UMMA ------------
 // None of the loads below is multicast: each CTA loads its own part of the operands; only the
 // completion signal (mbarrier) may live in the peer CTA.

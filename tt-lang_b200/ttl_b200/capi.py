@@ -126,6 +126,8 @@ def rowfused_source(desc: "RowFusedDesc") -> str:
     return buf.value.decode()
 
 
+ACTIVATIONS = {"relu": 1, "gelu": 2, "silu": 3, "sigmoid": 4, "tanh": 5}   # TTLB_ACT_*
+
 BFP8_MODE_DEFAULT = 0
 
 
@@ -180,6 +182,8 @@ def lib() -> C.CDLL:
     l.ttlb_matmul_bf16.restype = C.c_int
     l.ttlb_matmul_bf16_bias.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_int64, C.c_void_p]
     l.ttlb_matmul_bf16_bias.restype = C.c_int
+    l.ttlb_matmul_bf16_epilogue.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
+    l.ttlb_matmul_bf16_epilogue.restype = C.c_int
     l.ttlb_pack_bfp8_b.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
     l.ttlb_pack_bfp8_b.restype = C.c_int
     l.ttlb_unpack_bfp8_b.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
@@ -254,6 +258,11 @@ class Context:
         """C = A @ B + bias (bias: bf16 [m, n], added in fp32 before the rounding)."""
         self.check(self._lib.ttlb_matmul_bf16_bias(self.handle, C.byref(desc), C.c_void_p(bias_ptr), ldbias,
                                                    C.c_void_p(stream)))
+
+    def matmul_bf16_epilogue(self, desc: "GemmDesc", bias_ptr: int, ldbias: int, act: int, stream: int) -> None:
+        """C = act(A @ B + bias); bias_ptr 0: no bias; ldbias 0: the bias is one row added to every output row."""
+        self.check(self._lib.ttlb_matmul_bf16_epilogue(self.handle, C.byref(desc), C.c_void_p(bias_ptr or None), ldbias, act,
+                                                       C.c_void_p(stream)))
 
     def matmul_f32(self, desc: "GemmDesc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_f32(self.handle, C.byref(desc), C.c_void_p(stream)))

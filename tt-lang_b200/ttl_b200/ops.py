@@ -24,11 +24,13 @@ def _dev2d(t: "_ttnn.Tensor", what: str) -> torch.Tensor:
 
 def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_ttnn.Tensor",
                 rect: Tuple[int, int, int, int], stream: int, multicast_ptr: Optional[int] = None,
-                bias: Optional["_ttnn.Tensor"] = None) -> None:
+                bias: Optional["_ttnn.Tensor"] = None, act: int = 0) -> None:
     """out[r0:r1, c0:c1] = a[r0:r1, :] @ b[:, c0:c1] (+ bias[r0:r1, c0:c1]) (element coordinates).  With
     `multicast_ptr` (the NVLink multicast address of out's element (0, 0)) the result is stored through the
     switch to every GPU of the multicast group instead of through out's own mapping."""
     r0, r1, c0, c1 = rect
+    if act and (b._packed is not None or multicast_ptr is not None or a._tensor.dtype != torch.bfloat16):
+        raise Unsupported("matmul with an activation epilogue: bfloat16 A, B and output, own-memory output only")
     if bias is not None and (b._packed is not None or multicast_ptr is not None or a._tensor.dtype != torch.bfloat16):
         raise Unsupported("matmul with bias: bfloat16 A, B, bias and output, own-memory output only")
     if b._packed is not None:
@@ -67,11 +69,19 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
         ctx.matmul_f32(d, stream)
     elif multicast_ptr is not None:
         ctx.matmul_bf16_multicast(d, stream)
-    elif bias is not None:
-        xc = _dev2d(bias, "bias")
-        if xc.dtype != torch.bfloat16 or tuple(xc.shape) != tuple(xo.shape):
-            raise Unsupported("matmul with bias: the bias must be a bfloat16 tensor of the output's shape")
-        ctx.matmul_bf16_bias(d, xc.data_ptr() + (r0 * xc.stride(0) + c0) * 2, xc.stride(0), stream)
+    elif bias is not None or act:
+        ptr, ld = 0, 0
+        if bias is not None:
+            xc = _dev2d(bias, "bias")
+            row_vector = xc.shape[0] == 1 and xo.shape[0] != 1
+            if xc.dtype != torch.bfloat16 or (not row_vector and tuple(xc.shape) != tuple(xo.shape)) or xc.shape[1] != xo.shape[1]:
+                raise Unsupported("matmul with bias: the bias must be a bfloat16 tensor of the output's shape or one row of it")
+            ptr = xc.data_ptr() + ((0 if row_vector else r0 * xc.stride(0)) + c0) * 2
+            ld = 0 if row_vector else xc.stride(0)
+        if act or ld == 0:
+            ctx.matmul_bf16_epilogue(d, ptr, ld, act, stream)
+        else:
+            ctx.matmul_bf16_bias(d, ptr, ld, stream)
     else:
         ctx.matmul_bf16(d, stream)
 

@@ -498,6 +498,55 @@ class RowFusedLaunch:
         self.final.run(ctx, tensors, stream)
 
 
+def _fuse_epilogues(launches: List[Any]) -> List[Any]:
+    """With fp32 intermediates: [bf16 GEMM into a temporary] + [element-wise launch over the same rectangle that
+    only adds a bias (full matrix or one row) and/or applies an activation the GEMM epilogue knows] becomes the GEMM
+    alone, with bias and activation applied to its fp32 accumulators before the one rounding."""
+    readers: Dict[int, int] = {}
+    for l in launches:
+        for (ti, *_r) in getattr(l, "inputs", []):
+            readers[ti] = readers.get(ti, 0) + 1
+    out: List[Any] = []
+    gone: Dict[int, None] = {}
+    gemm_of = {l.out_index: l for l in launches if isinstance(l, GemmLaunch) and l.out_index >= TEMP_BASE}
+    for l in launches:
+        g = None
+        if isinstance(l, EltwiseLaunch) and not l.round_each_op and l.dtype == torch.bfloat16 and 1 <= len(l.inputs) <= 2:
+            temps_read = [k for k, inp in enumerate(l.inputs) if inp[0] in gemm_of]
+            if len(temps_read) == 1:
+                g = gemm_of[l.inputs[temps_read[0]][0]]
+        ok = (g is not None and g.kind == "matmul_bf16" and not g.b_is_bfp8 and g.bias_index is None and g.act is None
+              and g.rect == l.rect and readers.get(g.out_index, 0) == 1 and not l.imms)
+        bias = act = None
+        if ok:
+            t = temps_read[0]
+            ok = l.inputs[t][1:] == (capi.IDX_SAME, 0, capi.IDX_SAME, 0)
+            ops = list(l.ops)
+            if ok and len(l.inputs) == 2:
+                v = 1 - t
+                ti, rm, ro, cm, co = l.inputs[v]
+                # p + v or v + p, v a full matrix of the output's shape or one row
+                ok = (ops[:2] in ([("load", t), ("add", v)], [("load", v), ("add", t)]) and (cm, co) == (capi.IDX_SAME, 0)
+                      and ((rm, ro) == (capi.IDX_SAME, 0) or rm == capi.IDX_ZERO and ro == 0) and ti < TEMP_BASE)
+                bias, ops = ti, ops[2:]
+            elif ok:
+                ok = ops[:1] == [("load", t)]
+                ops = ops[1:]
+            if ok and ops:
+                ok = len(ops) == 1 and ops[0][0] in capi.ACTIVATIONS
+                act = ops[0][0] if ok else None
+            ok = ok and (bias is not None or act is not None)
+        if not ok:
+            out.append(l)
+            continue
+        fused = GemmLaunch(g.a_index, g.b_index, l.out_index, g.rect, g.k_tiles, False, bias, act)
+        fused.lines = {**(getattr(g, "lines", None) or {}), **(getattr(l, "lines", None) or {})}
+        fused._bias_row = bias is not None and l.inputs[1 - temps_read[0]][1] == capi.IDX_ZERO
+        gone[id(g)] = None
+        out.append(fused)
+    return [l for l in out if id(l) not in gone]
+
+
 def _fuse_rows(launches: List[Any]) -> List[Any]:
     """Merge [reductions over columns into temporaries] + [the element-wise launch that reads them] into
     RowFusedLaunch where every launch covers the same rows and full row length, and the temporaries have no
@@ -558,10 +607,13 @@ def _fuse_rows(launches: List[Any]) -> List[Any]:
 
 
 class GemmLaunch:
+    lines: Dict[Any, int] = {}
+
     def __init__(self, a_index: int, b_index: int, out_index: int, rect: Tuple[int, int, int, int], k_tiles: int,
-                 b_is_bfp8: bool, bias_index: Optional[int] = None):
+                 b_is_bfp8: bool, bias_index: Optional[int] = None, act: Optional[str] = None):
         self.a_index, self.b_index, self.out_index, self.rect = a_index, b_index, out_index, rect
         self.k_tiles, self.b_is_bfp8, self.bias_index = k_tiles, b_is_bfp8, bias_index
+        self.act = act    # activation applied in the GEMM epilogue (fused from a following element-wise launch)
         self.kind = "matmul_bf16"   # set to "matmul_f32" by the recogniser for float32 programs
 
     def describe(self) -> Dict[str, Any]:
@@ -569,6 +621,8 @@ class GemmLaunch:
              "out": self.out_index, "rect_tiles": self.rect, "k_tiles": self.k_tiles}
         if self.bias_index is not None:
             d["bias"] = self.bias_index
+        if self.act is not None:
+            d["act"] = self.act
         return d
 
     def run(self, ctx: capi.Context, tensors: Sequence[_ttnn.Tensor], stream: int) -> None:
@@ -577,7 +631,8 @@ class GemmLaunch:
         r0, r1, c0, c1 = self.rect
         ops.launch_gemm(ctx, tensors[self.a_index], tensors[self.b_index], tensors[self.out_index],
                         (r0 * TILE, r1 * TILE, c0 * TILE, c1 * TILE), stream,
-                        bias=None if self.bias_index is None else tensors[self.bias_index])
+                        bias=None if self.bias_index is None else tensors[self.bias_index],
+                        act=capi.ACTIVATIONS[self.act] if self.act else 0)
 
 
 class Plan:
@@ -943,8 +998,21 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
             launches.add(key, gl)
     # a launch that reads a temporary runs after the launch that fills it
     ordered = [l for _, l in sorted(launches, key=lambda p: p[0])]
+    if fp32_intermediates:
+        ordered = _fuse_epilogues(ordered)
     if ROW_FUSION:
         ordered = _fuse_rows(ordered)
+    # temporaries that the fusions made unnecessary keep their index but give their memory back
+    used: Dict[int, None] = {}
+    for l in ordered:
+        for part in list(getattr(l, "parts", [])) + [getattr(l, "final", l), l]:
+            for (ti, *_r) in getattr(part, "inputs", []):
+                used[ti] = None
+            for attr in ("out_index", "a_index", "b_index", "bias_index"):
+                used[getattr(part, attr, None)] = None  # type: ignore[index]
+    for i, t in enumerate(table.temps):
+        if TEMP_BASE + i not in used:
+            t._tensor = torch.empty((0, 0), dtype=t._tensor.dtype, device=t._tensor.device)
     return Plan(ordered, table.extras, len(table.args), table.temps)
 
 
