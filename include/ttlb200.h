@@ -427,6 +427,11 @@ TTLB_EXPORT int ttlb_matmul_bf16_bias(ttlb_ctx *ctx, const ttlb_gemm_desc *desc,
 TTLB_EXPORT int ttlb_matmul_bf16_epilogue(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, const void *bias, int64_t ldbias,
                                           int act, void *stream);
 
+/* The same epilogue for bfloat8_b weights (a quantised linear layer with bias and activation): the weight window
+ * is expanded to bf16 in the context's scratch, then the bf16 GEMM runs with the bias / activation epilogue. */
+TTLB_EXPORT int ttlb_matmul_bfp8w_epilogue(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, const void *bias,
+                                           int64_t ldbias, int act, void *stream);
+
 /* Which tensor-core GEMM kernel the bf16 / bfp8-weight matmuls use:
  *   0  always one CTA per 128x256 output tile (tcgen05 cta_group::1)
  *   1  (default) a cluster of two CTAs per 256x256 tile (cta_group::2: each CTA stages half of the

@@ -127,3 +127,28 @@ def test_chunked_expansion_overlapping_the_gemm_gives_the_same_bits():
         wq = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))
         assert rel_err(outs[(seed, 4)][0][:256], tile_oracle.matmul_tiles(x[:256].float(), wq, "f32")) <= 1e-2
     assert not torch.equal(outs[(21, 4)][0], outs[(22, 4)][0])
+
+
+@pytest.mark.parametrize("act", ["gelu", "relu"])
+def test_quantised_linear_program_with_bias_and_activation(backend, act):
+    """Y = act(X @ W + bias) as a tile program with W a bfloat8_b tensor and fp32 intermediates: one launch of
+    the unpack kernel and one GEMM launch with the bias row and the activation in its epilogue."""
+    _, mods = backend
+    import ttnn
+    from ttl_b200 import capi
+    m, k, n = 128, 256, 192
+    x = cases.gen((m, k), "normal", 4)
+    w = cases.gen((k, n), "normal*0.02", 5, torch.float32)
+    v = cases.gen((1, n), "normal", 6)
+    wq = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))
+    out = ttnn.from_torch(torch.zeros((m, n), dtype=torch.bfloat16))
+    W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+    prog = mods["matmul"].make_linear(act, fp32_dest_acc_en=True)
+    d = prog.plan(ttnn.from_torch(x), W, ttnn.from_torch(v), out).describe()
+    assert len(d) == 1 and d[0]["kind"] == "matmul_bfp8w" and d[0]["act"] == act and d[0]["bias"] == 2
+    before = capi.context().launch_count()
+    prog(ttnn.from_torch(x), W, ttnn.from_torch(v), out)
+    assert capi.context().launch_count() == before + 2     # weight expansion + GEMM
+    capi.context().check_status(capi.current_stream())
+    want = tile_oracle.UNARY[act](x.float() @ wq + v.float())
+    assert rel_err(ttnn.to_torch(out), want) <= 1e-2

@@ -30,6 +30,10 @@ int ttlb_launch_gemm_bf16(ttlb_ctx *ctx, const void *a, int64_t lda, const void 
 int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
                              int64_t m, int64_t n, int64_t k, bool multicast, cudaStream_t stream);
 
+int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
+                               int64_t m, int64_t n, int64_t k, bool multicast, const void *bias, int64_t ldbias,
+                               cudaStream_t stream);
+
 int ttlb_launch_gemm_bfp8w_fused(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, cudaStream_t stream);
 
 namespace {
@@ -252,6 +256,40 @@ extern "C" int ttlb_set_bfp8_mode(ttlb_ctx *ctx, int mode) {
 
 extern "C" int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, void *stream) {
   return matmul_bfp8w_impl(ctx, d, false, stream);
+}
+
+// The quantised linear layer with bias and activation: weights expanded to bf16 in the context's scratch, then
+// the bf16 GEMM with the bias / activation epilogue.
+extern "C" int ttlb_matmul_bfp8w_epilogue(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, const void *bias, int64_t ldbias,
+                                          int act, void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul_bfp8w: null descriptor");
+  if (act < TTLB_ACT_NONE || act > TTLB_ACT_TANH) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: unknown activation %d", act);
+  if (!bias && ldbias != 0) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: a bias pitch without a bias");
+  if (d->m == 0 || d->n == 0) return TTLB_OK;
+  int rc = check_bfp8_args(ctx, d->b_tiles, d->b_tile_cols, d->b_tile_col0, d->k, d->n);
+  if (rc) return rc;
+  ttlb_device_guard g(ctx->device);
+  if (!g.ok) return ttlb_fail(ctx, TTLB_ERR_CUDA, "matmul_bfp8w: cannot select device %d", ctx->device);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const size_t need = (size_t)d->k * (size_t)d->n * 2;
+  if (ctx->scratch_bytes < need) {
+    if (ctx->scratch) {
+      TTLB_CUDA_CHECK(ctx, cudaStreamSynchronize(s));
+      TTLB_CUDA_CHECK(ctx, cudaFree(ctx->scratch));
+      ctx->scratch = nullptr;
+      ctx->scratch_bytes = 0;
+    }
+    TTLB_CUDA_CHECK(ctx, cudaMalloc(&ctx->scratch, need));
+    ctx->scratch_bytes = need;
+  }
+  rc = launch_unpack(ctx, reinterpret_cast<const uint8_t *>(d->b_tiles), d->b_tile_cols, d->b_tile_col0, d->k / 32, d->n / 32,
+                     ctx->scratch, d->n, s);
+  if (rc) return rc;
+  ctx->gemm_act = act;
+  rc = ttlb_launch_gemm_bf16_full(ctx, d->a, d->lda, ctx->scratch, d->n, d->c, d->ldc, d->m, d->n, d->k, false, bias, ldbias, s);
+  ctx->gemm_act = 0;
+  return rc;
 }
 
 extern "C" int ttlb_matmul_bfp8w_multicast(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, void *stream) {

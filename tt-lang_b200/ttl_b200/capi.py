@@ -184,6 +184,8 @@ def lib() -> C.CDLL:
     l.ttlb_matmul_bf16_bias.restype = C.c_int
     l.ttlb_matmul_bf16_epilogue.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
     l.ttlb_matmul_bf16_epilogue.restype = C.c_int
+    l.ttlb_matmul_bfp8w_epilogue.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
+    l.ttlb_matmul_bfp8w_epilogue.restype = C.c_int
     l.ttlb_pack_bfp8_b.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
     l.ttlb_pack_bfp8_b.restype = C.c_int
     l.ttlb_unpack_bfp8_b.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
@@ -263,6 +265,10 @@ class Context:
         """C = act(A @ B + bias); bias_ptr 0: no bias; ldbias 0: the bias is one row added to every output row."""
         self.check(self._lib.ttlb_matmul_bf16_epilogue(self.handle, C.byref(desc), C.c_void_p(bias_ptr or None), ldbias, act,
                                                        C.c_void_p(stream)))
+
+    def matmul_bfp8w_epilogue(self, desc: "GemmBfp8Desc", bias_ptr: int, ldbias: int, act: int, stream: int) -> None:
+        self.check(self._lib.ttlb_matmul_bfp8w_epilogue(self.handle, C.byref(desc), C.c_void_p(bias_ptr or None), ldbias, act,
+                                                        C.c_void_p(stream)))
 
     def matmul_f32(self, desc: "GemmDesc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_f32(self.handle, C.byref(desc), C.c_void_p(stream)))

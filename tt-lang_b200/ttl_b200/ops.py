@@ -29,10 +29,18 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
     `multicast_ptr` (the NVLink multicast address of out's element (0, 0)) the result is stored through the
     switch to every GPU of the multicast group instead of through out's own mapping."""
     r0, r1, c0, c1 = rect
-    if act and (b._packed is not None or multicast_ptr is not None or a._tensor.dtype != torch.bfloat16):
-        raise Unsupported("matmul with an activation epilogue: bfloat16 A, B and output, own-memory output only")
-    if bias is not None and (b._packed is not None or multicast_ptr is not None or a._tensor.dtype != torch.bfloat16):
-        raise Unsupported("matmul with bias: bfloat16 A, B, bias and output, own-memory output only")
+    if (act or bias is not None) and (multicast_ptr is not None or a._tensor.dtype != torch.bfloat16):
+        raise Unsupported("matmul with bias / activation: bfloat16 A, bias and output, own-memory output only")
+
+    def bias_args(xo: torch.Tensor) -> Tuple[int, int]:
+        if bias is None:
+            return 0, 0
+        xc = _dev2d(bias, "bias")
+        row_vector = xc.shape[0] == 1 and xo.shape[0] != 1
+        if xc.dtype != torch.bfloat16 or (not row_vector and tuple(xc.shape) != tuple(xo.shape)) or xc.shape[1] != xo.shape[1]:
+            raise Unsupported("matmul with bias: the bias must be a bfloat16 tensor of the output's shape or one row of it")
+        return xc.data_ptr() + ((0 if row_vector else r0 * xc.stride(0)) + c0) * 2, 0 if row_vector else xc.stride(0)
+
     if b._packed is not None:
         xa, xo = _dev2d(a, "A"), _dev2d(out, "out")
         if xa.dtype != torch.bfloat16 or xo.dtype != torch.bfloat16:
@@ -47,7 +55,10 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
         c_base = xo.data_ptr() if multicast_ptr is None else multicast_ptr
         g.c, g.ldc = c_base + (r0 * xo.stride(0) + c0) * 2, xo.stride(0)
         g.m, g.n, g.k = r1 - r0, c1 - c0, xa.shape[1]
-        if multicast_ptr is None:
+        if bias is not None or act:
+            ptr, ld = bias_args(xo)
+            ctx.matmul_bfp8w_epilogue(g, ptr, ld, act, stream)
+        elif multicast_ptr is None:
             ctx.matmul_bfp8w(g, stream)
         else:
             ctx.matmul_bfp8w_multicast(g, stream)
@@ -70,14 +81,7 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
     elif multicast_ptr is not None:
         ctx.matmul_bf16_multicast(d, stream)
     elif bias is not None or act:
-        ptr, ld = 0, 0
-        if bias is not None:
-            xc = _dev2d(bias, "bias")
-            row_vector = xc.shape[0] == 1 and xo.shape[0] != 1
-            if xc.dtype != torch.bfloat16 or (not row_vector and tuple(xc.shape) != tuple(xo.shape)) or xc.shape[1] != xo.shape[1]:
-                raise Unsupported("matmul with bias: the bias must be a bfloat16 tensor of the output's shape or one row of it")
-            ptr = xc.data_ptr() + ((0 if row_vector else r0 * xc.stride(0)) + c0) * 2
-            ld = 0 if row_vector else xc.stride(0)
+        ptr, ld = bias_args(xo)
         if act or ld == 0:
             ctx.matmul_bf16_epilogue(d, ptr, ld, act, stream)
         else:

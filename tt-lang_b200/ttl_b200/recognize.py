@@ -515,7 +515,7 @@ def _fuse_epilogues(launches: List[Any]) -> List[Any]:
             temps_read = [k for k, inp in enumerate(l.inputs) if inp[0] in gemm_of]
             if len(temps_read) == 1:
                 g = gemm_of[l.inputs[temps_read[0]][0]]
-        ok = (g is not None and g.kind == "matmul_bf16" and not g.b_is_bfp8 and g.bias_index is None and g.act is None
+        ok = (g is not None and g.kind == "matmul_bf16" and g.bias_index is None and g.act is None
               and g.rect == l.rect and readers.get(g.out_index, 0) == 1 and not l.imms)
         bias = act = None
         if ok:
@@ -539,7 +539,7 @@ def _fuse_epilogues(launches: List[Any]) -> List[Any]:
         if not ok:
             out.append(l)
             continue
-        fused = GemmLaunch(g.a_index, g.b_index, l.out_index, g.rect, g.k_tiles, False, bias, act)
+        fused = GemmLaunch(g.a_index, g.b_index, l.out_index, g.rect, g.k_tiles, g.b_is_bfp8, bias, act)
         fused.lines = {**(getattr(g, "lines", None) or {}), **(getattr(l, "lines", None) or {})}
         fused._bias_row = bias is not None and l.inputs[1 - temps_read[0]][1] == capi.IDX_ZERO
         gone[id(g)] = None
@@ -989,8 +989,8 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
     for key, rects in mm_groups.items():
         _, ai, bi, oi, kt, b8, ci = key
         f32 = out_tensors[oi].dtype == torch.float32
-        if ci is not None and (f32 or b8):
-            raise Unsupported("matmul with bias: bfloat16 A, B, bias and output only")
+        if ci is not None and f32:
+            raise Unsupported("matmul with bias: bfloat16 A, bias and output only")
         for rect in merge_rects(rects):
             gl = GemmLaunch(ai, bi, oi, rect, kt, b8, ci)
             if f32:
