@@ -432,10 +432,7 @@ def run_sharded(args):
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in),
                     "d2h_bytes_per_step": int(result_holder["host"].numel() * 2) if "host" in result_holder else 0,
-                    "ms_per_step": e2e_ms, "steps": args.e2e_steps,
-                    "api": (f"ttl_b200.run_streamed(kernel, pinned inputs, pinned output, chunks={args.e2e_chunks}): "
-                            "host->HBM, kernel, HBM->host overlapped per row chunk" if args.e2e_chunks > 1 else
-                            "ttnn.from_torch, kernel call, ttnn.to_torch(out=pinned), one after the other")},
+                    "ms_per_step": e2e_ms, "steps": args.e2e_steps},
             "gpu_launches": launches,
             "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
         }
@@ -864,7 +861,10 @@ def main():
                          "kernel": "ttlb_eltwise_jit" if ctx.eltwise_last_path() == capi.ELTWISE_SPECIALISED
                          else "ttlb_eltwise_kernel<bf16>"},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms, "steps": args.e2e_steps},
+                    "ms_per_step": e2e_ms, "steps": args.e2e_steps,
+                    "api": (f"ttl_b200.run_streamed(kernel, pinned inputs, pinned output, chunks={args.e2e_chunks}): "
+                            "host->HBM, kernel, HBM->host overlapped per row chunk" if args.e2e_chunks > 1 else
+                            "ttnn.from_torch, kernel call, ttnn.to_torch(out=pinned), one after the other")},
             "gpu_launches": launches,
             "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
         }
