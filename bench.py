@@ -147,6 +147,10 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    import torch
+
+    # rank 0 runs alone: use every host core (torchrun starts its ranks with OMP_NUM_THREADS=1)
+    torch.set_num_threads(max(torch.get_num_threads(), os.cpu_count() or 1))
     rows = 1024
     for _ in range(max(args.warmup, 1)):
         cpu_baseline(rows, 1)
