@@ -16,6 +16,7 @@
 // --fmad=false keeps `a*b + c` as two roundings, which is what the simulator computes.
 #include <dlfcn.h>
 
+#include <cstdlib>
 #include <functional>
 
 #include <map>
@@ -104,8 +105,9 @@ __device__ __forceinline__ void st_stream(void* p, uint4 v) {
 __device__ __forceinline__ u32 pack_bf16x2(float lo, float hi) {
   u32 r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r;
 }
-__device__ __forceinline__ float nan_max(float a, float b) { return (a > b || a != a) ? a : b; }
-__device__ __forceinline__ float nan_min(float a, float b) { return (a < b || a != a) ? a : b; }
+// NaN-propagating like torch.maximum / torch.minimum: one instruction each
+__device__ __forceinline__ float nan_max(float a, float b) { float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ float nan_min(float a, float b) { float r; asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
 )SRC";
 
 const char *binary_expr(int op) {
@@ -870,7 +872,11 @@ std::string ttlb_rowfused_jit_source(const ttlb_rowfused_desc *f) {
   else
     s << "__device__ __forceinline__ float ld_elem(const void* q) { return *(const float*)q; }\n"
          "__device__ __forceinline__ void st_elem(void* base, i64 idx, float x) { ((float*)base)[idx] = x; }\n";
-  s << "extern \"C\" __global__ void __launch_bounds__(256) ttlb_rowfused_jit(const __grid_constant__ RowParams q) {\n"
+  // TTLB200_ROWFUSED_MIN_CTAS=n asks the compiler to fit n CTAs per SM (fewer registers, possibly spills)
+  int min_ctas = 0;
+  if (const char *e = getenv("TTLB200_ROWFUSED_MIN_CTAS")) min_ctas = atoi(e);
+  s << "extern \"C\" __global__ void __launch_bounds__(256" << (min_ctas > 0 ? ", " + std::to_string(min_ctas) : std::string())
+    << ") ttlb_rowfused_jit(const __grid_constant__ RowParams q) {\n"
        "  const JitParams& p = q.p;\n"
        "  __shared__ float sm[8];\n"
        "  const u32 lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;\n";
