@@ -47,3 +47,17 @@ def test_programs_that_mix_rows_are_refused(backend):
     with pytest.raises(ttl_b200.Unsupported, match="rows are independent"):
         ttl_b200.run_streamed(mods["reduce"].make_reduce("sum", [0]), [a, torch.ones(32, 32, dtype=torch.bfloat16)],
                               torch.zeros(32, 128, dtype=torch.bfloat16))
+
+
+@pytest.mark.gpu
+def test_row_softmax_streams_too(backend):
+    """A row-fused program (softmax: reductions over columns + element-wise) is row-parallel as well."""
+    import ttl_b200
+    _, mods = backend
+    case = cases.by_name("softmax_128x256")
+    host = [t.pin_memory() for t in case.make_inputs()]
+    out = torch.empty(case.out_shape, dtype=case.dtype).pin_memory()
+    ttl_b200.run_streamed(case.get_program(mods), host, out, chunks=2)
+    from conftest import golden_tensor, load_golden
+    from test_reduce import close
+    close(out, golden_tensor(load_golden(case.name)["out"], case.dtype), case.check, "streamed softmax")

@@ -19,7 +19,7 @@ import torch
 
 from . import capi
 from . import ttnn as _ttnn
-from .recognize import Unsupported
+from .recognize import TEMP_BASE, Unsupported
 
 TILE = 32
 
@@ -27,9 +27,14 @@ TILE = 32
 def _check_row_parallel(plan: Any, split: Sequence[bool], chunk_rows: int) -> None:
     for l in plan.launches:
         d = l.describe()
-        if d["kind"] != "eltwise":
+        if d["kind"] == "row_fused":     # reductions over columns + element-wise: every row on its own
+            inputs = [inp for ph in d["phases"] for inp in ph["inputs"]] + list(d["final"]["inputs"])
+            inputs = [inp for inp in inputs if inp[0] < TEMP_BASE]    # the others are results kept on chip
+        elif d["kind"] == "eltwise":
+            inputs = d["inputs"]
+        else:
             raise Unsupported(f"run_streamed needs a program whose output rows are independent; found a {d['kind']} launch")
-        for (ti, rm, ro, _cm, _co) in d["inputs"]:
+        for (ti, rm, ro, _cm, _co) in inputs:
             whole = ti >= len(split) or not split[ti]
             # a split operand is read row for row (a chunk of one tile row shows up as "one tile repeated")
             row_for_row = ro == 0 and (rm == capi.IDX_SAME or (rm == capi.IDX_TILE and chunk_rows == TILE))
