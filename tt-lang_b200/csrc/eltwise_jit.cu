@@ -257,6 +257,10 @@ int rows_per_iteration(const ttlb_eltwise_desc *d) {
   for (int k = 0; k < d->n_in; ++k)
     if (d->in[k].row_mode != TTLB_IDX_ZERO && (d->in[k].col_mode == TTLB_IDX_SAME || d->in[k].col_mode == TTLB_IDX_TILE))
       ++streaming;
+  if (const char *e = getenv("TTLB200_ELTWISE_ROWS")) {   // tuning knob: rows in flight per thread
+    const int v = atoi(e);
+    if (v >= 1 && v <= 8) return v;
+  }
   int u = 8 / (streaming > 0 ? streaming : 1);
   return u < 1 ? 1 : u > 4 ? 4 : u;
 }
@@ -279,7 +283,10 @@ std::string ttlb_eltwise_jit_source(const ttlb_eltwise_desc *d) {
   std::ostringstream s;
   s << kPrelude;
   s << "#define V " << V << "\n";
-  s << "extern \"C\" __global__ void __launch_bounds__(256) ttlb_eltwise_jit(const __grid_constant__ JitParams p) {\n"
+  int min_ctas = 0;   // tuning knob: ask the compiler to fit this many CTAs per SM
+  if (const char *e = getenv("TTLB200_ELTWISE_MIN_CTAS")) min_ctas = atoi(e);
+  s << "extern \"C\" __global__ void __launch_bounds__(256" << (min_ctas > 0 ? ", " + std::to_string(min_ctas) : std::string())
+    << ") ttlb_eltwise_jit(const __grid_constant__ JitParams p) {\n"
        "  const u32 tx = threadIdx.x & ((1u << p.bx_log2) - 1u), ty = threadIdx.x >> p.bx_log2;\n"
        "  const u32 by = 256u >> p.bx_log2;\n"
        "  const u32 cv = (blockIdx.x << p.bx_log2) + tx;\n"
