@@ -165,3 +165,81 @@ def test_random_reductions(seed, op, dims, backend):
     assert torch.equal(got[:out_rows, :out_cols].float(), block), (seed, op, dims, ops, inputs, rect)
     got[:out_rows, :out_cols] = 9.0
     assert (got == 9.0).all(), "the kernel wrote outside its result"
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_row_fused_programs(seed, backend):
+    """ttlb_rowfused: one to three reductions over columns, each program free to read the results of the earlier
+    ones, then a final element-wise program; against the same stages evaluated one after the other on the host."""
+    from ttl_b200 import capi
+    ctx = capi.context()
+    rng = random.Random(5000 + seed)
+    dtype = torch.bfloat16 if seed % 2 else torch.float32
+    vec = 8 if dtype == torch.bfloat16 else 4
+    rnd = dtype == torch.bfloat16 and seed % 4 == 1
+    rows, cols = rng.choice([1, 7, 33, 96]), rng.choice([1, 2, 5]) * vec
+    row0, col0 = rng.choice([0, 3, 32]), rng.choice([0, 1]) * vec
+    rect = (row0, rows, col0, cols)
+    n_mem = rng.randrange(1, 4)
+    tensors, mem_inputs = [], []
+    for k in range(n_mem):
+        t, (rm, ro, cm, co) = make_operand(rng, row0, rows, col0, cols, dtype, vec)
+        if k == 0:
+            rm, cm, ro, co = SAME, SAME, 0, 0      # at least one operand that varies along both dims
+            t = torch.randint(-3, 4, (row0 + rows, col0 + cols), generator=torch.Generator().manual_seed(seed)).to(dtype)
+        tensors.append(t)
+        mem_inputs.append((k, rm, ro, cm, co))
+    dev = [t.cuda() for t in tensors]
+    n_phases = rng.randrange(1, 4)
+    f = capi.RowFusedDesc()
+    f.n_phases = n_phases
+    results = []                    # host tensors [row0 + rows, 1] holding the phase results
+    scalers = []
+    for st in range(n_phases + 1):
+        # operands of this stage: the memory operands and the earlier results
+        inputs = list(mem_inputs) + [(n_mem + q, SAME, 0, ZERO, 0) for q in range(len(results))]
+        ops = make_program(rng, len(inputs), 2, False)
+        vals = plan_oracle._evaluate(inputs, ops, tensors + results, torch.arange(row0, row0 + rows),
+                                     torch.arange(col0, col0 + cols), rnd)
+        d = f.phase[st].src if st < n_phases else f.final
+        d.dtype = capi.TTLB_BF16 if dtype == torch.bfloat16 else capi.TTLB_F32
+        d.round_each_op = 1 if rnd else 0
+        d.n_in, d.n_ops = len(inputs), len(ops)
+        for k, (ti, rm, ro, cm, co) in enumerate(inputs):
+            if ti < n_mem:
+                d.inp[k].ptr, d.inp[k].ld = dev[ti].data_ptr(), dev[ti].stride(0)
+                d.inp[k].row_mode, d.inp[k].row_off, d.inp[k].col_mode, d.inp[k].col_off = rm, ro, cm, co
+            else:
+                d.inp[k].row_mode, d.inp[k].row_off = capi.IDX_PHASE, ti - n_mem
+        for k, (op, arg) in enumerate(ops):
+            d.ops[k].opcode, d.ops[k].arg = capi.OPCODES[op], arg
+        d.row0, d.rows, d.col0, d.cols = rect
+        if st == n_phases:
+            want = vals.to(dtype)
+            break
+        op = rng.choice(["sum", "max"])
+        scale = rng.choice([1.0, 0.5, 2.0])
+        red = vals.sum(dim=1, keepdim=True) if op == "sum" else vals.amax(dim=1, keepdim=True)
+        res = torch.zeros(row0 + rows, 1, dtype=dtype)
+        res[row0:] = (red * scale).to(dtype)
+        results.append(res)
+        scalers.append(torch.full((1, 1), scale, dtype=dtype, device="cuda"))
+        f.phase[st].op = capi.REDUCE_SUM if op == "sum" else capi.REDUCE_MAX
+        f.phase[st].dims = capi.REDUCE_COLS
+        f.phase[st].scaler = scalers[-1].data_ptr()
+    out = torch.full((row0 + rows + 1, col0 + cols + vec), 9.0, dtype=dtype, device="cuda")
+    # the second reduction's result is also written out, as ttlb_reduce would (fill 1)
+    red_out = torch.full((rows + 1, vec), 9.0, dtype=dtype, device="cuda")
+    if n_phases >= 2:
+        f.phase[1].out, f.phase[1].out_ld, f.phase[1].fill_cols = red_out.data_ptr(), red_out.stride(0), 1
+    f.final.out, f.final.out_ld = out.data_ptr(), out.stride(0)
+    ctx.rowfused(f, capi.current_stream())
+    got = out.cpu()
+    assert torch.equal(got[row0:row0 + rows, col0:col0 + cols].float(), want.float()), (seed, n_phases, rect)
+    got[row0:row0 + rows, col0:col0 + cols] = 9.0
+    assert (got == 9.0).all(), "the kernel wrote outside its rectangle"
+    if n_phases >= 2:
+        r = red_out.cpu()
+        assert torch.equal(r[:rows, 0].float(), results[1][row0:, 0].float())
+        r[:rows, 0] = 9.0
+        assert (r == 9.0).all()
