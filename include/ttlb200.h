@@ -102,6 +102,14 @@ enum ttlb_opcode {
   TTLB_OP_RDIV = 6, /* acc = x / acc */
   TTLB_OP_MAX = 7,
   TTLB_OP_MIN = 8,
+  /* The remaining block operators of the simulator (python/sim/block.py:975-1010, torch semantics of
+   * python/sim/ttnnsim.py:424-450); executed by the specialised kernel only. */
+  TTLB_OP_FLOORDIV = 9,   /* floor(acc / x) as torch.floor_divide computes it */
+  TTLB_OP_RFLOORDIV = 10, /* floor(x / acc) */
+  TTLB_OP_MOD = 11,       /* remainder with the sign of the divisor (torch.remainder) */
+  TTLB_OP_RMOD = 12,
+  TTLB_OP_POW = 13,       /* acc ** x */
+  TTLB_OP_RPOW = 14,      /* x ** acc */
   TTLB_OP_EXP = 16,
   TTLB_OP_LOG = 17,
   TTLB_OP_SQRT = 18,
@@ -142,7 +150,8 @@ enum ttlb_opcode {
   TTLB_OP_CELU = 69,       /* max(0, x) + min(0, p0 (exp(x p1) - 1)), p1 = 1 / p0 */
   TTLB_OP_SOFTPLUS = 70,   /* x p0 > p2 ? x : log(1 + exp(x p0)) p1, p1 = 1 / p0 */
   TTLB_OP_HARDTANH = 71,   /* min(max(x, p0), p1) */
-  TTLB_OP_SELU = 72        /* p0 (x > 0 ? x : p1 (exp(x) - 1)) */
+  TTLB_OP_SELU = 72,       /* p0 (x > 0 ? x : p1 (exp(x) - 1)) */
+  TTLB_OP_POW_IMM = 73     /* x ** p0 (block ** integer, python/sim/block.py:986-989); x*x and x*x*x for p0 = 2, 3 */
 };
 #define TTLB_MAX_IMM 8
 

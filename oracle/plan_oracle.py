@@ -16,13 +16,17 @@ from . import tile_oracle
 TILE = 32
 _SAME, _ZERO, _TILE, _FIRST = 0, 1, 2, 3
 
+_IN_TENSOR_TYPE = {"floordiv", "rfloordiv", "mod", "rmod"}
 _UNARY = dict(tile_oracle.UNARY)
 _PARAM_UNARY = tile_oracle.PARAM_UNARY
 _N_PARAMS = {"rsub_imm": 1, "relu_max": 1, "relu_min": 1, "leaky_relu": 1, "elu": 1, "celu": 2, "softplus": 3,
-             "hardtanh": 2, "selu": 2}
+             "hardtanh": 2, "selu": 2, "pow_imm": 1}
 _BINARY = {
     "add": lambda a, b: a + b, "sub": lambda a, b: a - b, "rsub": lambda a, b: b - a, "mul": lambda a, b: a * b,
     "div": lambda a, b: a / b, "rdiv": lambda a, b: b / a, "max": torch.maximum, "min": torch.minimum,
+    "floordiv": torch.floor_divide, "rfloordiv": lambda a, b: torch.floor_divide(b, a),
+    "mod": torch.remainder, "rmod": lambda a, b: torch.remainder(b, a),
+    "pow": torch.pow, "rpow": lambda a, b: torch.pow(b, a),
 }
 
 
@@ -55,9 +59,16 @@ def _evaluate(inputs: Any, ops: Any, tensors: Sequence[torch.Tensor], rows: torc
             continue
         if op == "load" or op in _BINARY:
             x = operand(arg) if arg >= 0 else stack.pop(0)
-            acc = x if op == "load" else _BINARY[op](acc, x)
+            if rnd and op in _IN_TENSOR_TYPE:
+                # torch evaluates floor division and remainder step by step in the tensor's own type
+                acc = _BINARY[op](acc.to(torch.bfloat16), x.to(torch.bfloat16)).to(torch.float32)
+            else:
+                acc = x if op == "load" else _BINARY[op](acc, x)
         elif op in _PARAM_UNARY:
-            acc = _PARAM_UNARY[op](acc, *imms[arg:arg + _N_PARAMS[op]])
+            if rnd and op == "pow_imm":     # in the tensor's own type, see tile_oracle.PARAM_UNARY
+                acc = _PARAM_UNARY[op](acc.to(torch.bfloat16), *imms[arg:arg + 1]).to(torch.float32)
+            else:
+                acc = _PARAM_UNARY[op](acc, *imms[arg:arg + _N_PARAMS[op]])
         else:
             acc = _UNARY[op](acc)
         if rnd and op != "load":

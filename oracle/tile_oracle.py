@@ -57,12 +57,18 @@ PARAM_UNARY: Dict[str, Callable[..., torch.Tensor]] = {name: _in_f32(fn) for nam
     "hardtanh": lambda x, lo, hi: _F.hardtanh(x, lo, hi),
     "selu": lambda x, scale, alpha: scale * torch.where(x > 0, x, alpha * torch.expm1(x)),
 }.items()}
+# block ** integer is torch.pow on the tile in the tile's own type (python/sim/block.py:986-989): torch squares and
+# cubes by multiplying in that type, so a bfloat16 cube rounds twice
+PARAM_UNARY["pow_imm"] = lambda x, n: torch.pow(x, int(n) if float(n).is_integer() else n)
 # spelling in ttl.math -> op name
 MATH_NAMES = {"rsub": "rsub_imm", "prelu": "leaky_relu"}
 
 BINARY: Dict[str, Callable[[torch.Tensor, torch.Tensor], torch.Tensor]] = {
     "add": torch.add, "sub": torch.sub, "mul": torch.mul, "div": torch.div,
     "max": torch.maximum, "min": torch.minimum,
+    # the simulator's other block operators are torch's `//`, `%`, `**` on the tile tensors
+    # (python/sim/ttnnsim.py:424-450)
+    "floordiv": torch.floor_divide, "mod": torch.remainder, "pow": torch.pow,
 }
 
 

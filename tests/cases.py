@@ -47,7 +47,7 @@ class Case:
         obj = getattr(modules[self.module], self.program)
         if self.factory_args or self.program.startswith("make_"):
             args = self.factory_args
-            if self.program == "make_unary_chain" or self.module == "reduce":
+            if self.program in ("make_unary_chain", "make_operator") or self.module == "reduce":
                 return obj(*args, fp32_dest_acc_en=f32acc)
             return obj(*args)
         if f32acc and hasattr(modules[self.module], self.program + "_f32acc"):
@@ -121,6 +121,26 @@ for _i, (_op, _dist, _check) in enumerate([
     _name = _op if isinstance(_op, str) else _op[0]
     MATH_CASES.append(Case(f"math_{_name}", "eltwise", "make_unary_chain", [((64, 96), _dist, 100 + _i), ((64, 96), "uniform", 140 + _i)],
                            (64, 96), "native", ("add", (_op, 0), 1), _check, factory_args=([_op],)))
+
+# the block operators // % ** (torch semantics through the simulator); inputs away from zero divisors
+OPERATOR_CASES: List[Case] = [
+    Case("op_floordiv", "eltwise", "make_operator", [((96, 128), "normal*3", 170), ((96, 128), "positive", 171)],
+         (96, 128), "native", ("floordiv", 0, 1), "exact", factory_args=("floordiv",)),
+    Case("op_floordiv_f32_negdiv", "eltwise", "make_operator", [((64, 96), "normal*3", 172), ((64, 96), "uniform", 173)],
+         (64, 96), "native", ("floordiv", 0, 1), "exact", factory_args=("floordiv",), dtype=torch.float32),
+    Case("op_mod", "eltwise", "make_operator", [((96, 128), "normal*3", 174), ((96, 128), "uniform", 175)],
+         (96, 128), "native", ("mod", 0, 1), "exact", factory_args=("mod",)),
+    Case("op_mod_f32", "eltwise", "make_operator", [((64, 96), "normal*3", 176), ((64, 96), "uniform", 177)],
+         (64, 96), "native", ("mod", 0, 1), "exact", factory_args=("mod",), dtype=torch.float32),
+    Case("op_pow_block", "eltwise", "make_operator", [((96, 128), "positive", 178), ((96, 128), "uniform", 179)],
+         (96, 128), "native", ("pow", 0, 1), "ulp1", factory_args=("pow",)),
+    Case("op_pow_2", "eltwise", "make_operator", [((64, 96), "normal", 180), ((64, 96), "uniform", 181)],
+         (64, 96), "native", ("add", (("pow_imm", 2), 0), 1), "exact", factory_args=("pow", 2)),
+    Case("op_pow_3", "eltwise", "make_operator", [((64, 96), "normal", 182), ((64, 96), "uniform", 183)],
+         (64, 96), "native", ("add", (("pow_imm", 3), 0), 1), "exact", factory_args=("pow", 3)),
+    Case("op_pow_5", "eltwise", "make_operator", [((64, 96), "normal", 184), ((64, 96), "uniform", 185)],
+         (64, 96), "native", ("add", (("pow_imm", 5), 0), 1), "ulp1", factory_args=("pow", 5)),
+]
 
 MATMUL_CASES: List[Case] = [
     # the reference's own simulator test sizes (examples/metal_examples/*/ttlang: 256^3) and smaller
@@ -196,7 +216,7 @@ EPILOGUE_CASES: List[Case] = [
 
 
 def by_name(name: str) -> Case:
-    for c in CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES + MATH_CASES + EPILOGUE_CASES:
+    for c in CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES + MATH_CASES + EPILOGUE_CASES + OPERATOR_CASES:
         if c.name == name:
             return c
     raise KeyError(name)

@@ -81,7 +81,7 @@ def main() -> None:
 
     mods = load_programs("sim")
     only = set(sys.argv[2:])   # optional: names of the fixtures to (re)generate
-    for case in cases.CASES + cases.MATMUL_CASES + cases.REDUCE_CASES + cases.COMPOSITE_CASES + cases.MATH_CASES + cases.EPILOGUE_CASES:
+    for case in cases.CASES + cases.MATMUL_CASES + cases.REDUCE_CASES + cases.COMPOSITE_CASES + cases.MATH_CASES + cases.EPILOGUE_CASES + cases.OPERATOR_CASES:
         if only and case.name not in only:
             continue
         t0 = time.time()

@@ -438,3 +438,48 @@ def make_hw_broadcast(dims, in_block, out_block):
                 tx.wait()
 
     return hw_broadcast
+
+
+def make_operator(name, exponent=None, fp32_dest_acc_en=False):
+    """Y = A <op> B for the Python operators `//`, `%`, `**` on blocks, or Y = A ** exponent with an integer
+    exponent (python/sim/block.py:975-1010); (1, ct)-tile blocks, rows dealt out over a 2x2 grid."""
+    import operator
+    fn = {"floordiv": operator.floordiv, "mod": operator.mod, "pow": operator.pow}[name]
+
+    @_kernel((2, 2), fp32_dest_acc_en)
+    def operator_prog(a, b, y):
+        rt, ct = a.shape[0] // 32, a.shape[1] // 32
+        n_cores = 4
+        a_cb = ttl.make_circular_buffer_like(a, shape=(1, ct), buffer_factor=2)
+        b_cb = ttl.make_circular_buffer_like(b, shape=(1, ct), buffer_factor=2)
+        y_cb = ttl.make_circular_buffer_like(y, shape=(1, ct), buffer_factor=2)
+
+        def my_rows():
+            return range(ttl.core(dims=1), rt, n_cores)
+
+        @ttl.compute()
+        def compute():
+            for _r in my_rows():
+                with a_cb.wait() as a_blk, b_cb.wait() as b_blk, y_cb.reserve() as y_blk:
+                    if exponent is None:
+                        y_blk.store(fn(a_blk, b_blk))
+                    else:
+                        y_blk.store(a_blk ** exponent + b_blk)
+
+        @ttl.datamovement()
+        def read():
+            for r in my_rows():
+                with a_cb.reserve() as a_blk, b_cb.reserve() as b_blk:
+                    t1 = ttl.copy(a[r:r + 1, 0:ct], a_blk)
+                    t2 = ttl.copy(b[r:r + 1, 0:ct], b_blk)
+                    t1.wait()
+                    t2.wait()
+
+        @ttl.datamovement()
+        def write():
+            for r in my_rows():
+                with y_cb.wait() as y_blk:
+                    tx = ttl.copy(y_blk, y[r:r + 1, 0:ct])
+                    tx.wait()
+
+    return operator_prog

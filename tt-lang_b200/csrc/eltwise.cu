@@ -194,7 +194,7 @@ __global__ void __launch_bounds__(256, 4) ttlb_eltwise_kernel(const __grid_const
   }
 }
 
-bool is_binary(int op) { return op >= TTLB_OP_ADD && op <= TTLB_OP_MIN; }
+bool is_binary(int op) { return op >= TTLB_OP_ADD && op <= TTLB_OP_RPOW; }
 bool is_unary(int op) {
   return (op >= TTLB_OP_EXP && op <= TTLB_OP_RELU) || (op >= TTLB_OP_EXP2 && op <= TTLB_OP_HARDSIGMOID);
 }
@@ -202,6 +202,7 @@ bool is_unary(int op) {
 int imm_params(int op) {
   switch (op) {
     case TTLB_OP_RSUB_IMM: case TTLB_OP_RELU_MAX: case TTLB_OP_RELU_MIN: case TTLB_OP_LEAKY_RELU: case TTLB_OP_ELU:
+    case TTLB_OP_POW_IMM:
       return 1;
     case TTLB_OP_CELU: case TTLB_OP_HARDTANH: case TTLB_OP_SELU:
       return 2;
@@ -335,7 +336,7 @@ extern "C" int ttlb_eltwise(ttlb_ctx *ctx, const ttlb_eltwise_desc *d, void *str
     if (ctx->eltwise_mode == TTLB_ELTWISE_SPECIALISED || ttlb_eltwise_jit_available()) return rc;
   }
   for (int pc = 0; pc < d->n_ops; ++pc)
-    if (d->ops[pc].opcode >= TTLB_OP_EXP2)
+    if (d->ops[pc].opcode >= TTLB_OP_EXP2 || (d->ops[pc].opcode >= TTLB_OP_FLOORDIV && d->ops[pc].opcode <= TTLB_OP_RPOW))
       return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED,
                        "eltwise: opcode %d is implemented by the specialised kernel only (NVRTC is needed)", d->ops[pc].opcode);
   const unsigned long long vpr = (unsigned long long)(d->cols / vec);

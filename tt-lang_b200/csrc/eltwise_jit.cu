@@ -108,6 +108,28 @@ __device__ __forceinline__ u32 pack_bf16x2(float lo, float hi) {
 // NaN-propagating like torch.maximum / torch.minimum: one instruction each
 __device__ __forceinline__ float nan_max(float a, float b) { float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
 __device__ __forceinline__ float nan_min(float a, float b) { float r; asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
+// a // b and a % b the way torch computes them on floating-point tensors (floor division through fmod with the
+// quotient fixed up, remainder with the sign of the divisor): the simulator's `//` and `%` are torch's
+// RB rounds an intermediate to bfloat16 when the program runs with per-op rounding on bfloat16 tensors: torch
+// evaluates these two algorithms in the tensor's own type, step by step, and so must this code to give the same bits.
+__device__ __forceinline__ float rb_bf16(float x) { return __uint_as_float(pack_bf16x2(x, 0.0f) << 16); }
+__device__ __forceinline__ float floor_div(float a, float b) {
+  if (b == 0.0f) return a / b;
+  const float mod = RB(fmodf(a, b));
+  float div = RB(RB(a - mod) / b);
+  if (mod != 0.0f && ((b < 0.0f) != (mod < 0.0f))) div = RB(div - 1.0f);
+  if (div == 0.0f) return copysignf(0.0f, a / b);
+  float fl = floorf(div);
+  if (RB(div - fl) > 0.5f) fl = RB(fl + 1.0f);
+  return fl;
+}
+__device__ __forceinline__ float py_mod(float a, float b) {
+  float mod = RB(fmodf(a, b));
+  if (mod != 0.0f && ((b < 0.0f) != (mod < 0.0f))) mod = RB(mod + b);
+  return mod;
+}
+// block ** integer: torch squares and cubes by multiplying (the cube in the tensor's type, hence RB), else pow()
+__device__ __forceinline__ float pow_imm(float a, float n) { return n == 2.0f ? a * a : n == 3.0f ? RB(a * a) * a : powf(a, n); }
 )SRC";
 
 const char *binary_expr(int op) {
@@ -120,6 +142,12 @@ const char *binary_expr(int op) {
     case TTLB_OP_RDIV: return "b / a";
     case TTLB_OP_MAX: return "nan_max(a, b)";
     case TTLB_OP_MIN: return "nan_min(a, b)";
+    case TTLB_OP_FLOORDIV: return "floor_div(a, b)";
+    case TTLB_OP_RFLOORDIV: return "floor_div(b, a)";
+    case TTLB_OP_MOD: return "py_mod(a, b)";
+    case TTLB_OP_RMOD: return "py_mod(b, a)";
+    case TTLB_OP_POW: return "powf(a, b)";
+    case TTLB_OP_RPOW: return "powf(b, a)";
   }
   return nullptr;
 }
@@ -163,6 +191,7 @@ const char *unary_expr(int op) {
     case TTLB_OP_SOFTPLUS: return "(a * P0 > P2 ? a : log1pf(expf(a * P0)) * P1)";
     case TTLB_OP_HARDTANH: return "fminf(fmaxf(a, P0), P1)";
     case TTLB_OP_SELU: return "P0 * (a > 0.0f ? a : P1 * expm1f(a))";
+    case TTLB_OP_POW_IMM: return "pow_imm(a, P0)";
   }
   return nullptr;
 }
@@ -281,7 +310,7 @@ std::string ttlb_eltwise_jit_source(const ttlb_eltwise_desc *d) {
   const int V = bf16 ? 8 : 4;
   const bool rnd = bf16 && d->round_each_op;
   std::ostringstream s;
-  s << kPrelude;
+  s << (rnd ? "#define RB(x) rb_bf16(x)\n" : "#define RB(x) (x)\n") << kPrelude;
   s << "#define V " << V << "\n";
   int min_ctas = 0;   // tuning knob: ask the compiler to fit this many CTAs per SM
   if (const char *e = getenv("TTLB200_ELTWISE_MIN_CTAS")) min_ctas = atoi(e);
@@ -504,7 +533,7 @@ std::string ttlb_reduce_jit_source(const ttlb_reduce_desc *r) {
   const bool is_max = r->op == TTLB_REDUCE_MAX;
   const char *init = is_max ? "__uint_as_float(0xff800000u)" : "0.0f";
   std::ostringstream s;
-  s << kPrelude << kRedPrelude;
+  s << (rnd ? "#define RB(x) rb_bf16(x)\n" : "#define RB(x) (x)\n") << kPrelude << kRedPrelude;
   s << "#define V " << V << "\n#define ESZ " << (bf16 ? 2 : 4) << "\n";
   s << "#define COMB(a, b) " << (is_max ? "nan_max((a), (b))" : "((a) + (b))") << "\n";
   if (bf16)
@@ -799,10 +828,11 @@ RowLayout row_layout(const ttlb_rowfused_desc *f) {
 
 bool per_vector(const ttlb_operand &o) { return o.col_mode != TTLB_IDX_ZERO; }
 
-bool takes_operand(int op) { return op <= TTLB_OP_MIN; }   // LOAD and the binary ops name an input (or the stack)
+bool takes_operand(int op) { return op <= TTLB_OP_RPOW; }   // LOAD and the binary ops name an input (or the stack)
 int n_imm(int op) {
   switch (op) {
-    case TTLB_OP_RSUB_IMM: case TTLB_OP_RELU_MAX: case TTLB_OP_RELU_MIN: case TTLB_OP_LEAKY_RELU: case TTLB_OP_ELU: return 1;
+    case TTLB_OP_RSUB_IMM: case TTLB_OP_RELU_MAX: case TTLB_OP_RELU_MIN: case TTLB_OP_LEAKY_RELU: case TTLB_OP_ELU:
+    case TTLB_OP_POW_IMM: return 1;
     case TTLB_OP_CELU: case TTLB_OP_HARDTANH: case TTLB_OP_SELU: return 2;
     case TTLB_OP_SOFTPLUS: return 3;
   }
@@ -870,7 +900,7 @@ std::string ttlb_rowfused_jit_source(const ttlb_rowfused_desc *f) {
   const int V = bf16 ? 8 : 4;
   const int VPT = rowfused_vpt(f);
   std::ostringstream s;
-  s << kPrelude << kRowPrelude;
+  s << (bf16 && f->final.round_each_op ? "#define RB(x) rb_bf16(x)\n" : "#define RB(x) (x)\n") << kPrelude << kRowPrelude;
   s << "#define V " << V << "\n#define ESZ " << (bf16 ? 2 : 4) << "\n";
   if (bf16)
     s << "__device__ __forceinline__ float ld_elem(const void* q) { return __uint_as_float(((u32)*(const unsigned short*)q) << 16); }\n"

@@ -25,6 +25,7 @@ IDX_SAME, IDX_ZERO, IDX_TILE, IDX_FIRST = 0, 1, 2, 3
 
 OPCODES = {
     "load": 0, "add": 1, "sub": 2, "rsub": 3, "mul": 4, "div": 5, "rdiv": 6, "max": 7, "min": 8,
+    "floordiv": 9, "rfloordiv": 10, "mod": 11, "rmod": 12, "pow": 13, "rpow": 14,
     "exp": 16, "log": 17, "sqrt": 18, "rsqrt": 19, "tanh": 20, "sigmoid": 21, "neg": 22, "abs": 23, "relu": 24,
     "push": 32,
     # the specification's Appendix B beyond the compiler's op table (specialised kernel only)
@@ -33,11 +34,11 @@ OPCODES = {
     "hardsigmoid": 57,
     # with scalar parameters (arg = index of the first one in EltwiseDesc.imm)
     "rsub_imm": 64, "relu_max": 65, "relu_min": 66, "leaky_relu": 67, "elu": 68, "celu": 69, "softplus": 70,
-    "hardtanh": 71, "selu": 72,
+    "hardtanh": 71, "selu": 72, "pow_imm": 73,
 }
 # number of scalar parameters of the parametrised functions
 IMM_PARAMS = {"rsub_imm": 1, "relu_max": 1, "relu_min": 1, "leaky_relu": 1, "elu": 1, "celu": 2, "softplus": 3,
-              "hardtanh": 2, "selu": 2}
+              "hardtanh": 2, "selu": 2, "pow_imm": 1}
 
 
 class Operand(C.Structure):

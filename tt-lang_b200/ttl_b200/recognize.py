@@ -35,11 +35,12 @@ class Unsupported(NotImplementedError):
     """The tile program is valid tt-lang but not (yet) runnable on the B200 backend."""
 
 
-_REVERSE = {"add": "add", "mul": "mul", "max": "max", "min": "min", "sub": "rsub", "div": "rdiv"}
+_REVERSE = {"add": "add", "mul": "mul", "max": "max", "min": "min", "sub": "rsub", "div": "rdiv",
+            "floordiv": "rfloordiv", "mod": "rmod", "pow": "rpow"}
 _UNARY = {"exp", "log", "sqrt", "rsqrt", "tanh", "sigmoid", "neg", "abs", "relu",
           "exp2", "expm1", "logp1", "square", "recip", "tan", "atan", "atanh", "sin", "asin", "asinh", "cos", "acos",
           "acosh", "gelu", "silu", "softsign", "hardsigmoid"} | set(capi.IMM_PARAMS)
-_BINARY = {"add", "sub", "mul", "div", "max", "min"}
+_BINARY = {"add", "sub", "mul", "div", "max", "min", "floordiv", "mod", "pow"}
 
 
 # --------------------------------------------------------------------------- #

@@ -399,16 +399,15 @@ class Block:
     def __truediv__(self, o: Any) -> "Block": return self._binary(o, "div")
     def __matmul__(self, o: Any) -> "Block": return self._binary(o, "matmul")
 
+    def __floordiv__(self, o: Any) -> "Block": return self._binary(o, "floordiv")
+    def __mod__(self, o: Any) -> "Block": return self._binary(o, "mod")
+
     def __pow__(self, o: Any) -> "Block":
+        """block ** block, or block ** integer: ONE op on every tile as in the simulator, which hands both to
+        torch (python/sim/block.py:981-1010)."""
         if isinstance(o, int) and not isinstance(o, bool):
-            if o < 1 or o > 8:
-                raise ValueError("block ** n is supported for 1 <= n <= 8")
-            v = self.value()
-            e: Expr = v
-            for _ in range(o - 1):
-                e = _tag(Bin("mul", e, v, self._shape))
-            return Block(self._shape, self.dtype, e, "FULL", "temp", temporary=True)
-        raise TypeError("block ** block is not supported by the B200 backend")
+            return self._unary("pow_imm", (float(o),))
+        return self._binary(o, "pow")
 
     def _unary(self, op: str, params: Tuple[float, ...] = ()) -> "Block":
         return Block(self._shape, self.dtype, _tag(Un(op, self.value(), params)), "FULL", "temp", temporary=True)
