@@ -287,3 +287,49 @@ def linear_relu(a, b, bias, out):
                 with y_cb.wait() as y_blk:
                     y_xf = ttl.copy(y_blk, out[m, n])
                     y_xf.wait()
+
+
+def make_kblock_matmul(bm, bk, bn, grid=(2, 2)):
+    """Blocks of (bm, bk) @ (bk, bn) tiles accumulated over K in steps of bk tiles: the specification's block
+    dot product (docs/sphinx/specs/TTLangSpecification.md:694) as the reference's reuse matmul uses it
+    (examples/metal_examples/multicore_reuse_matmul/ttlang/multicore_reuse_matmul.py:59-70)."""
+
+    @ttl.kernel(grid=grid)
+    def kblock_matmul(a, b, out):
+        Mt, Kt, Nt = a.shape[0] // 32, a.shape[1] // 32, b.shape[1] // 32
+        assert Mt % bm == 0 and Nt % bn == 0 and Kt % bk == 0
+        blocks = [(i, j) for i in range(Mt // bm) for j in range(Nt // bn)]
+        n_cores = ttl.grid_size(dims=1)
+        a_cb = ttl.make_circular_buffer_like(a, shape=(bm, bk), buffer_factor=2)
+        b_cb = ttl.make_circular_buffer_like(b, shape=(bk, bn), buffer_factor=2)
+        out_cb = ttl.make_circular_buffer_like(out, shape=(bm, bn), buffer_factor=1)
+
+        def mine():
+            return blocks[ttl.core(dims=1)::n_cores]
+
+        @ttl.compute()
+        def mm_compute():
+            for _ in mine():
+                with out_cb.reserve() as out_blk:
+                    for _ in range(Kt // bk):
+                        with a_cb.wait() as a_blk, b_cb.wait() as b_blk:
+                            out_blk.store(a_blk @ b_blk, acc=True)
+
+        @ttl.datamovement()
+        def mm_reader():
+            for i, j in mine():
+                for k in range(0, Kt, bk):
+                    with a_cb.reserve() as a_blk, b_cb.reserve() as b_blk:
+                        a_wr = ttl.copy(a[i * bm:(i + 1) * bm, k:k + bk], a_blk)
+                        b_wr = ttl.copy(b[k:k + bk, j * bn:(j + 1) * bn], b_blk)
+                        a_wr.wait()
+                        b_wr.wait()
+
+        @ttl.datamovement()
+        def mm_writer():
+            for i, j in mine():
+                with out_cb.wait() as out_blk:
+                    tx = ttl.copy(out_blk, out[i * bm:(i + 1) * bm, j * bn:(j + 1) * bn])
+                    tx.wait()
+
+    return kblock_matmul

@@ -179,3 +179,23 @@ def test_c_abi_matmul_f32_ragged():
     got = C.cpu()
     assert torch.allclose(got[:m, :n], a @ b, rtol=1e-5, atol=1e-5)
     assert (got[m:] == 7.0).all() and (got[:, n:] == 7.0).all()
+
+
+def test_k_blocked_matmul_program(backend):
+    """(bm, bk) @ (bk, bn) blocks (the reference's reuse matmul form, which its simulator cannot run): one GEMM
+    launch; against fp32 torch."""
+    _, mods = backend
+    import ttnn
+    from ttl_b200 import capi
+    a = cases.gen((512, 768), "normal*0.036", 30)
+    b = cases.gen((768, 384), "normal", 31)
+    out = ttnn.from_torch(torch.zeros((512, 384), dtype=torch.bfloat16))
+    prog = mods["matmul"].make_kblock_matmul(4, 3, 2)
+    d = prog.plan(ttnn.from_torch(a), ttnn.from_torch(b), out).describe()
+    assert len(d) == 1 and d[0]["kind"] == "matmul_bf16" and d[0]["k_tiles"] == 24
+    before = capi.context().launch_count()
+    prog(ttnn.from_torch(a), ttnn.from_torch(b), out)
+    assert capi.context().launch_count() == before + 1
+    want = a.float() @ b.float()
+    got = ttnn.to_torch(out).float()
+    assert ((got - want).abs().max() / want.abs().max()).item() <= 1e-2

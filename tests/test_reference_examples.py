@@ -68,3 +68,40 @@ def test_reference_error_examples_fail_the_same_way(rel, exc, text, backend, mon
     with pytest.raises(exc, match=text):
         with contextlib.redirect_stdout(io.StringIO()):
             runpy.run_path(str(path), run_name="__main__")
+
+
+def test_reuse_matmul_example_runs_as_one_gemm(backend, monkeypatch):
+    """examples/metal_examples/multicore_reuse_matmul: blocks of (per_core_M, 2) @ (2, per_core_N) tiles, the
+    specification's general block dot product.  The reference simulator cannot run it, and the file as checked
+    in does not import `ttl`, `get_large_matmul_params` or its `metal_examples.utils` helper: the test supplies
+    those three names and nothing else.  The launch is evaluated by the plan oracle and the example's own
+    `assert_with_ulp` check against torch.matmul judges the result."""
+    import importlib.util
+    import types
+
+    from oracle import plan_oracle
+    from ttl_b200 import recognize
+    monkeypatch.syspath_prepend(str(REFERENCE / "python"))
+    monkeypatch.syspath_prepend(str(REFERENCE / "examples"))
+    from utils.block_allocation import get_large_matmul_params
+    from utils.correctness import assert_with_ulp
+    stub = types.ModuleType("metal_examples.utils")
+    stub.assert_with_ulp = assert_with_ulp
+    monkeypatch.setitem(sys.modules, "metal_examples.utils", stub)
+    plans = []
+
+    def run(self, tensors):
+        plans.append(self.describe())
+        plan_oracle.run_plan(self, [t._tensor for t in list(tensors) + self.extras])
+
+    monkeypatch.setattr(recognize.Plan, "run", run)
+    path = REFERENCE / "examples/metal_examples/multicore_reuse_matmul/ttlang/multicore_reuse_matmul.py"
+    spec = importlib.util.spec_from_file_location("reference_reuse_matmul", path)
+    mod = importlib.util.module_from_spec(spec)
+    import ttl
+    mod.ttl, mod.get_large_matmul_params = ttl, get_large_matmul_params
+    with contextlib.redirect_stdout(io.StringIO()):
+        spec.loader.exec_module(mod)
+        mod.test_multicore_reuse_matmul_tt_lang(640, 640, 640)
+    assert len(plans) == 1 and [l["kind"] for l in plans[0]] == ["matmul_bf16"]
+    assert plans[0][0]["rect_tiles"] == (0, 20, 0, 20) and plans[0][0]["k_tiles"] == 20

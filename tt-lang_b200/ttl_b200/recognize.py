@@ -1041,15 +1041,16 @@ def _recognise_matmul(w: Write, terms: List[Bin], table: _TensorTable, oi: int) 
         a, b = t.a, t.b
         if not (isinstance(a, Leaf) and isinstance(b, Leaf)) or a.tensor is not ta or b.tensor is not tb:
             raise Unsupported("matmul accumulation must read the same A and B tensors in every step")
-        if a.shape[1] != 1 or b.shape[0] != 1:
-            # (M,K)@(K,N) with K>1 raises in the simulator; equal-shape blocks mean a tile-wise
-            # product there (python/sim/block.py:885-905) - neither is a block matmul
-            raise Unsupported(f"matmul of blocks {a.shape} @ {b.shape}: only (M,1)@(1,N) is a block matmul")
+        if a.shape[1] != b.shape[0] or (a.shape[1] > 1 and a.shape == b.shape):
+            # equal-shape multi-tile blocks mean a tile-wise product in the simulator (python/sim/block.py:885-905),
+            # a block dot product in the specification: refused rather than guessed
+            raise Unsupported(f"matmul of blocks {a.shape} @ {b.shape}: (M,K) @ (K,N) blocks only "
+                              "(equal-shape multi-tile blocks are ambiguous)")
         if (a.r0, a.r1) != (w.r0, w.r1) or (b.c0, b.c1) != (w.c0, w.c1):
             raise Unsupported("matmul operand rows/columns do not line up with the output block")
-        if a.c0 != b.r0:
+        if (a.c0, a.c1) != (b.r0, b.r1):
             raise Unsupported("matmul step multiplies different K tiles of A and B")
-        ks.append(a.c0)
+        ks.extend(range(a.c0, a.c1))
     if sorted(ks) != list(range(kt)):
         raise Unsupported(f"matmul accumulates K tiles {sorted(set(ks))[:4]}... instead of all {kt} exactly once")
     b8 = tb._packed is not None

@@ -387,7 +387,12 @@ class Block:
         if not isinstance(o, Block):
             raise TypeError(f"unsupported operand type(s) for {op}: 'Block' and '{type(other).__name__}'")
         a, b = self.value(), o.value()
-        if self._shape == o._shape:
+        if op == "matmul" and self._shape != o._shape:
+            # block dot product (docs/sphinx/specs/TTLangSpecification.md:694): (M, K) @ (K, N) -> (M, N)
+            if self._shape[1] != o._shape[0]:
+                raise ValueError(f"Incompatible block shapes for matmul: {self._shape} @ {o._shape}")
+            shape = (self._shape[0], o._shape[1])
+        elif self._shape == o._shape:
             shape = self._shape
         else:
             shape = infer_broadcast_shape(self._shape, o._shape)
