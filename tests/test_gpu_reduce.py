@@ -180,3 +180,27 @@ def test_c_abi_rejects_bad_descriptors(backend):
         assert e.value.code == code
     torch.cuda.synchronize()
     assert o.float().abs().sum().item() == 0.0
+
+
+def test_rows_too_long_for_the_row_resident_kernel_fall_back(backend, monkeypatch):
+    """The kernel itself refuses rows that do not fit in registers (TTLB_ERR_UNSUPPORTED, nothing launched);
+    the launch then runs stage by stage.  Forced here by lifting the recogniser's own limit."""
+    from ttl_b200 import capi, recognize
+    _, mods = backend
+    import ttnn
+    monkeypatch.setattr(recognize, "MAX_FUSED_VECTORS_PER_ROW", 1 << 30)
+    x = cases.gen((64, 16384), "normal", 94, torch.float32)       # 4096 vectors of 16 bytes per row
+    s = ttnn.from_torch(torch.ones(32, 32, dtype=torch.float32))
+    out = ttnn.from_torch(torch.zeros((64, 16384), dtype=torch.float32))
+    prog = mods["reduce"].make_softmax()
+    xin = ttnn.from_torch(x)
+    plan = prog.plan(xin, s, out)
+    assert [d["kind"] for d in plan.describe()] == ["row_fused"]
+    before = _launches()
+    prog(xin, s, out)
+    assert _launches() == before + 3, "three stage launches after the fused launch was refused"
+    assert plan.launches[0]._unfused
+    want = torch.softmax(x.double(), dim=1)
+    assert ((ttnn.to_torch(out).double() - want).abs() <= 1e-5 * want + 1e-9).all()
+    prog(xin, s, out)                                            # the refusal is remembered
+    assert _launches() == before + 6
