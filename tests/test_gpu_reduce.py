@@ -2,7 +2,6 @@
 user runs them: tt-lang program -> tracer -> recogniser -> C ABI -> CUDA kernel specialised for the program.
 Checked against the simulator fixtures (simulator + the reduction add-on) and the CPU oracle."""
 
-import ctypes
 
 import pytest
 import torch
