@@ -99,10 +99,11 @@ def test_row_fused_source_reads_each_operand_once(backend):
     plan = mods["reduce"].make_softmax(fp32_dest_acc_en=True).plan(*args)
     src = capi.rowfused_source(plan.launches[0].desc(plan.indexed(args), with_pointers=False))
     body = src.split("ttlb_rowfused_jit", 1)[1]
-    # x: 4 vectors per thread, loaded once for all three stages (written twice in the source: the first row,
-    # and inside the loop the prefetch of the CTA's next row)
-    assert body.count("ld_stream(") == 8 and body.count("g0_0 = h0_0") == 1
-    assert body.count("expf(") == 4, "exp(x - max) is evaluated once per vector and carried over to the last stage"
+    # x: 1024 vectors per row on 512 threads = 2 vectors per thread, loaded once for all three stages (written
+    # twice in the source: the first row, and inside the loop the prefetch of the CTA's next row)
+    assert "__launch_bounds__(512)" in body
+    assert body.count("ld_stream(") == 4 and body.count("g0_0 = h0_0") == 1
+    assert body.count("expf(") == 2, "exp(x - max) is evaluated once per vector and carried over to the last stage"
     assert body.count("__shfl_xor_sync") == 2 and "phv0" in body and "phv1" in body
     # rows too long to hold on chip are left as separate launches
     args = [z((32, 32768)), z((32, 32)), z((32, 32768))]

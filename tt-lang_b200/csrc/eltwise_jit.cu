@@ -382,7 +382,7 @@ void ttlb_jit_cache_destroy(ttlb_jit_cache *c) {
 
 // Compiles `src` (entry point `name`) for sm_100a unless `key` is already in the cache.
 static int get_kernel(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const std::string &key, const std::string &src,
-                      const char *name, JitKernel *out) {
+                      const char *name, JitKernel *out, int threads = 256) {
   Nvrtc &n = nvrtc();
   if (!n.ok) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "%s: NVRTC (libnvrtc.so.12) is not available", name);
   if (!*cachep) *cachep = new ttlb_jit_cache();
@@ -422,7 +422,7 @@ static int get_kernel(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const std::string 
   JitKernel jk;
   jk.kern = kern;
   jk.blocks_per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&jk.blocks_per_sm, reinterpret_cast<const void *>(kern), 256, 0) !=
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&jk.blocks_per_sm, reinterpret_cast<const void *>(kern), threads, 0) !=
           cudaSuccess ||
       jk.blocks_per_sm < 1) {
     cudaGetLastError();
@@ -871,9 +871,11 @@ int continue_from(const ttlb_rowfused_desc *f, const RowLayout &L, int st) {
 
 }  // namespace
 
+static int rowfused_threads(const ttlb_rowfused_desc *f);
+
 std::string ttlb_rowfused_jit_key(const ttlb_rowfused_desc *f, const RowLayout &L, int vpt) {
   std::ostringstream k;
-  k << "rowf" << vpt << ':' << f->n_phases << ':';
+  k << "rowf" << vpt << 't' << rowfused_threads(f) << ':' << f->n_phases << ':';
   for (int n = 0; n < L.g.n_in; ++n) k << L.g.in[n].row_mode << L.g.in[n].col_mode << ',';
   for (int st = 0; st <= f->n_phases; ++st) {
     const ttlb_eltwise_desc *d = st < f->n_phases ? &f->phase[st].src : &f->final;
@@ -887,10 +889,24 @@ std::string ttlb_rowfused_jit_key(const ttlb_rowfused_desc *f, const RowLayout &
   return k.str();
 }
 
+// Threads per CTA of the row-resident kernel: 256, or 512 / 1024 for long rows so that a thread holds at most
+// two vectors per operand (fewer registers per thread, more resident warps).  TTLB200_ROWFUSED_THREADS overrides.
+static int rowfused_threads(const ttlb_rowfused_desc *f) {
+  if (const char *e = getenv("TTLB200_ROWFUSED_THREADS")) {
+    const int t = atoi(e);
+    if (t == 128 || t == 256 || t == 512 || t == 1024) return t;
+  }
+  const int vec = f->final.dtype == TTLB_BF16 ? 8 : 4;
+  const long long vpr = f->final.cols / vec;
+  int t = 256;
+  while (t < 1024 && vpr > 2LL * t) t *= 2;
+  return t;
+}
 static int rowfused_vpt(const ttlb_rowfused_desc *f) {
   const int vec = f->final.dtype == TTLB_BF16 ? 8 : 4;
   const long long vpr = f->final.cols / vec;
-  return (int)((vpr + 255) / 256);
+  const int t = rowfused_threads(f);
+  return (int)((vpr + t - 1) / t);
 }
 
 std::string ttlb_rowfused_jit_source(const ttlb_rowfused_desc *f) {
@@ -899,6 +915,7 @@ std::string ttlb_rowfused_jit_source(const ttlb_rowfused_desc *f) {
   const bool bf16 = f->final.dtype == TTLB_BF16;
   const int V = bf16 ? 8 : 4;
   const int VPT = rowfused_vpt(f);
+  const int T = rowfused_threads(f);
   std::ostringstream s;
   s << (bf16 && f->final.round_each_op ? "#define RB(x) rb_bf16(x)\n" : "#define RB(x) (x)\n") << kPrelude << kRowPrelude;
   s << "#define V " << V << "\n#define ESZ " << (bf16 ? 2 : 4) << "\n";
@@ -912,13 +929,13 @@ std::string ttlb_rowfused_jit_source(const ttlb_rowfused_desc *f) {
   // TTLB200_ROWFUSED_MIN_CTAS=n asks the compiler to fit n CTAs per SM (fewer registers, possibly spills)
   int min_ctas = 0;
   if (const char *e = getenv("TTLB200_ROWFUSED_MIN_CTAS")) min_ctas = atoi(e);
-  s << "extern \"C\" __global__ void __launch_bounds__(256" << (min_ctas > 0 ? ", " + std::to_string(min_ctas) : std::string())
+  s << "extern \"C\" __global__ void __launch_bounds__(" << T << (min_ctas > 0 ? ", " + std::to_string(min_ctas) : std::string())
     << ") ttlb_rowfused_jit(const __grid_constant__ RowParams q) {\n"
        "  const JitParams& p = q.p;\n"
-       "  __shared__ float sm[8];\n"
+       "  __shared__ float sm[" << T / 32 << "];\n"
        "  const u32 lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;\n";
   for (int j = 0; j < VPT; ++j)
-    s << "  const u32 cv" << j << " = threadIdx.x + 256u * " << j << "; const bool ok" << j << " = cv" << j
+    s << "  const u32 cv" << j << " = threadIdx.x + " << T << "u * " << j << "; const bool ok" << j << " = cv" << j
       << " < p.vpr; const i64 gj" << j << " = p.col0 + (i64)cv" << j << " * V;\n";
   for (int ph = 0; ph < f->n_phases; ++ph)
     s << "  const float sc" << ph << " = q.scaler[" << ph << "] ? ld_elem(q.scaler[" << ph << "]) : 1.0f;\n";
@@ -993,7 +1010,7 @@ std::string ttlb_rowfused_jit_source(const ttlb_rowfused_desc *f) {
          "    if (lane == 0) sm[warp] = racc" << P << ";\n"
          "    __syncthreads();\n"
          "    float res" << P << " = sm[0];\n"
-         "    _Pragma(\"unroll\") for (int w = 1; w < 8; ++w) res" << P << " = " << comb("res" + P, "sm[w]") << ";\n"
+         "    _Pragma(\"unroll\") for (int w = 1; w < " << T / 32 << "; ++w) res" << P << " = " << comb("res" + P, "sm[w]") << ";\n"
          "    __syncthreads();\n"
          "    res" << P << " = res" << P << " * sc" << P << ";\n";
     if (bf16)
@@ -1038,7 +1055,8 @@ int ttlb_rowfused_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_
   {
     const std::string key = ttlb_rowfused_jit_key(f, L, vpt);
     const bool cached = *cachep && (*cachep)->kernels.count(key);
-    const int rc = get_kernel(ctx, cachep, key, cached ? std::string() : ttlb_rowfused_jit_source(f), "ttlb_rowfused_jit", &jk);
+    const int rc = get_kernel(ctx, cachep, key, cached ? std::string() : ttlb_rowfused_jit_source(f), "ttlb_rowfused_jit", &jk,
+                              rowfused_threads(f));
     if (rc != TTLB_OK) return rc;
   }
   const ttlb_eltwise_desc *d = &f->final;
@@ -1068,7 +1086,7 @@ int ttlb_rowfused_jit_launch(ttlb_ctx *ctx, ttlb_jit_cache **cachep, const ttlb_
   unsigned grid = (unsigned)(ctx->sm_count * jk.blocks_per_sm);
   if (grid > p.rows) grid = p.rows;
   void *args[] = {&q};
-  TTLB_CUDA_CHECK(ctx, cudaLaunchKernel(reinterpret_cast<const void *>(jk.kern), dim3(grid, 1, 1), dim3(256, 1, 1), args, 0,
-                                        stream));
+  TTLB_CUDA_CHECK(ctx, cudaLaunchKernel(reinterpret_cast<const void *>(jk.kern), dim3(grid, 1, 1),
+                                        dim3((unsigned)rowfused_threads(f), 1, 1), args, 0, stream));
   return TTLB_OK;
 }
