@@ -101,7 +101,7 @@ def test_row_fused_source_reads_each_operand_once(backend):
     body = src.split("ttlb_rowfused_jit", 1)[1]
     # x: 1024 vectors per row on 512 threads = 2 vectors per thread, loaded once for all three stages (written
     # twice in the source: the first row, and inside the loop the prefetch of the CTA's next row)
-    assert "__launch_bounds__(512)" in body
+    assert "__launch_bounds__(512)" in src
     assert body.count("ld_stream(") == 4 and body.count("g0_0 = h0_0") == 1
     assert body.count("expf(") == 2, "exp(x - max) is evaluated once per vector and carried over to the last stage"
     assert body.count("__shfl_xor_sync") == 2 and "phv0" in body and "phv1" in body
