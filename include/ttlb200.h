@@ -53,8 +53,11 @@ extern "C" {
 #define TTLB_F32 1    /* 4096-byte tiles */
 #define TTLB_BFP8_B 2 /* 1088-byte tiles: 64 shared exponents + 1024 sign/mantissa bytes */
 
+#define TTLB_BFP4_B 3 /* 576-byte tiles: 64 shared exponents + 512 bytes of sign/3-bit-mantissa nibbles */
+
 #define TTLB_TILE 32
 #define TTLB_BFP8_TILE_BYTES 1088
+#define TTLB_BFP4_TILE_BYTES 576
 
 typedef struct ttlb_ctx ttlb_ctx;
 
@@ -355,6 +358,19 @@ typedef struct {
 /* Expands the weight window to bf16 in scratch memory owned by the context (allocated on
  * first use, grown when a larger window arrives), then runs the tensor-core GEMM. */
 TTLB_EXPORT int ttlb_matmul_bfp8w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, void *stream);
+
+/* bfloat4_b weights: 576-byte tiles = 512 value bytes + 64 shared exponents (python/ttl/dtype_utils.py:178-179;
+ * the reference has no pack / unpack code for it either).  Same structure as bfloat8_b with 4-bit values: two values
+ * per byte (even index in the low nibble), nibble = sign | 3-bit magnitude, value = (-1)^s * m * 2^(E-129); the full
+ * layout is written at the top of csrc/bfp4.cu.  The matmul expands the weight window to bf16 in the context's
+ * scratch, then runs the tensor-core GEMM; the descriptor is the bfloat8_b one with b_tiles pointing at bfloat4_b
+ * tiles. */
+TTLB_EXPORT int ttlb_pack_bfp4_b(const float *src, int64_t rows, int64_t cols, uint8_t *dst_tiles);
+TTLB_EXPORT int ttlb_unpack_bfp4_b(const uint8_t *tiles, int64_t rows, int64_t cols, float *dst);
+TTLB_EXPORT int ttlb_unpack_bfp4_b_device(ttlb_ctx *ctx, const void *tiles, int64_t tile_cols_total,
+                                          int64_t tile_col0, int64_t k, int64_t n, void *out_bf16, int64_t ld,
+                                          void *stream);
+TTLB_EXPORT int ttlb_matmul_bfp4w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, void *stream);
 
 /* No counterpart in the reference: an addition of this library for callers that must not
  * allocate.  Same result as ttlb_matmul_bfp8w, but no context is needed and no cudaMalloc,

@@ -66,3 +66,50 @@ def unpack(tiles: np.ndarray, rows: int, cols: int) -> np.ndarray:
     # back from storage order to matrix order
     x = x.reshape(tr, tc, 2, 2, 16, 16).transpose(0, 2, 4, 1, 3, 5)
     return np.ascontiguousarray(x.reshape(rows, cols))
+
+
+# --------------------------------------------------------------------------- #
+# bfloat4_b: the same structure with 4-bit values (PARITY UNPINNED for the same reason: the reference gives only
+# the tile size, 576 = 512 + 64 bytes, python/ttl/dtype_utils.py:178-179).  Completion used by this build:
+#   bytes [0,64): block exponents as for bfloat8_b
+#   bytes [64,576): 8 bytes per block at 64 + f*128 + (r%16)*8; value j in the low (j even) / high (j odd) nibble
+#       of byte j//2; nibble = sign<<3 | m, m = round_half_even(|x| * 2**(129-E)) saturated at 7;
+#       x ~ (-1)**sign * m * 2**(E-129)
+# --------------------------------------------------------------------------- #
+BFP4_TILE_BYTES = 576
+
+
+def pack4(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    assert x.ndim == 2 and x.shape[0] % 32 == 0 and x.shape[1] % 32 == 0
+    b = _blocks(x)
+    bits = b.view(np.uint32)
+    e = ((bits >> 23) & 0xFF).astype(np.int64)
+    assert (e != 255).all(), "inf/nan cannot be represented"
+    E = e.max(axis=-1, keepdims=True)
+    sig = np.where(e == 0, 0, (bits & 0x7FFFFF) | 0x800000).astype(np.int64)
+    shift = np.minimum(21 + (E - e), 40)
+    q = sig >> shift
+    rem = sig & ((np.int64(1) << shift) - 1)
+    half = np.int64(1) << (shift - 1)
+    m = q + ((rem > half) | ((rem == half) & ((q & 1) == 1)))
+    m = np.where(E == 0, 0, np.minimum(m, 7))
+    nib = ((bits >> 31).astype(np.int64) << 3) | m                   # [tr, tc, 4, 16, 16]
+    byte = nib[..., 0::2] | (nib[..., 1::2] << 4)                    # two values per byte, even index low
+    tr, tc = b.shape[:2]
+    out = np.zeros((tr, tc, BFP4_TILE_BYTES), dtype=np.uint8)
+    out[:, :, :64] = E.reshape(tr, tc, 64)
+    out[:, :, 64:] = byte.reshape(tr, tc, 512)
+    return out.reshape(-1)
+
+
+def unpack4(tiles: np.ndarray, rows: int, cols: int) -> np.ndarray:
+    tr, tc = rows // 32, cols // 32
+    t = np.asarray(tiles, dtype=np.uint8).reshape(tr, tc, BFP4_TILE_BYTES)
+    E = t[:, :, :64].astype(np.int64).reshape(tr, tc, 4, 16, 1)
+    byte = t[:, :, 64:].astype(np.int64).reshape(tr, tc, 4, 16, 8)
+    nib = np.stack([byte & 0xF, byte >> 4], axis=-1).reshape(tr, tc, 4, 16, 16)
+    mag = np.ldexp((nib & 7).astype(np.float64), E - 129)
+    x = np.where(nib & 8, -mag, mag).astype(np.float32)
+    x = x.reshape(tr, tc, 2, 2, 16, 16).transpose(0, 2, 4, 1, 3, 5)
+    return np.ascontiguousarray(x.reshape(rows, cols))

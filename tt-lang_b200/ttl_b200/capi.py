@@ -194,6 +194,14 @@ def lib() -> C.CDLL:
     l.ttlb_unpack_bfp8_b_device.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                             C.c_void_p, C.c_int64, C.c_void_p]
     l.ttlb_unpack_bfp8_b_device.restype = C.c_int
+    for name in ("ttlb_pack_bfp4_b", "ttlb_unpack_bfp4_b"):
+        getattr(l, name).argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
+        getattr(l, name).restype = C.c_int
+    l.ttlb_unpack_bfp4_b_device.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                            C.c_void_p, C.c_int64, C.c_void_p]
+    l.ttlb_unpack_bfp4_b_device.restype = C.c_int
+    l.ttlb_matmul_bfp4w.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p]
+    l.ttlb_matmul_bfp4w.restype = C.c_int
     l.ttlb_matmul_bfp8w.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p]
     l.ttlb_matmul_bfp8w.restype = C.c_int
     l.ttlb_matmul_bfp8w_noalloc.argtypes = [C.POINTER(GemmBfp8Desc), C.c_void_p, C.c_int, C.c_char_p, C.c_size_t]
@@ -276,6 +284,14 @@ class Context:
 
     def matmul_bfp8w(self, desc: "GemmBfp8Desc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_bfp8w(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def matmul_bfp4w(self, desc: "GemmBfp8Desc", stream: int) -> None:
+        self.check(self._lib.ttlb_matmul_bfp4w(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def unpack_bfp4_b(self, tiles_ptr: int, tile_cols_total: int, tile_col0: int, k: int, n: int, out_ptr: int,
+                      ld: int, stream: int) -> None:
+        self.check(self._lib.ttlb_unpack_bfp4_b_device(self.handle, C.c_void_p(tiles_ptr), tile_cols_total, tile_col0,
+                                                       k, n, C.c_void_p(out_ptr), ld, C.c_void_p(stream)))
 
     def unpack_bfp8_b(self, tiles_ptr: int, tile_cols_total: int, tile_col0: int, k: int, n: int, out_ptr: int,
                       ld: int, stream: int) -> None:

@@ -516,7 +516,7 @@ def _fuse_epilogues(launches: List[Any]) -> List[Any]:
             temps_read = [k for k, inp in enumerate(l.inputs) if inp[0] in gemm_of]
             if len(temps_read) == 1:
                 g = gemm_of[l.inputs[temps_read[0]][0]]
-        ok = (g is not None and g.kind == "matmul_bf16" and g.bias_index is None and g.act is None
+        ok = (g is not None and g.kind == "matmul_bf16" and g.b_is_bfp8 != 4 and g.bias_index is None and g.act is None
               and g.rect == l.rect and readers.get(g.out_index, 0) == 1 and not l.imms)
         bias = act = None
         if ok:
@@ -618,7 +618,7 @@ class GemmLaunch:
         self.kind = "matmul_bf16"   # set to "matmul_f32" by the recogniser for float32 programs
 
     def describe(self) -> Dict[str, Any]:
-        d = {"kind": "matmul_bfp8w" if self.b_is_bfp8 else self.kind, "a": self.a_index, "b": self.b_index,
+        d = {"kind": ("matmul_bfp4w" if self.b_is_bfp8 == 4 else "matmul_bfp8w") if self.b_is_bfp8 else self.kind, "a": self.a_index, "b": self.b_index,
              "out": self.out_index, "rect_tiles": self.rect, "k_tiles": self.k_tiles}
         if self.bias_index is not None:
             d["bias"] = self.bias_index
@@ -1053,7 +1053,7 @@ def _recognise_matmul(w: Write, terms: List[Bin], table: _TensorTable, oi: int) 
         ks.extend(range(a.c0, a.c1))
     if sorted(ks) != list(range(kt)):
         raise Unsupported(f"matmul accumulates K tiles {sorted(set(ks))[:4]}... instead of all {kt} exactly once")
-    b8 = tb._packed is not None
+    b8 = 0 if tb._packed is None else tb._packed_bits    # 0: plain weights; 8 / 4: block-float tiles
     all_bf16 = ta.dtype == torch.bfloat16 and (b8 or tb.dtype == torch.bfloat16) and w.tensor.dtype == torch.bfloat16
     all_f32 = ta.dtype == torch.float32 and not b8 and tb.dtype == torch.float32 and w.tensor.dtype == torch.float32
     if not (all_bf16 or all_f32):

@@ -35,6 +35,16 @@ class _BlockFloat8:
 
 bfloat8_b = _BlockFloat8()
 
+
+class _BlockFloat4:
+    """Marker dtype for bfloat4_b (576-byte tiles; python/ttl/dtype_utils.py:178-179)."""
+
+    def __repr__(self) -> str:
+        return "ttnn.bfloat4_b"
+
+
+bfloat4_b = _BlockFloat4()
+
 Shape = Tuple[int, ...]
 
 
@@ -129,10 +139,12 @@ class Tensor:
     """
 
     def __init__(self, tensor: torch.Tensor, *, _origin: Optional[Tuple["Tensor", int, int, int, int]] = None,
-                 _packed: Optional[torch.Tensor] = None, _logical_shape: Optional[Shape] = None) -> None:
+                 _packed: Optional[torch.Tensor] = None, _logical_shape: Optional[Shape] = None,
+                 _packed_bits: int = 8) -> None:
         self._tensor = tensor
         self._origin = _origin          # (base tensor, r0, r1, c0, c1) in tiles
-        self._packed = _packed          # bfloat8_b payload (uint8, 1088 bytes per tile)
+        self._packed = _packed          # block-float payload (uint8: 1088 bytes per bfloat8_b tile, 576 per bfloat4_b tile)
+        self._packed_bits = _packed_bits
         self._logical_shape = _logical_shape
 
     # -- basic properties ------------------------------------------------
@@ -145,7 +157,7 @@ class Tensor:
     @property
     def dtype(self) -> Any:
         if self._packed is not None:
-            return bfloat8_b
+            return bfloat8_b if self._packed_bits == 8 else bfloat4_b
         return self._tensor.dtype
 
     def __repr__(self) -> str:
@@ -197,7 +209,7 @@ class Tensor:
         base, br, _, bc, _ = self._origin if self._origin is not None else (self, 0, 0, 0, 0)
         origin = (base, br + rs.start, br + rs.stop, bc + cs.start, bc + cs.stop)
         if self._packed is not None:
-            return Tensor(self._tensor, _origin=origin, _packed=self._packed,
+            return Tensor(self._tensor, _origin=origin, _packed=self._packed, _packed_bits=self._packed_bits,
                           _logical_shape=((rs.stop - rs.start) * TILE_SIZE, (cs.stop - cs.start) * TILE_SIZE))
         view = self._tensor[rs.start * TILE_SIZE:rs.stop * TILE_SIZE, cs.start * TILE_SIZE:cs.stop * TILE_SIZE]
         return Tensor(view, _origin=origin)
@@ -267,8 +279,8 @@ def to_torch(t: Union[Tensor, torch.Tensor], out: Optional[torch.Tensor] = None)
     pinned buffer, instead of allocating a pageable one; the call returns after the copy."""
     if isinstance(t, Tensor):
         if t._packed is not None:
-            from .bfp8 import unpack_bfp8_b
-            return unpack_bfp8_b(t._packed.cpu(), t.shape[0], t.shape[1])
+            from .bfp8 import unpack_bfp4_b, unpack_bfp8_b
+            return (unpack_bfp8_b if t._packed_bits == 8 else unpack_bfp4_b)(t._packed.cpu(), t.shape[0], t.shape[1])
         if out is not None:
             out.copy_(t._tensor, non_blocking=True)
             if t._tensor.is_cuda:
@@ -288,13 +300,14 @@ def from_torch(tensor: torch.Tensor, dtype: Any = None, layout: Any = None, devi
     dev = _default_device()
     if device is not None and torch.cuda.is_available():
         dev = torch.device("cuda", device.device_id)
-    if isinstance(dtype, _BlockFloat8):
-        from .bfp8 import pack_bfp8_b
+    if isinstance(dtype, (_BlockFloat8, _BlockFloat4)):
+        from .bfp8 import pack_bfp4_b, pack_bfp8_b
         if tensor.dim() != 2 or tensor.shape[0] % TILE_SIZE or tensor.shape[1] % TILE_SIZE:
-            raise ValueError("bfloat8_b needs a 2-D tensor whose dims are multiples of 32")
-        packed = pack_bfp8_b(tensor.detach().to(torch.float32).cpu().contiguous())
+            raise ValueError(f"{dtype!r} needs a 2-D tensor whose dims are multiples of 32")
+        bits = 8 if isinstance(dtype, _BlockFloat8) else 4
+        packed = (pack_bfp8_b if bits == 8 else pack_bfp4_b)(tensor.detach().to(torch.float32).cpu().contiguous())
         return Tensor(torch.empty(0), _packed=packed.to(dev, non_blocking=True),
-                      _logical_shape=tuple(tensor.shape))
+                      _logical_shape=tuple(tensor.shape), _packed_bits=bits)
     if dtype is not None and tensor.dtype != dtype:
         tensor = tensor.to(dtype)
     return Tensor(tensor.to(dev, non_blocking=True))
