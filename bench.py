@@ -234,16 +234,19 @@ def run_sharded(args):
             return shard.sharded_matmul(x[0], x[1], n, lambda p, q: ops.matmul(T(p), T(q))._tensor, chunks=chunks)
         desc = ("A,B bf16 [8192,8192] N(0,1/sqrt(8192)) seeds 0/1, fp32 accumulate, bf16 out; output row tiles "
                 f"sharded in {chunks} round(s), all-gather of a round overlaps the next round's GEMM")
-    elif wl == "matmul_bfp8w":
+    elif wl in ("matmul_bfp8w", "matmul_bfp4w"):
+        bits = 8 if wl == "matmul_bfp8w" else 4
+        if bits == 4 and world > 1:
+            raise SystemExit("matmul_bfp4w is a one-GPU workload")
         m, k, n = 4096, 8192, 28672
         x = cases.gen((m, k), "normal", 0)
         s0, c0 = shard.split_units(n // 32, world)[rank]
         # the weight shard is generated and packed per rank (N(0, 0.02), seed 1 + first column tile)
         w = cases.gen((k, c0 * 32), "normal*0.02", 1 + s0, torch.float32)
-        W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+        W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b if bits == 8 else ttnn.bfloat4_b)
         host_in = [x.pin_memory()]
         flops = 2.0 * m * k * n
-        kernel = "ttlb_unpack_bfp8_kernel + " + ("ttlb_gemm_bf16_kernel" if args.gemm_variant == 0 else "ttlb_gemm_bf16_2cta_kernel")
+        kernel = f"ttlb_unpack_bfp{bits}_kernel + " + ("ttlb_gemm_bf16_kernel" if args.gemm_variant == 0 else "ttlb_gemm_bf16_2cta_kernel")
         chunks = 2 if world > 1 else 1
 
         def compute(xs):
@@ -251,7 +254,7 @@ def run_sharded(args):
 
         def step(xs):
             return shard.sharded_matmul_cols(xs[0], W, n, lambda p, q: ops.matmul(T(p), q)._tensor, chunks=chunks)
-        desc = ("activations bf16 [4096,8192] N(0,1); weights [8192,28672] N(0,0.02) packed to bfloat8_b tiles "
+        desc = (f"activations bf16 [4096,8192] N(0,1); weights [8192,28672] N(0,0.02) packed to bfloat{bits}_b tiles "
                 f"(resident in HBM); fp32 accumulate, bf16 out; weight column tiles sharded, {chunks} row round(s)")
     elif wl == "attention":
         B, H, S, D = 8, 32, 4096, 128
