@@ -25,9 +25,13 @@ _hardware_broadcast = False
 
 
 def set_hardware_broadcast(enabled: bool) -> None:
-    """Give `ttl.math.broadcast` the compiler's (hardware) meaning on full tiles instead of the simulator's."""
+    """Follow the compiler front end where it differs from the simulator: `ttl.math.broadcast` has the hardware
+    meaning on full tiles, and `ttl.grid_size()` keeps answering after a kernel call has returned."""
     global _hardware_broadcast
     _hardware_broadcast = bool(enabled)
+    # programs written for the compiler also read the grid back after a kernel call (trace.GRID_OUTLIVES_KERNEL)
+    from . import trace
+    trace.set_grid_outlives_kernel(enabled)
 
 
 def broadcast(block: Any, out_block: Optional[Any] = None, dims: Optional[List[int]] = None) -> Block:

@@ -173,11 +173,20 @@ def current_core() -> int:
     return c
 
 
+# The compiler front end keeps the grid of the last kernel in a module global (python/ttl/operators.py:36), which
+# programs written against it read back with ttl.grid_size() after the kernel has returned; the simulator raises
+# outside a kernel (python/sim/kernel.py:116-118).  The simulator's behaviour is the default.
+GRID_OUTLIVES_KERNEL = False
+
+
+def set_grid_outlives_kernel(enabled: bool) -> None:
+    global GRID_OUTLIVES_KERNEL
+    GRID_OUTLIVES_KERNEL = bool(enabled)
+
+
 def current_grid() -> Tuple[int, ...]:
     g = getattr(_tls, "grid", None)
-    if g is None:
-        # after a kernel has run the compiler keeps its grid in a module global
-        # (python/ttl/operators.py:36), which programs read back with ttl.grid_size()
+    if g is None and GRID_OUTLIVES_KERNEL:
         g = getattr(_tls, "last_grid", None)
     if g is None:
         raise RuntimeError("grid not available - function must be called within a kernel context")
@@ -642,9 +651,12 @@ def grid_size_of(grid: Tuple[int, ...], dims: int) -> Any:
     return res[0] if dims == 1 else res
 
 
-def flatten_core_index(core_coord: Any, grid: Tuple[int, ...]) -> int:
+def flatten_core_index(core_coord: Any, grid: Optional[Tuple[int, ...]] = None) -> int:
+    """python/sim/kernel.py:52-87 (there the grid always comes from the kernel context)."""
     if isinstance(core_coord, int):
         return core_coord
+    if grid is None:
+        grid = current_grid()
     coords = list(core_coord)
     lin = coords[0]
     for i in range(1, len(coords)):

@@ -198,6 +198,8 @@ class Tensor:
         return index
 
     def _tile_view(self, key: Tuple[Any, Any]) -> "Tensor":
+        if len(self.shape) != 2:
+            raise ValueError("Tile-style indexing requires a 2D tensor")   # python/sim/ttnnsim.py:364-366
         if not self._is_tile_indexable():
             for i, d in enumerate(self.shape):
                 if d != 1 and d % TILE_SIZE != 0:
