@@ -371,6 +371,9 @@ TTLB_EXPORT int ttlb_unpack_bfp4_b_device(ttlb_ctx *ctx, const void *tiles, int6
                                           int64_t tile_col0, int64_t k, int64_t n, void *out_bf16, int64_t ld,
                                           void *stream);
 TTLB_EXPORT int ttlb_matmul_bfp4w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, void *stream);
+/* ... with the bias / activation epilogue (arguments as for ttlb_matmul_bf16_epilogue, TTLB_ACT_* below). */
+TTLB_EXPORT int ttlb_matmul_bfp4w_epilogue(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, const void *bias,
+                                           int64_t ldbias, int act, void *stream);
 
 /* No counterpart in the reference: an addition of this library for callers that must not
  * allocate.  Same result as ttlb_matmul_bfp8w, but no context is needed and no cudaMalloc,

@@ -129,8 +129,9 @@ def test_chunked_expansion_overlapping_the_gemm_gives_the_same_bits():
     assert not torch.equal(outs[(21, 4)][0], outs[(22, 4)][0])
 
 
+@pytest.mark.parametrize("bits", [8, 4])
 @pytest.mark.parametrize("act", ["gelu", "relu"])
-def test_quantised_linear_program_with_bias_and_activation(backend, act):
+def test_quantised_linear_program_with_bias_and_activation(backend, act, bits):
     """Y = act(X @ W + bias) as a tile program with W a bfloat8_b tensor and fp32 intermediates: one launch of
     the unpack kernel and one GEMM launch with the bias row and the activation in its epilogue."""
     _, mods = backend
@@ -140,12 +141,15 @@ def test_quantised_linear_program_with_bias_and_activation(backend, act):
     x = cases.gen((m, k), "normal", 4)
     w = cases.gen((k, n), "normal*0.02", 5, torch.float32)
     v = cases.gen((1, n), "normal", 6)
-    wq = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))
+    if bits == 8:
+        wq = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))
+    else:
+        wq = torch.from_numpy(bfp8_oracle.unpack4(bfp8_oracle.pack4(w.numpy()), k, n))
     out = ttnn.from_torch(torch.zeros((m, n), dtype=torch.bfloat16))
-    W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+    W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b if bits == 8 else ttnn.bfloat4_b)
     prog = mods["matmul"].make_linear(act, fp32_dest_acc_en=True)
     d = prog.plan(ttnn.from_torch(x), W, ttnn.from_torch(v), out).describe()
-    assert len(d) == 1 and d[0]["kind"] == "matmul_bfp8w" and d[0]["act"] == act and d[0]["bias"] == 2
+    assert len(d) == 1 and d[0]["kind"] == f"matmul_bfp{bits}w" and d[0]["act"] == act and d[0]["bias"] == 2
     before = capi.context().launch_count()
     prog(ttnn.from_torch(x), W, ttnn.from_torch(v), out)
     assert capi.context().launch_count() == before + 2     # weight expansion + GEMM

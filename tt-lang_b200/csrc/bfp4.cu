@@ -23,6 +23,10 @@
 int ttlb_launch_gemm_bf16_ex(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
                              int64_t m, int64_t n, int64_t k, bool multicast, cudaStream_t stream);
 
+int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
+                               int64_t m, int64_t n, int64_t k, bool multicast, const void *bias, int64_t ldbias,
+                               cudaStream_t stream);
+
 namespace {
 
 inline uint32_t f32_bits(float f) {
@@ -161,11 +165,15 @@ extern "C" int ttlb_unpack_bfp4_b_device(ttlb_ctx *ctx, const void *tiles, int64
                        ld, reinterpret_cast<cudaStream_t>(stream));
 }
 
-// C = A x W with W stored as bfloat4_b tiles: the weight window is expanded to bf16 in the context's scratch
-// (the same buffer the bfloat8_b path uses), then the tensor-core GEMM runs on it.
-extern "C" int ttlb_matmul_bfp4w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, void *stream) {
+// C = act(A x W + bias) with W stored as bfloat4_b tiles: the weight window is expanded to bf16 in the context's
+// scratch (the same buffer the bfloat8_b path uses), then the tensor-core GEMM runs on it with the bias / activation
+// epilogue of ttlb_matmul_bf16_epilogue (bias NULL and act 0: the plain product).
+extern "C" int ttlb_matmul_bfp4w_epilogue(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, const void *bias, int64_t ldbias,
+                                          int act, void *stream) {
   if (!ctx) return TTLB_ERR_INVALID_ARG;
   if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul_bfp4w: null descriptor");
+  if (act < TTLB_ACT_NONE || act > TTLB_ACT_TANH) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: unknown activation %d", act);
+  if (!bias && ldbias != 0) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: a bias pitch without a bias");
   if (d->m == 0 || d->n == 0) return TTLB_OK;
   int rc = check_args(ctx, d->b_tiles, d->b_tile_cols, d->b_tile_col0, d->k, d->n);
   if (rc) return rc;
@@ -186,5 +194,12 @@ extern "C" int ttlb_matmul_bfp4w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, vo
   rc = launch_unpack(ctx, reinterpret_cast<const uint8_t *>(d->b_tiles), d->b_tile_cols, d->b_tile_col0, d->k / 32, d->n / 32,
                      ctx->scratch, d->n, s);
   if (rc) return rc;
-  return ttlb_launch_gemm_bf16_ex(ctx, d->a, d->lda, ctx->scratch, d->n, d->c, d->ldc, d->m, d->n, d->k, false, s);
+  ctx->gemm_act = act;
+  rc = ttlb_launch_gemm_bf16_full(ctx, d->a, d->lda, ctx->scratch, d->n, d->c, d->ldc, d->m, d->n, d->k, false, bias, ldbias, s);
+  ctx->gemm_act = 0;
+  return rc;
+}
+
+extern "C" int ttlb_matmul_bfp4w(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, void *stream) {
+  return ttlb_matmul_bfp4w_epilogue(ctx, d, nullptr, 0, TTLB_ACT_NONE, stream);
 }

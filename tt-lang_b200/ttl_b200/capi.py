@@ -202,6 +202,8 @@ def lib() -> C.CDLL:
     l.ttlb_unpack_bfp4_b_device.restype = C.c_int
     l.ttlb_matmul_bfp4w.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p]
     l.ttlb_matmul_bfp4w.restype = C.c_int
+    l.ttlb_matmul_bfp4w_epilogue.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p, C.c_int64, C.c_int, C.c_void_p]
+    l.ttlb_matmul_bfp4w_epilogue.restype = C.c_int
     l.ttlb_matmul_bfp8w.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p]
     l.ttlb_matmul_bfp8w.restype = C.c_int
     l.ttlb_matmul_bfp8w_noalloc.argtypes = [C.POINTER(GemmBfp8Desc), C.c_void_p, C.c_int, C.c_char_p, C.c_size_t]
@@ -287,6 +289,10 @@ class Context:
 
     def matmul_bfp4w(self, desc: "GemmBfp8Desc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_bfp4w(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def matmul_bfp4w_epilogue(self, desc: "GemmBfp8Desc", bias_ptr: int, ldbias: int, act: int, stream: int) -> None:
+        self.check(self._lib.ttlb_matmul_bfp4w_epilogue(self.handle, C.byref(desc), C.c_void_p(bias_ptr or None), ldbias, act,
+                                                        C.c_void_p(stream)))
 
     def unpack_bfp4_b(self, tiles_ptr: int, tile_cols_total: int, tile_col0: int, k: int, n: int, out_ptr: int,
                       ld: int, stream: int) -> None:

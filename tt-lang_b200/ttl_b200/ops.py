@@ -56,9 +56,10 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
         g.c, g.ldc = c_base + (r0 * xo.stride(0) + c0) * 2, xo.stride(0)
         g.m, g.n, g.k = r1 - r0, c1 - c0, xa.shape[1]
         if b._packed_bits == 4:
-            if bias is not None or act or multicast_ptr is not None:
-                raise Unsupported("matmul with bfloat4_b weights: no bias, activation or multicast output yet")
-            ctx.matmul_bfp4w(g, stream)
+            if multicast_ptr is not None:
+                raise Unsupported("matmul with bfloat4_b weights: no multicast output")
+            ptr, ld = bias_args(xo)
+            ctx.matmul_bfp4w_epilogue(g, ptr, ld, act, stream)
         elif bias is not None or act:
             ptr, ld = bias_args(xo)
             ctx.matmul_bfp8w_epilogue(g, ptr, ld, act, stream)

@@ -516,7 +516,7 @@ def _fuse_epilogues(launches: List[Any]) -> List[Any]:
             temps_read = [k for k, inp in enumerate(l.inputs) if inp[0] in gemm_of]
             if len(temps_read) == 1:
                 g = gemm_of[l.inputs[temps_read[0]][0]]
-        ok = (g is not None and g.kind == "matmul_bf16" and g.b_is_bfp8 != 4 and g.bias_index is None and g.act is None
+        ok = (g is not None and g.kind == "matmul_bf16" and g.bias_index is None and g.act is None
               and g.rect == l.rect and readers.get(g.out_index, 0) == 1 and not l.imms)
         bias = act = None
         if ok:
