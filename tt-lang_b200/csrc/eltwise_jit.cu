@@ -310,7 +310,18 @@ std::string ttlb_eltwise_jit_source(const ttlb_eltwise_desc *d) {
   const int V = bf16 ? 8 : 4;
   const bool rnd = bf16 && d->round_each_op;
   std::ostringstream s;
-  s << (rnd ? "#define RB(x) rb_bf16(x)\n" : "#define RB(x) (x)\n") << kPrelude;
+  {
+    // tuning knobs: cache operators of the streaming load / store (defaults: evict-first both ways)
+    std::string pre = kPrelude;
+    const char *ld = getenv("TTLB200_ELTWISE_LD"), *st = getenv("TTLB200_ELTWISE_ST");
+    auto swap = [&](const std::string &from, const std::string &to) {
+      const size_t at = pre.find(from);
+      if (at != std::string::npos) pre.replace(at, from.size(), to);
+    };
+    if (ld && *ld) swap("ld.global.cs.v4.u32", std::string("ld.global.") + ld + ".v4.u32");
+    if (st && *st) swap("st.global.cs.v4.u32", std::string(st) == "default" ? "st.global.v4.u32" : std::string("st.global.") + st + ".v4.u32");
+    s << (rnd ? "#define RB(x) rb_bf16(x)\n" : "#define RB(x) (x)\n") << pre;
+  }
   s << "#define V " << V << "\n";
   int min_ctas = 0;   // tuning knob: ask the compiler to fit this many CTAs per SM
   if (const char *e = getenv("TTLB200_ELTWISE_MIN_CTAS")) min_ctas = atoi(e);
