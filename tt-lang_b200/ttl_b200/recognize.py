@@ -542,7 +542,6 @@ def _fuse_epilogues(launches: List[Any]) -> List[Any]:
             continue
         fused = GemmLaunch(g.a_index, g.b_index, l.out_index, g.rect, g.k_tiles, g.b_is_bfp8, bias, act)
         fused.lines = {**(getattr(g, "lines", None) or {}), **(getattr(l, "lines", None) or {})}
-        fused._bias_row = bias is not None and l.inputs[1 - temps_read[0]][1] == capi.IDX_ZERO
         gone[id(g)] = None
         out.append(fused)
     return [l for l in out if id(l) not in gone]
@@ -613,6 +612,7 @@ class GemmLaunch:
     def __init__(self, a_index: int, b_index: int, out_index: int, rect: Tuple[int, int, int, int], k_tiles: int,
                  b_is_bfp8: bool, bias_index: Optional[int] = None, act: Optional[str] = None):
         self.a_index, self.b_index, self.out_index, self.rect = a_index, b_index, out_index, rect
+        # b_is_bfp8: 0 for plain weights, else the bits per value of the block-float tiles (8: bfloat8_b, 4: bfloat4_b)
         self.k_tiles, self.b_is_bfp8, self.bias_index = k_tiles, b_is_bfp8, bias_index
         self.act = act    # activation applied in the GEMM epilogue (fused from a following element-wise launch)
         self.kind = "matmul_bf16"   # set to "matmul_f32" by the recogniser for float32 programs
