@@ -343,3 +343,24 @@ def test_translate_prints_plan_and_cuda_source(tmp_path):
                        cwd=root, env={**__import__("os").environ, "PYTHONPATH": str(root / "tt-lang_b200")}, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
     assert '"kind": "eltwise"' in r.stdout and "ttlb_eltwise_jit" in r.stdout and "expf(a)" in r.stdout
+
+
+def test_translate_prints_reduction_and_row_fused_sources(tmp_path):
+    """ttlang-b200-translate on programs with reductions: the generated reduction kernel and the row-resident kernel."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    prog = tmp_path / "prog.py"
+    prog.write_text(
+        "import importlib.util, torch, ttnn\n"
+        "spec = importlib.util.spec_from_file_location('pr', %r); m = importlib.util.module_from_spec(spec); spec.loader.exec_module(m)\n"
+        "z = lambda s: ttnn.from_torch(torch.zeros(s, dtype=torch.bfloat16))\n"
+        "m.make_reduce('sum', [0])(z((128, 256)), z((32, 32)), z((1, 256)))\n"
+        "m.make_softmax()(z((128, 256)), z((32, 32)), z((128, 256)))\n"
+        % str(root / "tests" / "programs" / "reduce.py"))
+    r = subprocess.run([sys.executable, "-m", "ttl_b200.translate", str(prog)], capture_output=True, text=True,
+                       cwd=root, env={**__import__("os").environ, "PYTHONPATH": str(root / "tt-lang_b200")}, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert '"kind": "reduce_sum"' in r.stdout and "ttlb_reduce_jit" in r.stdout
+    assert '"kind": "row_fused"' in r.stdout and "ttlb_rowfused_jit" in r.stdout and "source unavailable" not in r.stdout

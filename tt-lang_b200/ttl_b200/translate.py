@@ -33,14 +33,19 @@ def translate_file(path: str, with_source: bool = True) -> List[dict]:
         if with_source:
             allt = list(tensors) + self.extras
             srcs = []
+            ix = self.indexed(tensors)     # arguments, tensors derived in the body, temporaries of the plan
             for launch in self.launches:
-                if isinstance(launch, recognize.EltwiseLaunch):
-                    try:
+                try:
+                    if isinstance(launch, recognize.EltwiseLaunch):
                         srcs.append(capi.eltwise_source(_fake_pointers(launch.desc_cpu(allt))))
-                    except Exception as e:  # noqa: BLE001
-                        srcs.append(f"// source unavailable: {e}")
-                else:
-                    srcs.append(None)
+                    elif isinstance(launch, recognize.ReduceLaunch):
+                        srcs.append(capi.reduce_source(launch.desc(ix, with_pointers=False)))
+                    elif isinstance(launch, recognize.RowFusedLaunch):
+                        srcs.append(capi.rowfused_source(launch.desc(ix, with_pointers=False)))
+                    else:
+                        srcs.append(None)      # hand-written kernels (GEMM, attention): nothing is generated
+                except Exception as e:  # noqa: BLE001
+                    srcs.append(f"// source unavailable: {e}")
             rec["cuda"] = srcs
         records.append(rec)
 
