@@ -880,8 +880,8 @@ def main():
             line["cpu_baseline"] = {
                 "value": v, "unit": "GB/s", "cores": cores, "kind": "port",
                 "sample": f"oracle/tile_oracle.eval_expression on a 1024x{N} row slab, mean of 5 runs ({dt * 1e3:.1f} ms each)"}
-        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, from the ncu capture
-        # summarised in profiles/eltwise_jit_fused_bcast_8192.md (268.5 MB read + 97.6 MB written)
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this workload, from an ncu capture of this
+        # kernel on this workload (268.5 MB read + 97.6 MB written)
         line["roofline"]["traffic"] = 366.0e6
         print(json.dumps(line))
     if dist is not None:
