@@ -168,6 +168,19 @@ def matmul_tiles(a: torch.Tensor, b: torch.Tensor, mode: str, bias: Optional[tor
     return acc.to(dt)
 
 
+def attention_rows(q: torch.Tensor, kt: torch.Tensor, v: torch.Tensor, mask: torch.Tensor, scale: torch.Tensor,
+                   one: torch.Tensor, mode: str = "native") -> torch.Tensor:
+    """The attention tile program of tests/programs/attention.py op by op, the way the simulator evaluates it: every
+    block op in the tensors' dtype ("native") - S = Q @ K^T accumulated over K tiles, z = S * scale + mask,
+    m = reduce_max(z), e = exp(z - m), d = reduce_sum(e), O = (e / d) @ V; reductions as `reduce_expression`."""
+    s = matmul_tiles(q, kt, mode)
+    z = s * scale[0, 0] + mask
+    m = (z.to(torch.float32).amax(dim=1, keepdim=True) * one[0, 0].to(torch.float32)).to(z.dtype)
+    e = torch.exp(z - m)
+    d = (e.to(torch.float32).sum(dim=1, keepdim=True) * one[0, 0].to(torch.float32)).to(z.dtype)
+    return matmul_tiles(e / d, v, mode)
+
+
 def bf16_ulp_diff(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     """Distance in bf16 units-in-the-last-place between two bf16 tensors (monotone integer map)."""
     def key(t: torch.Tensor) -> torch.Tensor:

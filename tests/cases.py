@@ -22,6 +22,8 @@ def gen(shape: Tuple[int, int], dist: str, seed: int, dtype: torch.dtype = torch
         t = torch.rand(shape, generator=g, dtype=torch.float32) * 9.99 + 0.01
     elif dist == "ge1":               # U(1, 10): acosh domain
         t = torch.rand(shape, generator=g, dtype=torch.float32) * 9 + 1
+    elif dist == "causal_mask":       # 0 where key <= query, a large negative number above the diagonal
+        t = torch.triu(torch.full(shape, -1e4, dtype=torch.float32), diagonal=1)
     elif dist.startswith("const:"):
         t = torch.full(shape, float(dist.split(":")[1]), dtype=torch.float32)
     elif dist.startswith("normal*"):  # N(0, sigma)
@@ -215,8 +217,22 @@ EPILOGUE_CASES: List[Case] = [
 ]
 
 
+# attention written as a tile program (tests/programs/attention.py); the one-tile size is what the reference
+# simulator can run (its block matmul needs K = 1 tile); inputs: q, k^T, v, additive causal mask, scale tile, ones tile
+def _attn_inputs(s, d):
+    return [((s, d), "normal", 200), ((d, s), "normal", 201), ((s, d), "normal", 202), ((s, s), "causal_mask", 0),
+            ((32, 32), f"const:{d ** -0.5}", 0), ((32, 32), "const:1.0", 0)]
+
+
+ATTENTION_CASES: List[Case] = [
+    Case("attention_tile_32", "attention", "attention_rows", _attn_inputs(32, 32), (32, 32), "native", None, "rel1e-2"),
+    Case("attention_tile_32_f32", "attention", "attention_rows", _attn_inputs(32, 32), (32, 32), "native", None, "rel1e-5",
+         dtype=torch.float32),
+]
+
+
 def by_name(name: str) -> Case:
-    for c in CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES + MATH_CASES + EPILOGUE_CASES + OPERATOR_CASES:
+    for c in CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES + MATH_CASES + EPILOGUE_CASES + OPERATOR_CASES + ATTENTION_CASES:
         if c.name == name:
             return c
     raise KeyError(name)

@@ -31,7 +31,7 @@ def backend():
 
     ttl_b200.install()
     mods = {}
-    for name in ("eltwise", "matmul", "reduce"):
+    for name in ("eltwise", "matmul", "reduce", "attention"):
         spec = importlib.util.spec_from_file_location(f"programs_b200_{name}", ROOT / "tests" / "programs" / f"{name}.py")
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)

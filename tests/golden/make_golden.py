@@ -41,7 +41,7 @@ def load_sim(reference: Path):
 
 def load_programs(tag: str):
     mods = {}
-    for name in ("eltwise", "matmul", "reduce"):
+    for name in ("eltwise", "matmul", "reduce", "attention"):
         spec = importlib.util.spec_from_file_location(f"programs_{tag}_{name}", TESTS / "programs" / f"{name}.py")
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
@@ -81,7 +81,7 @@ def main() -> None:
 
     mods = load_programs("sim")
     only = set(sys.argv[2:])   # optional: names of the fixtures to (re)generate
-    for case in cases.CASES + cases.MATMUL_CASES + cases.REDUCE_CASES + cases.COMPOSITE_CASES + cases.MATH_CASES + cases.EPILOGUE_CASES + cases.OPERATOR_CASES:
+    for case in cases.CASES + cases.MATMUL_CASES + cases.REDUCE_CASES + cases.COMPOSITE_CASES + cases.MATH_CASES + cases.EPILOGUE_CASES + cases.OPERATOR_CASES + cases.ATTENTION_CASES:
         if only and case.name not in only:
             continue
         t0 = time.time()

@@ -577,9 +577,11 @@ def _fuse_rows(launches: List[Any]) -> List[Any]:
             for (ti, rm, ro, cm, co) in inputs:
                 if ti < TEMP_BASE or not ok:
                     continue
-                inside[ti] = inside.get(ti, 0) + 1
                 p = producer.get(ti)
-                if (p is None or p.dims != (1,) or p.rect != (r0, r1, 0, 1) or c0 != 0 or p.extent[1] != c1
+                if p is None:
+                    continue     # a temporary filled by another kind of launch (a matmul): an ordinary operand here
+                inside[ti] = inside.get(ti, 0) + 1
+                if (p.dims != (1,) or p.rect != (r0, r1, 0, 1) or c0 != 0 or p.extent[1] != c1
                         or (rm, ro, cm, co) != (capi.IDX_SAME, 0, capi.IDX_ZERO, 0) or p.dtype != l.dtype
                         or p.round_each_op != l.round_each_op):
                     ok = False
@@ -766,7 +768,7 @@ def _recognise_reduce(w: Write, terms: List[Red], table: _TensorTable, oi: int, 
         if t.dtype != odt:
             raise Unsupported(f"mixed element types ({t.dtype} operand, {odt} output)")
     for d, name in ((0, "row"), (1, "column")):
-        if d in dims and not any((inp[1] if d == 0 else inp[3]) == capi.IDX_SAME for inp in base.inputs):
+        if d in dims and not any((inp[1] if d == 0 else inp[3]) in (capi.IDX_SAME, capi.IDX_TILE) for inp in base.inputs):
             raise Unsupported(f"a reduction over {name}s needs an operand that varies along them")
     # the blocks of the terms must tile a rectangle of the reduced dims
     deltas = []
@@ -856,8 +858,8 @@ def _lower_reductions(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tens
             t = temps.get(key)
             if t is None:
                 t = temps[key] = table.new_temp(tuple(w.tensor.shape), w.tensor)
-            out.append((Write(t, w.r0, w.r1, w.c0, w.c1, e, w.core), 0))
-            res0: Tuple[Expr, int] = (Leaf(t, w.r0, w.r1, w.c0, w.c1), 1)
+            lvl = _expand_write(Write(t, w.r0, w.r1, w.c0, w.c1, e, w.core, getattr(e, "line", None)), table, temps, out)
+            res0: Tuple[Expr, int] = (Leaf(t, w.r0, w.r1, w.c0, w.c1), lvl + 1)
             memo[id(e)] = res0
             return res0
         if isinstance(e, Un):
@@ -897,6 +899,98 @@ def _lower_reductions(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tens
     return go(w.expr)
 
 
+def _first_leaf_like(e: Expr, shape: Tuple[int, int]) -> Optional[Leaf]:
+    stack = [e]
+    while stack:
+        x = stack.pop()
+        if isinstance(x, Leaf):
+            if x.shape == shape and not any(x.first):
+                return x
+        elif isinstance(x, Bin):
+            stack += [x.b, x.a]
+        elif isinstance(x, Un):
+            stack.append(x.x)
+        elif isinstance(x, Acc):
+            stack.extend(reversed(x.terms))
+        elif isinstance(x, Red):
+            stack.append(x.x)
+    return None
+
+
+def _lower_matmul_operands(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tensor],
+                           out: List[Tuple[Write, int]]) -> Tuple[Expr, int]:
+    """A block matmul write whose operands are expressions rather than blocks straight from a circular buffer
+    (`relu(a_blk) @ b_blk`, `softmax(s_blk) @ v_blk`): every such operand is first written to a temporary laid out
+    like a matrix operand - [output rows, K] for the left one, [K, output columns] for the right one - by writes of
+    their own, and the matmul reads the temporaries.  The K range of an operand block comes from the other operand
+    when that is a plain block, else from a block of equal shape inside the expression."""
+    e = w.expr
+    terms = list(e.terms) if isinstance(e, Acc) else [e]
+    bias = None
+    if len(terms) > 1 and isinstance(terms[0], Leaf):
+        bias, terms = terms[0], terms[1:]
+    oi = table.index(w.tensor)
+    level = 0
+    new_terms: List[Expr] = []
+    for t in terms:
+        a, b = _unwrap(t.a), _unwrap(t.b)
+        ops = {"a": a, "b": b}
+        for side in ("a", "b"):
+            x = ops[side]
+            if isinstance(x, Leaf):
+                continue
+            other = ops["b" if side == "a" else "a"]
+            if isinstance(other, Leaf):
+                k0, k1, k_total = ((other.r0, other.r1, other.tensor.shape[0]) if side == "a"
+                                   else (other.c0, other.c1, other.tensor.shape[1]))
+            else:
+                inner = _first_leaf_like(x, x.shape)
+                if inner is None:
+                    raise Unsupported("cannot tell which K tiles a computed matmul operand covers")
+                k0, k1, k_total = ((inner.c0, inner.c1, inner.tensor.shape[1]) if side == "a"
+                                   else (inner.r0, inner.r1, inner.tensor.shape[0]))
+            if x.shape != ((w.r1 - w.r0, k1 - k0) if side == "a" else (k1 - k0, w.c1 - w.c0)) or 1 in w.tensor.shape:
+                raise Unsupported("a computed matmul operand must have the shape of the operand block")
+            key = (oi, "mm_" + side)
+            tmp = temps.get(key)
+            if tmp is None:
+                shape = (w.tensor.shape[0], k_total) if side == "a" else (k_total, w.tensor.shape[1])
+                tmp = temps[key] = table.new_temp(shape, w.tensor)
+            region = (w.r0, w.r1, k0, k1) if side == "a" else (k0, k1, w.c0, w.c1)
+            lvl = _expand_write(Write(tmp, region[0], region[1], region[2], region[3], x, w.core, getattr(x, "line", None)),
+                                table, temps, out)
+            level = max(level, lvl + 1)
+            ops[side] = Leaf(tmp, *region)
+        nt = Bin("matmul", ops["a"], ops["b"], t.shape)
+        if getattr(t, "line", None) is not None:
+            nt.line = t.line
+        new_terms.append(nt)
+    if not isinstance(e, Acc):
+        return new_terms[0], level
+    acc = Acc(([bias] if bias is not None else []) + new_terms, e.shape)
+    if getattr(e, "line", None) is not None:
+        acc.line = e.line
+    return acc, level
+
+
+def _expand_write(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tensor], out: List[Tuple[Write, int]]) -> int:
+    """Append write `w` to `out`, preceded by the writes that fill the temporaries it needs (reductions and matmuls
+    inside its expression, computed matmul operands).  Returns the level of `w` (0: reads inputs only)."""
+    mm = _matmul_terms(w)
+    if mm is not None:
+        if all(isinstance(_unwrap(t.a), Leaf) and isinstance(_unwrap(t.b), Leaf) for t in mm[0]):
+            out.append((w, 0))
+            return 0
+        expr, level = _lower_matmul_operands(w, table, temps, out)
+    elif _reduce_terms(w) is None and (_contains_matmul(w.expr) or _contains_red(w.expr)):
+        expr, level = _lower_reductions(w, table, temps, out)
+    else:
+        out.append((w, 0))
+        return 0
+    out.append((Write(w.tensor, w.r0, w.r1, w.c0, w.c1, expr, w.core, w.line), level))
+    return level
+
+
 def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermediates: bool = False) -> Plan:
     table = _TensorTable(arg_tensors)
     # 1. every write gets a key (what is computed, from where); 2. writes must not overlap, except that
@@ -913,11 +1007,7 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
     temps: Dict[Any, _ttnn.Tensor] = {}
     writes: List[Tuple[Write, int]] = []
     for w in trace.writes:
-        if _reduce_terms(w) is None and _matmul_terms(w) is None and (_contains_matmul(w.expr) or _contains_red(w.expr)):
-            expr, level = _lower_reductions(w, table, temps, writes)
-            writes.append((Write(w.tensor, w.r0, w.r1, w.c0, w.c1, expr, w.core, w.line), level))
-        else:
-            writes.append((w, 0))
+        _expand_write(w, table, temps, writes)
     level_of: Dict[Any, int] = {}
     lines_of: Dict[Any, Dict[Tuple[str, int], int]] = {}   # per launch key: program line -> writes it took part in
     for w, level in writes:
