@@ -156,3 +156,33 @@ def test_quantised_linear_program_with_bias_and_activation(backend, act, bits):
     capi.context().check_status(capi.current_stream())
     want = tile_oracle.UNARY[act](x.float() @ wq + v.float())
     assert rel_err(ttnn.to_torch(out), want) <= 1e-2
+
+
+def test_config4_as_the_unchanged_tile_program_at_full_size(backend):
+    """configs[3] through `@ttl.kernel`: the multicore matmul tile program in 1x1-tile blocks with the weights a
+    bfloat8_b tensor [8192, 28672] (29.4 million tile multiply-accumulates, traced with batched loops): one
+    weight expansion + one GEMM launch; 256 activation rows of two 1024-column stripes checked against the oracle."""
+    import time
+    _, mods = backend
+    import ttnn
+    from ttl_b200 import capi
+    m, k, n = 4096, 8192, 28672
+    x = cases.gen((m, k), "normal", 0)
+    w = cases.gen((k, n), "normal*0.02", 1, torch.float32)
+    W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+    X = ttnn.from_torch(x)
+    out = ttnn.from_torch(torch.zeros((m, n), dtype=torch.bfloat16))
+    prog = mods["matmul"].multicore_matmul
+    t0 = time.perf_counter()
+    plan = prog.plan(X, W, out)
+    assert time.perf_counter() - t0 < 10, "trace + recognise of the 4096 x 8192 x 28672 program took too long"
+    assert [d["kind"] for d in plan.describe()] == ["matmul_bfp8w"]
+    prog(X, W, out)
+    capi.context().check_status(capi.current_stream())
+    got = ttnn.to_torch(out)
+    for c0 in (0, n - 1024):
+        stripe = w[:, c0:c0 + 1024].contiguous()
+        wq = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(stripe.numpy()), k, 1024))
+        for r0 in (0, m - 256):
+            want = tile_oracle.matmul_tiles(x[r0:r0 + 256].float(), wq, "f32")
+            assert rel_err(got[r0:r0 + 256, c0:c0 + 1024], want) <= 1e-2, (r0, c0)

@@ -199,3 +199,30 @@ def test_k_blocked_matmul_program(backend):
     want = a.float() @ b.float()
     got = ttnn.to_torch(out).float()
     assert ((got - want).abs().max() / want.abs().max()).item() <= 1e-2
+
+
+def test_config3_as_the_unchanged_tile_program_at_full_size(backend):
+    """configs[2] through `@ttl.kernel`: the reference's multicore matmul program in 1x1-tile blocks
+    (examples/multicore_matmul.py:28-139, restated in tests/programs/matmul.py) on 8192^3 - 16.7 million tile
+    multiply-accumulates traced with batched loops - becomes one GEMM launch; checked on three row slabs."""
+    import time
+    from ttl_b200 import capi
+    _, mods = backend
+    import ttnn
+    n = 8192
+    a = cases.gen((n, n), f"normal*{n ** -0.5}", 0)
+    b = cases.gen((n, n), f"normal*{n ** -0.5}", 1)
+    A, B = ttnn.from_torch(a), ttnn.from_torch(b)
+    out = ttnn.from_torch(torch.zeros((n, n), dtype=torch.bfloat16))
+    prog = mods["matmul"].multicore_matmul
+    t0 = time.perf_counter()
+    plan = prog.plan(A, B, out)
+    assert time.perf_counter() - t0 < 10, "trace + recognise of the 8192^3 program took too long"
+    assert [d["kind"] for d in plan.describe()] == ["matmul_bf16"]
+    n0 = capi.context().launch_count()
+    prog(A, B, out)
+    capi.context().check_status(capi.current_stream())
+    assert capi.context().launch_count() == n0 + 1
+    got = ttnn.to_torch(out)
+    for r0 in (0, 4064, 8128):
+        assert rel_err(got[r0:r0 + 64], tile_oracle.matmul_tiles(a[r0:r0 + 64], b, "f32")) <= TOL, f"rows {r0}..{r0 + 63}"

@@ -58,13 +58,14 @@ def broadcast(block: Any, out_block: Optional[Any] = None, dims: Optional[List[i
                 if shape[d] != out_shape[d] and shape[d] != 1:
                     raise ValueError(f"Cannot broadcast block of shape {shape} to output block of shape {out_shape}")
         leaf = Leaf(v.tensor, v.r0, v.r1, v.c0, v.c1, first)
-        return Block(out_shape, b.dtype, leaf, "FULL", "temp", temporary=True)
+        leaf.shape = v.shape
+        return Block(out_shape, b.dtype, leaf, "FULL", "temp", temporary=True, nest=b.nest)
     for dim in dims:
         if shape[dim] != 1:
             raise ValueError(
                 f"Cannot broadcast along dimension {dim}: dimension must have size 1, "
                 f"but has size {shape[dim]}")
-    return Block(shape, b.dtype, v, "FULL", "temp", temporary=True)
+    return Block(shape, b.dtype, v, "FULL", "temp", temporary=True, nest=b.nest)
 
 
 def _unary(name: str):
@@ -185,7 +186,7 @@ def _reduce(op: str, block: Any, scaler: Any, dims: Optional[List[int]]) -> Bloc
             raise ValueError(f"reduce_{op}(): the scaler must be a block of one tile, got shape {sb.shape}")
         sc = sb.value()
     e = _tag(Red(op, b.value(), sc, ds))
-    return Block(e.shape, b.dtype, e, "FULL", "temp", temporary=True)
+    return Block(e.shape, b.dtype, e, "FULL", "temp", temporary=True, nest=b.nest)
 
 
 def reduce_sum(block: Any, scaler: Any = None, dims: Optional[List[int]] = None) -> Block:

@@ -26,7 +26,7 @@ import torch
 
 from . import capi
 from . import ttnn as _ttnn
-from .trace import PROFILE, Acc, Bin, Expr, Leaf, Red, Trace, Un, Write, Zero
+from .trace import PROFILE, Acc, BatchedWrite, Bin, Expr, Leaf, Red, Rep, Trace, Un, Write, Zero
 
 TILE = 32
 
@@ -91,6 +91,8 @@ def _lines_of(w: Write) -> List[Tuple[str, int]]:
             stack.append(x.x)
         elif isinstance(x, Acc):
             stack.extend(x.terms)
+        elif isinstance(x, Rep):
+            stack.append(x.x)
         elif isinstance(x, Red):
             stack.append(x.x)
             if x.scaler is not None:
@@ -107,11 +109,76 @@ def _contains_matmul(e: Expr) -> bool:
                 return True
             stack.append(x.a)
             stack.append(x.b)
-        elif isinstance(x, Un):
+        elif isinstance(x, (Un, Rep)):
             stack.append(x.x)
         elif isinstance(x, Acc):
             stack.extend(x.terms)
     return False
+
+
+def _expand_runs(e: Expr) -> Expr:
+    """`e` with every run of accumulated terms (trace.Rep, made by batched loops) written out term by term."""
+    if isinstance(e, Acc):
+        terms: List[Expr] = []
+        changed = False
+        for t in e.terms:
+            if isinstance(t, Rep):
+                terms.extend(_expand_runs(x) for x in t.terms())
+                changed = True
+            else:
+                n = _expand_runs(t)
+                changed = changed or n is not t
+                terms.append(n)
+        if not changed:
+            return e
+        r: Expr = Acc(terms, e.shape)
+    elif isinstance(e, Un):
+        x = _expand_runs(e.x)
+        if x is e.x:
+            return e
+        r = Un(e.op, x, e.params)
+    elif isinstance(e, Bin):
+        a, b = _expand_runs(e.a), _expand_runs(e.b)
+        if a is e.a and b is e.b:
+            return e
+        r = Bin(e.op, a, b, e.shape)
+    elif isinstance(e, Red):
+        x = _expand_runs(e.x)
+        sc = _expand_runs(e.scaler) if e.scaler is not None else None
+        if x is e.x and sc is e.scaler:
+            return e
+        r = Red(e.op, x, sc, e.dims)
+    elif isinstance(e, Rep):   # a run outside an accumulation cannot be made; keep the first term's meaning explicit
+        r = Acc([_expand_runs(x) for x in e.terms()], e.shape)
+    else:
+        return e
+    if getattr(e, "line", None) is not None:
+        r.line = e.line
+    return r
+
+
+def _has_run(e: Expr) -> bool:
+    stack = [e]
+    while stack:
+        x = stack.pop()
+        if isinstance(x, Rep):
+            return True
+        if isinstance(x, Bin):
+            stack += [x.a, x.b]
+        elif isinstance(x, Un):
+            stack.append(x.x)
+        elif isinstance(x, Acc):
+            stack.extend(x.terms)
+        elif isinstance(x, Red):
+            stack.append(x.x)
+    return False
+
+
+def _plain_matmul(t: Expr) -> bool:
+    """`a_blk @ b_blk` with both operands straight from circular buffers, or a run of such terms."""
+    if isinstance(t, Rep):
+        t = t.x
+    return isinstance(t, Bin) and t.op == "matmul" and isinstance(_unwrap(t.a), Leaf) and isinstance(_unwrap(t.b), Leaf)
 
 
 TEMP_BASE = 1000   # tensor indices from here on name temporaries owned by the plan
@@ -696,7 +763,8 @@ def _matmul_terms(w: Write) -> Optional[Tuple[List[Bin], Optional[Leaf]]]:
     bias = None
     if len(terms) > 1 and isinstance(terms[0], Leaf):
         bias, terms = terms[0], terms[1:]
-    if terms and all(isinstance(t, Bin) and t.op == "matmul" for t in terms):
+    if terms and all(isinstance(t.x if isinstance(t, Rep) else t, Bin) and (t.x if isinstance(t, Rep) else t).op == "matmul"
+                     for t in terms):
         return terms, bias  # type: ignore[return-value]
     return None
 
@@ -813,7 +881,7 @@ def _contains_red(e: Expr) -> bool:
             return True
         if isinstance(x, Bin):
             stack += [x.a, x.b]
-        elif isinstance(x, Un):
+        elif isinstance(x, (Un, Rep)):
             stack.append(x.x)
         elif isinstance(x, Acc):
             stack.extend(x.terms)
@@ -976,9 +1044,17 @@ def _lower_matmul_operands(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn
 def _expand_write(w: Write, table: _TensorTable, temps: Dict[Any, _ttnn.Tensor], out: List[Tuple[Write, int]]) -> int:
     """Append write `w` to `out`, preceded by the writes that fill the temporaries it needs (reductions and matmuls
     inside its expression, computed matmul operands).  Returns the level of `w` (0: reads inputs only)."""
+    if _has_run(w.expr):
+        # runs of accumulated terms stay compact only where the matmul recogniser reads them directly
+        e = w.expr
+        terms = list(e.terms) if isinstance(e, Acc) else [e]
+        if len(terms) > 1 and isinstance(terms[0], Leaf):
+            terms = terms[1:]
+        if not all(_plain_matmul(t) for t in terms):
+            w = Write(w.tensor, w.r0, w.r1, w.c0, w.c1, _expand_runs(w.expr), w.core, w.line)
     mm = _matmul_terms(w)
     if mm is not None:
-        if all(isinstance(_unwrap(t.a), Leaf) and isinstance(_unwrap(t.b), Leaf) for t in mm[0]):
+        if all(_plain_matmul(t) for t in mm[0]):
             out.append((w, 0))
             return 0
         expr, level = _lower_matmul_operands(w, table, temps, out)
@@ -1007,13 +1083,43 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
     temps: Dict[Any, _ttnn.Tensor] = {}
     writes: List[Tuple[Write, int]] = []
     for w in trace.writes:
-        _expand_write(w, table, temps, writes)
+        if isinstance(w, BatchedWrite):
+            writes.append((w, 0))     # a matmul written by batched loops: all its iterations are recognised at once
+        else:
+            _expand_write(w, table, temps, writes)
     level_of: Dict[Any, int] = {}
     lines_of: Dict[Any, Dict[Tuple[str, int], int]] = {}   # per launch key: program line -> writes it took part in
     for w, level in writes:
         oi = table.index(w.tensor)
         out_tensors[oi] = w.tensor
         tr, tc = w.tensor.tile_shape()
+        if isinstance(w, BatchedWrite):
+            key = _recognise_matmul_batched(w, table, oi)
+            if key is None:
+                # its iterations differ in more than the output block: one write per iteration, the ordinary way
+                for x in w.expand():
+                    _expand_write(x, table, temps, writes)
+                continue
+            grid = cover.setdefault(oi, np.zeros((tr, tc), dtype=bool))
+            regions = w.regions()
+            for region in regions:
+                r0, r1, c0, c1 = region
+                if not (0 <= r0 < r1 <= tr and 0 <= c0 < c1 <= tc):
+                    raise ValueError(f"write region [{r0}:{r1}, {c0}:{c1}] is outside the {tr}x{tc}-tile tensor")
+                covered = grid[r0:r1, c0:c1]
+                if covered.any():
+                    if seen.get((oi, region)) == key:
+                        continue
+                    raise Unsupported(f"output tiles [{r0}:{r1}, {c0}:{c1}] are written more than once")
+                covered[...] = True
+                seen[(oi, region)] = key
+                mm_groups.setdefault(key, []).append(region)
+            level_of[key] = max(level_of.get(key, 0), level)
+            if PROFILE.enabled:
+                per_key = lines_of.setdefault(key, {})
+                for ln in _lines_of(w):
+                    per_key[ln] = per_key.get(ln, 0) + len(regions)
+            continue
         if not (0 <= w.r0 < w.r1 <= tr and 0 <= w.c0 < w.c1 <= tc):
             raise ValueError(f"write region [{w.r0}:{w.r1}, {w.c0}:{w.c1}] is outside the {tr}x{tc}-tile tensor")
         region = (w.r0, w.r1, w.c0, w.c1)
@@ -1107,6 +1213,40 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
     return Plan(ordered, table.extras, len(table.args), table.temps)
 
 
+def _recognise_matmul_batched(w: BatchedWrite, table: _TensorTable, oi: int) -> Any:
+    """Key of a matmul written by batched loops, all iterations checked at once with array comparisons (the same
+    conditions as _recognise_matmul / _recognise_bias); None when the K tiles differ between iterations, in which
+    case the caller goes through the iterations one by one."""
+    mm = _matmul_terms(w)
+    assert mm is not None
+    terms, bias = mm
+    na = 4   # loop axes of the tile-coordinate arrays (symloop.NEST_AXES)
+    for t in terms:
+        x = t.x if isinstance(t, Rep) else t
+        for v in (x.a.c0, x.a.c1, x.b.r0, x.b.r1):
+            if isinstance(v, np.ndarray) and any(sz > 1 for sz in v.shape[:na]):
+                return None
+
+    def same(p: Any, q: Any) -> bool:
+        return bool(np.all(np.equal(p, q)))
+
+    for t in terms:
+        x = t.x if isinstance(t, Rep) else t
+        if not (same(x.a.r0, w.r0) and same(x.a.r1, w.r1) and same(x.b.c0, w.c0) and same(x.b.c1, w.c1)):
+            raise Unsupported("matmul operand rows/columns do not line up with the output block")
+    # the K side does not depend on the iteration: judged on the first one
+    first = w.expand(1)[0]
+    mm1 = _matmul_terms(first)
+    assert mm1 is not None
+    key = tuple(_recognise_matmul(first, mm1[0], table, oi))
+    ci = None
+    if bias is not None:
+        if not (same(bias.r0, w.r0) and same(bias.r1, w.r1) and same(bias.c0, w.c0) and same(bias.c1, w.c1)):
+            raise Unsupported("matmul with bias: the bias block is not the block of the output tile being computed")
+        ci = _recognise_bias(first, mm1[1], table)
+    return ("mm",) + key + (ci,)
+
+
 def _recognise_bias(w: Write, bias: Optional[Leaf], table: _TensorTable) -> Optional[int]:
     if bias is None:
         return None
@@ -1118,17 +1258,20 @@ def _recognise_bias(w: Write, bias: Optional[Leaf], table: _TensorTable) -> Opti
     return table.index(t)
 
 
-def _recognise_matmul(w: Write, terms: List[Bin], table: _TensorTable, oi: int) -> Any:
-    a0, b0 = terms[0].a, terms[0].b
+def _recognise_matmul(w: Write, terms: List[Any], table: _TensorTable, oi: int) -> Any:
+    first = terms[0].x if isinstance(terms[0], Rep) else terms[0]
+    a0, b0 = _unwrap(first.a), _unwrap(first.b)
     if not (isinstance(a0, Leaf) and isinstance(b0, Leaf)):
         raise Unsupported("matmul operands must come straight from circular buffers")
     ta, tb = a0.tensor, b0.tensor
     kt = ta.tile_shape()[1]
     if tb.tile_shape()[0] != kt:
         raise ValueError(f"Incompatible matrix shapes for multiplication: {ta.shape} @ {tb.shape}")
-    ks = []
+    ks: List[Any] = []
     for t in terms:
-        a, b = t.a, t.b
+        run = isinstance(t, Rep)
+        x = t.x if run else t
+        a, b = _unwrap(x.a), _unwrap(x.b)
         if not (isinstance(a, Leaf) and isinstance(b, Leaf)) or a.tensor is not ta or b.tensor is not tb:
             raise Unsupported("matmul accumulation must read the same A and B tensors in every step")
         if a.shape[1] != b.shape[0] or (a.shape[1] > 1 and a.shape == b.shape):
@@ -1136,13 +1279,40 @@ def _recognise_matmul(w: Write, terms: List[Bin], table: _TensorTable, oi: int) 
             # a block dot product in the specification: refused rather than guessed
             raise Unsupported(f"matmul of blocks {a.shape} @ {b.shape}: (M,K) @ (K,N) blocks only "
                               "(equal-shape multi-tile blocks are ambiguous)")
-        if (a.r0, a.r1) != (w.r0, w.r1) or (b.c0, b.c1) != (w.c0, w.c1):
+        if not run:
+            if (a.r0, a.r1) != (w.r0, w.r1) or (b.c0, b.c1) != (w.c0, w.c1):
+                raise Unsupported("matmul operand rows/columns do not line up with the output block")
+            if (a.c0, a.c1) != (b.r0, b.r1):
+                raise Unsupported("matmul step multiplies different K tiles of A and B")
+            ks.append(np.arange(a.c0, a.c1))
+            continue
+        # a run of steps (a batched K loop): the same checks on whole arrays of tile coordinates
+        n = 1
+        for sz in t.sizes:
+            n *= sz
+
+        def col(v: Any) -> "np.ndarray":
+            """The coordinate for every step of the run, in the order the steps accumulate."""
+            if isinstance(v, np.ndarray):
+                if v.size == n and len(t.axes) == 1:
+                    return v.reshape(-1)
+                full = [1] * v.ndim
+                for ax, sz in zip(t.axes, t.sizes):
+                    full[ax] = sz
+                return np.broadcast_to(v, full).reshape(-1)
+            return np.full(n, v, dtype=np.int64)
+
+        ar0, ar1, ac0, ac1 = (col(v) for v in (a.r0, a.r1, a.c0, a.c1))
+        br0, br1, bc0, bc1 = (col(v) for v in (b.r0, b.r1, b.c0, b.c1))
+        if ((ar0 != w.r0).any() or (ar1 != w.r1).any() or (bc0 != w.c0).any() or (bc1 != w.c1).any()):
             raise Unsupported("matmul operand rows/columns do not line up with the output block")
-        if (a.c0, a.c1) != (b.r0, b.r1):
+        if (ac0 != br0).any() or (ac1 != br1).any():
             raise Unsupported("matmul step multiplies different K tiles of A and B")
-        ks.extend(range(a.c0, a.c1))
-    if sorted(ks) != list(range(kt)):
-        raise Unsupported(f"matmul accumulates K tiles {sorted(set(ks))[:4]}... instead of all {kt} exactly once")
+        width = a.shape[1]
+        ks.append((ac0[:, None] + np.arange(width)[None, :]).reshape(-1))
+    allk = np.sort(np.concatenate(ks)) if ks else np.zeros(0, dtype=np.int64)
+    if allk.size != kt or (allk != np.arange(kt)).any():
+        raise Unsupported(f"matmul accumulates K tiles {sorted(set(allk.tolist()))[:4]}... instead of all {kt} exactly once")
     b8 = 0 if tb._packed is None else tb._packed_bits    # 0: plain weights; 8 / 4: block-float tiles
     all_bf16 = ta.dtype == torch.bfloat16 and (b8 or tb.dtype == torch.bfloat16) and w.tensor.dtype == torch.bfloat16
     all_f32 = ta.dtype == torch.float32 and not b8 and tb.dtype == torch.float32 and w.tensor.dtype == torch.float32

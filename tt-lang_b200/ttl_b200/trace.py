@@ -34,7 +34,11 @@ import types
 from collections import deque
 from typing import Any, Callable, Deque, Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
+
+from . import symloop as _sl
 from . import ttnn as _ttnn
+from .symloop import NeedsConcrete
 
 TILE_SHAPE = (32, 32)
 MAX_CBS = 32
@@ -84,7 +88,10 @@ class Leaf(Expr):
     def __init__(self, tensor: "_ttnn.Tensor", r0: int, r1: int, c0: int, c1: int,
                  first: Tuple[bool, bool] = (False, False)):
         self.tensor, self.r0, self.r1, self.c0, self.c1, self.first = tensor, r0, r1, c0, c1, first
-        self.shape = (r1 - r0, c1 - c0)
+        # tile coordinates are ints, or (traced with batched loops, symloop.py) int64 arrays with one axis per loop;
+        # the extent is the same for every iteration and is then set by the creator
+        self.shape = (r1 - r0, c1 - c0) if type(r0) is int and type(r1) is int and type(c0) is int and type(c1) is int \
+            else (0, 0)
 
 
 class Zero(Expr):
@@ -135,6 +142,96 @@ class Red(Expr):
         self.shape = (1 if 0 in dims else x.shape[0], 1 if 1 in dims else x.shape[1])
 
 
+class Rep(Expr):
+    """A run of accumulated terms: `x` once for every index of the sequence axes `axes` (array axes of the tile
+    coordinates inside `x`, sizes `sizes`, first axis slowest).  Made when `store(..., acc=True)` runs in a
+    batched loop nested deeper than the block it accumulates into (the K loop of a matmul)."""
+
+    __slots__ = ("x", "axes", "sizes")
+
+    def __init__(self, x: Expr, axes: Tuple[int, ...], sizes: Tuple[int, ...]):
+        self.x, self.axes, self.sizes, self.shape = x, axes, sizes, x.shape
+
+    def terms(self) -> List[Expr]:
+        """The terms the run stands for, in order."""
+        out = []
+        for idx in np.ndindex(*self.sizes):
+            sel = dict(zip(self.axes, idx))
+            out.append(map_coords(self.x, lambda a: _pick(a, sel)))
+        return out
+
+
+def _pick(a: "np.ndarray", sel: Dict[int, int]) -> Any:
+    """Array `a` at index sel[axis] along the given axes (kept with size 1); an int when nothing is left."""
+    ix = tuple(slice(sel[ax], sel[ax] + 1) if ax in sel and a.shape[ax] > 1 else slice(None) for ax in range(a.ndim))
+    b = a[ix]
+    return int(b.reshape(-1)[0]) if b.size == 1 else b
+
+
+def map_coords(e: Expr, fn: Callable[["np.ndarray"], Any], memo: Optional[Dict[int, Expr]] = None) -> Expr:
+    """`e` with every array-valued tile coordinate replaced by fn(array); shared subtrees stay shared."""
+    if memo is None:
+        memo = {}
+    hit = memo.get(id(e))
+    if hit is not None:
+        return hit
+    r: Expr
+    if isinstance(e, Leaf):
+        cs = [fn(c) if isinstance(c, np.ndarray) else c for c in (e.r0, e.r1, e.c0, e.c1)]
+        if all(a is b for a, b in zip(cs, (e.r0, e.r1, e.c0, e.c1))):
+            r = e
+        else:
+            r = Leaf(e.tensor, cs[0], cs[1], cs[2], cs[3], e.first)
+            r.shape = e.shape
+    elif isinstance(e, Un):
+        x = map_coords(e.x, fn, memo)
+        r = e if x is e.x else Un(e.op, x, e.params)
+    elif isinstance(e, Bin):
+        a, b = map_coords(e.a, fn, memo), map_coords(e.b, fn, memo)
+        r = e if (a is e.a and b is e.b) else Bin(e.op, a, b, e.shape)
+    elif isinstance(e, Acc):
+        ts = [map_coords(t, fn, memo) for t in e.terms]
+        r = e if all(a is b for a, b in zip(ts, e.terms)) else Acc(ts, e.shape)
+    elif isinstance(e, Red):
+        x = map_coords(e.x, fn, memo)
+        sc = map_coords(e.scaler, fn, memo) if e.scaler is not None else None
+        r = e if (x is e.x and sc is e.scaler) else Red(e.op, x, sc, e.dims)
+    elif isinstance(e, Rep):
+        x = map_coords(e.x, fn, memo)
+        r = e if x is e.x else Rep(x, e.axes, e.sizes)
+    else:
+        r = e
+    if r is not e and getattr(e, "line", None) is not None:
+        r.line = e.line
+    memo[id(e)] = r
+    return r
+
+
+def _rep_axes_used(e: Expr) -> int:
+    """Number of sequence axes the runs inside `e` already occupy."""
+    top = 0
+    stack, seen = [e], set()
+    while stack:
+        x = stack.pop()
+        if id(x) in seen:
+            continue
+        seen.add(id(x))
+        if isinstance(x, Rep):
+            top = max(top, max(x.axes) - _sl.NEST_AXES + 1)
+            stack.append(x.x)
+        elif isinstance(x, Bin):
+            stack += [x.a, x.b]
+        elif isinstance(x, Un):
+            stack.append(x.x)
+        elif isinstance(x, Acc):
+            stack.extend(x.terms)
+        elif isinstance(x, Red):
+            stack.append(x.x)
+            if x.scaler is not None:
+                stack.append(x.scaler)
+    return top
+
+
 class Write:
     """`tensor[r0:r1, c0:c1] <- expr` (tile coordinates)."""
 
@@ -144,6 +241,74 @@ class Write:
                  line: Optional[Tuple[str, int]] = None):
         self.tensor, self.r0, self.r1, self.c0, self.c1, self.expr, self.core = tensor, r0, r1, c0, c1, expr, core
         self.line = line
+
+
+class BatchedWrite(Write):
+    """The writes of all iterations of the batched loops live at the copy (`sizes`: their trip counts): the tile
+    coordinates and those inside `expr` are arrays over the loop axes.  Trace.finish() turns it into one Write per
+    iteration."""
+
+    __slots__ = ("sizes",)
+
+    def __init__(self, tensor: "_ttnn.Tensor", r0: Any, r1: Any, c0: Any, c1: Any, expr: Expr, core: int,
+                 line: Optional[Tuple[str, int]], sizes: Tuple[int, ...]):
+        super().__init__(tensor, r0, r1, c0, c1, expr, core, line)
+        self.sizes = sizes
+
+    def count(self) -> int:
+        count = 1
+        for n in self.sizes:
+            count *= n
+        return count
+
+    def regions(self) -> List[Tuple[int, int, int, int]]:
+        """(r0, r1, c0, c1) of every iteration, in order."""
+        n = self.count()
+        cols = [np.broadcast_to(c, tuple(self.sizes) + c.shape[len(self.sizes):]).reshape(n).tolist()
+                if isinstance(c, np.ndarray) else [c] * n for c in (self.r0, self.r1, self.c0, self.c1)]
+        return list(zip(*cols))
+
+    def plain_matmul(self) -> bool:
+        """`sum_k a_blk @ b_blk` (optionally starting from a bias block) with every operand straight from a
+        circular buffer: the form the recogniser reads for all iterations at once."""
+        e = self.expr
+        terms = list(e.terms) if isinstance(e, Acc) else [e]
+        if len(terms) > 1 and isinstance(terms[0], Leaf):
+            terms = terms[1:]
+        for t in terms:
+            x = t.x if isinstance(t, Rep) else t
+            if not (isinstance(x, Bin) and x.op == "matmul" and isinstance(x.a, Leaf) and isinstance(x.b, Leaf)):
+                return False
+        return bool(terms)
+
+    def expand(self, limit: Optional[int] = None) -> List[Write]:
+        count = self.count()
+        d = len(self.sizes)
+        columns: Dict[int, Any] = {}     # id(array) -> per-iteration values (list of ints, or of arrays over the sequence axes)
+
+        def column(a: "np.ndarray") -> Any:
+            col = columns.get(id(a))
+            if col is None:
+                rest = a.shape[_sl.NEST_AXES:]
+                full = np.broadcast_to(a, tuple(self.sizes) + a.shape[d:])
+                if all(s == 1 for s in rest):
+                    col = full.reshape(count).tolist()
+                else:
+                    flat = full.reshape((count,) + (1,) * _sl.NEST_AXES + rest)
+                    col = [flat[i] for i in range(count)]
+                columns[id(a)] = (a, col)
+                return col
+            return col[1]
+
+        def coord(c: Any, i: int) -> Any:
+            return column(c)[i] if isinstance(c, np.ndarray) else c
+
+        out = []
+        for i in range(count if limit is None else min(count, limit)):
+            expr = map_coords(self.expr, lambda a, i=i: column(a)[i])
+            out.append(Write(self.tensor, coord(self.r0, i), coord(self.r1, i), coord(self.c0, i), coord(self.c1, i), expr,
+                             self.core, self.line))
+        return out
 
 
 def infer_broadcast_shape(left: Tuple[int, ...], right: Tuple[int, ...]) -> Tuple[int, int]:
@@ -221,14 +386,20 @@ class _Worker:
         _tls.kind = self.kind
         _tls.worker = self
         _tls.trace = self.sched.trace
+        st = _sl.STATE
+        st.nest, st.enabled, st.nobatch, st.batched_loops = [], self.sched.batching, self.sched.nobatch, 0
+        self.nest = st.nest
+        self.budget = self.sched.trace.budget or 0
         try:
             if not self.sched.aborting:
                 self.fn()
-        except _Abort:
+        except (_Abort, _BudgetSpent):   # a verification probe stops a thread that has done its share
             pass
         except BaseException as e:  # noqa: BLE001 - reported to the caller of the kernel
             self.error = e
         finally:
+            self.sched.trace.batched_loops += st.batched_loops
+            st.nest = None
             self.done = True
             self.sched.back.set()
 
@@ -248,6 +419,10 @@ class _Abort(BaseException):
     pass
 
 
+class _BudgetSpent(BaseException):
+    pass
+
+
 class Scheduler:
     def __init__(self, grid: Tuple[int, ...], trace: "Trace"):
         self.grid = grid
@@ -255,6 +430,8 @@ class Scheduler:
         self.workers: List[_Worker] = []
         self.back = threading.Event()
         self.aborting = False
+        self.batching = False                 # run batchable loops once for all their iterations (symloop.py)
+        self.nobatch: Any = frozenset()       # loop sites that must run iteration by iteration
 
     def add(self, name: str, fn: Callable[[], Any], core: int, kind: str) -> None:
         self.workers.append(_Worker(self, name, fn, core, kind))
@@ -287,6 +464,13 @@ class Scheduler:
             if not progressed and error is None:
                 lines = [f"  {w.name}: blocked on {w.blocked_desc}" for w in pending]
                 error = DeadlockError("Deadlock detected: all threads are blocked\n" + "\n".join(lines))
+                # a loop that feeds itself through a circular buffer starves when it runs once for all its
+                # iterations: run the loops the blocked threads are in iteration by iteration and look again
+                sites = set()
+                for w in pending:
+                    sites |= _sl.sites_of(getattr(w, "nest", None) or ())
+                if sites:
+                    error = NeedsConcrete(sites, "threads starve while their loops are batched")
         if error is not None:
             self.aborting = True
             for w in self.workers:
@@ -313,18 +497,94 @@ def _worker() -> _Worker:
 # --------------------------------------------------------------------------- #
 # Blocks and circular buffers
 # --------------------------------------------------------------------------- #
+def _make_rep(v: Expr, extra: Sequence[Any]) -> Expr:
+    """`v`, whose tile coordinates vary along the axes of the batched loops `extra`, as the run of terms those
+    loops store one after the other: their axes are moved to free sequence axes."""
+    used = _rep_axes_used(v)
+    if used + len(extra) > _sl.REP_AXES:
+        raise NeedsConcrete(_sl.sites_of(extra), "accumulation nested too deeply")
+    axes = tuple(_sl.NEST_AXES + used + i for i in range(len(extra)))
+    moves = [(f.axis, ax) for f, ax in zip(extra, axes)]
+
+    def move(a: "np.ndarray") -> "np.ndarray":
+        for src, dst in moves:
+            if a.shape[src] > 1:
+                a = np.swapaxes(a, src, dst)
+        return a
+
+    return Rep(map_coords(v, move), axes, tuple(f.n for f in extra))
+
+
+class _Seg:
+    """A run of pushed blocks in a circular buffer's queue: what a reserve / push pair inside batched loops with
+    trip counts `sizes` pushed, first loop slowest.  `off` entries have been popped already."""
+
+    __slots__ = ("shape", "dtype", "expr", "sizes", "count", "off")
+
+    def __init__(self, shape: Tuple[int, int], dtype: Any, expr: Expr, sizes: Tuple[int, ...]):
+        self.shape, self.dtype, self.expr, self.sizes, self.off = shape, dtype, expr, sizes, 0
+        self.count = 1
+        for n in sizes:
+            self.count *= n
+
+    def left(self) -> int:
+        return self.count - self.off
+
+    def element(self) -> "Block":
+        """The next entry as an ordinary block."""
+        idx = np.unravel_index(self.off, self.sizes)
+        sel = {ax: int(i) for ax, i in enumerate(idx)}
+        return Block(self.shape, self.dtype, map_coords(self.expr, lambda a: _pick(a, sel)), "FULL", "wait")
+
+    def take(self, m: int, frames: Sequence[Any]) -> Optional["Block"]:
+        """The next `m` entries as one block batched over the loops `frames` (m = product of their trip counts);
+        None when the run cannot be cut that way."""
+        want = tuple(f.n for f in frames)
+        if m > self.left():
+            return None
+        d, e = len(self.sizes), len(want)
+        if self.off == 0 and m == self.count and want == self.sizes:
+            return Block(self.shape, self.dtype, self.expr, "FULL", "wait", nest=tuple(frames))
+        # the run's trailing loops as a unit: `m` entries = all of sizes[j:], starting at a multiple of m
+        j, tail = d, 1
+        while j > 0 and tail < m:
+            j -= 1
+            tail *= self.sizes[j]
+        if tail != m or self.off % m:
+            return None
+        lead = np.unravel_index(self.off // m, self.sizes[:j]) if j else ()
+        sel = {ax: int(i) for ax, i in enumerate(lead)}
+        na = _sl.NEST_AXES
+
+        def cut(a: "np.ndarray") -> Any:
+            b = _pick(a, sel)
+            if not isinstance(b, np.ndarray):
+                return b
+            rest = b.shape[na:]
+            if want == self.sizes[j:]:
+                # same loop structure: the run's axes j.. become axes 0..
+                return b.reshape(b.shape[j:na] + (1,) * j + rest)
+            full = np.broadcast_to(b, (1,) * j + tuple(self.sizes[j:]) + b.shape[d:])
+            return full.reshape(want + (1,) * (na - e) + rest)
+
+        return Block(self.shape, self.dtype, map_coords(self.expr, cut), "FULL", "wait", nest=tuple(frames))
+
+
 class Block:
     """A reserved or waited window of a circular buffer, or a temporary (the value of
     an expression).  Holds the symbolic value of its tiles."""
 
-    __slots__ = ("_shape", "expr", "dtype", "state", "kind", "temporary")
+    __slots__ = ("_shape", "expr", "dtype", "state", "kind", "temporary", "nest", "_acc_frames")
 
     # states: "MW" must-write (reserved), "NAW" copy in flight into it, "FULL" holds a value,
     #         "ACC" accumulating, "OS" out of scope (pushed / popped)
     def __init__(self, shape: Tuple[int, int], dtype: Any, expr: Optional[Expr], state: str, kind: str,
-                 temporary: bool = False):
+                 temporary: bool = False, nest: Tuple[Any, ...] = ()):
         self._shape, self.dtype, self.expr, self.state, self.kind, self.temporary = (
             tuple(shape), dtype, expr, state, kind, temporary)
+        # the batched loops (symloop.Frame) live when the block was made: its tile coordinates vary along their axes
+        self.nest = nest
+        self._acc_frames: Optional[set] = None   # loops nested deeper under which terms were accumulated into it
 
     @property
     def shape(self) -> Tuple[int, int]:
@@ -355,6 +615,12 @@ class Block:
             raise RuntimeError(
                 f"Cannot read from Block: Block has no access ({self.state} state). Current state: {self.state}")
         assert self.expr is not None
+        if self.nest:
+            _sl.require_live(self.nest, "a block")
+        if self._acc_frames is not None:
+            live = [f for f in _sl.nest() if f in self._acc_frames]
+            if live:
+                raise NeedsConcrete(_sl.sites_of(live), "a block is read while a loop is still accumulating into it")
         return self.expr
 
     # -- writing ---------------------------------------------------------
@@ -377,6 +643,18 @@ class Block:
         if not isinstance(src, Block):
             raise TypeError("store() of a sequence of tile tensors is not supported on the GPU: store a block or a block expression")
         v = src.value()
+        cur = _sl.nest()
+        if cur or self.nest:
+            _sl.require_live(self.nest, "a block")
+            extra = tuple(cur[len(self.nest):])
+            if extra:
+                # the store runs in loops nested deeper than the block: it stands for a sequence of stores
+                if not acc:
+                    raise NeedsConcrete(_sl.sites_of(extra), "a block of an outer loop is overwritten inside the loop")
+                if self._acc_frames is not None and any(f in self._acc_frames for f in extra):
+                    raise NeedsConcrete(_sl.sites_of(extra), "two accumulating stores into one block in one loop body")
+                v = _make_rep(v, extra)
+                self._acc_frames = (self._acc_frames or set()) | set(extra)
         if acc:
             if self.state == "MW":  # first accumulating store assigns
                 self.expr = _tag(Acc([v], self._shape))
@@ -405,7 +683,8 @@ class Block:
             shape = self._shape
         else:
             shape = infer_broadcast_shape(self._shape, o._shape)
-        return Block(shape, self.dtype, _tag(Bin(op, a, b, shape)), "FULL", "temp", temporary=True)
+        return Block(shape, self.dtype, _tag(Bin(op, a, b, shape)), "FULL", "temp", temporary=True,
+                     nest=tuple(_sl.nest()) if (self.nest or o.nest) else ())
 
     def __add__(self, o: Any) -> "Block": return self._binary(o, "add")
     def __sub__(self, o: Any) -> "Block": return self._binary(o, "sub")
@@ -424,7 +703,8 @@ class Block:
         return self._binary(o, "pow")
 
     def _unary(self, op: str, params: Tuple[float, ...] = ()) -> "Block":
-        return Block(self._shape, self.dtype, _tag(Un(op, self.value(), params)), "FULL", "temp", temporary=True)
+        return Block(self._shape, self.dtype, _tag(Un(op, self.value(), params)), "FULL", "temp", temporary=True,
+                     nest=self.nest)
 
 
 class _BlockContext:
@@ -449,6 +729,8 @@ class _BlockContext:
         return self._block
 
     def __exit__(self, exc_type: Any, exc: Any, tb: Any) -> None:
+        if exc_type is not None and issubclass(exc_type, (_Abort, _BudgetSpent, NeedsConcrete)):
+            return    # the trace is being abandoned: a half-written block must not travel on
         try:
             self._on_exit()
         except Exception:
@@ -506,10 +788,13 @@ class CircularBuffer:
         self._buffer_factor = buffer_factor
         self._live = _live
         self._name = "cb"
-        self._queue: Deque[Block] = deque()
+        self._queue: Deque[Any] = deque()      # Block, or _Seg (a run pushed by batched loops)
         self._pending_reserved: Optional[Block] = None
         self._pending_waited: Optional[Block] = None
+        self._pending_n = 1                    # queue entries the waited block stands for
         self._strict = False
+        self._pushed_in: set = set()           # live batched loops in whose body a push / a wait has happened
+        self._waited_in: set = set()
 
     @property
     def shape(self) -> Tuple[int, int]:
@@ -542,8 +827,23 @@ class CircularBuffer:
     def can_wait(self) -> bool:
         return len(self._queue) > 0
 
+    def _available(self) -> int:
+        return sum(q.left() if type(q) is _Seg else 1 for q in self._queue)
+
+    @staticmethod
+    def _once_per_body(seen: set, cur: Sequence[Any], what: str) -> set:
+        """A batched loop body may touch one end of a circular buffer once: a second push (wait) would have to be
+        interleaved with the first, iteration by iteration."""
+        again = [f for f in cur if f in seen]
+        if again:
+            raise NeedsConcrete(_sl.sites_of(again), f"a loop body {what} the same circular buffer twice")
+        return {f for f in seen if f in cur} | set(cur)
+
     def reserve(self) -> ReserveContext:
         self._check_live()
+        tr = getattr(_tls, "trace", None)
+        if tr is not None and tr.budget is not None:
+            _spend()
         if self._pending_reserved is not None:
             raise RuntimeError(
                 "Cannot call reserve() again before push(): "
@@ -551,7 +851,7 @@ class CircularBuffer:
                 "You must call push() before calling reserve() again.")
         if not self.can_reserve():
             _worker().block(self.can_reserve, f"{self._name}.reserve()")
-        blk = Block(self._shape, self._dtype(), Zero(self._shape), "MW", "reserve")
+        blk = Block(self._shape, self._dtype(), Zero(self._shape), "MW", "reserve", nest=tuple(_sl.nest()))
         self._pending_reserved = blk
         return ReserveContext(self, blk, self.push)
 
@@ -566,21 +866,51 @@ class CircularBuffer:
                 "(expected copy(..., blk) or blk.store(...))")
         if blk.state == "NAW":
             raise RuntimeError("Cannot push Block: copy into it has not been waited on (expected tx.wait())")
+        cur = _sl.nest()
+        if cur or blk.nest:
+            if tuple(cur) != blk.nest:
+                raise NeedsConcrete(_sl.sites_of(cur) | _sl.sites_of(blk.nest), "a block is pushed outside the loop that reserved it")
+            self._pushed_in = self._once_per_body(self._pushed_in, cur, "pushes into")
+            self._pending_reserved = None
+            assert blk.expr is not None
+            self._queue.append(_Seg(blk.shape, blk.dtype, blk.expr, tuple(f.n for f in cur)))
+            blk.state = "OS"
+            return
         self._pending_reserved = None
         self._queue.append(Block(blk.shape, blk.dtype, blk.expr, "FULL", "wait"))
         blk.state = "OS"
 
     def wait(self) -> WaitContext:
         self._check_live()
+        tr = getattr(_tls, "trace", None)
+        if tr is not None and tr.budget is not None:
+            _spend()
         if self._pending_waited is not None:
             raise RuntimeError(
                 "Cannot call wait() again before pop(): "
                 "CircularBuffer already has a pending waited block. "
                 "You must call pop() before calling wait() again.")
+        cur = _sl.nest()
+        if cur:
+            # inside batched loops: one wait per iteration = the next m entries, which must be one pushed run
+            self._waited_in = self._once_per_body(self._waited_in, cur, "waits on")
+            m = 1
+            for f in cur:
+                m *= f.n
+            if self._available() < m:
+                _worker().block(lambda: self._available() >= m, f"{self._name}.wait()")
+            head = self._queue[0]
+            blk = head.take(m, cur) if type(head) is _Seg else None
+            if blk is None:
+                raise NeedsConcrete({cur[-1].site}, "the blocks a loop waits for were not pushed by a loop of the same shape")
+            self._pending_waited, self._pending_n = blk, m
+            return WaitContext(self, blk, self.pop)
         if not self._queue:
             _worker().block(self.can_wait, f"{self._name}.wait()")
         blk = self._queue[0]
-        self._pending_waited = blk
+        if type(blk) is _Seg:
+            blk = blk.element()
+        self._pending_waited, self._pending_n = blk, 1
         return WaitContext(self, blk, self.pop)
 
     def pop(self) -> None:
@@ -589,7 +919,13 @@ class CircularBuffer:
         if blk is None:
             raise RuntimeError("pop() without a pending wait()")
         self._pending_waited = None
-        self._queue.popleft()
+        head = self._queue[0]
+        if type(head) is _Seg:
+            head.off += self._pending_n
+            if head.off >= head.count:
+                self._queue.popleft()
+        else:
+            self._queue.popleft()
         blk.state = "OS"
 
     def validate_no_pending_blocks(self) -> None:
@@ -599,7 +935,7 @@ class CircularBuffer:
         if self._pending_waited is not None:
             errs.append("Pending waited block. Did you forget to call pop()?")
         if self._queue:
-            errs.append(f"{len(self._queue)} pushed block(s) were never consumed")
+            errs.append(f"{self._available()} pushed block(s) were never consumed")
         if errs:
             raise RuntimeError(f"CircularBuffer {self._name} has incomplete blocks at end of execution:\n"
                                + "\n".join(f"  - {e}" for e in errs))
@@ -819,9 +1155,13 @@ class CopyTransaction:
                     f"Block shape {s.shape} tiles (={tuple(a * b for a, b in zip(s.shape, TILE_SHAPE))} elements)")
             s.value()
         elif isinstance(s, Block) and isinstance(d, Pipe):
+            if _sl.nest():
+                raise NeedsConcrete(_sl.live_sites(), "a pipe is used inside the loop")
             self._mode = "b2p"
             s.value()
         elif isinstance(s, Pipe) and isinstance(d, Block):
+            if _sl.nest():
+                raise NeedsConcrete(_sl.live_sites(), "a pipe is used inside the loop")
             self._mode = "p2b"
             self._check_dst_block(d)
             d.state = "NAW"
@@ -856,13 +1196,24 @@ class CopyTransaction:
         if self._mode == "t2b":
             base, r0, r1, c0, c1 = s._origin if s._origin is not None else (s, 0, s.tile_shape()[0], 0, s.tile_shape()[1])
             tr.note_input(base)
+            cur = _sl.nest()
+            if cur or d.nest:
+                if tuple(cur) != d.nest:
+                    raise NeedsConcrete(_sl.sites_of(cur) | _sl.sites_of(d.nest), "a copy fills a block of another loop")
+                r0, r1, c0, c1 = (_sl.as_coord(x) for x in (r0, r1, c0, c1))
             d.expr = Leaf(base, r0, r1, c0, c1)
             d.expr.shape = d.shape
             d.expr.line = self._line
             d.state = "FULL"
         elif self._mode == "b2t":
             base, r0, r1, c0, c1 = d._origin if d._origin is not None else (d, 0, d.tile_shape()[0], 0, d.tile_shape()[1])
-            tr.writes.append(Write(base, r0, r1, c0, c1, s.value(), current_core(), self._line))
+            v = s.value()
+            cur = _sl.nest()
+            if cur:
+                r0, r1, c0, c1 = (_sl.as_coord(x) for x in (r0, r1, c0, c1))
+                tr.writes.append(BatchedWrite(base, r0, r1, c0, c1, v, current_core(), self._line, tuple(f.n for f in cur)))
+            else:
+                tr.writes.append(Write(base, r0, r1, c0, c1, v, current_core(), self._line))
         elif self._mode == "b2p":
             tr.pipe_send(d, s.value(), len(_dst_cores(d.dst_core_range, current_grid())))
         else:  # p2b
@@ -891,6 +1242,20 @@ class Trace:
         self.writes: List[Write] = []
         self.inputs: List[_ttnn.Tensor] = []
         self._pipes: Dict[Pipe, Deque[List[Any]]] = {}
+        self.batched_loops = 0          # batched loop instances that ran (symloop.py)
+        self.budget: Optional[int] = None    # circular-buffer operations each thread may make (verification runs only)
+
+    def finish(self) -> None:
+        """One Write per iteration in place of every BatchedWrite, in program order; batched matmul writes stay
+        as they are (the recogniser checks all their iterations at once)."""
+        if any(isinstance(w, BatchedWrite) for w in self.writes):
+            out: List[Write] = []
+            for w in self.writes:
+                if isinstance(w, BatchedWrite) and not w.plain_matmul():
+                    out.extend(w.expand())
+                else:
+                    out.append(w)
+            self.writes = out
 
     def note_input(self, t: "_ttnn.Tensor") -> None:
         for x in self.inputs:
@@ -950,16 +1315,128 @@ def _rebind(func: types.FunctionType, per_core: Dict[int, Any]) -> types.Functio
     return types.FunctionType(func.__code__, func.__globals__, func.__name__, func.__defaults__, tuple(cells))
 
 
+BATCH_LOOPS = os.environ.get("TTLB200_BATCH_LOOPS", "1") != "0"
+VERIFY_BATCHED = os.environ.get("TTLB200_TRACE_VERIFY", "1") != "0"
+VERIFY_BUDGET = 6000      # circular-buffer operations traced iteration by iteration per sampled core
+_NOBATCH: Dict[Any, set] = {}      # per program (code objects of its threads): loop sites that must stay concrete
+
+
+def _spend() -> None:
+    w = _tls.worker
+    w.budget -= 1
+    if w.budget < 0:
+        raise _BudgetSpent()
+
+
 def run_program(threads: List[Tuple[str, types.FunctionType]], grid: Tuple[int, ...], strict_cb: bool = False) -> Trace:
     """Execute the thread functions of one kernel call on every core and return the trace.
 
-    `threads` is [(kind, function)] with kind "compute" or "dm".
+    `threads` is [(kind, function)] with kind "compute" or "dm".  Counted loops that pass the checks of
+    symloop.py run once for all their iterations; when a loop body turns out to need its iterations one by one
+    the trace starts again with that loop run conventionally.  A batched trace is checked against a conventional
+    trace of the first writes of a few sampled cores before it is used.
     """
+    batching = BATCH_LOOPS and not strict_cb
+    if not batching:
+        return _run_once(threads, grid, strict_cb, False, frozenset())
+    key = tuple(fn.__code__ for _, fn in threads)
+    nobatch = _NOBATCH.setdefault(key, set())
+    fast = [(kind, _sl.transform(fn)) for kind, fn in threads]
+    if all(a[1] is b[1] for a, b in zip(fast, threads)):
+        return _run_once(threads, grid, strict_cb, False, frozenset())
+    for _ in range(64):
+        try:
+            trace = _run_once(fast, grid, strict_cb, True, frozenset(nobatch))
+        except NeedsConcrete as e:
+            if not e.sites or e.sites <= nobatch:
+                break         # no loop left to blame: trace conventionally
+            nobatch |= e.sites
+            continue
+        if trace.batched_loops and VERIFY_BATCHED and not _verify(threads, grid, trace):
+            import warnings
+
+            warnings.warn("ttl_b200: the batched trace of a tile program disagrees with its iteration-by-iteration trace "
+                          "on a sampled core; tracing every iteration instead (TTLB200_BATCH_LOOPS=0 skips the attempt)",
+                          RuntimeWarning, stacklevel=2)
+            break
+        return trace
+    return _run_once(threads, grid, strict_cb, False, frozenset())
+
+
+def same_expr(a: Expr, b: Expr) -> bool:
+    """Structural equality of two expressions; runs of accumulated terms are compared term by term."""
+    if isinstance(a, Acc) or isinstance(b, Acc):
+        ta = _flat_terms(a)
+        tb = _flat_terms(b)
+        return len(ta) == len(tb) and all(same_expr(x, y) for x, y in zip(ta, tb))
+    if type(a) is not type(b) or tuple(a.shape) != tuple(b.shape):
+        return False
+    if isinstance(a, Leaf):
+        return (a.tensor is b.tensor and a.first == b.first
+                and all(int(np.asarray(x).reshape(-1)[0]) == int(np.asarray(y).reshape(-1)[0])
+                        for x, y in zip((a.r0, a.r1, a.c0, a.c1), (b.r0, b.r1, b.c0, b.c1))))
+    if isinstance(a, Un):
+        return a.op == b.op and a.params == b.params and same_expr(a.x, b.x)
+    if isinstance(a, Bin):
+        return a.op == b.op and same_expr(a.a, b.a) and same_expr(a.b, b.b)
+    if isinstance(a, Red):
+        return (a.op == b.op and a.dims == b.dims and same_expr(a.x, b.x) and (a.scaler is None) == (b.scaler is None)
+                and (a.scaler is None or same_expr(a.scaler, b.scaler)))
+    if isinstance(a, Rep):
+        ta, tb = a.terms(), b.terms()
+        return len(ta) == len(tb) and all(same_expr(x, y) for x, y in zip(ta, tb))
+    return isinstance(a, Zero)
+
+
+def _flat_terms(e: Expr) -> List[Expr]:
+    out: List[Expr] = []
+    for t in (e.terms if isinstance(e, Acc) else [e]):
+        if isinstance(t, Rep):
+            out.extend(t.terms())
+        else:
+            out.append(t)
+    return out
+
+
+def _verify(threads: List[Tuple[str, types.FunctionType]], grid: Tuple[int, ...], trace: Trace) -> bool:
+    """Trace the first, the middle and the last core that wrote anything iteration by iteration (each thread up
+    to VERIFY_BUDGET circular-buffer operations) and compare the writes they get that far with the batched trace's."""
+    cores = sorted({w.core for w in trace.writes})
+    if not cores:
+        return True
+    for core in sorted({cores[0], cores[len(cores) // 2], cores[-1]}):
+        probe = Trace(grid)
+        probe.budget = VERIFY_BUDGET
+        try:
+            _run_once(threads, grid, False, False, frozenset(), only_core=core, trace=probe)
+        except BaseException:   # noqa: BLE001 - a probe that stops early (budget, starvation) still gives a prefix
+            pass
+        want = probe.writes
+        got: List[Write] = []
+        for w in trace.writes:
+            if w.core != core:
+                continue
+            if len(got) >= len(want):
+                break
+            got.extend(w.expand(len(want) - len(got)) if isinstance(w, BatchedWrite) else [w])
+        if len(want) > len(got) or not want:
+            return False
+        for a, b in zip(want, got):
+            if (a.tensor is not b.tensor or (a.r0, a.r1, a.c0, a.c1) != (b.r0, b.r1, b.c0, b.c1)
+                    or not same_expr(a.expr, b.expr)):
+                return False
+    return True
+
+
+def _run_once(threads: List[Tuple[str, types.FunctionType]], grid: Tuple[int, ...], strict_cb: bool, batching: bool,
+              nobatch: Any, only_core: Optional[int] = None, trace: Optional[Trace] = None) -> Trace:
     total = 1
     for g in grid:
         total *= g
-    trace = Trace(grid)
+    if trace is None:
+        trace = Trace(grid)
     sched = Scheduler(grid, trace)
+    sched.batching, sched.nobatch = batching, nobatch
     all_cbs: List[Tuple[int, CircularBuffer]] = []
     # closure values shared by the thread functions
     shared: Dict[int, Any] = {}
@@ -974,7 +1451,7 @@ def run_program(threads: List[Tuple[str, types.FunctionType]], grid: Tuple[int, 
         sum(1 for x in v if isinstance(x, CircularBuffer)) for v in shared.values() if isinstance(v, (list, tuple)))
     if n_cbs > MAX_CBS:
         raise RuntimeError(f"A kernel may use at most {MAX_CBS} circular buffers, got {n_cbs}")
-    for core in range(total):
+    for core in range(total) if only_core is None else [only_core]:
         per_core: Dict[int, Any] = {}
 
         def fresh_cb(v: CircularBuffer) -> CircularBuffer:
@@ -1028,4 +1505,5 @@ def run_program(threads: List[Tuple[str, types.FunctionType]], grid: Tuple[int, 
             errs.append(f"core{core}.{cb._name}: {e}")
     if errs:
         raise RuntimeError("Kernel execution completed with incomplete CircularBuffer operations:\n" + "\n".join(errs))
+    trace.finish()
     return trace

@@ -15,6 +15,11 @@ from typing import Any, List, Optional, Tuple, Union
 
 import torch
 
+from .symloop import NeedsConcrete as _NeedsConcrete
+from .symloop import SymInt as _SymInt
+from .symloop import const_extent as _const_extent
+from .symloop import live_sites as _live_sites
+
 TILE_SIZE: int = 32
 TILE_SHAPE: Tuple[int, int] = (32, 32)
 TILE_LAYOUT = "TILE"
@@ -130,6 +135,17 @@ def _tile_dim(n: int) -> int:
     return 1 if n == 1 else n // TILE_SIZE
 
 
+def _extent(sl: slice, what: str) -> int:
+    return _const_extent(sl.start, sl.stop, what)
+
+
+def _bounds(x: Any) -> Tuple[int, int]:
+    """(smallest, largest) value of a tile index."""
+    if isinstance(x, _SymInt):
+        return int(x.v.min()), int(x.v.max())
+    return int(x), int(x)
+
+
 class Tensor:
     """Row-major 2-D tensor in device memory.
 
@@ -141,13 +157,27 @@ class Tensor:
     def __init__(self, tensor: torch.Tensor, *, _origin: Optional[Tuple["Tensor", int, int, int, int]] = None,
                  _packed: Optional[torch.Tensor] = None, _logical_shape: Optional[Shape] = None,
                  _packed_bits: int = 8) -> None:
-        self._tensor = tensor
+        self._t = tensor                # None for a tile view whose torch view has not been asked for yet
         self._origin = _origin          # (base tensor, r0, r1, c0, c1) in tiles
         self._packed = _packed          # block-float payload (uint8: 1088 bytes per bfloat8_b tile, 576 per bfloat4_b tile)
         self._packed_bits = _packed_bits
         self._logical_shape = _logical_shape
 
     # -- basic properties ------------------------------------------------
+    @property
+    def _tensor(self) -> torch.Tensor:
+        """The torch tensor; for a tile view made by indexing, the torch view is created on first use (a tile
+        program indexes a tensor once per copy and only ever hands the view to ttl.copy)."""
+        t = self._t
+        if t is None:
+            base, r0, r1, c0, c1 = self._origin  # type: ignore[misc]
+            t = self._t = base._tensor[int(r0) * TILE_SIZE:int(r1) * TILE_SIZE, int(c0) * TILE_SIZE:int(c1) * TILE_SIZE]
+        return t
+
+    @_tensor.setter
+    def _tensor(self, value: torch.Tensor) -> None:
+        self._t = value
+
     @property
     def shape(self) -> Shape:
         if self._logical_shape is not None:
@@ -158,7 +188,9 @@ class Tensor:
     def dtype(self) -> Any:
         if self._packed is not None:
             return bfloat8_b if self._packed_bits == 8 else bfloat4_b
-        return self._tensor.dtype
+        if self._t is None:
+            return self._origin[0].dtype  # type: ignore[index]
+        return self._t.dtype
 
     def __repr__(self) -> str:
         return f"Tensor(shape={self.shape}, dtype={self.dtype})"
@@ -182,8 +214,8 @@ class Tensor:
 
     # -- tile indexing ---------------------------------------------------
     @staticmethod
-    def _norm(index: Union[int, slice], name: str) -> slice:
-        if isinstance(index, int):
+    def _norm(index: Any, name: str) -> slice:
+        if isinstance(index, (int, _SymInt)):
             return slice(index, index + 1)
         if index.start is None:
             raise ValueError(
@@ -210,9 +242,28 @@ class Tensor:
         cs = self._norm(key[1], "col")
         base, br, _, bc, _ = self._origin if self._origin is not None else (self, 0, 0, 0, 0)
         origin = (base, br + rs.start, br + rs.stop, bc + cs.start, bc + cs.stop)
+        symbolic = any(isinstance(x, _SymInt) for x in (rs.start, rs.stop, cs.start, cs.stop))
         if self._packed is not None:
-            return Tensor(self._tensor, _origin=origin, _packed=self._packed, _packed_bits=self._packed_bits,
-                          _logical_shape=((rs.stop - rs.start) * TILE_SIZE, (cs.stop - cs.start) * TILE_SIZE))
+            return Tensor(self._t, _origin=origin, _packed=self._packed, _packed_bits=self._packed_bits,
+                          _logical_shape=(_extent(rs, "a tile view") * TILE_SIZE, _extent(cs, "a tile view") * TILE_SIZE))
+        if self._origin is None:
+            # a window of a whole tensor: only its shape is worked out now (what slicing would give)
+            shape = []
+            for sl, n in ((rs, self.shape[0]), (cs, self.shape[1])):
+                if symbolic:
+                    lo, hi = _bounds(sl.start), _bounds(sl.stop)
+                    if lo[0] < 0 or hi[1] * TILE_SIZE > max(n, TILE_SIZE):
+                        raise _NeedsConcrete(_live_sites(), "a tile index leaves the tensor")
+                    shape.append(1 if n == 1 else _extent(sl, "a tile view") * TILE_SIZE)
+                elif sl.start < 0 or sl.stop < 0:
+                    shape = []
+                    break
+                else:
+                    shape.append(max(0, min(n, sl.stop * TILE_SIZE) - min(n, sl.start * TILE_SIZE)))
+            if shape:
+                return Tensor(None, _origin=origin, _logical_shape=tuple(shape))  # type: ignore[arg-type]
+        if symbolic:
+            raise _NeedsConcrete(_live_sites(), "a view of a tile view is indexed with the loop variable")
         view = self._tensor[rs.start * TILE_SIZE:rs.stop * TILE_SIZE, cs.start * TILE_SIZE:cs.stop * TILE_SIZE]
         return Tensor(view, _origin=origin)
 
@@ -221,7 +272,7 @@ class Tensor:
             rk, ck = key
             if isinstance(rk, int) and isinstance(ck, int) and not self._is_tile_indexable():
                 return Tensor(self._tensor[key])
-            if isinstance(rk, (slice, int)) and isinstance(ck, (slice, int)):
+            if isinstance(rk, (slice, int, _SymInt)) and isinstance(ck, (slice, int, _SymInt)):
                 return self._tile_view(key)
         return Tensor(self._tensor[key])
 
