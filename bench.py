@@ -527,8 +527,12 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
                     shard.SymmetricOutput((world, m, c0 * 32), torch.bfloat16, dev)
             else:
                 so = shard.SymmetricOutput((B * H, S, D), torch.bfloat16, dev)
-            if mode == "fused" and (wl == "attention" or not so.has_multicast):
+            if mode == "fused" and not so.has_multicast:
+                mode = "peers"
+            if mode in ("fused", "peers") and wl == "attention":
                 mode = "multicast"
+            if mode == "multicast" and not so.has_multicast:
+                mode = "p2p"
             if mode == "multicast" and so.has_multicast:
                 # compute into the local copy, then one kernel re-sends the shard through the switch
                 # (multimem.st, coalesced): 1x outgoing traffic instead of (world-1)x
@@ -581,26 +585,33 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
                     return so.barrier()
                 gather = (f"local compute in {rounds} round(s); each round's part of the shard is re-sent once through the "
                           "NVSwitch (multimem.st kernel) under the next round's compute; barrier")
-            elif mode == "fused" and so.has_multicast:
-                # publication fused into the GEMM epilogue: every tile is stored once with multimem.st and
-                # the NVSwitch delivers it to all ranks; one launch per rank, then a cross-rank barrier
+            elif mode in ("fused", "peers"):
+                # publication fused into the GEMM epilogue: every tile is stored while the tensor cores work on the
+                # next one - once with multimem.st (the NVSwitch delivers it to all ranks), or with plain stores into
+                # every rank's copy of the buffer; one launch per rank, then a cross-rank barrier
                 if wl == "matmul_bf16_8192":
                     ml = n // world
                     a_contig = a[rank * ml:(rank + 1) * ml].contiguous().to(dev)
                     mine_view = so.buf[rank * ml:(rank + 1) * ml]
+                    where = ({"multicast_ptr": so.multicast_ptr_of(mine_view)} if mode == "fused" else
+                             {"peer_ptrs": so.peer_ptrs_of(mine_view)})
 
                     def step(x):
-                        ops.matmul(T(a_contig), T(x[1]), out=T(mine_view), multicast_ptr=so.multicast_ptr_of(mine_view))
+                        ops.matmul(T(a_contig), T(x[1]), out=T(mine_view), **where)
                         return so.barrier()
                 else:
                     nl = c0 * 32
                     mine_view = so.buf[:, rank * nl:(rank + 1) * nl]
+                    where = ({"multicast_ptr": so.multicast_ptr_of(mine_view)} if mode == "fused" else
+                             {"peer_ptrs": so.peer_ptrs_of(mine_view)})
 
                     def step(xs):
-                        ops.launch_gemm(ctx, T(xs[0]), W, T(mine_view), (0, m, 0, nl), capi.current_stream(),
-                                        so.multicast_ptr_of(mine_view))
+                        ops.launch_gemm(ctx, T(xs[0]), W, T(mine_view), (0, m, 0, nl), capi.current_stream(), **where)
                         return so.barrier()
-                gather = "multimem.st in the GEMM epilogue (NVSwitch multicast, row-contiguous stores), then a cross-rank barrier"
+                gather = ("multimem.st in the GEMM epilogue (NVSwitch multicast, row-contiguous stores), then a cross-rank barrier"
+                          if mode == "fused" else
+                          "plain stores from the GEMM epilogue into every rank's copy of the output (peer memory, "
+                          "row-contiguous), then a cross-rank barrier")
             else:
                 mode = "p2p"
                 if wl == "matmul_bf16_8192":
@@ -629,6 +640,17 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
     ms_step = timed(env, lambda: step(dev_in), steps, args.warmup) if world > 1 else ms_compute
     ms_single = timed(env, lambda: full_compute(dev_in), min(steps, 10), args.warmup) if full_compute is not None else ms_compute
     ctx.check_status(capi.current_stream())
+    gathered_same = None
+    if world > 1:
+        # every rank must now hold the same full output, bit for bit: compare a checksum of it across the ranks
+        full = step(dev_in)
+        env.barrier()
+        chk = full.reshape(-1).view(torch.int16).to(torch.int64)
+        chk = torch.stack([chk.sum(), (chk * (torch.arange(chk.numel(), device=dev) % 8191 + 1)).sum()])
+        allc = [torch.empty_like(chk) for _ in range(world)]
+        env.dist.all_gather(allc, chk)
+        gathered_same = all(torch.equal(allc[0], c) for c in allc)
+        del full, chk, allc
 
     result_holder = {}
 
@@ -665,7 +687,7 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
         recv = out_bytes * (world - 1) / world
         floor = recv / (NVLINK_MEASURED_GBS * 1e9) * 1e3
         rec["gather"].update({
-            "rounds": rounds_used, "bytes_received_per_gpu": recv, "gather_floor_ms": floor,
+            "rounds": rounds_used, "every_rank_holds_the_same_output": gathered_same, "bytes_received_per_gpu": recv, "gather_floor_ms": floor,
             "gather_floor_note": (f"every GPU must receive (N-1)/N of the output; {NVLINK_MEASURED_GBS:.0f} GB/s per direction "
                                   f"measured peer-copy rate ({NVLINK_NOMINAL_GBS:.0f} nominal)"),
             "step_floor_ms": max(floor, ms_compute), "frac_of_step_floor": max(floor, ms_compute) / ms_step})
@@ -683,7 +705,7 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
 
 def run_sharded(args, env: "Env") -> None:
     """`--workload matmul_bf16_8192 | matmul_bfp8w | matmul_bfp4w | attention`: one JSON line for that workload."""
-    modes = ["p2p", "multicast", "fused", "nccl"] if args.gather == "all" else [args.gather]
+    modes = ["p2p", "multicast", "fused", "peers", "nccl"] if args.gather == "all" else [args.gather]
     for mode in modes:
         rec = measure_sharded(args, args.workload, env, mode)
         if env.rank == 0:
@@ -1103,7 +1125,7 @@ def main():
                     help="multicast gather: rounds the local shard is computed and re-sent in (0: 4 rounds on 4 or more GPUs, else 1)")
     ap.add_argument("--bfp8-mode", type=int, default=None, choices=[0, 1, 2],
                     help="bfp8 weights: 0 unpack kernel + GEMM, 1 unpack inside the GEMM mainloop for large outputs, 2 always inside")
-    ap.add_argument("--gather", default="auto", choices=["auto", "p2p", "multicast", "fused", "nccl", "all"],
+    ap.add_argument("--gather", default="auto", choices=["auto", "p2p", "multicast", "fused", "peers", "nccl", "all"],
                     help="sharded workloads: how output shards reach the other ranks (p2p: peer-to-peer copies overlapped with "
                          "compute; multicast: multimem.st re-send kernel per round under the next round's compute; fused: "
                          "multimem.st from the GEMM epilogue; nccl: all-gather; all: one line per mode)")

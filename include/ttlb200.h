@@ -426,10 +426,21 @@ TTLB_EXPORT int ttlb_attention(ttlb_ctx *ctx, const ttlb_attn_desc *desc, void *
  * ------------------------------------------------------------------------ */
 /* The matmuls with the publication fused into the epilogue: desc->c is the multicast address of
  * the output region (same pitch); every output tile is stored once with multimem.st while the tensor
- * cores work on the next tile, and arrives in the output buffer of every GPU.  n must be a multiple
+ * cores work on the next tile, and arrives in the output buffer of every GPU.  The epilogue passes the tile
+ * through shared memory so that each store instruction of a warp covers two whole 256-byte row segments
+ * (16-byte stores scattered over 32 rows reach a small fraction of the NVLink rate).  n must be a multiple
  * of 32.  Nothing is written through the ordinary (unicast) mapping. */
 TTLB_EXPORT int ttlb_matmul_bf16_multicast(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, void *stream);
 TTLB_EXPORT int ttlb_matmul_bfp8w_multicast(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, void *stream);
+/* The same publication without the switch's replication: `peers[0..n_peers)` (1..8) are the addresses of the
+ * output region in every GPU's copy of the buffer - peer-mapped memory of the other GPUs and this GPU's own copy,
+ * all with the pitch desc->ldc; desc->c is ignored.  The epilogue stores every tile to each of them with ordinary
+ * 16-byte stores, row-contiguous (256 bytes per row segment).  Peer memory is only ever written, never read.
+ * No counterpart in the reference (it is single-chip). */
+TTLB_EXPORT int ttlb_matmul_bf16_peers(ttlb_ctx *ctx, const ttlb_gemm_desc *desc, void *const *peers, int n_peers,
+                                       void *stream);
+TTLB_EXPORT int ttlb_matmul_bfp8w_peers(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, void *const *peers, int n_peers,
+                                        void *stream);
 TTLB_EXPORT int ttlb_multimem_bcast(ttlb_ctx *ctx, const void *src, int64_t src_ld_bytes, void *mc_dst,
                                     int64_t dst_ld_bytes, int64_t rows, int64_t row_bytes, void *stream);
 

@@ -226,3 +226,35 @@ def test_config3_as_the_unchanged_tile_program_at_full_size(backend):
     got = ttnn.to_torch(out)
     for r0 in (0, 4064, 8128):
         assert rel_err(got[r0:r0 + 64], tile_oracle.matmul_tiles(a[r0:r0 + 64], b, "f32")) <= TOL, f"rows {r0}..{r0 + 63}"
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 288, 136), (1024, 2048, 512)])
+def test_c_abi_matmul_published_to_several_buffers(m, n, k):
+    """ttlb_matmul_bf16_peers: the epilogue that passes every tile through shared memory and stores it, whole
+    256-byte row segments at a time, into the output region of several buffers (on a box with several GPUs: every
+    GPU's copy of a shared output).  Here all buffers live on this GPU: each must hold exactly what the plain
+    matmul gives, and nothing may be written around the output regions."""
+    from ttl_b200 import capi
+    g = torch.Generator().manual_seed(m + n + k)
+    a = (torch.randn(m, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    b = torch.randn(k, n, generator=g).to(torch.bfloat16)
+    A, B = a.cuda(), b.cuda()
+    ctx = capi.context()
+    ctx.set_gemm_variant(0)
+    try:
+        plain = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        d = capi.GemmDesc()
+        d.a, d.lda, d.b, d.ldb, d.c, d.ldc, d.m, d.n, d.k = A.data_ptr(), k, B.data_ptr(), n, plain.data_ptr(), n, m, n, k
+        ctx.matmul_bf16(d, capi.current_stream())
+        bufs = [torch.full((m + 64, n + 64), 3.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+        d.c, d.ldc = None, n + 64
+        ctx.matmul_bf16_peers(d, [x.data_ptr() + (32 * (n + 64) + 32) * 2 for x in bufs], capi.current_stream())
+        ctx.check_status(capi.current_stream())
+    finally:
+        ctx.set_gemm_variant(1)
+    assert rel_err(plain.cpu(), tile_oracle.matmul_tiles(a, b, "f32")) <= TOL
+    for x in bufs:
+        got = x.cpu()
+        assert torch.equal(got[32:32 + m, 32:32 + n], plain.cpu()), "published tile differs from the plain matmul"
+        got[32:32 + m, 32:32 + n] = 3.0
+        assert (got == 3.0).all(), "the publishing epilogue wrote outside the output region"

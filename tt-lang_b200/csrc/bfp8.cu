@@ -296,6 +296,21 @@ extern "C" int ttlb_matmul_bfp8w_multicast(ttlb_ctx *ctx, const ttlb_gemm_bfp8_d
   return matmul_bfp8w_impl(ctx, d, true, stream);
 }
 
+int ttlb_set_pub_peers(ttlb_ctx *ctx, void *const *peers, int n_peers);
+
+extern "C" int ttlb_matmul_bfp8w_peers(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, void *const *peers, int n_peers,
+                                       void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul_bfp8w: null descriptor");
+  int rc = ttlb_set_pub_peers(ctx, peers, n_peers);
+  if (rc) return rc;
+  ttlb_gemm_bfp8_desc own = *d;
+  own.c = peers[0];
+  rc = matmul_bfp8w_impl(ctx, &own, true, stream);
+  ctx->pub_n_peers = 0;
+  return rc;
+}
+
 // Context-free launch of the unpack kernel (used by the allocation-free entry point).
 int ttlb_bfp8_unpack_launch_raw(const uint8_t *tiles, int64_t tile_cols_total, int64_t tile_col0, int64_t tile_rows,
                                 int64_t tile_cols, void *out, int64_t ld, int sm_count, cudaStream_t s) {

@@ -33,6 +33,9 @@ struct ttlb_ctx {
   int gemm_variant = 1;  // 0: always one-CTA 128x256 tiles; 1: two-CTA (cta_group::2) 256x256 tiles for large outputs
   bool gemm_fused_attr_set = false;
   int gemm_act = 0;  // activation of the GEMM being launched (set by ttlb_matmul_bf16_epilogue around its launch)
+  // output region in each GPU's copy of a shared buffer, for the GEMM being launched (ttlb_matmul_*_peers)
+  void *pub_peers[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int pub_n_peers = 0;
   int bfp8_mode = 0;  // 0: unpack kernel + bf16 GEMM; 1: unpack inside the GEMM mainloop for large outputs; 2: always inside
   bool attn_attr_set = false;
   long long wait_limit_cycles = 4000000000LL;  // ~2 s at 1.9 GHz

@@ -52,6 +52,12 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int GROUP_M = 16;
 constexpr int THREADS = 192;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+// Publishing epilogue (the output goes to every GPU of a group): each epilogue warp stages 32 rows x 128 columns
+// (256 bytes per row) so that a store instruction covers whole 256-byte row segments.
+constexpr int PUB_COLS = 128;
+constexpr int PUB_WARP_BYTES = 32 * PUB_COLS * 2;  // 8 KB
+constexpr int SMEM_BYTES_PUB = SMEM_BYTES + 4 * PUB_WARP_BYTES;
+constexpr int MAX_PEERS = 8;
 
 struct GemmParams {
   __nv_bfloat16 *c;
@@ -60,7 +66,12 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int *status;
   long long wait_limit;
-  int multicast;  // 1: `c` is an NVLink multicast address; the epilogue stores with multimem.st
+  // 0: plain stores to `c`.  1: `c` is an NVLink multicast address, stored with multimem.st (the switch
+  // replicates every store to all GPUs of the group).  2: the same tile is stored to `peer_c[0..n_peers)`, the
+  // output region in every GPU's copy of the buffer (peer-mapped memory, this GPU's own copy included).
+  int multicast;
+  __nv_bfloat16 *peer_c[MAX_PEERS] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int n_peers = 0;
   const __nv_bfloat16 *bias = nullptr;  // optional [m, n] matrix added to the product before rounding
   long long ldbias = 0;                 // 0: the bias is one row of n values, added to every output row
   int act = 0;                          // TTLB_ACT_*: applied to product + bias before the rounding
@@ -85,7 +96,8 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
 
 // ACT: the instantiation with the activation epilogue (its transcendental code costs registers; the plain
 // instantiation is the kernel the matmul configurations are measured with)
-template <bool ACT>
+// PUB: the instantiation whose epilogue publishes the tile to several GPUs through a shared-memory stage
+template <bool ACT, bool PUB = false>
 __global__ void __launch_bounds__(THREADS, 1)
 ttlb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
@@ -198,11 +210,63 @@ ttlb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_limit)) {
+      // the outcome of the wait is made the same for the whole warp: what follows is warp-collective
+      if (!__all_sync(0xffffffffu, mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_limit))) {
         fail = 3;
         break;
       }
       tc_fence_after();
+      if constexpr (PUB) {
+        // tcgen05.ld hands every thread one row; the rows go through a swizzled stage so that each store
+        // instruction of the warp writes two whole 256-byte row segments (16 lanes x 16 bytes each) - through
+        // NVLink, 16-byte stores scattered over 32 rows reach a small fraction of the link rate
+        uint8_t *stage = gen + 256 + (warp - 2) * PUB_WARP_BYTES;
+#pragma unroll 1
+        for (int half = 0; half < BN / PUB_COLS; ++half) {
+#pragma unroll 1
+          for (int cc = 0; cc < PUB_COLS / 32; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + half * PUB_COLS + cc * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              const int unit = cc * 4 + v;  // 16-byte unit within the 256-byte row
+              *reinterpret_cast<uint4 *>(stage + lane * (PUB_COLS * 2) + ((unit ^ (lane & 7)) << 4)) = o;
+            }
+          }
+          if (half == BN / PUB_COLS - 1) {
+            // every accumulator column has been read: the issuer may start the next tile into this buffer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+          } else {
+            __syncwarp();
+          }
+          const int unit = lane & 15;
+          const long long gcol = (long long)tn * BN + half * PUB_COLS + unit * 8;
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int rl = 2 * i + (lane >> 4);
+            const uint4 o = *reinterpret_cast<const uint4 *>(stage + rl * (PUB_COLS * 2) + ((unit ^ (rl & 7)) << 4));
+            const long long grow = (long long)tm * BM + q * 32 + rl;
+            if (grow < p.m && gcol < p.n) {
+              const long long off = grow * p.ldc + gcol;
+              if (p.multicast == 1) {
+                st_multimem_16(p.c + off, o);
+              } else {
+                for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(p.peer_c[d] + off) = o;
+              }
+            }
+          }
+          __syncwarp();
+        }
+        continue;
+      }
       const int row = tm * BM + q * 32 + lane;
       __nv_bfloat16 *crow = p.c + (long long)row * p.ldc + (long long)tn * BN;
       const __nv_bfloat16 *brow = p.bias ? p.bias + (long long)row * p.ldbias + (long long)tn * BN : nullptr;
@@ -223,10 +287,7 @@ ttlb_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
               o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
               o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
               o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-              if (p.multicast)
-                st_multimem_16(crow + c * 32 + v * 8, o);
-              else
-                *reinterpret_cast<uint4 *>(crow + c * 32 + v * 8) = o;
+              *reinterpret_cast<uint4 *>(crow + c * 32 + v * 8) = o;
             }
           } else {
 #pragma unroll
@@ -339,6 +400,8 @@ int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const 
                                               SMEM_BYTES));
     TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bf16_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               SMEM_BYTES));
+    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bf16_kernel<false, true>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES_PUB));
     ctx->gemm_attr_set = true;
   }
 
@@ -353,12 +416,22 @@ int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const 
   p.status = ctx->d_status;
   p.wait_limit = ctx->wait_limit_cycles;
   p.multicast = multicast ? 1 : 0;
+  if (multicast && ctx->pub_n_peers > 0) {
+    // the output region in every GPU's copy of the buffer, given by the caller of ttlb_matmul_*_peers
+    p.multicast = 2;
+    p.n_peers = ctx->pub_n_peers;
+    for (int i = 0; i < ctx->pub_n_peers; ++i) p.peer_c[i] = reinterpret_cast<__nv_bfloat16 *>(ctx->pub_peers[i]);
+  }
+  if (multicast && (bias || ctx->gemm_act))
+    return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "matmul: bias / activation with a published output");
   p.bias = reinterpret_cast<const __nv_bfloat16 *>(bias);
   p.ldbias = ldbias;
   p.act = ctx->gemm_act;
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-  if (p.act)
+  if (multicast)
+    ttlb_gemm_bf16_kernel<false, true><<<grid, THREADS, SMEM_BYTES_PUB, stream>>>(map_a, map_b, p);
+  else if (p.act)
     ttlb_gemm_bf16_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
   else
     ttlb_gemm_bf16_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(map_a, map_b, p);
@@ -400,6 +473,30 @@ extern "C" int ttlb_matmul_bf16_multicast(ttlb_ctx *ctx, const ttlb_gemm_desc *d
   if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null descriptor");
   return ttlb_launch_gemm_bf16_ex(ctx, d->a, d->lda, d->b, d->ldb, d->c, d->ldc, d->m, d->n, d->k, true,
                                   reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Peer pointers of ttlb_matmul_*_peers, checked and parked in the context for the launch that follows.
+int ttlb_set_pub_peers(ttlb_ctx *ctx, void *const *peers, int n_peers) {
+  if (!peers || n_peers < 1 || n_peers > MAX_PEERS)
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: 1 to %d peer outputs", MAX_PEERS);
+  for (int i = 0; i < n_peers; ++i) {
+    if (!peers[i] || ((uintptr_t)peers[i] % 16))
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: peer output %d is null or not 16-byte aligned", i);
+    ctx->pub_peers[i] = peers[i];
+  }
+  ctx->pub_n_peers = n_peers;
+  return TTLB_OK;
+}
+
+extern "C" int ttlb_matmul_bf16_peers(ttlb_ctx *ctx, const ttlb_gemm_desc *d, void *const *peers, int n_peers, void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null descriptor");
+  int rc = ttlb_set_pub_peers(ctx, peers, n_peers);
+  if (rc) return rc;
+  rc = ttlb_launch_gemm_bf16_ex(ctx, d->a, d->lda, d->b, d->ldb, peers[0], d->ldc, d->m, d->n, d->k, true,
+                                reinterpret_cast<cudaStream_t>(stream));
+  ctx->pub_n_peers = 0;
+  return rc;
 }
 
 extern "C" int ttlb_check_status(ttlb_ctx *ctx, void *stream) {

@@ -218,6 +218,10 @@ def lib() -> C.CDLL:
     l.ttlb_matmul_bf16_multicast.restype = C.c_int
     l.ttlb_matmul_bfp8w_multicast.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.c_void_p]
     l.ttlb_matmul_bfp8w_multicast.restype = C.c_int
+    l.ttlb_matmul_bf16_peers.argtypes = [C.c_void_p, C.POINTER(GemmDesc), C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
+    l.ttlb_matmul_bf16_peers.restype = C.c_int
+    l.ttlb_matmul_bfp8w_peers.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
+    l.ttlb_matmul_bfp8w_peers.restype = C.c_int
     l.ttlb_multimem_bcast.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                       C.c_void_p]
     l.ttlb_multimem_bcast.restype = C.c_int
@@ -316,6 +320,15 @@ class Context:
 
     def matmul_bfp8w_multicast(self, desc: "GemmBfp8Desc", stream: int) -> None:
         self.check(self._lib.ttlb_matmul_bfp8w_multicast(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def matmul_bf16_peers(self, desc: "GemmDesc", peers: "list[int]", stream: int) -> None:
+        """C = A @ B stored into the output region of every buffer in `peers` (peer-mapped copies, own copy included)."""
+        arr = (C.c_void_p * len(peers))(*peers)
+        self.check(self._lib.ttlb_matmul_bf16_peers(self.handle, C.byref(desc), arr, len(peers), C.c_void_p(stream)))
+
+    def matmul_bfp8w_peers(self, desc: "GemmBfp8Desc", peers: "list[int]", stream: int) -> None:
+        arr = (C.c_void_p * len(peers))(*peers)
+        self.check(self._lib.ttlb_matmul_bfp8w_peers(self.handle, C.byref(desc), arr, len(peers), C.c_void_p(stream)))
 
     def multimem_bcast(self, src_ptr: int, src_ld_bytes: int, mc_dst_ptr: int, dst_ld_bytes: int, rows: int,
                        row_bytes: int, stream: int) -> None:

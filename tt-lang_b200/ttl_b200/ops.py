@@ -24,11 +24,17 @@ def _dev2d(t: "_ttnn.Tensor", what: str) -> torch.Tensor:
 
 def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_ttnn.Tensor",
                 rect: Tuple[int, int, int, int], stream: int, multicast_ptr: Optional[int] = None,
-                bias: Optional["_ttnn.Tensor"] = None, act: int = 0) -> None:
+                bias: Optional["_ttnn.Tensor"] = None, act: int = 0, peer_ptrs: Optional[list] = None) -> None:
     """out[r0:r1, c0:c1] = a[r0:r1, :] @ b[:, c0:c1] (+ bias[r0:r1, c0:c1]) (element coordinates).  With
     `multicast_ptr` (the NVLink multicast address of out's element (0, 0)) the result is stored through the
-    switch to every GPU of the multicast group instead of through out's own mapping."""
+    switch to every GPU of the multicast group instead of through out's own mapping; with `peer_ptrs` (the
+    address of out's element (0, 0) in every GPU's copy of the buffer, own copy included) it is stored into each
+    of them with ordinary stores."""
     r0, r1, c0, c1 = rect
+    if peer_ptrs is not None and multicast_ptr is not None:
+        raise ValueError("multicast_ptr and peer_ptrs are alternatives")
+    if peer_ptrs is not None:
+        multicast_ptr = peer_ptrs[0]     # the descriptor's output pointer; the kernel stores to every entry of peer_ptrs
     if (act or bias is not None) and (multicast_ptr is not None or a._tensor.dtype != torch.bfloat16):
         raise Unsupported("matmul with bias / activation: bfloat16 A, bias and output, own-memory output only")
 
@@ -65,6 +71,8 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
             ctx.matmul_bfp8w_epilogue(g, ptr, ld, act, stream)
         elif multicast_ptr is None:
             ctx.matmul_bfp8w(g, stream)
+        elif peer_ptrs is not None:
+            ctx.matmul_bfp8w_peers(g, [p + (r0 * xo.stride(0) + c0) * 2 for p in peer_ptrs], stream)
         else:
             ctx.matmul_bfp8w_multicast(g, stream)
         return
@@ -83,6 +91,8 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
         if multicast_ptr is not None:
             raise Unsupported("multicast output: bfloat16 matmuls only")
         ctx.matmul_f32(d, stream)
+    elif peer_ptrs is not None:
+        ctx.matmul_bf16_peers(d, [p + (r0 * xo.stride(0) + c0) * es for p in peer_ptrs], stream)
     elif multicast_ptr is not None:
         ctx.matmul_bf16_multicast(d, stream)
     elif bias is not None or act:
@@ -96,15 +106,16 @@ def launch_gemm(ctx: capi.Context, a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: "_
 
 
 def matmul(a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: Optional["_ttnn.Tensor"] = None,
-           multicast_ptr: Optional[int] = None) -> "_ttnn.Tensor":
-    """C = A @ B on the tensor cores (bf16 in, fp32 accumulate, bf16 out).  `multicast_ptr`: see launch_gemm."""
+           multicast_ptr: Optional[int] = None, peer_ptrs: Optional[list] = None) -> "_ttnn.Tensor":
+    """C = A @ B on the tensor cores (bf16 in, fp32 accumulate, bf16 out).  `multicast_ptr`, `peer_ptrs`: see
+    launch_gemm."""
     m, n = a.shape[0], b.shape[1]
     if a.shape[1] != b.shape[0]:
         raise ValueError(f"Incompatible matrix shapes for multiplication: {a.shape} @ {b.shape}")
     if out is None:
         out = _ttnn.empty((m, n), dtype=a._tensor.dtype)
     dev = a._tensor.device.index if a._tensor.is_cuda else None
-    launch_gemm(capi.context(dev), a, b, out, (0, m, 0, n), capi.current_stream(), multicast_ptr)
+    launch_gemm(capi.context(dev), a, b, out, (0, m, 0, n), capi.current_stream(), multicast_ptr, peer_ptrs=peer_ptrs)
     return out
 
 

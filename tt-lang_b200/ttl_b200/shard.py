@@ -206,6 +206,16 @@ class SymmetricOutput:
             raise ValueError("not a view of this symmetric buffer, or no multicast support")
         return int(self.hdl.multicast_ptr) + off
 
+    def peer_ptrs_of(self, view: torch.Tensor) -> List[int]:
+        """Address of element 0 of `view` (a view of this rank's buffer) in every rank's copy of the buffer, own
+        copy first, then the other ranks starting with the next one (so that the ranks do not all write to the
+        same GPU at the same moment)."""
+        off = view.data_ptr() - self.buf.data_ptr()
+        if off < 0 or off >= self.buf.numel() * self.buf.element_size():
+            raise ValueError("not a view of this symmetric buffer")
+        order = [(self.rank + k) % self.world for k in range(self.world)]
+        return [int(self.peers[r].data_ptr()) + off for r in order]
+
     def barrier(self) -> torch.Tensor:
         self.hdl.barrier()
         return self.buf
