@@ -705,7 +705,9 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
 
 def run_sharded(args, env: "Env") -> None:
     """`--workload matmul_bf16_8192 | matmul_bfp8w | matmul_bfp4w | attention`: one JSON line for that workload."""
-    modes = ["p2p", "multicast", "fused", "peers", "nccl"] if args.gather == "all" else [args.gather]
+    modes = [args.gather]
+    if args.gather == "all":
+        modes = ["p2p", "multicast", "nccl"] if args.workload == "attention" else ["p2p", "multicast", "fused", "peers", "nccl"]
     for mode in modes:
         rec = measure_sharded(args, args.workload, env, mode)
         if env.rank == 0:
