@@ -317,7 +317,7 @@ class Env:
 
             import torch.distributed as dist
 
-            dist.init_process_group("nccl", device_id=self.dev, timeout=datetime.timedelta(seconds=300))
+            dist.init_process_group("nccl", device_id=self.dev, timeout=datetime.timedelta(seconds=120))
             self.dist = dist
         bind_to_gpu_numa_node(physical_gpu_index(self.local))
 
@@ -515,22 +515,31 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
     dev_in = [t.to(dev) for t in host_in]
     gather = "nccl all-gather"
     mode = gather_mode
-    if mode == "auto":   # measured: peer copies win at 2 ranks; at 4 and 8 publication through the switch
-        mode = "p2p" if world < 4 else ("fused" if wl == "matmul_bf16_8192" else "multicast")
+    if mode == "auto":   # measured on 2 GPUs: publication from the kernel's epilogue beats every separate gather
+        mode = "fused"
     rounds_used = None
     if world > 1 and mode != "nccl":
+        so, why = None, ""
         try:
             if wl == "matmul_bf16_8192":
                 so = shard.SymmetricOutput((n, n), torch.bfloat16, dev)
             elif wl == "matmul_bfp8w":
-                so = shard.SymmetricOutput((m, n), torch.bfloat16, dev) if mode in ("multicast", "fused") else \
+                so = shard.SymmetricOutput((m, n), torch.bfloat16, dev) if mode in ("multicast", "fused", "peers") else \
                     shard.SymmetricOutput((world, m, c0 * 32), torch.bfloat16, dev)
             else:
                 so = shard.SymmetricOutput((B * H, S, D), torch.bfloat16, dev)
+        except Exception as e:   # symmetric memory unavailable on this rank
+            why = f"{type(e).__name__}: {e}"
+        # every rank takes the same path: one rank without symmetric memory sends all of them to NCCL
+        flag = torch.tensor([1 if so is not None else 0], device=dev)
+        env.dist.all_reduce(flag, op=env.dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            mode = "nccl"
+            gather = f"nccl all-gather (symmetric memory unavailable on some rank{': ' + why if why else ''})"[:160]
+            so = None
+        if so is not None:
             if mode == "fused" and not so.has_multicast:
                 mode = "peers"
-            if mode in ("fused", "peers") and wl == "attention":
-                mode = "multicast"
             if mode == "multicast" and not so.has_multicast:
                 mode = "p2p"
             if mode == "multicast" and so.has_multicast:
@@ -599,6 +608,17 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
                     def step(x):
                         ops.matmul(T(a_contig), T(x[1]), out=T(mine_view), **where)
                         return so.barrier()
+                elif wl == "attention":
+                    ul = (B * H) // world
+                    mine_view = so.buf[rank * ul:(rank + 1) * ul]
+                    host_in = [cases.gen((ul * S, D), "normal", sd + 10 * rank).reshape(ul, S, D).pin_memory() for sd in (0, 1, 2)]
+                    dev_in = [t.to(dev) for t in host_in]
+                    where = ({"multicast_ptr": so.multicast_ptr_of(mine_view)} if mode == "fused" else
+                             {"peer_ptrs": so.peer_ptrs_of(mine_view)})
+
+                    def step(x):
+                        ops.attention(T(x[0]), T(x[1]), T(x[2]), causal=True, scale=D ** -0.5, out=T(mine_view), **where)
+                        return so.barrier()
                 else:
                     nl = c0 * 32
                     mine_view = so.buf[:, rank * nl:(rank + 1) * nl]
@@ -608,9 +628,9 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
                     def step(xs):
                         ops.launch_gemm(ctx, T(xs[0]), W, T(mine_view), (0, m, 0, nl), capi.current_stream(), **where)
                         return so.barrier()
-                gather = ("multimem.st in the GEMM epilogue (NVSwitch multicast, row-contiguous stores), then a cross-rank barrier"
+                gather = ("multimem.st in the kernel's epilogue (NVSwitch multicast, row-contiguous stores), then a cross-rank barrier"
                           if mode == "fused" else
-                          "plain stores from the GEMM epilogue into every rank's copy of the output (peer memory, "
+                          "plain stores from the kernel's epilogue into every rank's copy of the output (peer memory, "
                           "row-contiguous), then a cross-rank barrier")
             else:
                 mode = "p2p"
@@ -626,9 +646,6 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
                         so, x[0], x[1], x[2], lambda q_, k_, v_, o_: ops.attention(T(q_), T(k_), T(v_), causal=True,
                                                                                  scale=D ** -0.5, out=T(o_)), chunks)
                 gather = "peer-to-peer copies into a symmetric buffer (copy engines), overlapped with compute"
-        except Exception as e:  # symmetric memory unavailable: keep the NCCL path
-            mode = "nccl"
-            gather = f"nccl all-gather (symmetric memory unavailable: {type(e).__name__}: {e})"[:160]
 
     steps = min(args.steps, 30)
     sampler = ClockSampler(physical_gpu_index(env.local))
@@ -707,7 +724,7 @@ def run_sharded(args, env: "Env") -> None:
     """`--workload matmul_bf16_8192 | matmul_bfp8w | matmul_bfp4w | attention`: one JSON line for that workload."""
     modes = [args.gather]
     if args.gather == "all":
-        modes = ["p2p", "multicast", "nccl"] if args.workload == "attention" else ["p2p", "multicast", "fused", "peers", "nccl"]
+        modes = ["p2p", "multicast", "fused", "peers", "nccl"]
     for mode in modes:
         rec = measure_sharded(args, args.workload, env, mode)
         if env.rank == 0:

@@ -441,6 +441,13 @@ TTLB_EXPORT int ttlb_matmul_bf16_peers(ttlb_ctx *ctx, const ttlb_gemm_desc *desc
                                        void *stream);
 TTLB_EXPORT int ttlb_matmul_bfp8w_peers(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *desc, void *const *peers, int n_peers,
                                         void *stream);
+/* ttlb_attention with the same two ways of publishing the output of this rank's heads: desc->o is the multicast
+ * address of the output (multicast), or `peers` are the addresses of the output in every GPU's copy of a shared
+ * buffer and desc->o is ignored (peers).  The epilogue stages every tile's rows in shared memory and stores whole
+ * 128-byte half rows. */
+TTLB_EXPORT int ttlb_attention_multicast(ttlb_ctx *ctx, const ttlb_attn_desc *desc, void *stream);
+TTLB_EXPORT int ttlb_attention_peers(ttlb_ctx *ctx, const ttlb_attn_desc *desc, void *const *peers, int n_peers,
+                                     void *stream);
 TTLB_EXPORT int ttlb_multimem_bcast(ttlb_ctx *ctx, const void *src, int64_t src_ld_bytes, void *mc_dst,
                                     int64_t dst_ld_bytes, int64_t rows, int64_t row_bytes, void *stream);
 

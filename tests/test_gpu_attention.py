@@ -103,3 +103,26 @@ def test_c_abi_attention_rejects_bad_descriptors():
     assert rc(desc(o=x.data_ptr() + 2)) == capi.TTLB_ERR_INVALID_ARG
     assert rc(desc(seq=0)) == capi.TTLB_OK
     assert ctx.launch_count() == n0
+
+
+@pytest.mark.parametrize("shape,causal", [((1, 2, 384, 128), True), ((1, 3, 200, 128), True), ((2, 2, 512, 128), False)])
+def test_c_abi_attention_published_to_several_buffers(shape, causal):
+    """ttlb_attention_peers: the epilogue that stages every tile's rows in shared memory and stores them, whole
+    128-byte half rows at a time, into several buffers (on a box with several GPUs: every GPU's copy of a shared
+    output).  Here all buffers live on this GPU: each must hold exactly what the plain kernel gives, and nothing
+    may be written around the outputs (ragged last tile included)."""
+    from ttl_b200 import capi, ops, ttnn
+    q, k, v = qkv(shape)
+    scale = shape[-1] ** -0.5
+    Q, K, V = ttnn.from_torch(q), ttnn.from_torch(k), ttnn.from_torch(v)
+    plain = ttnn.to_torch(ops.attention(Q, K, V, causal=causal, scale=scale))
+    assert rel_err(plain, attention_oracle.attention_tiles(q, k, v, causal, scale)) <= TOL
+    n = q.numel()
+    bufs = [torch.full((n + 4096,), 3.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    out = ttnn.Tensor(bufs[0][2048:2048 + n].view(shape))
+    ops.attention(Q, K, V, causal=causal, scale=scale, out=out, peer_ptrs=[b.data_ptr() + 4096 for b in bufs])
+    capi.context().check_status(capi.current_stream())
+    for b in bufs:
+        got = b.cpu()
+        assert torch.equal(got[2048:2048 + n].view(shape), plain), "published output differs from the plain kernel's"
+        assert (got[:2048] == 3.0).all() and (got[2048 + n:] == 3.0).all(), "the publishing epilogue wrote outside the output"

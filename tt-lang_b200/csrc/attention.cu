@@ -51,7 +51,15 @@ constexpr int OFF_BAR = OFF_X + XCH_BYTES;
 constexpr int ATT_SMEM = OFF_BAR + 512 + 1024;
 constexpr float RESCALE_THRESHOLD = 8.0f;    // in log2 units
 
+constexpr int MAX_PEERS = 8;
+
 struct AttnParams {
+  // pub == 0: plain stores to `o`.  1: `o` is an NVLink multicast address, stored with multimem.st (the switch
+  // replicates every store to all GPUs of the group).  2: every row is stored to `peer_o[0..n_peers)`, the output
+  // in every GPU's copy of a shared buffer (peer-mapped memory, this GPU's own copy included).
+  int pub = 0;
+  __nv_bfloat16 *peer_o[MAX_PEERS] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int n_peers = 0;
   __nv_bfloat16 *o;
   int seq, bh, q_tiles, q_pairs;
   int causal;
@@ -80,6 +88,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// 16-byte store to a multicast address: the switch replicates it to every GPU of the group.
+__device__ __forceinline__ void st_multimem_16(void *p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+// PUB: the instantiation whose epilogue publishes the output to several GPUs through a shared-memory stage
+template <bool PUB>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
 ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                       const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -228,7 +245,8 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     float m_used = -INFINITY, l_run = 0.f;
 
     for (int j = 0; j < n_t; ++j) {
-      if (!mbar_wait(bar(B_SFULL + t), (uint32_t)(j & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
+      // the outcome of a wait is made the same for the whole warp: what follows is warp-collective
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + t), (uint32_t)(j & 1), abort_flag, p.wait_limit))) { fail = 4; break; }
       tc_fence_after();
       uint32_t s0[32], s1[32];
       tmem_ld_32x32(my_s + part * PCOLS, s0);
@@ -255,7 +273,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       float *xrow = xbase + (j & 1) * NPART * 128;
       xrow[part * 128] = mx;
       mbar_arrive(xbar);
-      if (!mbar_wait(xbar, (uint32_t)(j & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(xbar, (uint32_t)(j & 1), abort_flag, p.wait_limit))) { fail = 4; break; }
       const float m_new = fmaxf(m_used, fmaxf(mx, xrow[(part ^ 1) * 128]));
       // raise the max used for the exponentials only when the true max has moved far; both
       // threads of a row take the same decision from the same numbers
@@ -267,7 +285,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
         // O_t *= alpha, after the last PV UMMA of this tile has landed and before the next is released
-        if (!mbar_wait(bar(B_ODONE + t), (uint32_t)((j - 1) & 1), abort_flag, p.wait_limit)) { fail = 4; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(bar(B_ODONE + t), (uint32_t)((j - 1) & 1), abort_flag, p.wait_limit))) { fail = 4; break; }
         tc_fence_after();
 #pragma unroll 1
         for (int h = 0; h < PCOLS / 16; ++h) {   // 16 columns at a time: this path must not cost registers
@@ -320,13 +338,52 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       float *xrow = xbase + slot * NPART * 128;
       xrow[part * 128] = l_run;
       mbar_arrive(xbar);
-      if (!mbar_wait(xbar, (uint32_t)slot, abort_flag, p.wait_limit) ||
-          !mbar_wait(bar(B_ODONE + t), (uint32_t)((n_t - 1) & 1), abort_flag, p.wait_limit))
+      if (!__all_sync(0xffffffffu, mbar_wait(xbar, (uint32_t)slot, abort_flag, p.wait_limit) &&
+                                       mbar_wait(bar(B_ODONE + t), (uint32_t)((n_t - 1) & 1), abort_flag, p.wait_limit)))
         fail = 4;
       if (!fail) {
         tc_fence_after();
         const float inv = 1.0f / (l_run + xrow[(part ^ 1) * 128]);
         __nv_bfloat16 *dst = p.o + ((long long)bh * p.seq + q_idx) * HD + part * PCOLS;
+        if constexpr (PUB) {
+          // tcgen05.ld hands every thread one row (its 64 columns = 128 bytes); the rows go through a swizzled
+          // stage in the tile's own Q buffer - every score UMMA of the tile has completed, nothing reads Q any
+          // more - so that each store instruction of the warp writes four whole 128-byte half rows instead of
+          // 16 bytes to each of 32 rows, which through NVLink reaches a small fraction of the link rate
+          uint8_t *stage = gen + OFF_Q + t * TILE_BYTES + (q * NPART + part) * (32 * PCOLS * 2);
+#pragma unroll 1
+          for (int h = 0; h < PCOLS / 32; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32(my_o + h * 32, r);
+            tmem_ld_wait_dep(r);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]) * inv, __uint_as_float(r[8 * u + 1]) * inv);
+              v.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]) * inv, __uint_as_float(r[8 * u + 3]) * inv);
+              v.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]) * inv, __uint_as_float(r[8 * u + 5]) * inv);
+              v.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]) * inv, __uint_as_float(r[8 * u + 7]) * inv);
+              const int unit = h * 4 + u;   // 16-byte unit within the 128-byte half row
+              *reinterpret_cast<uint4 *>(stage + lane * (PCOLS * 2) + ((unit ^ (lane & 7)) << 4)) = v;
+            }
+          }
+          __syncwarp();
+          const int unit = lane & 7;
+          const long long row0 = (long long)bh * p.seq + qt * BQ + q * 32;
+#pragma unroll 2
+          for (int i = 0; i < 8; ++i) {
+            const int rl = 4 * i + (lane >> 3);
+            const uint4 v = *reinterpret_cast<const uint4 *>(stage + rl * (PCOLS * 2) + ((unit ^ (rl & 7)) << 4));
+            if (qt * BQ + q * 32 + rl < p.seq) {
+              const long long off = (row0 + rl) * HD + part * PCOLS + unit * 8;
+              if (p.pub == 1) {
+                st_multimem_16(p.o + off, v);
+              } else {
+                for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(p.peer_o[d] + off) = v;
+              }
+            }
+          }
+        } else {
 #pragma unroll 1
         for (int h = 0; h < PCOLS / 32; ++h) {
           uint32_t r[32];
@@ -343,6 +400,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
               *reinterpret_cast<uint4 *>(dst + h * 32 + 8 * u) = v;
             }
           }
+        }
         }
       }
     }
@@ -378,11 +436,31 @@ int make_map3(ttlb_ctx *ctx, CUtensorMap *map, const void *ptr, uint64_t seq, ui
 
 }  // namespace
 
+static int attention_impl(ttlb_ctx *ctx, const ttlb_attn_desc *d, int pub, void *const *peers, int n_peers, void *stream);
+
 extern "C" int ttlb_attention(ttlb_ctx *ctx, const ttlb_attn_desc *d, void *stream) {
+  return attention_impl(ctx, d, 0, nullptr, 0, stream);
+}
+
+extern "C" int ttlb_attention_multicast(ttlb_ctx *ctx, const ttlb_attn_desc *d, void *stream) {
+  return attention_impl(ctx, d, 1, nullptr, 0, stream);
+}
+
+extern "C" int ttlb_attention_peers(ttlb_ctx *ctx, const ttlb_attn_desc *d, void *const *peers, int n_peers, void *stream) {
+  if (!ctx) return TTLB_ERR_INVALID_ARG;
+  if (!peers || n_peers < 1 || n_peers > MAX_PEERS)
+    return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "attention: 1 to %d peer outputs", MAX_PEERS);
+  for (int i = 0; i < n_peers; ++i)
+    if (!peers[i] || ((uintptr_t)peers[i] % 16))
+      return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "attention: peer output %d is null or not 16-byte aligned", i);
+  return attention_impl(ctx, d, 2, peers, n_peers, stream);
+}
+
+static int attention_impl(ttlb_ctx *ctx, const ttlb_attn_desc *d, int pub, void *const *peers, int n_peers, void *stream) {
   if (!ctx) return TTLB_ERR_INVALID_ARG;
   if (!d) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "attention: null descriptor");
   if (d->batch_heads == 0 || d->seq == 0) return TTLB_OK;
-  if (!d->q || !d->k || !d->v || !d->o) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "attention: null tensor");
+  if (!d->q || !d->k || !d->v || (!d->o && pub != 2)) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "attention: null tensor");
   if (d->head_dim != HD) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "attention: head_dim %d (128 only)", (int)d->head_dim);
   if (d->batch_heads < 0 || d->seq < 0 || d->seq > (1 << 24) || d->batch_heads > (1 << 24))
     return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "attention: bad shape");
@@ -397,11 +475,15 @@ extern "C" int ttlb_attention(ttlb_ctx *ctx, const ttlb_attn_desc *d, void *stre
   if ((rc = make_map3(ctx, &mk, d->k, (uint64_t)d->seq, (uint64_t)d->batch_heads))) return rc;
   if ((rc = make_map3(ctx, &mv, d->v, (uint64_t)d->seq, (uint64_t)d->batch_heads))) return rc;
   if (!ctx->attn_attr_set) {
-    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM));
+    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM));
+    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM));
     ctx->attn_attr_set = true;
   }
   AttnParams p;
-  p.o = reinterpret_cast<__nv_bfloat16 *>(d->o);
+  p.o = reinterpret_cast<__nv_bfloat16 *>(pub == 2 ? peers[0] : d->o);
+  p.pub = pub;
+  p.n_peers = pub == 2 ? n_peers : 0;
+  for (int i = 0; i < p.n_peers; ++i) p.peer_o[i] = reinterpret_cast<__nv_bfloat16 *>(peers[i]);
   p.seq = (int)d->seq;
   p.bh = (int)d->batch_heads;
   p.q_tiles = (int)((d->seq + BQ - 1) / BQ);
@@ -412,7 +494,10 @@ extern "C" int ttlb_attention(ttlb_ctx *ctx, const ttlb_attn_desc *d, void *stre
   p.wait_limit = ctx->wait_limit_cycles;
   const long long grid = (long long)p.q_pairs * p.bh;
   if (grid > 0x7fffffffLL) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "attention: too many tiles");
-  ttlb_attention_kernel<<<(unsigned)grid, ATT_THREADS, ATT_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
+  if (pub)
+    ttlb_attention_kernel<true><<<(unsigned)grid, ATT_THREADS, ATT_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
+  else
+    ttlb_attention_kernel<false><<<(unsigned)grid, ATT_THREADS, ATT_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
   TTLB_CUDA_CHECK(ctx, cudaGetLastError());
   ctx->launches += 1;
   return TTLB_OK;

@@ -156,7 +156,8 @@ ttlb_gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
       tile_coords2<GROUP_M2>(t, p.tiles_m, p.tiles_n, tm, tn);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1u;
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_limit)) { fail = 3; break; }
+      // the outcome of the wait is made the same for the whole warp: what follows is warp-collective
+      if (!__all_sync(0xffffffffu, mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_limit))) { fail = 3; break; }
       tc_fence_after();
       const int row = tm * BM2 + (int)rank * 128 + q * 32 + lane;
       __nv_bfloat16 *crow = p.c + (long long)row * p.ldc + (long long)tn * BN2;

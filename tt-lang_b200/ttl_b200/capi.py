@@ -222,6 +222,10 @@ def lib() -> C.CDLL:
     l.ttlb_matmul_bf16_peers.restype = C.c_int
     l.ttlb_matmul_bfp8w_peers.argtypes = [C.c_void_p, C.POINTER(GemmBfp8Desc), C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
     l.ttlb_matmul_bfp8w_peers.restype = C.c_int
+    l.ttlb_attention_multicast.argtypes = [C.c_void_p, C.POINTER(AttnDesc), C.c_void_p]
+    l.ttlb_attention_multicast.restype = C.c_int
+    l.ttlb_attention_peers.argtypes = [C.c_void_p, C.POINTER(AttnDesc), C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
+    l.ttlb_attention_peers.restype = C.c_int
     l.ttlb_multimem_bcast.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                       C.c_void_p]
     l.ttlb_multimem_bcast.restype = C.c_int
@@ -310,6 +314,13 @@ class Context:
 
     def attention(self, desc: "AttnDesc", stream: int) -> None:
         self.check(self._lib.ttlb_attention(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def attention_multicast(self, desc: "AttnDesc", stream: int) -> None:
+        self.check(self._lib.ttlb_attention_multicast(self.handle, C.byref(desc), C.c_void_p(stream)))
+
+    def attention_peers(self, desc: "AttnDesc", peers: "list[int]", stream: int) -> None:
+        arr = (C.c_void_p * len(peers))(*peers)
+        self.check(self._lib.ttlb_attention_peers(self.handle, C.byref(desc), arr, len(peers), C.c_void_p(stream)))
 
     def check_status(self, stream: int = 0) -> None:
         """Synchronise `stream` and raise if a bounded device-side wait ran out since the last check."""

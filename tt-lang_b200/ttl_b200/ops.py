@@ -120,9 +120,13 @@ def matmul(a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: Optional["_ttnn.Tensor"] =
 
 
 def attention(q: "_ttnn.Tensor", k: "_ttnn.Tensor", v: "_ttnn.Tensor", causal: bool = True,
-              scale: Optional[float] = None, out: Optional["_ttnn.Tensor"] = None) -> "_ttnn.Tensor":
+              scale: Optional[float] = None, out: Optional["_ttnn.Tensor"] = None,
+              multicast_ptr: Optional[int] = None, peer_ptrs: Optional[list] = None) -> "_ttnn.Tensor":
     """Fused attention forward on [B, H, S, D] (or [BH, S, D]) bf16 tensors, D = 128:
-    softmax(scale * Q K^T + causal mask) V with fp32 scores and online softmax."""
+    softmax(scale * Q K^T + causal mask) V with fp32 scores and online softmax.  With `multicast_ptr` (the NVLink
+    multicast address of out's first element) or `peer_ptrs` (the address of out's first element in every GPU's
+    copy of a shared buffer, own copy included) the result is published to all those GPUs from the kernel's
+    epilogue instead of being stored through out's own mapping."""
     xq, xk, xv = q._tensor, k._tensor, v._tensor
     for x, name in ((xq, "Q"), (xk, "K"), (xv, "V")):
         if not x.is_cuda:
@@ -144,5 +148,12 @@ def attention(q: "_ttnn.Tensor", k: "_ttnn.Tensor", v: "_ttnn.Tensor", causal: b
     d.batch_heads, d.seq, d.head_dim = bh, seq, hd
     d.causal = 1 if causal else 0
     d.scale = float(scale) if scale is not None else float(hd) ** -0.5
-    capi.context(xq.device.index).attention(d, capi.current_stream())
+    ctx = capi.context(xq.device.index)
+    if peer_ptrs is not None:
+        ctx.attention_peers(d, list(peer_ptrs), capi.current_stream())
+    elif multicast_ptr is not None:
+        d.o = multicast_ptr
+        ctx.attention_multicast(d, capi.current_stream())
+    else:
+        ctx.attention(d, capi.current_stream())
     return out
