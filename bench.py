@@ -722,9 +722,10 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
 
 def run_sharded(args, env: "Env") -> None:
     """`--workload matmul_bf16_8192 | matmul_bfp8w | matmul_bfp4w | attention`: one JSON line for that workload."""
-    modes = [args.gather]
-    if args.gather == "all":
-        modes = ["p2p", "multicast", "fused", "peers", "nccl"]
+    known = ["auto", "p2p", "multicast", "fused", "peers", "nccl"]
+    modes = known[1:] if args.gather == "all" else args.gather.split(",")
+    if any(m not in known for m in modes):
+        raise SystemExit(f"--gather: one of {known + ['all']}, or several of them separated by commas")
     for mode in modes:
         rec = measure_sharded(args, args.workload, env, mode)
         if env.rank == 0:
@@ -1144,10 +1145,11 @@ def main():
                     help="multicast gather: rounds the local shard is computed and re-sent in (0: 4 rounds on 4 or more GPUs, else 1)")
     ap.add_argument("--bfp8-mode", type=int, default=None, choices=[0, 1, 2],
                     help="bfp8 weights: 0 unpack kernel + GEMM, 1 unpack inside the GEMM mainloop for large outputs, 2 always inside")
-    ap.add_argument("--gather", default="auto", choices=["auto", "p2p", "multicast", "fused", "peers", "nccl", "all"],
+    ap.add_argument("--gather", default="auto",
                     help="sharded workloads: how output shards reach the other ranks (p2p: peer-to-peer copies overlapped with "
                          "compute; multicast: multimem.st re-send kernel per round under the next round's compute; fused: "
-                         "multimem.st from the GEMM epilogue; nccl: all-gather; all: one line per mode)")
+                         "multimem.st from the kernel's epilogue; peers: plain stores from the epilogue into every rank's copy; "
+                         "nccl: all-gather; all, or a comma-separated list: one line per mode)")
     ap.add_argument("--sim-sample", type=float, default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
