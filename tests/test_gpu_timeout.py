@@ -26,3 +26,31 @@ def test_bounded_wait_reports_timeout_and_context_stays_usable():
     assert (c == 64).all()
     with pytest.raises(capi.BackendError):
         ctx.selftest_wait_timeout(0, stream)       # limit out of range: rejected on the host
+
+
+def test_timeout_surfaces_where_the_host_reads_results_back():
+    """A device-side wait that ran out must not pass silently: `ttnn.to_torch`, `ttl_b200.synchronize` and
+    `run_streamed` check the status word where they already wait for the GPU.  The wait that runs out is the
+    self-test's (a barrier nothing arrives on, 1 ms limit): the kernel returns normally."""
+    import ttl_b200
+    from ttl_b200 import capi, ttnn
+    ctx = capi.context()
+    stream = capi.current_stream()
+    ctx.check_status(stream)
+    x = ttnn.from_torch(torch.ones(64, 64, dtype=torch.bfloat16))
+    ctx.selftest_wait_timeout(2_000_000, stream)
+    with pytest.raises(capi.BackendError) as e:
+        ttnn.to_torch(x)
+    assert e.value.code == capi.TTLB_ERR_TIMEOUT
+    assert (ttnn.to_torch(x) == 1).all()           # reported once; the context carries on
+    ctx.selftest_wait_timeout(2_000_000, stream)
+    with pytest.raises(capi.BackendError) as e:
+        ttl_b200.synchronize()
+    assert e.value.code == capi.TTLB_ERR_TIMEOUT
+    ttl_b200.synchronize()
+    pinned = torch.empty(64, 64, dtype=torch.bfloat16).pin_memory()
+    ctx.selftest_wait_timeout(2_000_000, stream)
+    with pytest.raises(capi.BackendError):
+        ttnn.to_torch(x, out=pinned)
+    ttnn.to_torch(x, out=pinned)
+    assert (pinned == 1).all()

@@ -364,3 +364,87 @@ def test_translate_prints_reduction_and_row_fused_sources(tmp_path):
     assert r.returncode == 0, r.stderr[-2000:]
     assert '"kind": "reduce_sum"' in r.stdout and "ttlb_reduce_jit" in r.stdout
     assert '"kind": "row_fused"' in r.stdout and "ttlb_rowfused_jit" in r.stdout and "source unavailable" not in r.stdout
+
+
+def _shift_program():
+    import ttl
+
+    @ttl.kernel(grid=(1, 1))
+    def shift(t, b):
+        t_cb = ttl.make_circular_buffer_like(t, shape=(1, 1), buffer_factor=2)
+        b_cb = ttl.make_circular_buffer_like(b, shape=(1, 1), buffer_factor=2)
+        o_cb = ttl.make_circular_buffer_like(t, shape=(1, 1), buffer_factor=2)
+
+        @ttl.compute()
+        def comp():
+            for _ in range(2):
+                with t_cb.wait() as x, b_cb.wait() as y, o_cb.reserve() as o:
+                    o.store(x + y)
+
+        @ttl.datamovement()
+        def rd():
+            for i in range(2):
+                with t_cb.reserve() as x, b_cb.reserve() as y:
+                    ttl.copy(t[i, 0], x).wait()
+                    ttl.copy(b[i, 0], y).wait()
+
+        @ttl.datamovement()
+        def wr():
+            for i in range(2):
+                with o_cb.wait() as o:
+                    ttl.copy(o, t[i + 1, 0]).wait()
+
+    return shift
+
+
+def test_program_that_reads_tiles_it_also_writes_is_refused(backend):
+    """t[i+1] = t[i] + b: every launch of a plan runs in parallel, so a program whose result depends on the order
+    of its own writes and reads is refused instead of being turned into a racing launch; updating a tensor in
+    place, tile for tile, is fine."""
+    import torch
+    import ttl
+    import ttnn
+    from ttl_b200 import Unsupported
+    t = ttnn.Tensor(torch.zeros(96, 32, dtype=torch.bfloat16))
+    b = ttnn.Tensor(torch.zeros(64, 32, dtype=torch.bfloat16))
+    with pytest.raises(Unsupported, match="also writes"):
+        _shift_program().plan(t, b)
+
+    @ttl.kernel(grid=(1, 1))
+    def in_place(t, b):
+        t_cb = ttl.make_circular_buffer_like(t, shape=(1, 1), buffer_factor=2)
+        b_cb = ttl.make_circular_buffer_like(b, shape=(1, 1), buffer_factor=2)
+        o_cb = ttl.make_circular_buffer_like(t, shape=(1, 1), buffer_factor=2)
+
+        @ttl.compute()
+        def comp():
+            for _ in range(2):
+                with t_cb.wait() as x, b_cb.wait() as y, o_cb.reserve() as o:
+                    o.store(x + y)
+
+        @ttl.datamovement()
+        def rd():
+            for i in range(2):
+                with t_cb.reserve() as x, b_cb.reserve() as y:
+                    ttl.copy(t[i, 0], x).wait()
+                    ttl.copy(b[i, 0], y).wait()
+
+        @ttl.datamovement()
+        def wr():
+            for i in range(2):
+                with o_cb.wait() as o:
+                    ttl.copy(o, t[i, 0]).wait()
+
+    d = in_place.plan(ttnn.Tensor(torch.zeros(64, 32, dtype=torch.bfloat16)), b).describe()
+    assert len(d) == 1 and d[0]["kind"] == "eltwise" and d[0]["out"] == 0 and d[0]["inputs"][0][:1] == (0,)
+
+
+def test_matmul_whose_operand_is_its_output_is_refused(backend):
+    import torch
+    import ttnn
+    from ttl_b200 import Unsupported
+    _, mods = backend
+    a = ttnn.Tensor(torch.zeros(64, 64, dtype=torch.bfloat16))
+    b = ttnn.Tensor(torch.zeros(64, 64, dtype=torch.bfloat16))
+    with pytest.raises(Unsupported, match="also writes"):
+        mods["matmul"].singlecore_matmul.plan(a, b, a)

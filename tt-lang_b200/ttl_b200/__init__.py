@@ -22,6 +22,18 @@ from .stream import run_streamed  # noqa: F401
 __version__ = "0.1"
 
 
+def synchronize(device=None) -> None:
+    """Wait for the work queued on `device` (default: the current CUDA device) on the current stream and raise
+    `BackendError` (TTLB_ERR_TIMEOUT) if a bounded device-side wait of one of this backend's kernels ran out
+    since the last check.  `ttnn.to_torch` and `run_streamed` make the same check."""
+    import torch
+
+    from . import capi
+
+    dev = torch.cuda.current_device() if device is None else (device if isinstance(device, int) else torch.device(device).index)
+    capi.context(dev).check_status(int(torch.cuda.current_stream(dev).cuda_stream))
+
+
 def install() -> None:
     """Make `import ttl` / `import ttnn` resolve to this backend, and give programs that
     import the simulator's helper modules (`sim.testing`, `sim.typedefs`) working

@@ -396,7 +396,8 @@ def context(device: Optional[int] = None) -> Context:
     return ctx
 
 
-def current_stream() -> int:
+def current_stream(device: Optional[int] = None) -> int:
+    """Handle of torch's current stream on `device` (default: the current CUDA device)."""
     import torch
 
-    return int(torch.cuda.current_stream().cuda_stream)
+    return int(torch.cuda.current_stream(device).cuda_stream)

@@ -115,7 +115,7 @@ def matmul(a: "_ttnn.Tensor", b: "_ttnn.Tensor", out: Optional["_ttnn.Tensor"] =
     if out is None:
         out = _ttnn.empty((m, n), dtype=a._tensor.dtype)
     dev = a._tensor.device.index if a._tensor.is_cuda else None
-    launch_gemm(capi.context(dev), a, b, out, (0, m, 0, n), capi.current_stream(), multicast_ptr, peer_ptrs=peer_ptrs)
+    launch_gemm(capi.context(dev), a, b, out, (0, m, 0, n), capi.current_stream(dev), multicast_ptr, peer_ptrs=peer_ptrs)
     return out
 
 
@@ -149,11 +149,12 @@ def attention(q: "_ttnn.Tensor", k: "_ttnn.Tensor", v: "_ttnn.Tensor", causal: b
     d.causal = 1 if causal else 0
     d.scale = float(scale) if scale is not None else float(hd) ** -0.5
     ctx = capi.context(xq.device.index)
+    stream = capi.current_stream(xq.device.index)
     if peer_ptrs is not None:
-        ctx.attention_peers(d, list(peer_ptrs), capi.current_stream())
+        ctx.attention_peers(d, list(peer_ptrs), stream)
     elif multicast_ptr is not None:
         d.o = multicast_ptr
-        ctx.attention_multicast(d, capi.current_stream())
+        ctx.attention_multicast(d, stream)
     else:
-        ctx.attention(d, capi.current_stream())
+        ctx.attention(d, stream)
     return out

@@ -705,6 +705,76 @@ class GemmLaunch:
                         act=capi.ACTIVATIONS[self.act] if self.act else 0)
 
 
+def _read_span(mode: int, off: int, lo: int, hi: int) -> Tuple[int, int]:
+    """Elements [a, b) an operand reads along one dim for an output range of tiles [lo, hi)."""
+    if mode in (capi.IDX_SAME, capi.IDX_FIRST):
+        return lo * TILE + off, hi * TILE + off
+    if mode == capi.IDX_TILE:
+        return off, off + TILE
+    return off, off + 1      # IDX_ZERO: one fixed row / column
+
+
+def _check_hazards(launches: Sequence[Any]) -> None:
+    """A plan's launches run as parallel kernels, ordered only where one reads a temporary another fills.  A
+    program that reads tiles of a tensor it also writes (a shifted copy `t[i+1] = t[i] + b`, a read-back of a tile it
+    stored, A or B of a matmul aliasing its output) would depend on an order the plan does not keep: refused.
+    The one exception is an element-wise launch that reads exactly the elements it writes (in-place update)."""
+    written: Dict[int, List[Tuple[int, int, int, int]]] = {}
+    for l in launches:
+        if l.out_index < TEMP_BASE:
+            written.setdefault(l.out_index, []).append(l.rect)
+    if not written:
+        return
+
+    def clash(what: str) -> Unsupported:
+        return Unsupported(f"the program {what} a tensor it also writes; the launches of a plan run in parallel, so "
+                           "the result would depend on their order")
+
+    for l in launches:
+        if isinstance(l, EltwiseLaunch):
+            r0, r1, c0, c1 = l.rect
+            for (ti, rm, ro, cm, co) in l.inputs:
+                if ti not in written:
+                    continue
+                def same_place(mode: int, off: int, lo: int, hi: int) -> bool:
+                    # element for element: SAME without a shift, or "one tile repeated" over a range of one tile
+                    return (mode == capi.IDX_SAME and off == 0) or (mode == capi.IDX_TILE and hi - lo == 1 and off == lo * TILE)
+
+                in_place = same_place(rm, ro, r0, r1) and same_place(cm, co, c0, c1)
+                ra, rb = _read_span(rm, ro, r0, r1)
+                ca, cb = _read_span(cm, co, c0, c1)
+                for other in launches:
+                    if other.out_index != ti:
+                        continue
+                    if other is l and in_place:
+                        continue
+                    o0, o1, p0, p1 = other.rect
+                    if ra < o1 * TILE and o0 * TILE < rb and ca < p1 * TILE and p0 * TILE < cb:
+                        raise clash("reads, at other positions, tiles of")
+        else:
+            parts = list(getattr(l, "parts", [])) + [getattr(l, "final", None)]
+            reads = [inp[0] for part in parts if part is not None for inp in getattr(part, "inputs", [])]
+            reads += [inp[0] for inp in getattr(l, "inputs", [])]
+            reads += [getattr(l, a, None) for a in ("a_index", "b_index", "bias_index")]
+            sc = getattr(l, "scaler", None)
+            if sc is not None:
+                reads.append(sc[0])
+            for part in parts:
+                sc = getattr(part, "scaler", None) if part is not None else None
+                if sc is not None:
+                    reads.append(sc[0])
+            if any(ti is not None and ti in written for ti in reads):
+                raise clash("reduces, or multiplies, tiles of")
+
+
+def _extent(x: torch.Tensor) -> Tuple[int, int]:
+    """[first byte, one past the last byte) a 2-D tensor can touch."""
+    if x.numel() == 0:
+        return 0, 0
+    last = sum((n - 1) * st for n, st in zip(x.shape, x.stride()))
+    return x.data_ptr(), x.data_ptr() + (last + 1) * x.element_size()
+
+
 class Plan:
     """The launches one kernel call turns into."""
 
@@ -726,6 +796,25 @@ class Plan:
     def describe(self) -> List[Dict[str, Any]]:
         return [l.describe() for l in self.launches]
 
+    def _check_overlap(self, tensors: Sequence[_ttnn.Tensor]) -> None:
+        """Two different argument tensors over the same memory (views of one storage), one of them written: the
+        plan was built as if they were independent, so the call is refused."""
+        outs = {l.out_index for l in self.launches if l.out_index < TEMP_BASE}
+        if not outs:
+            return
+        spans = []
+        for i, t in enumerate(tensors):
+            x = t._packed if t._packed is not None else t._tensor
+            spans.append(_extent(x) if x.is_cuda else (0, 0))
+        for w in outs:
+            if w >= len(spans):
+                continue
+            w0, w1 = spans[w]
+            for i, (a0, a1) in enumerate(spans):
+                if i != w and a0 < w1 and w0 < a1 and tensors[i] is not tensors[w]:
+                    raise Unsupported(f"kernel arguments {i} and {w} share memory and argument {w} is written: the launches "
+                                      "of a plan treat different arguments as independent tensors")
+
     def run(self, tensors: Sequence[_ttnn.Tensor]) -> None:
         allt = list(tensors) + self.extras
         dev = None
@@ -738,7 +827,8 @@ class Plan:
                 dev = x.device.index
                 break
         ctx = capi.context(dev)
-        stream = capi.current_stream()
+        stream = capi.current_stream(dev)     # of the tensors' device, which need not be the current one
+        self._check_overlap(allt)
         for t in self.temps:
             if not t._tensor.is_cuda or t._tensor.device.index != dev:
                 t._tensor = torch.zeros(t._tensor.shape, dtype=t._tensor.dtype, device=torch.device("cuda", dev))
@@ -1199,6 +1289,7 @@ def build_plan(trace: Trace, arg_tensors: Sequence[_ttnn.Tensor], fp32_intermedi
         ordered = _fuse_epilogues(ordered)
     if ROW_FUSION:
         ordered = _fuse_rows(ordered)
+    _check_hazards(ordered)
     # temporaries that the fusions made unnecessary keep their index but give their memory back
     used: Dict[int, None] = {}
     for l in ordered:

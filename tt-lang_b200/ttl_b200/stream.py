@@ -89,4 +89,5 @@ def run_streamed(kernel: Callable[..., Any], host_inputs: Sequence[torch.Tensor]
     cur.wait_stream(s_in)
     cur.wait_stream(s_out)
     s_out.synchronize()
+    capi.context(dev.index).check_status(int(cur.cuda_stream))   # a device-side wait that ran out must not pass silently
     return host_out

@@ -338,11 +338,25 @@ def to_torch(t: Union[Tensor, torch.Tensor], out: Optional[torch.Tensor] = None)
             out.copy_(t._tensor, non_blocking=True)
             if t._tensor.is_cuda:
                 torch.cuda.current_stream(t._tensor.device).synchronize()
+                _check_device_status(t._tensor.device)
             return out
-        return t._tensor.cpu()
+        host = t._tensor.cpu()
+        if t._tensor.is_cuda:
+            _check_device_status(t._tensor.device)
+        return host
     if isinstance(t, torch.Tensor):
         return t.cpu()
     raise TypeError(f"Unsupported type for to_torch: {type(t)}")
+
+
+def _check_device_status(device: torch.device) -> None:
+    """Reading results back is where the host already waits for the GPU: raise here if a bounded device-side wait
+    of a kernel launched on that GPU ran out (the kernel unwound and left its output partly written)."""
+    from . import capi
+
+    ctx = capi._CONTEXTS.get(device.index)
+    if ctx is not None:
+        ctx.check_status(int(torch.cuda.current_stream(device).cuda_stream))
 
 
 def from_torch(tensor: torch.Tensor, dtype: Any = None, layout: Any = None, device: Optional[Device] = None,
