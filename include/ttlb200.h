@@ -388,7 +388,8 @@ TTLB_EXPORT int ttlb_matmul_bfp4w_epilogue(ttlb_ctx *ctx, const ttlb_gemm_bfp8_d
  * one GPU share the array, so calls that can overlap on the GPU race - serialise them.  The first
  * call on a device does a one-time set-up (symbol address look-up, kernel attribute); make it
  * before any stream capture.  The current CUDA device is used.
- * check != 0: synchronise `stream` and return TTLB_ERR_TIMEOUT if a bounded device wait ran out.
+ * check != 0: synchronise `stream` and return TTLB_ERR_TIMEOUT if a bounded device wait ran out; with check == 0
+ * such a timeout is not reported at all (the status word is private to this entry point and cleared by its next call).
  * err / err_len: optional buffer that receives a message on failure. */
 #define TTLB_NOALLOC_MAX_WEIGHT_ELEMS (16 * 1024 * 1024)
 TTLB_EXPORT int ttlb_matmul_bfp8w_noalloc(const ttlb_gemm_bfp8_desc *desc, void *stream, int check, char *err,

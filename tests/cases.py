@@ -13,6 +13,8 @@ import torch
 
 
 def gen(shape: Tuple[int, int], dist: str, seed: int, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    if dist.startswith("bf16:"):      # values that bfloat16 represents exactly, whatever dtype carries them
+        return gen(shape, dist[5:], seed, torch.bfloat16).to(dtype)
     g = torch.Generator().manual_seed(seed)
     if dist == "normal":
         t = torch.randn(shape, generator=g, dtype=torch.float32)
@@ -219,9 +221,10 @@ EPILOGUE_CASES: List[Case] = [
 
 # attention written as a tile program (tests/programs/attention.py); the one-tile size is what the reference
 # simulator can run (its block matmul needs K = 1 tile); inputs: q, k^T, v, additive causal mask, scale tile, ones tile
-def _attn_inputs(s, d):
-    return [((s, d), "normal", 200), ((d, s), "normal", 201), ((s, d), "normal", 202), ((s, s), "causal_mask", 0),
-            ((32, 32), f"const:{d ** -0.5}", 0), ((32, 32), "const:1.0", 0)]
+def _attn_inputs(s, d, exact_in_bf16=False):
+    pre = "bf16:" if exact_in_bf16 else ""
+    return [((s, d), pre + "normal", 200), ((d, s), pre + "normal", 201), ((s, d), pre + "normal", 202),
+            ((s, s), "causal_mask", 0), ((32, 32), f"{pre}const:{d ** -0.5}", 0), ((32, 32), "const:1.0", 0)]
 
 
 ATTENTION_CASES: List[Case] = [
@@ -230,9 +233,21 @@ ATTENTION_CASES: List[Case] = [
          dtype=torch.float32),
 ]
 
+# the same attention as three kernels (scores, masked softmax, probabilities @ V) in 1x1-tile block matmuls, which the
+# simulator runs at the fused kernel's head dimension: these fixtures pin the fused attention kernel to the simulator
+ATTENTION_PIPELINE_CASES: List[Case] = [
+    Case("attention_pipeline_256x128_f32", "attention", "attention_pipeline", _attn_inputs(256, 128, True), (256, 128), "native",
+         None, "rel1e-5", dtype=torch.float32),
+    Case("attention_pipeline_256x128", "attention", "attention_pipeline", _attn_inputs(256, 128), (256, 128), "native",
+         None, "rel1e-2"),
+    Case("attention_pipeline_128x128_f32", "attention", "attention_pipeline", _attn_inputs(128, 128, True), (128, 128), "native",
+         None, "rel1e-5", dtype=torch.float32),
+]
+
 
 def by_name(name: str) -> Case:
-    for c in CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES + MATH_CASES + EPILOGUE_CASES + OPERATOR_CASES + ATTENTION_CASES:
+    for c in (CASES + MATMUL_CASES + REDUCE_CASES + COMPOSITE_CASES + MATH_CASES + EPILOGUE_CASES + OPERATOR_CASES + ATTENTION_CASES
+              + ATTENTION_PIPELINE_CASES):
         if c.name == name:
             return c
     raise KeyError(name)

@@ -1,7 +1,7 @@
 """Generate tests/golden/*.npz by running the tile programs in tests/programs/ on the
 UNMODIFIED reference simulator (python/sim under the reference checkout).
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/tt-lang-checkout [fixture names...]
 
 Run where the reference tree exists; the fixtures are committed so that the tests need no
 reference at run time.  Each fixture holds the simulator's output (bf16 as uint16 bit
@@ -73,7 +73,11 @@ def run_case_on_sim(case, mods, ttnn) -> torch.Tensor:
 
 
 def main() -> None:
-    reference = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    import os
+
+    reference = Path(sys.argv[1]) if len(sys.argv) > 1 and sys.argv[1] != "-" else Path(os.environ.get("TTLANG_REFERENCE", ""))
+    if not (reference / "python" / "sim").is_dir():
+        raise SystemExit("usage: make_golden.py /path/to/tt-lang-checkout [fixture names...]  (or set TTLANG_REFERENCE and pass -)")
     sim = load_sim(reference)
     import ttnn  # the simulator's, after shadowing
 
@@ -81,7 +85,7 @@ def main() -> None:
 
     mods = load_programs("sim")
     only = set(sys.argv[2:])   # optional: names of the fixtures to (re)generate
-    for case in cases.CASES + cases.MATMUL_CASES + cases.REDUCE_CASES + cases.COMPOSITE_CASES + cases.MATH_CASES + cases.EPILOGUE_CASES + cases.OPERATOR_CASES + cases.ATTENTION_CASES:
+    for case in cases.CASES + cases.MATMUL_CASES + cases.REDUCE_CASES + cases.COMPOSITE_CASES + cases.MATH_CASES + cases.EPILOGUE_CASES + cases.OPERATOR_CASES + cases.ATTENTION_CASES + cases.ATTENTION_PIPELINE_CASES:
         if only and case.name not in only:
             continue
         t0 = time.time()

@@ -126,3 +126,67 @@ def test_c_abi_attention_published_to_several_buffers(shape, causal):
         got = b.cpu()
         assert torch.equal(got[2048:2048 + n].view(shape), plain), "published output differs from the plain kernel's"
         assert (got[:2048] == 3.0).all() and (got[2048 + n:] == 3.0).all(), "the publishing epilogue wrote outside the output"
+
+
+@pytest.mark.parametrize("case", cases.ATTENTION_PIPELINE_CASES, ids=lambda c: c.name)
+def test_fused_kernel_and_tile_programs_match_the_simulator(case, backend):
+    """Pinned to the reference simulator: the fixtures are its outputs for attention run as three tile kernels (1x1-tile
+    block matmuls accumulated over K, masked row softmax in between; tests/programs/attention.py, generated by
+    tests/golden/make_golden.py) at head dimension 128.  Against them, within max |diff| / max |want| <= 1e-2:
+    the fused kernel `ttlb_attention`; the same three kernels through `@ttl.kernel` on the GPU (GEMM, row-resident
+    softmax, GEMM); and the single-kernel tile program with block matmuls whose plan has the same three launches."""
+    from conftest import golden_tensor, load_golden
+    from ttl_b200 import capi, ops
+    _, mods = backend
+    import ttnn
+    want = golden_tensor(load_golden(case.name)["out"], case.dtype)
+    host = case.make_inputs()
+    q, kt, v, mask, scale, one = host
+    bf = torch.bfloat16
+    # 1. the fused kernel (bf16 in / out)
+    shape = (1, 1) + tuple(q.shape)
+    got = ttnn.to_torch(ops.attention(ttnn.from_torch(q.to(bf).reshape(shape)), ttnn.from_torch(kt.t().contiguous().to(bf).reshape(shape)),
+                                      ttnn.from_torch(v.to(bf).reshape(shape)), causal=True, scale=float(scale[0, 0])))
+    assert rel_err(got.reshape(q.shape), want) <= TOL
+    # 2. three kernels, in the fixture's element type
+    prog = mods["attention"]
+    out = ttnn.from_torch(torch.zeros(case.out_shape, dtype=case.dtype))
+    n0 = capi.context().launch_count()
+    prog.attention_pipeline(*[ttnn.from_torch(t) for t in host], out)
+    assert capi.context().launch_count() == n0 + 3
+    assert rel_err(ttnn.to_torch(out), want) <= (TOL if case.dtype == bf else 1e-4)
+    # 3. one kernel with block matmuls and reductions (bf16; the specification's block dot product)
+    if case.dtype == bf:
+        out2 = ttnn.from_torch(torch.zeros(case.out_shape, dtype=bf))
+        plan = prog.attention_rows.plan(*[ttnn.from_torch(t) for t in host], out2)
+        assert [d["kind"] for d in plan.describe()] == ["matmul_bf16", "row_fused", "matmul_bf16"]
+        prog.attention_rows(*[ttnn.from_torch(t) for t in host], out2)
+        capi.context().check_status(capi.current_stream())
+        assert rel_err(ttnn.to_torch(out2), want) <= TOL
+
+
+def test_config5_full_shape_properties_and_sampled_heads():
+    """configs[4] at its full shape, B 8 x H 32 x S 4096 x D 128 (1 GB of tensors), checked on the whole output:
+    with a causal mask row 0 of every head equals V's row 0 exactly; heads are independent (a second run with
+    all other heads' Q / K / V changed leaves a head's output bits unchanged); and the oracle on sampled heads -
+    the first and the last head of what each of 8 ranks would own (32 consecutive (batch, head) pairs)."""
+    from ttl_b200 import capi, ops, ttnn
+    B, H, S, D = 8, 32, 4096, 128
+    g = torch.Generator().manual_seed(5)
+    q, k, v = (torch.randn(B * H, S, D, generator=g, dtype=torch.float32).to(torch.bfloat16) for _ in range(3))
+    Q, K, V = (ttnn.from_torch(t) for t in (q, k, v))
+    scale = D ** -0.5
+    out = ttnn.to_torch(ops.attention(Q, K, V, causal=True, scale=scale))
+    capi.context().check_status(capi.current_stream())
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out[:, 0, :], v[:, 0, :]), "row 0 of a causal head must be V's row 0"
+    heads = sorted({0, 31, 32, 127, 128, 223, 224, 255})
+    for h in heads[:4] + heads[-2:]:
+        want = attention_oracle.attention_tiles(q[h:h + 1], k[h:h + 1], v[h:h + 1], True, scale)
+        assert rel_err(out[h:h + 1], want) <= TOL, f"head {h}"
+    # head independence: scramble every other head, the kept heads must not change by a bit
+    keep = torch.tensor(heads)
+    q2, k2, v2 = q.flip(0).clone(), k.flip(0).clone(), v.flip(0).clone()
+    q2[keep], k2[keep], v2[keep] = q[keep], k[keep], v[keep]
+    out2 = ttnn.to_torch(ops.attention(ttnn.from_torch(q2), ttnn.from_torch(k2), ttnn.from_torch(v2), causal=True, scale=scale))
+    assert torch.equal(out2[keep], out[keep]), "a head's output depends on other heads"

@@ -258,3 +258,38 @@ def test_c_abi_matmul_published_to_several_buffers(m, n, k):
         assert torch.equal(got[32:32 + m, 32:32 + n], plain.cpu()), "published tile differs from the plain matmul"
         got[32:32 + m, 32:32 + n] = 3.0
         assert (got == 3.0).all(), "the publishing epilogue wrote outside the output region"
+
+
+def bf16_ulp_distance(golden: torch.Tensor, got: torch.Tensor) -> float:
+    """max |got - golden| / ULP(golden), ULP = the gap from |golden| to the next bfloat16 above it: the measure of
+    the reference's `assert_with_ulp` (python/utils/correctness.py:168-213)."""
+    g = golden.to(torch.bfloat16)
+    a = g.abs()
+    gap = (torch.nextafter(a, torch.full_like(a, float("inf"))) - a).float()
+    return ((got.float() - g.float()).abs() / gap).max().item()
+
+
+@pytest.mark.parametrize("variant", [0, 2], ids=["one_cta", "two_cta"])
+@pytest.mark.parametrize("n", [256, 512])
+def test_matmul_within_10_bf16_ulp_of_torch_matmul(backend, n, variant):
+    """The reference's own criterion for its matmul kernels
+    (examples/metal_examples/singlecore_matmul/ttlang/singlecore_matmul.py:63-79): uniform [0, 1) bfloat16 operands,
+    golden = torch.matmul in bfloat16, at most 10 bfloat16 ULP apart - next to the norm-wise 1e-2 bound, which
+    would hide large relative errors on small outputs."""
+    from ttl_b200 import capi
+    _, mods = backend
+    import ttnn
+    torch.manual_seed(n)
+    a, b = ttnn.rand((n, n), dtype=ttnn.bfloat16), ttnn.rand((n, n), dtype=ttnn.bfloat16)
+    c = ttnn.empty((n, n), dtype=ttnn.bfloat16)
+    ctx = capi.context()
+    ctx.set_gemm_variant(variant)
+    try:
+        mods["matmul"].singlecore_matmul(a, b, c)
+        ctx.check_status(capi.current_stream())
+    finally:
+        ctx.set_gemm_variant(1)
+    golden = torch.matmul(ttnn.to_torch(a).to(torch.bfloat16), ttnn.to_torch(b).to(torch.bfloat16))
+    result = ttnn.to_torch(c).to(torch.bfloat16)
+    assert bf16_ulp_distance(golden, result) <= 10
+    assert rel_err(result, golden) <= TOL

@@ -8,7 +8,7 @@ instead of the context's cudaMalloc'ed scratch.  The test calls it through the C
 row, with different shapes and data, so that whatever the first call left in the shared array and
 status word would show up in the second, and compares each result with the regular entry point,
 ttlb_matmul_bfp8w, within the matmul tolerance used throughout the suite (1e-2 of the largest
-magnitude; the two run the same kernels, so in practice the bits agree).  It also checks that a
+magnitude; the two run the same kernels, so in practice the bits agree) and with the CPU oracle.  It also checks that a
 weight window larger than the fixed array is refused with a message instead of overrunning it.
 This file sorts last on purpose: a run that stops at the first failure has then already run every
 other test.
@@ -59,6 +59,11 @@ def test_noalloc_entry_point_matches_regular_one_on_two_calls_in_a_row():
         torch.cuda.synchronize()
         assert torch.isfinite(got.float()).all()
         assert rel_err(got.cpu(), want.cpu()) <= TOL
+        # and against the CPU oracle (dequantised weights, fp32-accumulated tile matmul): a fault shared by both
+        # entry points would not show in the comparison above
+        from oracle import bfp8_oracle, tile_oracle
+        wq = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n_total))[:, col0_tiles * 32:col0_tiles * 32 + n]
+        assert rel_err(got.cpu(), tile_oracle.matmul_tiles(x.cpu().float(), wq, "f32")) <= TOL
 
 
 def test_noalloc_entry_point_rejects_windows_beyond_its_fixed_scratch():

@@ -17,8 +17,11 @@
 //     (k * n <= 16,777,216, e.g. 4096 x 4096 or 8192 x 2048); larger windows are rejected;
 //   * all calls on one GPU share the array: two calls whose kernels may overlap on the GPU (two
 //     streams, two threads) race on it - serialise them;
-//   * the first call on a device looks up the array's device address and raises the GEMM kernel's
-//     shared-memory limit; make that first call before any stream capture begins.
+//   * the first call on a device that passes the argument checks looks up the array's device address and
+//     raises the GEMM kernel's shared-memory limit (under a lock); make that first call before any stream
+//     capture begins;
+//   * with check == 0 a bounded device-side wait that ran out goes unreported: the status word is private to
+//     this entry point and the next call clears it.  Pass check != 0 where that matters.
 #include <cuda_runtime.h>
 
 #include <cstdio>
@@ -29,6 +32,7 @@
 int ttlb_gemm_bf16_launch_raw(const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc, int64_t m,
                               int64_t n, int64_t k, int sm_count, int *d_status, long long wait_limit, bool *attr_set,
                               cudaStream_t stream);
+int ttlb_gemm_bf16_raw_prepare();
 int ttlb_bfp8_unpack_launch_raw(const uint8_t *tiles, int64_t tile_cols_total, int64_t tile_col0, int64_t tile_rows,
                                 int64_t tile_cols, void *out, int64_t ld, int sm_count, cudaStream_t s);
 
@@ -103,6 +107,10 @@ extern "C" int ttlb_matmul_bfp8w_noalloc(const ttlb_gemm_bfp8_desc *d, void *str
       if (e != cudaSuccess || !p)
         return fail(err, err_len, TTLB_ERR_CUDA, "matmul_bfp8w_noalloc: cudaGetSymbolAddress(status) failed");
       su->status = reinterpret_cast<int *>(p);
+      // the GEMM kernel's shared-memory limit is raised here, under the lock, not by whichever thread launches first
+      if (ttlb_gemm_bf16_raw_prepare() != TTLB_OK)
+        return fail(err, err_len, TTLB_ERR_CUDA, "matmul_bfp8w_noalloc: cannot raise the GEMM kernel's shared-memory limit");
+      su->gemm_attr_set = true;
       su->ready = true;
     }
   }

@@ -528,6 +528,14 @@ extern "C" int ttlb_set_wait_limit(ttlb_ctx *ctx, int64_t cycles) {
   return TTLB_OK;
 }
 
+// One-time, per-device preparation of the context-free launch below (with that device current).
+int ttlb_gemm_bf16_raw_prepare() {
+  return cudaFuncSetAttribute(ttlb_gemm_bf16_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) ==
+                 cudaSuccess
+             ? TTLB_OK
+             : TTLB_ERR_CUDA;
+}
+
 // Context-free launch of the GEMM kernel for callers that bring their own status word and device
 // facts (used by the allocation-free bfp8-weight entry point).  Arguments are assumed validated.
 int ttlb_gemm_bf16_launch_raw(const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc, int64_t m,
