@@ -1,6 +1,6 @@
 """Install the reference simulator, unmodified, next to the oracle so that it can be TIMED on the GPU box.
 
-    python oracle/make_ref.py [/path/to/reference]
+    python oracle/make_ref.py /path/to/tt-lang-checkout      (or set TTLANG_REFERENCE)
 
 TEST / MEASUREMENT INFRASTRUCTURE ONLY (see oracle/__init__.py).  Copies the reference's `python/sim`
 package byte for byte into `oracle/_ref/sim/` (kept out of version control; it travels with the working
@@ -63,5 +63,9 @@ def load():
 
 
 if __name__ == "__main__":
-    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
-    print(install(ref))
+    import os
+
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TTLANG_REFERENCE")
+    if not where:
+        raise SystemExit("usage: make_ref.py /path/to/tt-lang-checkout  (or set TTLANG_REFERENCE)")
+    print(install(Path(where)))

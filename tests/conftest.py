@@ -9,6 +9,17 @@ for p in (ROOT, ROOT / "tt-lang_b200", ROOT / "tests"):
         sys.path.insert(0, str(p))
 
 
+def reference_root():
+    """The tt-lang checkout the reference-driven tests read: $TTLANG_REFERENCE, else a directory named `reference`
+    next to this repository; None when neither holds the simulator (those tests then skip)."""
+    import os
+
+    for cand in (os.environ.get("TTLANG_REFERENCE"), ROOT.parent / "reference"):
+        if cand and (Path(cand) / "python" / "sim").is_dir():
+            return Path(cand)
+    return None
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu on the GPU box)")
     # the native library is built in-tree and is not under version control: build it when it is missing

@@ -8,10 +8,10 @@ import pytest
 import torch
 
 import cases
-from conftest import digest, golden_tensor, load_golden
+from conftest import reference_root, digest, golden_tensor, load_golden
 from oracle import tile_oracle
 
-REFERENCE = Path("/root/reference")
+REFERENCE = reference_root() or Path("reference-checkout-not-found")
 
 
 def oracle_output(case):
@@ -64,7 +64,7 @@ def test_fixtures_reproduce_from_live_simulator():
     code = (
         "import sys; sys.argv=['x'];"
         "sys.path.insert(0, 'tests/golden'); import make_golden as m, numpy as np;"
-        "from pathlib import Path; sim = m.load_sim(Path('/root/reference')); import ttnn, cases;"
+        f"from pathlib import Path; sim = m.load_sim(Path({str(REFERENCE)!r})); import ttnn, cases;"
         "mods = m.load_programs('sim');\n"
         "for n in ['bcast_row_tilecol', 'unary_exp', 'mm_single_128x256x64']:\n"
         "    c = cases.by_name(n); out = m.run_case_on_sim(c, mods, ttnn);"

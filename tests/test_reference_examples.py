@@ -12,7 +12,9 @@ from pathlib import Path
 
 import pytest
 
-REFERENCE = Path("/root/reference")
+from conftest import reference_root  # noqa: E402
+
+REFERENCE = reference_root() or Path("reference-checkout-not-found")
 pytestmark = pytest.mark.skipif(not (REFERENCE / "examples").exists(), reason="reference checkout not present")
 
 EXPECTED = {

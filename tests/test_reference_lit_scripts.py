@@ -14,7 +14,9 @@ from pathlib import Path
 
 import pytest
 
-REFERENCE = Path("/root/reference")
+from conftest import reference_root  # noqa: E402
+
+REFERENCE = reference_root() or Path("reference-checkout-not-found")
 ROOT = Path(__file__).resolve().parent.parent
 pytestmark = pytest.mark.skipif(not (REFERENCE / "test" / "python").exists(), reason="reference checkout not present")
 
