@@ -24,7 +24,8 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu on the GPU box)")
     # the native library is built in-tree and is not under version control: build it when it is missing
     lib = ROOT / "tt-lang_b200" / "ttl_b200" / "libttlb200.so"
-    if not lib.exists():
+    runner = ROOT / "tt-lang_b200" / "ttl_b200" / "ttlang-b200-run"
+    if not lib.exists() or not runner.exists():
         import importlib.util
 
         spec = importlib.util.spec_from_file_location("ttlb200_build", ROOT / "tt-lang_b200" / "build.py")

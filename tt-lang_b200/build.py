@@ -20,6 +20,8 @@ ROOT = Path(__file__).resolve().parent
 CSRC = ROOT / "csrc"
 INCLUDE = ROOT.parent / "include"
 OUT = ROOT / "ttl_b200" / "libttlb200.so"
+CLI_SRC = ROOT / "cli" / "ttlang_b200_run.cpp"
+CLI_OUT = ROOT / "ttl_b200" / "ttlang-b200-run"    # the native runner, next to the library it loads
 OBJ_DIR = ROOT / "build"
 
 NVCC_FLAGS = [
@@ -80,6 +82,11 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if force or procs or not OUT.exists():
         cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-cudart", "static",
                "-o", str(OUT), *map(str, objs), "-ldl"]
+        subprocess.run(cmd, check=True)
+    if force or _newer(CLI_SRC, CLI_OUT, [OUT, *sorted(INCLUDE.glob("*.h"))]):
+        # host-only program over the C ABI; finds libttlb200.so in its own directory
+        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", f"-I{INCLUDE}", str(CLI_SRC), "-o", str(CLI_OUT), f"-L{OUT.parent}", "-lttlb200",
+               "-Xlinker", "-rpath=$ORIGIN", "-cudart", "static"]
         subprocess.run(cmd, check=True)
     return OUT
 
