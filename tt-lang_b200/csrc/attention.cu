@@ -41,13 +41,11 @@ constexpr int TILE_BYTES = 128 * 128 * 2;    // 32 KB: a 128 x 128 bf16 tile (Q 
 constexpr int CHUNK_BYTES = 128 * 64 * 2;    // 16 KB: 128 rows x 64 elements (one 128-byte swizzle span)
 constexpr int KV_STAGES = 2;
 constexpr int NT = 2;                         // query tiles per CTA
-constexpr int NPART = 2;                      // column halves per row: softmax thread = (tile, row, half)
+constexpr int NPART = 1;                      // one softmax thread per query row: it sees all 128 scores of a block
 constexpr int PCOLS = 128 / NPART;            // score / output columns per softmax thread
 constexpr int ATT_THREADS = 64 + NT * NPART * 128;
 constexpr int OFF_Q = 0, OFF_K = NT * TILE_BYTES, OFF_V = OFF_K + KV_STAGES * TILE_BYTES,
-              OFF_X = OFF_V + KV_STAGES * TILE_BYTES;  // X: row max / row sum exchange
-constexpr int XCH_BYTES = NT * 2 * NPART * 128 * 4;    // [tile][parity][half][row] floats
-constexpr int OFF_BAR = OFF_X + XCH_BYTES;
+              OFF_BAR = OFF_V + KV_STAGES * TILE_BYTES;
 constexpr int ATT_SMEM = OFF_BAR + 512 + 1024;
 constexpr float RESCALE_THRESHOLD = 8.0f;    // in log2 units
 
@@ -76,10 +74,9 @@ enum {
   B_VFULL = 5,    // [2]
   B_VEMPTY = 7,   // [2]
   B_SFULL = 9,    // [NT]
-  B_PFULL = 11,   // [NT][2]  count 4*NPART: the first / second 32 keys of each column half of P are written
+  B_PFULL = 11,   // [NT][2]  count 4 (the tile's softmax warps): keys [0, 64) / [64, 128) of P are written
   B_ODONE = 15,   // [NT]  a PV UMMA of the tile has completed
-  B_XCH = 17,     // [NT*4]  count 32*NPART (the threads of one tile that share a TMEM lane quarter)
-  B_COUNT = 25
+  B_COUNT = 17
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -106,7 +103,6 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   auto bar = [&](int i) { return base + OFF_BAR + 8u * i; };
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen + OFF_BAR + 8 * B_COUNT);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(gen + OFF_BAR + 8 * B_COUNT + 8);
-  float *xch = reinterpret_cast<float *>(gen + OFF_X);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heavy pairs first: with a causal mask the last query tiles have the most KV blocks
@@ -126,8 +122,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     *abort_flag = 0;
     for (int i = 0; i < B_COUNT; ++i) {
       uint32_t count = 1;
-      if (i >= B_PFULL && i < B_PFULL + 2 * NT) count = 4 * NPART;
-      if (i >= B_XCH) count = 32 * NPART;
+      if (i >= B_PFULL && i < B_PFULL + 2 * NT) count = 4;
       mbar_init(bar(i), count);
     }
     fence_barrier_init();
@@ -184,15 +179,15 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       };
       auto issue_pv = [&](int t, int j) -> bool {  // O_t (+)= P_t V_j; the caller has waited for V_j
         const uint32_t sv = base + OFF_V + (j & 1) * TILE_BYTES;
-        // P arrives in two steps: keys [0,32) + [64,96) first, then [32,64) + [96,128); the first half
-        // of the product runs under the second half of the exponentials
+        // P arrives in two steps: keys [0,64) first, then [64,128); the first half of the product runs under the
+        // second half of the exponentials
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if (!mbar_wait(bar(B_PFULL + t * 2 + h), (uint32_t)(j & 1), abort_flag, p.wait_limit)) return false;
           tc_fence_after();
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            const int kk = (i >> 1) * 4 + h * 2 + (i & 1);   // 16 keys = 8 columns (two bf16 per column) of P
+            const int kk = h * 4 + i;   // 16 keys = 8 columns (two bf16 per column) of P
             const uint64_t db = desc_mnmajor_sw128(sv, CHUNK_BYTES) + (uint64_t)(kk * 128);
             umma_f16_ts(tm_o + t * HD, tm_s + t * BKV + kk * 8, db, idesc_o, (j | h | i) != 0);
           }
@@ -229,54 +224,52 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
     }
   } else {
-    // ---- softmax warps: thread = (tile, query row, column half) ------------------------------
-    const int t = (warp - 2) >> 3;          // query tile of the pair
+    // ---- softmax warps: thread = (tile, query row); four warps per tile ------------------------
+    const int t = (warp - 2) >> 2;          // query tile of the pair
     const int q = warp & 3;                 // TMEM lane quarter this warp may access
-    const int part = ((warp - 2) & 7) >> 2; // which 64-wide half of the key / head-dim columns
     const int row = q * 32 + lane;          // row inside the query tile
     const int qt = 2 * pr + t;
     const int q_idx = qt * BQ + row;
     const int n_t = t == 0 ? n_a : n_b;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t my_s = tm_s + lane_addr + t * BKV, my_o = tm_o + lane_addr + t * HD + part * PCOLS;
+    const uint32_t my_s = tm_s + lane_addr + t * BKV, my_o = tm_o + lane_addr + t * HD;
     const float sl2e = p.scale_log2e;
-    float *xbase = xch + t * (2 * NPART * 128) + row;   // + parity * NPART * 128 + part * 128
-    const uint32_t xbar = bar(B_XCH + t * 4 + q);
     float m_used = -INFINITY, l_run = 0.f;
 
     for (int j = 0; j < n_t; ++j) {
       // the outcome of a wait is made the same for the whole warp: what follows is warp-collective
       if (!__all_sync(0xffffffffu, mbar_wait(bar(B_SFULL + t), (uint32_t)(j & 1), abort_flag, p.wait_limit))) { fail = 4; break; }
       tc_fence_after();
-      uint32_t s0[32], s1[32];
-      tmem_ld_32x32(my_s + part * PCOLS, s0);
-      tmem_ld_32x32(my_s + part * PCOLS + 32, s1);
+      uint32_t s0[32], s1[32], s2[32], s3[32];
+      tmem_ld_32x32(my_s, s0);
+      tmem_ld_32x32(my_s + 32, s1);
+      tmem_ld_32x32(my_s + 64, s2);
+      tmem_ld_32x32(my_s + 96, s3);
       tmem_ld_wait_dep(s0);
       tmem_ld_wait_dep(s1);
+      tmem_ld_wait_dep(s2);
+      tmem_ld_wait_dep(s3);
 
-      const int key0 = j * BKV + part * PCOLS;
+      const int key0 = j * BKV;
       if ((p.causal && j >= qt) || (j + 1) * BKV > p.seq) {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
           if ((p.causal && key0 + c > q_idx) || key0 + c >= p.seq) s0[c] = 0xff800000u;  // -inf
           if ((p.causal && key0 + 32 + c > q_idx) || key0 + 32 + c >= p.seq) s1[c] = 0xff800000u;
+          if ((p.causal && key0 + 64 + c > q_idx) || key0 + 64 + c >= p.seq) s2[c] = 0xff800000u;
+          if ((p.causal && key0 + 96 + c > q_idx) || key0 + 96 + c >= p.seq) s3[c] = 0xff800000u;
         }
       }
-      float mx0 = -INFINITY, mx1 = -INFINITY;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
         mx0 = max3(mx0, __uint_as_float(s0[c]), __uint_as_float(s0[c + 1]));
         mx1 = max3(mx1, __uint_as_float(s1[c]), __uint_as_float(s1[c + 1]));
+        mx2 = max3(mx2, __uint_as_float(s2[c]), __uint_as_float(s2[c + 1]));
+        mx3 = max3(mx3, __uint_as_float(s3[c]), __uint_as_float(s3[c + 1]));
       }
-      const float mx = fmaxf(mx0, mx1);
-      // exchange the block's row max with the partner warp (the other half of the same rows)
-      float *xrow = xbase + (j & 1) * NPART * 128;
-      xrow[part * 128] = mx;
-      mbar_arrive(xbar);
-      if (!__all_sync(0xffffffffu, mbar_wait(xbar, (uint32_t)(j & 1), abort_flag, p.wait_limit))) { fail = 4; break; }
-      const float m_new = fmaxf(m_used, fmaxf(mx, xrow[(part ^ 1) * 128]));
-      // raise the max used for the exponentials only when the true max has moved far; both
-      // threads of a row take the same decision from the same numbers
+      const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+      // raise the max used for the exponentials only when the true max has moved far
       float alpha = 1.0f;
       const bool raise = (m_new - m_used) * sl2e > RESCALE_THRESHOLD;
       if (raise) {
@@ -284,11 +277,12 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         m_used = m_new;
       }
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
-        // O_t *= alpha, after the last PV UMMA of this tile has landed and before the next is released
+        // O_t *= alpha (1 for the rows that keep their max), after the last PV UMMA of this tile has landed and
+        // before the next is released
         if (!__all_sync(0xffffffffu, mbar_wait(bar(B_ODONE + t), (uint32_t)((j - 1) & 1), abort_flag, p.wait_limit))) { fail = 4; break; }
         tc_fence_after();
 #pragma unroll 1
-        for (int h = 0; h < PCOLS / 16; ++h) {   // 16 columns at a time: this path must not cost registers
+        for (int h = 0; h < HD / 16; ++h) {   // 16 columns at a time: this path must not cost registers
           uint32_t r[16];
           tmem_ld_32x16_sync(my_o + h * 16, r);
 #pragma unroll
@@ -299,33 +293,30 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
       const float neg = -m_used * sl2e;
       float rs0 = 0.f, rs1 = 0.f;
-      {
-        uint32_t pk[16];
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s0[c]), sl2e, neg));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s0[c + 1]), sl2e, neg));
-          rs0 += p0;
-          rs1 += p1;
-          pk[c >> 1] = pack_bf16x2(p0, p1);
-        }
-        // P over the first 64 columns of the tile's score buffer: every thread of this lane quarter
-        // has read its scores (it arrived on the exchange barrier after its loads completed)
-        tmem_st_32x16(my_s + part * (PCOLS / 2), pk);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_PFULL + t * 2));
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(s1[c]), sl2e, neg));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(s1[c + 1]), sl2e, neg));
-          rs0 += p0;
-          rs1 += p1;
-          pk[c >> 1] = pack_bf16x2(p0, p1);
-        }
-        tmem_st_32x16(my_s + part * (PCOLS / 2) + 16, pk);
-      }
+      uint32_t pk[16];
+      // P (bf16 pairs) over the first 64 columns of the tile's score buffer; this thread is the only reader of its
+      // row of scores, which are all in registers by now
+#define TTLB_EXP_PACK(SRC)                                                                    \
+  _Pragma("unroll") for (int c = 0; c < 32; c += 2) {                                         \
+    const float p0 = fast_exp2(fmaf(__uint_as_float(SRC[c]), sl2e, neg));                     \
+    const float p1 = fast_exp2(fmaf(__uint_as_float(SRC[c + 1]), sl2e, neg));                 \
+    rs0 += p0;                                                                                \
+    rs1 += p1;                                                                                \
+    pk[c >> 1] = pack_bf16x2(p0, p1);                                                         \
+  }
+      TTLB_EXP_PACK(s0)
+      tmem_st_32x16(my_s, pk);
+      TTLB_EXP_PACK(s1)
+      tmem_st_32x16(my_s + 16, pk);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_PFULL + t * 2));
+      TTLB_EXP_PACK(s2)
+      tmem_st_32x16(my_s + 32, pk);
+      TTLB_EXP_PACK(s3)
+      tmem_st_32x16(my_s + 48, pk);
+#undef TTLB_EXP_PACK
       l_run = l_run * alpha + (rs0 + rs1);
       tmem_st_wait();
       tc_fence_before();
@@ -333,26 +324,20 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       if (lane == 0) mbar_arrive(bar(B_PFULL + t * 2 + 1));
     }
     if (!fail && n_t > 0) {
-      // the row sum of the other half, then O / l -> bf16
-      const int slot = n_t & 1;
-      float *xrow = xbase + slot * NPART * 128;
-      xrow[part * 128] = l_run;
-      mbar_arrive(xbar);
-      if (!__all_sync(0xffffffffu, mbar_wait(xbar, (uint32_t)slot, abort_flag, p.wait_limit) &&
-                                       mbar_wait(bar(B_ODONE + t), (uint32_t)((n_t - 1) & 1), abort_flag, p.wait_limit)))
-        fail = 4;
+      // O / l -> bf16
+      if (!__all_sync(0xffffffffu, mbar_wait(bar(B_ODONE + t), (uint32_t)((n_t - 1) & 1), abort_flag, p.wait_limit))) fail = 4;
       if (!fail) {
         tc_fence_after();
-        const float inv = 1.0f / (l_run + xrow[(part ^ 1) * 128]);
-        __nv_bfloat16 *dst = p.o + ((long long)bh * p.seq + q_idx) * HD + part * PCOLS;
+        const float inv = 1.0f / l_run;
+        __nv_bfloat16 *dst = p.o + ((long long)bh * p.seq + q_idx) * HD;
         if constexpr (PUB) {
-          // tcgen05.ld hands every thread one row (its 64 columns = 128 bytes); the rows go through a swizzled
-          // stage in the tile's own Q buffer - every score UMMA of the tile has completed, nothing reads Q any
-          // more - so that each store instruction of the warp writes four whole 128-byte half rows instead of
-          // 16 bytes to each of 32 rows, which through NVLink reaches a small fraction of the link rate
-          uint8_t *stage = gen + OFF_Q + t * TILE_BYTES + (q * NPART + part) * (32 * PCOLS * 2);
+          // tcgen05.ld hands every thread one row (256 bytes); the rows go through a swizzled stage in the tile's
+          // own Q buffer - every score UMMA of the tile has completed, nothing reads Q any more - so that each
+          // store instruction of the warp writes two whole rows instead of 16 bytes to each of 32 rows, which
+          // through NVLink reaches a small fraction of the link rate
+          uint8_t *stage = gen + OFF_Q + t * TILE_BYTES + q * (32 * HD * 2);
 #pragma unroll 1
-          for (int h = 0; h < PCOLS / 32; ++h) {
+          for (int h = 0; h < HD / 32; ++h) {
             uint32_t r[32];
             tmem_ld_32x32(my_o + h * 32, r);
             tmem_ld_wait_dep(r);
@@ -363,19 +348,19 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
               v.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]) * inv, __uint_as_float(r[8 * u + 3]) * inv);
               v.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]) * inv, __uint_as_float(r[8 * u + 5]) * inv);
               v.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]) * inv, __uint_as_float(r[8 * u + 7]) * inv);
-              const int unit = h * 4 + u;   // 16-byte unit within the 128-byte half row
-              *reinterpret_cast<uint4 *>(stage + lane * (PCOLS * 2) + ((unit ^ (lane & 7)) << 4)) = v;
+              const int unit = h * 4 + u;   // 16-byte unit within the 256-byte row
+              *reinterpret_cast<uint4 *>(stage + lane * (HD * 2) + ((unit ^ (lane & 7)) << 4)) = v;
             }
           }
           __syncwarp();
-          const int unit = lane & 7;
+          const int unit = lane & 15;
           const long long row0 = (long long)bh * p.seq + qt * BQ + q * 32;
 #pragma unroll 2
-          for (int i = 0; i < 8; ++i) {
-            const int rl = 4 * i + (lane >> 3);
-            const uint4 v = *reinterpret_cast<const uint4 *>(stage + rl * (PCOLS * 2) + ((unit ^ (rl & 7)) << 4));
+          for (int i = 0; i < 16; ++i) {
+            const int rl = 2 * i + (lane >> 4);
+            const uint4 v = *reinterpret_cast<const uint4 *>(stage + rl * (HD * 2) + ((unit ^ (rl & 7)) << 4));
             if (qt * BQ + q * 32 + rl < p.seq) {
-              const long long off = (row0 + rl) * HD + part * PCOLS + unit * 8;
+              const long long off = (row0 + rl) * HD + unit * 8;
               if (p.pub == 1) {
                 st_multimem_16(p.o + off, v);
               } else {
@@ -385,22 +370,22 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           }
         } else {
 #pragma unroll 1
-        for (int h = 0; h < PCOLS / 32; ++h) {
-          uint32_t r[32];
-          tmem_ld_32x32(my_o + h * 32, r);
-          tmem_ld_wait_dep(r);
-          if (q_idx < p.seq) {
+          for (int h = 0; h < HD / 32; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32(my_o + h * 32, r);
+            tmem_ld_wait_dep(r);
+            if (q_idx < p.seq) {
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              uint4 v;
-              v.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]) * inv, __uint_as_float(r[8 * u + 1]) * inv);
-              v.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]) * inv, __uint_as_float(r[8 * u + 3]) * inv);
-              v.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]) * inv, __uint_as_float(r[8 * u + 5]) * inv);
-              v.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]) * inv, __uint_as_float(r[8 * u + 7]) * inv);
-              *reinterpret_cast<uint4 *>(dst + h * 32 + 8 * u) = v;
+              for (int u = 0; u < 4; ++u) {
+                uint4 v;
+                v.x = pack_bf16x2(__uint_as_float(r[8 * u + 0]) * inv, __uint_as_float(r[8 * u + 1]) * inv);
+                v.y = pack_bf16x2(__uint_as_float(r[8 * u + 2]) * inv, __uint_as_float(r[8 * u + 3]) * inv);
+                v.z = pack_bf16x2(__uint_as_float(r[8 * u + 4]) * inv, __uint_as_float(r[8 * u + 5]) * inv);
+                v.w = pack_bf16x2(__uint_as_float(r[8 * u + 6]) * inv, __uint_as_float(r[8 * u + 7]) * inv);
+                *reinterpret_cast<uint4 *>(dst + h * 32 + 8 * u) = v;
+              }
             }
           }
-        }
         }
       }
     }
@@ -494,10 +479,11 @@ static int attention_impl(ttlb_ctx *ctx, const ttlb_attn_desc *d, int pub, void 
   p.wait_limit = ctx->wait_limit_cycles;
   const long long grid = (long long)p.q_pairs * p.bh;
   if (grid > 0x7fffffffLL) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "attention: too many tiles");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (pub)
-    ttlb_attention_kernel<true><<<(unsigned)grid, ATT_THREADS, ATT_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
+    ttlb_attention_kernel<true><<<(unsigned)grid, ATT_THREADS, ATT_SMEM, st>>>(mq, mk, mv, p);
   else
-    ttlb_attention_kernel<false><<<(unsigned)grid, ATT_THREADS, ATT_SMEM, reinterpret_cast<cudaStream_t>(stream)>>>(mq, mk, mv, p);
+    ttlb_attention_kernel<false><<<(unsigned)grid, ATT_THREADS, ATT_SMEM, st>>>(mq, mk, mv, p);
   TTLB_CUDA_CHECK(ctx, cudaGetLastError());
   ctx->launches += 1;
   return TTLB_OK;
