@@ -5,7 +5,7 @@
 // in the tree); this is the tile program "for each KV block: S = Q @ K^T; online-softmax update;
 // O += P @ V" written directly as a B200 kernel.
 //
-// One CTA per (batch*head, PAIR of 128-query tiles), 576 threads.  The two query tiles A and B
+// One CTA per (batch*head, PAIR of 128-query tiles), 320 threads.  The two query tiles A and B
 // share every K / V block (loaded once) and take turns on the tensor pipe, so the softmax of one
 // tile runs under the UMMAs of the other:
 //   warp 0      TMA producer: Q_A, Q_B once; K and V blocks (128 keys) through 2-stage rings
@@ -14,14 +14,19 @@
 //               (A operand) and O_T accumulated in tensor memory.  Issue order
 //               ... PV_A(j), S_A(j+1), PV_B(j), S_B(j+1) ...; UMMAs execute in issue order, which is
 //               what makes S_T(j+1) safe to overwrite the P_T(j) that aliases its buffer.
-//   warps 2..17 softmax, 8 warps per tile: thread (row, half) reads its 64 scores with tcgen05.ld,
-//               exchanges the row max with its partner through shared memory, writes P (bf16 pairs)
-//               with tcgen05.st over the first 64 columns of the score buffer, and keeps only the
+//   warps 2..9  softmax, 4 warps per tile, ONE THREAD PER QUERY ROW: the thread reads its 128 scores with
+//               tcgen05.ld, takes their maximum without talking to any other thread, writes P (bf16 pairs)
+//               with tcgen05.st over the first 64 columns of the score buffer - keys [0, 64) first, so that
+//               the first half of P*V runs under the second half of the exponentials - and keeps only the
 //               running max and sum.  O is rescaled LAZILY: the max used for the exponentials is
 //               raised only when the true max has grown by more than 2^8 (P stays below 256, exact
-//               enough in bf16 and fp32); when it is, the threads wait for the last PV UMMA of
-//               their tile and multiply their 64 columns of O in tensor memory by the correction.
-//               At the end they read O once, divide by the row sum and store bf16.
+//               enough in bf16 and fp32); when it is, the warp waits for the last PV UMMA of
+//               its tile and multiplies its rows of O in tensor memory by the correction.
+//               At the end the threads read O once, divide by the row sum and store bf16.
+//               (Two threads per row - 16 softmax warps - cost an exchange of the row maximum through shared
+//               memory in every block and were 4 % slower; a polynomial exp2 on the FMA pipe for part of
+//               the exponentials was slower in both layouts: the softmax warps are bound by instruction
+//               issue and by the chain score -> P -> next score, not by the special-function unit.)
 // Tensor memory: S_A, S_B, O_A, O_B, 128 columns each.  Shared memory: Q_A, Q_B, K[2], V[2] of 32 KB.
 // The shared-memory data path is the scarce resource (a 128x128x128 UMMA with both operands in
 // shared memory reads 512 wavefronts of 128 bytes in its 512 cycles): P and O never touch it, and
@@ -42,7 +47,6 @@ constexpr int CHUNK_BYTES = 128 * 64 * 2;    // 16 KB: 128 rows x 64 elements (o
 constexpr int KV_STAGES = 2;
 constexpr int NT = 2;                         // query tiles per CTA
 constexpr int NPART = 1;                      // one softmax thread per query row: it sees all 128 scores of a block
-constexpr int PCOLS = 128 / NPART;            // score / output columns per softmax thread
 constexpr int ATT_THREADS = 64 + NT * NPART * 128;
 constexpr int OFF_Q = 0, OFF_K = NT * TILE_BYTES, OFF_V = OFF_K + KV_STAGES * TILE_BYTES,
               OFF_BAR = OFF_V + KV_STAGES * TILE_BYTES;
