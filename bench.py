@@ -283,7 +283,7 @@ SHARDED_WORKLOADS = ("matmul_bf16_8192", "matmul_bfp8w", "attention")
 TRAFFIC_BYTES = {
     "fused_eltwise_bcast_8192": 366.0e6,     # profiles/eltwise_jit_fused_bcast_8192.md (268.5 MB read + 97.6 MB written)
     "matmul_bf16_8192": 1331.0e6 + 134.2e6,  # profiles/gemm_bf16_8192.md (operands re-read from L2 misses + C written)
-    "matmul_bfp8w": None,
+    "matmul_bfp8w": 778.0e6 + 224.0e6,        # profiles/matmul_bfp8w_4096x8192x28672.md (unpack kernel + GEMM of one step)
     "attention": 805.0e6 + 249.0e6,          # profiles/attention_b8_h32_s4096_d128.md
     "eltwise_add_1024": None,
 }
