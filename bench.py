@@ -515,8 +515,11 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
     dev_in = [t.to(dev) for t in host_in]
     gather = "nccl all-gather"
     mode = gather_mode
-    if mode == "auto":   # measured on 2 GPUs: publication from the kernel's epilogue beats every separate gather
-        mode = "fused"
+    if mode == "auto":
+        # measured on 2 and 4 GPUs: publication from the kernel's epilogue beats every separate gather; through the
+        # switch (multimem.st) for the matmuls, and for attention on 2 GPUs; attention on 4 GPUs is faster with plain
+        # peer stores (0.365 against 0.399 ms)
+        mode = "peers" if (wl == "attention" and world >= 4) else "fused"
     rounds_used = None
     if world > 1 and mode != "nccl":
         so, why = None, ""

@@ -67,7 +67,11 @@ TTLB_EXPORT const char *ttlb_version(void);
 /* Create / destroy a context bound to CUDA device `device_ordinal`.
  * Replaces ttnn.open_device / close_device in user code
  * (python/sim/ttnnsim.py:218-226).  ttlb_init fails with TTLB_ERR_CUDA when no
- * usable sm_100 device is present: there is no CPU fallback. */
+ * usable sm_100 device is present: there is no CPU fallback.
+ * A context is used by one host thread and ONE STREAM at a time: the bf16 expansion of block-float weights, the
+ * partial rows and arrival counters of reductions over rows and the status word are scratch memory owned by the
+ * context and shared by all its launches without ordering between streams.  Callers that want concurrent streams on
+ * one GPU create one context per stream. */
 TTLB_EXPORT int ttlb_init(int device_ordinal, ttlb_ctx **out);
 TTLB_EXPORT void ttlb_destroy(ttlb_ctx *ctx);
 
