@@ -24,6 +24,7 @@ import torch, ttnn
 import cases
 import eltwise as E
 import matmul as M
+import reduce as R
 
 case = cases.by_name("fused_f32_256x512")
 ins = [ttnn.from_torch(t) for t in case.make_inputs()]
@@ -37,6 +38,13 @@ M.multicore_matmul(ttnn.from_torch(a), ttnn.from_torch(b), c)
 w = cases.gen((192, 320), "normal*0.02", 2, torch.float32)
 c2 = ttnn.from_torch(torch.zeros((256, 320), dtype=torch.bfloat16))
 M.multicore_matmul(ttnn.from_torch(a), ttnn.from_torch(w, dtype=ttnn.bfloat8_b), c2)
+
+x = cases.gen((128, 256), "normal", 7)
+ones = ttnn.from_torch(torch.ones(32, 32, dtype=torch.bfloat16))
+s1 = ttnn.from_torch(torch.zeros((128, 1), dtype=torch.bfloat16))
+R.make_reduce("sum", [1])(ttnn.from_torch(x), ones, s1)
+y = ttnn.from_torch(torch.zeros((128, 256), dtype=torch.bfloat16))
+R.make_softmax(fp32_dest_acc_en=True)(ttnn.from_torch(x), ones, y)
 '''
 
 
@@ -54,14 +62,16 @@ def emitted(tmp_path_factory):
 
 def test_emitted_plans_describe_the_launches_and_tensors(emitted):
     kinds = []
-    for i in range(3):
+    for i in range(5):
         plan = json.loads((emitted / f"call{i}" / "plan.json").read_text())
         kinds.append([l["kind"] for l in plan["launches"]])
         for t in plan["tensors"]:
             size = (emitted / f"call{i}" / t["file"]).stat().st_size
             r, c = t["shape"]
             assert size == {"bf16": r * c * 2, "f32": r * c * 4, "bfp8_b": (r // 32) * (c // 32) * 1088}[t["dtype"]]
-    assert kinds == [["eltwise"], ["matmul_bf16"], ["matmul_bfp8w"]]
+    assert kinds[:3] == [["eltwise"], ["matmul_bf16"], ["matmul_bfp8w"]]
+    more = [[l["kind"] for l in json.loads((emitted / f"call{i}" / "plan.json").read_text())["launches"]] for i in (3, 4)]
+    assert more == [["reduce_sum"], ["row_fused"]]
     first = json.loads((emitted / "call0" / "plan.json").read_text())["launches"][0]
     assert len(first["opcodes"]) == len(first["ops"]) and first["round_each_op"] is False
 
@@ -107,3 +117,15 @@ def test_runner_reproduces_the_python_backend_bit_for_bit(emitted, backend):
     got = run(2, 2, (256, 320))
     want = tile_oracle.matmul_tiles(a.float(), wq, "f32")
     assert ((got.float() - want.float()).abs().max() / want.float().abs().max()).item() <= 1e-2
+    # a reduction over columns and the row-resident softmax: the same bits as through `@ttl.kernel`
+    x = cases.gen((128, 256), "normal", 7)
+    ones = ttnn.from_torch(torch.ones(32, 32, dtype=torch.bfloat16))
+    s1 = ttnn.from_torch(torch.zeros((128, 1), dtype=torch.bfloat16))
+    mods["reduce"].make_reduce("sum", [1])(ttnn.from_torch(x), ones, s1)
+    assert torch.equal(run(3, 2, (128, 1)), ttnn.to_torch(s1))
+    y = ttnn.from_torch(torch.zeros((128, 256), dtype=torch.bfloat16))
+    mods["reduce"].make_softmax(fp32_dest_acc_en=True)(ttnn.from_torch(x), ones, y)
+    got = run(4, 2, (128, 256))
+    assert torch.equal(got, ttnn.to_torch(y))
+    want = torch.softmax(x.double(), dim=1)
+    assert ((got.double() - want).abs() <= 2.0 ** -6 * want + 1e-7).all()

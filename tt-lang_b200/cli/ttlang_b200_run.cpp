@@ -10,7 +10,8 @@
 // device memory, issues the launches through the C ABI of libttlb200 (include/ttlb200.h), times them with CUDA
 // events on the launching stream, and writes every tensor a launch wrote to `<file>.out`.
 //
-// Supported launch kinds: eltwise, matmul_bf16 (optional bias / activation), matmul_f32, matmul_bfp8w.
+// Supported launch kinds: eltwise, reduce_sum / reduce_max, row_fused, matmul_bf16 (optional bias / activation),
+// matmul_f32, matmul_bfp8w.
 // One JSON line on stdout: {"launches": n, "steps": k, "ms_per_step": t, "outputs": [...]}.
 #include <cuda_runtime.h>
 
@@ -200,6 +201,73 @@ int main(int argc, char **argv) {
     return args[(size_t)idx];
   };
 
+  // the element-wise program of a launch (`l`: inputs, opcodes, imm, round_each_op) over rows [row0, +rows) x columns
+  // [col0, +cols); operands named in `produced` stand for results of earlier phases of a row-fused launch
+  auto fill_program = [&](ttlb_eltwise_desc &d, const Json &l, const Tensor &like, const std::map<int64_t, int> *produced) {
+    memset(&d, 0, sizeof(d));
+    d.dtype = like.dtype == "f32" ? TTLB_F32 : TTLB_BF16;
+    d.round_each_op = l.at("round_each_op").b ? 1 : 0;
+    const std::vector<Json> &ins = l.at("inputs").arr;
+    const std::vector<Json> &ops = l.at("opcodes").arr;
+    d.n_in = (int32_t)ins.size();
+    d.n_ops = (int32_t)ops.size();
+    if (d.n_in > TTLB_MAX_IN || d.n_ops > TTLB_MAX_OPS) { fprintf(stderr, "plan: launch too large\n"); exit(2); }
+    for (int k = 0; k < d.n_in; ++k) {
+      const std::vector<Json> &v = ins[(size_t)k].arr;
+      const int64_t ti = v[0].i();
+      if (produced && produced->count(ti)) {
+        d.in[k].ptr = nullptr;
+        d.in[k].row_mode = TTLB_IDX_PHASE;
+        d.in[k].row_off = produced->at(ti);
+        d.in[k].col_mode = TTLB_IDX_ZERO;
+        d.in[k].col_off = 0;
+        d.in[k].ld = 1;
+        continue;
+      }
+      Tensor &t = tensor(ti);
+      d.in[k].ptr = t.dev;
+      d.in[k].ld = t.rows > 1 ? t.ld() : t.cols;
+      d.in[k].row_mode = (int32_t)v[1].i();
+      d.in[k].row_off = v[2].i();
+      d.in[k].col_mode = (int32_t)v[3].i();
+      d.in[k].col_off = v[4].i();
+    }
+    for (int k = 0; k < d.n_ops; ++k) {
+      d.ops[k].opcode = (int16_t)ops[(size_t)k].arr[0].i();
+      d.ops[k].arg = (int16_t)ops[(size_t)k].arr[1].i();
+    }
+    if (l.has("imm"))
+      for (size_t k = 0; k < l.at("imm").arr.size() && k < TTLB_MAX_IMM; ++k) d.imm[k] = (float)l.at("imm").arr[k].num;
+  };
+  // a reduction launch (`l`: kind reduce_sum / reduce_max, dims, rect_tiles, reduced_tiles, scaler) as a descriptor
+  auto fill_reduce = [&](ttlb_reduce_desc &r, const Json &l, const std::map<int64_t, int> *produced, bool with_out) {
+    Tensor &out = tensor(l.at("out").i());
+    fill_program(r.src, l, out, produced);
+    const std::vector<Json> &rt = l.at("rect_tiles").arr;
+    const std::vector<Json> &ext = l.at("reduced_tiles").arr;
+    bool rows_reduced = false, cols_reduced = false;
+    for (const Json &dm : l.at("dims").arr) (dm.i() == 0 ? rows_reduced : cols_reduced) = true;
+    r.src.row0 = rows_reduced ? 0 : rt[0].i() * 32;
+    r.src.rows = rows_reduced ? ext[0].i() * 32 : (rt[1].i() - rt[0].i()) * 32;
+    r.src.col0 = cols_reduced ? 0 : rt[2].i() * 32;
+    r.src.cols = cols_reduced ? ext[1].i() * 32 : (rt[3].i() - rt[2].i()) * 32;
+    r.op = l.at("kind").str == "reduce_sum" ? TTLB_REDUCE_SUM : TTLB_REDUCE_MAX;
+    r.dims = (rows_reduced ? TTLB_REDUCE_ROWS : 0) | (cols_reduced ? TTLB_REDUCE_COLS : 0);
+    const int es = out.esz();
+    r.out_ld = out.rows > 1 ? out.ld() : out.cols;
+    const int64_t orow = out.rows == 1 ? 0 : rt[0].i() * 32, ocol = out.cols == 1 ? 0 : rt[2].i() * 32;
+    r.fill_rows = out.rows == 1 ? 1 : 32;
+    r.fill_cols = out.cols == 1 ? 1 : 32;
+    r.out = with_out ? (char *)out.dev + (orow * r.out_ld + ocol) * es : nullptr;
+    r.scaler = nullptr;
+    if (l.has("scaler")) {
+      const std::vector<Json> &sc = l.at("scaler").arr;
+      Tensor &st = tensor(sc[0].i());
+      r.scaler = (char *)st.dev + (sc[1].i() * (st.rows > 1 ? st.ld() : 0) + sc[2].i()) * es;
+    }
+    if (with_out) out.written = true;
+  };
+
   cudaStream_t stream;
   CUDA_OK(cudaStreamCreate(&stream));
   const std::vector<Json> &launches = plan.at("launches").arr;
@@ -213,30 +281,7 @@ int main(int argc, char **argv) {
       int st = TTLB_OK;
       if (kind == "eltwise") {
         ttlb_eltwise_desc d;
-        memset(&d, 0, sizeof(d));
-        d.dtype = out.dtype == "f32" ? TTLB_F32 : TTLB_BF16;
-        d.round_each_op = l.at("round_each_op").b ? 1 : 0;
-        const std::vector<Json> &ins = l.at("inputs").arr;
-        const std::vector<Json> &ops = l.at("opcodes").arr;
-        d.n_in = (int32_t)ins.size();
-        d.n_ops = (int32_t)ops.size();
-        if (d.n_in > TTLB_MAX_IN || d.n_ops > TTLB_MAX_OPS) { fprintf(stderr, "plan: launch too large\n"); exit(2); }
-        for (int k = 0; k < d.n_in; ++k) {
-          const std::vector<Json> &v = ins[(size_t)k].arr;
-          Tensor &t = tensor(v[0].i());
-          d.in[k].ptr = t.dev;
-          d.in[k].ld = t.rows > 1 ? t.ld() : t.cols;
-          d.in[k].row_mode = (int32_t)v[1].i();
-          d.in[k].row_off = v[2].i();
-          d.in[k].col_mode = (int32_t)v[3].i();
-          d.in[k].col_off = v[4].i();
-        }
-        for (int k = 0; k < d.n_ops; ++k) {
-          d.ops[k].opcode = (int16_t)ops[(size_t)k].arr[0].i();
-          d.ops[k].arg = (int16_t)ops[(size_t)k].arr[1].i();
-        }
-        if (l.has("imm"))
-          for (size_t k = 0; k < l.at("imm").arr.size() && k < TTLB_MAX_IMM; ++k) d.imm[k] = (float)l.at("imm").arr[k].num;
+        fill_program(d, l, out, nullptr);
         d.out = out.dev;
         d.out_ld = out.ld();
         const bool deg_r = out.rows == 1, deg_c = out.cols == 1;
@@ -245,6 +290,29 @@ int main(int argc, char **argv) {
         d.col0 = deg_c ? 0 : c0;
         d.cols = deg_c ? 1 : c1 - c0;
         st = ttlb_eltwise(ctx, &d, stream);
+      } else if (kind == "reduce_sum" || kind == "reduce_max") {
+        ttlb_reduce_desc r;
+        fill_reduce(r, l, nullptr, true);
+        st = ttlb_reduce(ctx, &r, stream);
+      } else if (kind == "row_fused") {
+        // reductions over columns whose results stay on chip, then the element-wise program that reads them
+        static ttlb_rowfused_desc f;
+        memset(&f, 0, sizeof(f));
+        const std::vector<Json> &phases = l.at("phases").arr;
+        if (phases.size() > TTLB_MAX_PHASES) { fprintf(stderr, "plan: too many phases\n"); exit(2); }
+        std::map<int64_t, int> produced;
+        for (size_t i = 0; i < phases.size(); ++i) produced[phases[i].at("out").i()] = (int)i;
+        f.n_phases = (int32_t)phases.size();
+        for (size_t i = 0; i < phases.size(); ++i) fill_reduce(f.phase[i], phases[i], &produced, false);
+        const Json &fin = l.at("final");
+        fill_program(f.final, fin, out, &produced);
+        f.final.out = out.dev;
+        f.final.out_ld = out.ld();
+        f.final.row0 = r0;
+        f.final.rows = r1 - r0;
+        f.final.col0 = c0;
+        f.final.cols = c1 - c0;
+        st = ttlb_rowfused(ctx, &f, stream);
       } else if (kind == "matmul_bf16" || kind == "matmul_f32") {
         Tensor &a = tensor(l.at("a").i()), &b = tensor(l.at("b").i());
         const int es = a.esz();
@@ -288,7 +356,7 @@ int main(int argc, char **argv) {
         g.k = a.cols;
         st = ttlb_matmul_bfp8w(ctx, &g, stream);
       } else {
-        fprintf(stderr, "launch kind \"%s\" is not supported by this tool (eltwise, matmul_bf16, matmul_f32, matmul_bfp8w)\n", kind.c_str());
+        fprintf(stderr, "launch kind \"%s\" is not supported by this tool (eltwise, reduce_sum, reduce_max, row_fused, matmul_bf16, matmul_f32, matmul_bfp8w)\n", kind.c_str());
         exit(2);
       }
       if (st != TTLB_OK) { fprintf(stderr, "launch \"%s\" failed (%d): %s\n", kind.c_str(), st, ttlb_last_error(ctx)); exit(3); }

@@ -50,14 +50,18 @@ def emit_plan(plan: Any, tensors: Any, directory: Path) -> None:
     table = [_tensor_entry(t, directory, f"t{k}.bin") for k, t in enumerate(allt)]
     temps = [{"shape": list(t._tensor.shape) if t._tensor.numel() else [0, 0],
               "dtype": {torch.bfloat16: "bf16", torch.float32: "f32"}[t._tensor.dtype]} for t in plan.temps]
-    launches = []
-    for d in plan.describe():
+    def numeric(d: dict) -> dict:
         d = dict(d)
         if "ops" in d:
             d["opcodes"] = [[capi.OPCODES[op], arg] for op, arg in d["ops"]]
         if d.get("act"):
             d["act_code"] = capi.ACTIVATIONS[d["act"]]
-        launches.append(d)
+        if "phases" in d:
+            d["phases"] = [numeric(ph) for ph in d["phases"]]
+            d["final"] = numeric(d["final"])
+        return d
+
+    launches = [numeric(d) for d in plan.describe()]
     (directory / "plan.json").write_text(json.dumps({"tensors": table, "temps": temps, "launches": launches}, indent=1))
 
 
