@@ -1194,10 +1194,13 @@ def main():
             for wl in SHARDED_WORKLOADS:
                 gc.collect()
                 torch.cuda.empty_cache()
-                workloads[wl] = measure_sharded(args, wl, env)
+                try:
+                    workloads[wl] = measure_sharded(args, wl, env)
+                except Exception as e:   # a workload that fails the same way on every rank must not cost the whole line
+                    workloads[wl] = {"error": f"{type(e).__name__}: {e}"[:300]}
             line["workloads"] = workloads
             if env.world > 1:
-                line["sharded_efficiency"] = {wl: workloads[wl]["sharded_efficiency"] for wl in SHARDED_WORKLOADS}
+                line["sharded_efficiency"] = {wl: workloads[wl].get("sharded_efficiency") for wl in SHARDED_WORKLOADS}
             line["gpu_launches_all_workloads"] = line["gpu_launches"] + sum(
                 w.get("gpu_launches", 0) + w.get("gpu_launches_per_step", 0) * w.get("steps", 0) for w in workloads.values())
         if env.rank == 0:
