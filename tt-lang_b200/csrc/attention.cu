@@ -5,7 +5,7 @@
 // in the tree); this is the tile program "for each KV block: S = Q @ K^T; online-softmax update;
 // O += P @ V" written directly as a B200 kernel.
 //
-// One CTA per (batch*head, PAIR of 128-query tiles), 320 threads.  The two query tiles A and B
+// One CTA per (batch*head, PAIR of 128-query tiles), 384 threads.  The two query tiles A and B
 // share every K / V block (loaded once) and take turns on the tensor pipe, so the softmax of one
 // tile runs under the UMMAs of the other:
 //   warp 0      TMA producer: Q_A, Q_B once; K and V blocks (128 keys) through 2-stage rings
@@ -14,7 +14,10 @@
 //               (A operand) and O_T accumulated in tensor memory.  Issue order
 //               ... PV_A(j), S_A(j+1), PV_B(j), S_B(j+1) ...; UMMAs execute in issue order, which is
 //               what makes S_T(j+1) safe to overwrite the P_T(j) that aliases its buffer.
-//   warps 2..9  softmax, 4 warps per tile, ONE THREAD PER QUERY ROW: the thread reads its 128 scores with
+//   warps 2, 3  idle: with warps 0 and 1 they form the warpgroup that gives its registers away (setmaxnreg:
+//               56 per thread there, 224 per softmax thread - the softmax holds a row's 128 scores, its 16 packed
+//               probabilities and the running statistics in registers and schedules better with room to spare)
+//   warps 4..11 softmax, 4 warps per tile, ONE THREAD PER QUERY ROW: the thread reads its 128 scores with
 //               tcgen05.ld, takes their maximum without talking to any other thread, writes P (bf16 pairs)
 //               with tcgen05.st over the first 64 columns of the score buffer - keys [0, 64) first, so that
 //               the first half of P*V runs under the second half of the exponentials - and keeps only the
@@ -26,7 +29,12 @@
 //               (Two threads per row - 16 softmax warps - cost an exchange of the row maximum through shared
 //               memory in every block and were 4 % slower; a polynomial exp2 on the FMA pipe for part of
 //               the exponentials was slower in both layouts: the softmax warps are bound by instruction
-//               issue and by the chain score -> P -> next score, not by the special-function unit.)
+//               issue and by the chain score -> P -> next score, not by the special-function unit.
+//               The scale-and-subtract and the row sum use packed fp32 pairs (fma / add .f32x2).
+//               Measured and not kept: scores in two 64-key halves with the second half computed ahead
+//               (twice as many, less efficient UMMAs: the tensor pipe became the limit); one UMMA
+//               issuer thread per tile (their instructions interleave and the pipe switches accumulator
+//               at every instruction).)
 // Tensor memory: S_A, S_B, O_A, O_B, 128 columns each.  Shared memory: Q_A, Q_B, K[2], V[2] of 32 KB.
 // The shared-memory data path is the scarce resource (a 128x128x128 UMMA with both operands in
 // shared memory reads 512 wavefronts of 128 bytes in its 512 cycles): P and O never touch it, and
@@ -47,7 +55,12 @@ constexpr int CHUNK_BYTES = 128 * 64 * 2;    // 16 KB: 128 rows x 64 elements (o
 constexpr int KV_STAGES = 2;
 constexpr int NT = 2;                         // query tiles per CTA
 constexpr int NPART = 1;                      // one softmax thread per query row: it sees all 128 scores of a block
-constexpr int ATT_THREADS = 64 + NT * NPART * 128;
+constexpr int SM_WARP0 = 4;                   // warps 0-3: TMA producer, UMMA issuer, two idle (the register donors)
+constexpr int ATT_THREADS = SM_WARP0 * 32 + NT * NPART * 128;
+// Registers move from the first warpgroup to the softmax warps (setmaxnreg); 128 * REG_LOW + 256 * REG_HIGH must not
+// exceed what the CTA was launched with (384 threads x 168), or the raise would wait for registers for ever.
+constexpr int REG_LOW = 56, REG_HIGH = 224;
+static_assert(128 * REG_LOW + 256 * REG_HIGH <= ATT_THREADS * 168, "register pool of the CTA exceeded");
 constexpr int OFF_Q = 0, OFF_K = NT * TILE_BYTES, OFF_V = OFF_K + KV_STAGES * TILE_BYTES,
               OFF_BAR = OFF_V + KV_STAGES * TILE_BYTES;
 constexpr int ATT_SMEM = OFF_BAR + 512 + 1024;
@@ -87,6 +100,54 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+
+// ---- packed fp32 pairs: one instruction works on two values (fma / add .f32x2), which halves the issue slots the
+// softmax spends on the scale-and-subtract and on the row sum
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+typedef unsigned long long f2_t;
+__device__ __forceinline__ f2_t f2_pack(float lo, float hi) {
+  f2_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ f2_t f2_pack_u(uint32_t lo, uint32_t hi) {
+  f2_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(f2_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f2_t f2_fma(f2_t a, f2_t b, f2_t c) {
+  f2_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ f2_t f2_add(f2_t a, f2_t b) {
+  f2_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
+// 32 scores -> 32 probabilities exp2(s * scale - max * scale) as 16 bf16 pairs; the row sum is kept as a pair
+__device__ __forceinline__ void exp_pack32(const uint32_t (&src)[32], f2_t sl2e2, f2_t neg2, f2_t &rs2, uint32_t (&pk)[16]) {
+#pragma unroll
+  for (int c = 0; c < 32; c += 2) {
+    float a0, a1;
+    f2_unpack(f2_fma(f2_pack_u(src[c], src[c + 1]), sl2e2, neg2), a0, a1);
+    const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+    rs2 = f2_add(rs2, f2_pack(p0, p1));
+    pk[c >> 1] = pack_bf16x2(p0, p1);
+  }
 }
 
 // 16-byte store to a multicast address: the switch replicates it to every GPU of the group.
@@ -145,7 +206,9 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   const uint32_t tm_s = tmem_base, tm_o = tmem_base + NT * BKV;  // S_A, S_B at columns 0 / 128; O_A, O_B at 256 / 384
 
   int fail = 0;
+  // every role branch starts with its own register move: after a join the lower limit would apply to all
   if (warp == 0) {
+    reg_dec<REG_LOW>();
     if (lane == 0) {
       mbar_expect_tx(bar(B_QFULL), (n_b > 0 ? 2 : 1) * TILE_BYTES);
       for (int t = 0; t < NT; ++t) {
@@ -167,6 +230,7 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
     }
   } else if (warp == 1) {
+    reg_dec<REG_LOW>();
     if (lane == 0) {
       constexpr uint32_t idesc_s = idesc_bf16(BQ, BKV, false, false);  // Q (K-major) x K^T (K-major)
       constexpr uint32_t idesc_o = idesc_bf16(BQ, HD, false, true);    // P (tensor memory) x V (N-major)
@@ -227,9 +291,12 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (!fail && more) umma_commit(bar(B_KEMPTY + (s ^ 1)));
       }
     }
+  } else if (warp < SM_WARP0) {
+    reg_dec<REG_LOW>();
   } else {
+    reg_inc<REG_HIGH>();
     // ---- softmax warps: thread = (tile, query row); four warps per tile ------------------------
-    const int t = (warp - 2) >> 2;          // query tile of the pair
+    const int t = (warp - SM_WARP0) >> 2;          // query tile of the pair
     const int q = warp & 3;                 // TMEM lane quarter this warp may access
     const int row = q * 32 + lane;          // row inside the query tile
     const int qt = 2 * pr + t;
@@ -295,32 +362,25 @@ ttlb_attention_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         }
         tmem_st_wait();
       }
-      const float neg = -m_used * sl2e;
-      float rs0 = 0.f, rs1 = 0.f;
+      const f2_t neg2 = f2_pack(-m_used * sl2e, -m_used * sl2e), sl2e2 = f2_pack(sl2e, sl2e);
+      f2_t rs2 = f2_pack(0.f, 0.f);
       uint32_t pk[16];
       // P (bf16 pairs) over the first 64 columns of the tile's score buffer; this thread is the only reader of its
       // row of scores, which are all in registers by now
-#define TTLB_EXP_PACK(SRC)                                                                    \
-  _Pragma("unroll") for (int c = 0; c < 32; c += 2) {                                         \
-    const float p0 = fast_exp2(fmaf(__uint_as_float(SRC[c]), sl2e, neg));                     \
-    const float p1 = fast_exp2(fmaf(__uint_as_float(SRC[c + 1]), sl2e, neg));                 \
-    rs0 += p0;                                                                                \
-    rs1 += p1;                                                                                \
-    pk[c >> 1] = pack_bf16x2(p0, p1);                                                         \
-  }
-      TTLB_EXP_PACK(s0)
+      exp_pack32(s0, sl2e2, neg2, rs2, pk);
       tmem_st_32x16(my_s, pk);
-      TTLB_EXP_PACK(s1)
+      exp_pack32(s1, sl2e2, neg2, rs2, pk);
       tmem_st_32x16(my_s + 16, pk);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_PFULL + t * 2));
-      TTLB_EXP_PACK(s2)
+      exp_pack32(s2, sl2e2, neg2, rs2, pk);
       tmem_st_32x16(my_s + 32, pk);
-      TTLB_EXP_PACK(s3)
+      exp_pack32(s3, sl2e2, neg2, rs2, pk);
       tmem_st_32x16(my_s + 48, pk);
-#undef TTLB_EXP_PACK
+      float rs0, rs1;
+      f2_unpack(rs2, rs0, rs1);
       l_run = l_run * alpha + (rs0 + rs1);
       tmem_st_wait();
       tc_fence_before();
