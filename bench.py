@@ -284,6 +284,7 @@ TRAFFIC_BYTES = {
     "fused_eltwise_bcast_8192": 366.0e6,     # profiles/eltwise_jit_fused_bcast_8192.md (268.5 MB read + 97.6 MB written)
     "matmul_bf16_8192": 1331.0e6 + 134.2e6,  # profiles/gemm_bf16_8192.md (operands re-read from L2 misses + C written)
     "matmul_bfp8w": 778.0e6 + 224.0e6,        # profiles/matmul_bfp8w_4096x8192x28672.md (unpack kernel + GEMM of one step)
+    "matmul_bfp8w_in_mainloop": 769.8e6 + 225.2e6,   # same file, ttlb_gemm_bfp8w_tmem_kernel
     "attention": 805.0e6 + 249.0e6,          # profiles/attention_b8_h32_s4096_d128.md
     "eltwise_add_1024": None,
 }
@@ -443,6 +444,8 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
         flops = 2.0 * m * k * n
         out_bytes = m * n * 2
         kernel = f"ttlb_unpack_bfp{bits}_kernel + " + ("ttlb_gemm_bf16_kernel" if args.gemm_variant == 0 else "ttlb_gemm_bf16_2cta_kernel")
+        if bits == 8 and args.bfp8_mode in (1, 2) and world == 1:
+            kernel = "ttlb_gemm_bfp8w_tmem_kernel"   # expansion inside the mainloop (ttlb_set_bfp8_mode)
         chunks = 2 if world > 1 else 1
 
         def compute(xs):
@@ -694,7 +697,8 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
         "gather": {"mode": mode if world > 1 else "none (1 GPU)", "how": gather if world > 1 else None},
         "l2": "operands exceed the 126 MB L2" if wl != "attention" else "Q,K,V,O 1 GB total exceed L2",
         "roofline": {"bound": "tensor", "achieved": per_gpu_kernel_tf, "peak": burst, "unit": "TFLOP/s",
-                     "frac": per_gpu_kernel_tf / burst, "traffic": TRAFFIC_BYTES.get(wl) if world == 1 else None,
+                     "frac": per_gpu_kernel_tf / burst, "traffic": (TRAFFIC_BYTES.get(wl + "_in_mainloop" if kernel == "ttlb_gemm_bfp8w_tmem_kernel" else wl)
+                                 if world == 1 else None),
                      "peak_source": src, "peak_sustained": sustained, "kernel": kernel},
         "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in),
@@ -1147,7 +1151,8 @@ def main():
     ap.add_argument("--mc-rounds", type=int, default=0,
                     help="multicast gather: rounds the local shard is computed and re-sent in (0: 4 rounds on 4 or more GPUs, else 1)")
     ap.add_argument("--bfp8-mode", type=int, default=None, choices=[0, 1, 2],
-                    help="bfp8 weights: 0 unpack kernel + GEMM, 1 unpack inside the GEMM mainloop for large outputs, 2 always inside")
+                    help="bfp8 weights: 0 unpack kernel + GEMM (default), 1 expansion inside the GEMM mainloop (operand through tensor "
+                         "memory) for large outputs, 2 always inside")
     ap.add_argument("--gather", default="auto",
                     help="sharded workloads: how output shards reach the other ranks (p2p: peer-to-peer copies overlapped with "
                          "compute; multicast: multimem.st re-send kernel per round under the next round's compute; fused: "

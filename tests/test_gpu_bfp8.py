@@ -85,6 +85,35 @@ def test_matmul_program_with_bfloat8_b_weights(backend, bfp8_mode):
     assert rel_err(ttnn.to_torch(out), tile_oracle.matmul_tiles(x.float(), wq, "f32")) <= 1e-2
 
 
+def test_in_mainloop_expansion_is_exact_for_every_exponent():
+    """The kernel that expands the weights inside the mainloop multiplies by 2^(E-126), which is a bf16 only up to
+    E = 253, and produces bf16 denormals for the smallest exponents.  With a one-hot activation matrix the product
+    IS the expanded weight matrix: it must equal the oracle's unpack value for value, blocks with exponents 254 / 255
+    (values of 2^121 and more, expanded the slow way), denormal results and all-zero blocks included."""
+    from ttl_b200 import capi, ops, ttnn
+    k, n = 256, 416
+    w = cases.gen((k, n), "normal*0.02", 7, torch.float32)
+    w[0, :16] = torch.tensor([1e-30] * 8 + [3e-39] * 8)
+    w[1, :16] = torch.tensor([3e-38, -1.5e-38] + [2e-39] * 14)          # results that are bf16 denormals
+    w[2, 16:32] = torch.tensor([-3e38, 1e38, 2.5e37, -7.0] + [1e30] * 12)   # exponent 254
+    w[3, :16] = torch.tensor([1.0, -1.0, 1.5, 1.9921875, -0.0078125, 0.0] + [0.33] * 10)
+    w[65, 32:48] = torch.tensor([2.0, -3.99, 2.5] + [1.0] * 13)
+    w[66, 400:416] = torch.tensor([1.7e38, -1.7e38] + [5e37] * 14)
+    w[129, :16] = 0.0                                                   # an all-zero block (exponent 0)
+    want = torch.from_numpy(bfp8_oracle.unpack(bfp8_oracle.pack(w.numpy()), k, n))
+    x = torch.eye(k, dtype=torch.bfloat16)
+    W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+    ctx = capi.context()
+    try:
+        for mode in (2, 0):
+            ctx.set_bfp8_mode(mode)
+            got = ttnn.to_torch(ops.matmul(ttnn.from_torch(x), W))
+            ctx.check_status(capi.current_stream())
+            assert torch.equal(got.float(), want), f"mode {mode}"   # value for value (a sum does not keep the sign of -0)
+    finally:
+        ctx.set_bfp8_mode(capi.BFP8_MODE_DEFAULT)
+
+
 def test_config4_shard_slab(bfp8_mode):
     """configs[3] shapes on one 2048-column stripe (what one of 14 column blocks looks like) with 256
     activation rows checked against the oracle, plus the full 4096 rows for the exact-scaling property."""

@@ -34,7 +34,7 @@ int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const 
                                int64_t m, int64_t n, int64_t k, bool multicast, const void *bias, int64_t ldbias,
                                cudaStream_t stream);
 
-int ttlb_launch_gemm_bfp8w_fused(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, cudaStream_t stream);
+int ttlb_launch_gemm_bfp8w_tmem(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, cudaStream_t stream);
 
 namespace {
 
@@ -184,7 +184,7 @@ static int matmul_bfp8w_impl(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, bool m
                        "matmul: pointers must be 16-byte aligned and K, N and the row pitches multiples of 8");
     if (d->lda < d->k || d->ldc < d->n)
       return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: row pitch smaller than the row");
-    return ttlb_launch_gemm_bfp8w_fused(ctx, d, s);
+    return ttlb_launch_gemm_bfp8w_tmem(ctx, d, s);
   }
   // otherwise expand the weight window to bf16 in scratch memory owned by the context, then run the bf16 GEMM
   const size_t need = (size_t)d->k * (size_t)d->n * 2;

@@ -31,7 +31,7 @@ struct ttlb_ctx {
   bool gemm_attr_set = false;
   bool gemm2_attr_set = false;
   int gemm_variant = 1;  // 0: always one-CTA 128x256 tiles; 1: two-CTA (cta_group::2) 256x256 tiles for large outputs
-  bool gemm_fused_attr_set = false;
+  bool gemm_tmem_attr_set = false;
   int gemm_act = 0;  // activation of the GEMM being launched (set by ttlb_matmul_bf16_epilogue around its launch)
   // output region in each GPU's copy of a shared buffer, for the GEMM being launched (ttlb_matmul_*_peers)
   void *pub_peers[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
