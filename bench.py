@@ -381,6 +381,33 @@ def timed(env: "Env", fn, steps: int, warmup: int) -> float:
     return env.max_over_ranks(e0.elapsed_time(e1) / steps)
 
 
+def through_the_dsl(a_dev, b_operand, direct_out):
+    """The same product through `@ttl.kernel`: the reference's multicore matmul tile program in 1x1-tile blocks
+    (examples/multicore_matmul.py:28-139, restated in tests/programs/matmul.py) is traced, recognised as one launch
+    and run; the record carries the time of trace + recognition and whether the bits equal the direct call's."""
+    import importlib.util
+
+    import torch
+
+    import ttl_b200
+    ttl_b200.install()
+    import ttnn
+    spec = importlib.util.spec_from_file_location("bench_programs_matmul", ROOT / "tests" / "programs" / "matmul.py")
+    programs = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(programs)
+    A = ttnn.Tensor(a_dev)
+    B = b_operand if isinstance(b_operand, ttnn.Tensor) else ttnn.Tensor(b_operand)
+    out = ttnn.Tensor(torch.zeros_like(direct_out))
+    t0 = time.perf_counter()
+    plan = programs.multicore_matmul.plan(A, B, out)
+    trace_s = time.perf_counter() - t0
+    programs.multicore_matmul(A, B, out)
+    torch.cuda.synchronize()
+    return {"program": "multicore matmul tile program, 1x1-tile blocks, through @ttl.kernel (tests/programs/matmul.py)",
+            "trace_and_recognise_s": round(trace_s, 3), "launches": [d["kind"] for d in plan.describe()],
+            "same_bits_as_the_direct_call": bool(torch.equal(out._tensor, direct_out))}
+
+
 def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dict:
     """One record for a sharded workload.  One GPU: the single-GPU kernel on the whole problem.  N GPUs: strong
     scaling - the problem is split over the ranks (output row tiles / weight column tiles / heads,
@@ -707,6 +734,8 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
         "gpu_launches_per_step": launches,
         "clocks": {k: clocks[k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
     }
+    if world == 1 and wl in ("matmul_bf16_8192", "matmul_bfp8w") and not args.no_dsl:
+        rec["dsl"] = through_the_dsl(dev_in[0], dev_in[1] if wl == "matmul_bf16_8192" else W, compute(dev_in))
     if world > 1:
         recv = out_bytes * (world - 1) / world
         floor = recv / (NVLINK_MEASURED_GBS * 1e9) * 1e3
@@ -1150,6 +1179,8 @@ def main():
                     help="bfp8 weights, two-step path: column chunks whose expansion overlaps the previous chunk's GEMM")
     ap.add_argument("--mc-rounds", type=int, default=0,
                     help="multicast gather: rounds the local shard is computed and re-sent in (0: 4 rounds on 4 or more GPUs, else 1)")
+    ap.add_argument("--no-dsl", action="store_true",
+                    help="matmul workloads on one GPU: skip the run of the same product through @ttl.kernel")
     ap.add_argument("--bfp8-mode", type=int, default=None, choices=[0, 1, 2],
                     help="bfp8 weights: 0 unpack kernel + GEMM (default), 1 expansion inside the GEMM mainloop (operand through tensor "
                          "memory) for large outputs, 2 always inside")
