@@ -113,10 +113,11 @@ __device__ __forceinline__ void tmem_st_16x256b_x2(uint32_t taddr, const uint32_
                : "memory");
 }
 
-__device__ __forceinline__ uint32_t hfma2_bf16(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
+// a * s - s on bf16 pairs (one instruction: the negation is an operand modifier)
+__device__ __forceinline__ uint32_t scale_minus_one(uint32_t a, uint32_t s) {
+  const __nv_bfloat162 a2 = *reinterpret_cast<const __nv_bfloat162 *>(&a), s2 = *reinterpret_cast<const __nv_bfloat162 *>(&s);
+  const __nv_bfloat162 d = __hfma2(a2, s2, __hneg2(s2));
+  return *reinterpret_cast<const uint32_t *>(&d);
 }
 
 // (Ea, Eb) -> the bf16 pair (2^(Ea-126), 2^(Eb-126)); exponents up to 253
@@ -306,13 +307,25 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
         if (!__all_sync(0xffffffffu, mbar_wait(pfull_bar(stage), phase, abort_flag, p.wait_limit))) { fail = 4; break; }
         const uint8_t *ms = gbase + TSTAGES * X_BYTES + stage * MANT_BYTES;
         const uint8_t *es = gbase + TSTAGES * (X_BYTES + MANT_BYTES) + stage * EXP_BYTES;
-        // block exponents of this thread's rows, all four (tile row, face row) pairs; 254 and 255 take the slow way
-        uint32_t e4s[4];
+        // Block exponents and scale pairs.  The four lanes that share this thread's rows and face column (lanes
+        // j & 3 = 0..3 of the group) need the same eight scale pairs - (tile row, face row) u = 0..3 x row pairs
+        // (0,1), (2,3): each lane makes two of them, u = (j & 3) >> 1 and that + 2, row pair (j & 3) & 1, and they
+        // go round by shuffle.  Exponents 254 and 255 (anywhere in the warp's tiles) take the slow way.
+        const int sr = j & 3;
+        const uint32_t e_lo = *reinterpret_cast<const uint32_t *>(es + q * 64 + (2 * (sr >> 1) + face_lo) * 16 + 4 * t4);
+        const uint32_t e_hi = *reinterpret_cast<const uint32_t *>(es + (4 + q) * 64 + (2 * (sr >> 1) + face_lo) * 16 + 4 * t4);
+        const bool huge = __any_sync(0xffffffffu, (__vcmpgeu4(e_lo, 0xfefefefeu) | __vcmpgeu4(e_hi, 0xfefefefeu)) != 0u);
+        const uint32_t psel = (sr & 1) ? 0x4342u : 0x4140u;
+        const uint32_t my_s_lo = scale_pair(e_lo, psel), my_s_hi = scale_pair(e_hi, psel);
+        const int grp = lane & ~12;                  // lane of the group with j & 3 = 0 (lane = 4 * j + t4)
+        uint32_t sc[4][2], e4s[4];                   // [u][row pair]
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          e4s[u] = *reinterpret_cast<const uint32_t *>(es + ((u >> 1) * 4 + q) * 64 + (2 * (u & 1) + face_lo) * 16 + 4 * t4);
-        const bool huge = __any_sync(0xffffffffu, (__vcmpgeu4(e4s[0], 0xfefefefeu) | __vcmpgeu4(e4s[1], 0xfefefefeu) |
-                                                   __vcmpgeu4(e4s[2], 0xfefefefeu) | __vcmpgeu4(e4s[3], 0xfefefefeu)) != 0u);
+        for (int u = 0; u < 4; ++u) {
+#pragma unroll
+          for (int pr = 0; pr < 2; ++pr)
+            sc[u][pr] = __shfl_sync(0xffffffffu, u < 2 ? my_s_lo : my_s_hi, grp + 4 * (2 * (u & 1) + pr));
+          e4s[u] = huge ? __shfl_sync(0xffffffffu, u < 2 ? e_lo : e_hi, grp + 4 * (2 * (u & 1))) : 0u;
+        }
 #pragma unroll
         for (int trow = 0; trow < 2; ++trow) {
           uint32_t o[2][8];   // [lane half of the store][register]
@@ -337,14 +350,13 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
                 o[a >> 1][kf * 4 + (a & 1) * 2 + 1] = expand_pair_slow(w[2] >> sh, (e4 >> 16) & 0xffu, w[3] >> sh, e4 >> 24);
               }
             } else {
-              const uint32_t s01 = scale_pair(e4, 0x4140u), s23 = scale_pair(e4, 0x4342u);
-              const uint32_t c01 = s01 | 0x80008000u, c23 = s23 | 0x80008000u;
+              const uint32_t s01 = sc[trow * 2 + kf][0], s23 = sc[trow * 2 + kf][1];
 #pragma unroll
               for (int a = 0; a < 4; ++a) {   // column 4j + a: lane j (+8 for a odd) of lane half a/2
                 const uint32_t sel = 0x4400u + 0x1111u * a;
                 const uint32_t x01 = __byte_perm(w[0], w[1], sel), x23 = __byte_perm(w[2], w[3], sel);
-                const uint32_t y01 = hfma2_bf16((x01 & 0x007f007fu) | 0x3f803f80u, s01, c01);
-                const uint32_t y23 = hfma2_bf16((x23 & 0x007f007fu) | 0x3f803f80u, s23, c23);
+                const uint32_t y01 = scale_minus_one((x01 & 0x007f007fu) | 0x3f803f80u, s01);
+                const uint32_t y23 = scale_minus_one((x23 & 0x007f007fu) | 0x3f803f80u, s23);
                 o[a >> 1][kf * 4 + (a & 1) * 2 + 0] = y01 | (x01 & 0x80008000u);
                 o[a >> 1][kf * 4 + (a & 1) * 2 + 1] = y23 | (x23 & 0x80008000u);
               }
