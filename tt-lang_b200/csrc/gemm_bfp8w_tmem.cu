@@ -113,22 +113,19 @@ __device__ __forceinline__ void tmem_st_16x256b_x2(uint32_t taddr, const uint32_
                : "memory");
 }
 
-// a * s - s on bf16 pairs (one instruction: the negation is an operand modifier)
-__device__ __forceinline__ uint32_t scale_minus_one(uint32_t a, uint32_t s) {
-  const __nv_bfloat162 a2 = *reinterpret_cast<const __nv_bfloat162 *>(&a), s2 = *reinterpret_cast<const __nv_bfloat162 *>(&s);
-  const __nv_bfloat162 d = __hfma2(a2, s2, __hneg2(s2));
+// product of two bf16 pairs, denormal operands and results included
+__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 d = __hmul2(*reinterpret_cast<const __nv_bfloat162 *>(&a), *reinterpret_cast<const __nv_bfloat162 *>(&b));
   return *reinterpret_cast<const uint32_t *>(&d);
 }
 
-// (Ea, Eb) -> the bf16 pair (2^(Ea-126), 2^(Eb-126)); exponents up to 253
-__device__ __forceinline__ uint32_t scale_pair(uint32_t e4, uint32_t sel) {
-  return (__byte_perm(e4, 0u, sel) + 0x00010001u) << 7;
-}
-
-// the slow way, for block exponents 254 and 255 (values of 2^121 and more), whose scale is not a bf16
-__device__ __noinline__ uint32_t expand_pair_slow(uint32_t b0, uint32_t e0, uint32_t b1, uint32_t e1) {
-  const float v0 = (float)(b0 & 0x7fu) * exp2f((float)e0 - 133.0f), v1 = (float)(b1 & 0x7fu) * exp2f((float)e1 - 133.0f);
-  return pack_bf16x2((b0 & 0x80u) ? -v0 : v0, (b1 & 0x80u) ? -v1 : v1);
+// Block exponents (Ea, Eb) of a row pair -> two bf16 pairs of powers of two whose product is (2^Ea, 2^Eb): 2^E itself is
+// a bf16 only up to E = 127, 2^(E/2) and 2^(E - E/2) always are (E <= 254: 255 is not a finite value's exponent).
+__device__ __forceinline__ void scale_pairs(uint32_t e4, uint32_t sel, uint32_t &s1, uint32_t &s2) {
+  const uint32_t u = __byte_perm(e4, 0u, sel);             // Ea in the low half, Eb in the high half
+  const uint32_t h = (u >> 1) & 0x007f007fu;
+  s1 = (h + 0x007f007fu) << 7;
+  s2 = (u - h + 0x007f007fu) << 7;
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TTHREADS, 1)
@@ -307,24 +304,26 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
         if (!__all_sync(0xffffffffu, mbar_wait(pfull_bar(stage), phase, abort_flag, p.wait_limit))) { fail = 4; break; }
         const uint8_t *ms = gbase + TSTAGES * X_BYTES + stage * MANT_BYTES;
         const uint8_t *es = gbase + TSTAGES * (X_BYTES + MANT_BYTES) + stage * EXP_BYTES;
-        // Block exponents and scale pairs.  The four lanes that share this thread's rows and face column (lanes
-        // j & 3 = 0..3 of the group) need the same eight scale pairs - (tile row, face row) u = 0..3 x row pairs
-        // (0,1), (2,3): each lane makes two of them, u = (j & 3) >> 1 and that + 2, row pair (j & 3) & 1, and they
-        // go round by shuffle.  Exponents 254 and 255 (anywhere in the warp's tiles) take the slow way.
+        // Scale pairs.  The four lanes that share this thread's rows and face column (lanes j & 3 = 0..3 of the
+        // group) need the same eight - (tile row, face row) u = 0..3 x row pairs (0,1), (2,3): each lane makes two
+        // of them, u = (j & 3) >> 1 and that + 2, row pair (j & 3) & 1, and they go round by shuffle.
         const int sr = j & 3;
         const uint32_t e_lo = *reinterpret_cast<const uint32_t *>(es + q * 64 + (2 * (sr >> 1) + face_lo) * 16 + 4 * t4);
         const uint32_t e_hi = *reinterpret_cast<const uint32_t *>(es + (4 + q) * 64 + (2 * (sr >> 1) + face_lo) * 16 + 4 * t4);
-        const bool huge = __any_sync(0xffffffffu, (__vcmpgeu4(e_lo, 0xfefefefeu) | __vcmpgeu4(e_hi, 0xfefefefeu)) != 0u);
         const uint32_t psel = (sr & 1) ? 0x4342u : 0x4140u;
-        const uint32_t my_s_lo = scale_pair(e_lo, psel), my_s_hi = scale_pair(e_hi, psel);
+        uint32_t my1_lo, my2_lo, my1_hi, my2_hi;
+        scale_pairs(e_lo, psel, my1_lo, my2_lo);
+        scale_pairs(e_hi, psel, my1_hi, my2_hi);
         const int grp = lane & ~12;                  // lane of the group with j & 3 = 0 (lane = 4 * j + t4)
-        uint32_t sc[4][2], e4s[4];                   // [u][row pair]
+        uint32_t sc1[4][2], sc2[4][2];               // [u][row pair]
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
 #pragma unroll
-          for (int pr = 0; pr < 2; ++pr)
-            sc[u][pr] = __shfl_sync(0xffffffffu, u < 2 ? my_s_lo : my_s_hi, grp + 4 * (2 * (u & 1) + pr));
-          e4s[u] = huge ? __shfl_sync(0xffffffffu, u < 2 ? e_lo : e_hi, grp + 4 * (2 * (u & 1))) : 0u;
+          for (int pr = 0; pr < 2; ++pr) {
+            const int src = grp + 4 * (2 * (u & 1) + pr);
+            sc1[u][pr] = __shfl_sync(0xffffffffu, u < 2 ? my1_lo : my1_hi, src);
+            sc2[u][pr] = __shfl_sync(0xffffffffu, u < 2 ? my2_lo : my2_hi, src);
+          }
         }
 #pragma unroll
         for (int trow = 0; trow < 2; ++trow) {
@@ -333,7 +332,6 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
 #pragma unroll
           for (int kf = 0; kf < 2; ++kf) {     // rows 0..15 / 16..31 of the tile row
             const int f = 2 * kf + face_lo;
-            const uint32_t e4 = e4s[trow * 2 + kf];
             uint32_t w[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -342,24 +340,17 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
               const int chunk = (r & 7) ^ row128;             // the TMA load's swizzle: 16-byte chunk ^ (row % 8)
               w[i] = *reinterpret_cast<const uint32_t *>(tile + row128 * 128 + chunk * 16 + cbyte);
             }
-            if (huge) {
+            // A byte is sign | magnitude m and means (-1)^s m 2^(E-133); placed as sign and mantissa of a bf16 with a
+            // zero exponent field it IS (-1)^s m 2^-133 (a denormal): two multiplications by powers of two, both
+            // exact, finish the job.  The byte permute doubles the column's byte of row r into the low half and
+            // that of row r+1 into the high half.
+            const int u = trow * 2 + kf;
 #pragma unroll
-              for (int a = 0; a < 4; ++a) {
-                const uint32_t sh = 8u * a;
-                o[a >> 1][kf * 4 + (a & 1) * 2 + 0] = expand_pair_slow(w[0] >> sh, e4 & 0xffu, w[1] >> sh, (e4 >> 8) & 0xffu);
-                o[a >> 1][kf * 4 + (a & 1) * 2 + 1] = expand_pair_slow(w[2] >> sh, (e4 >> 16) & 0xffu, w[3] >> sh, e4 >> 24);
-              }
-            } else {
-              const uint32_t s01 = sc[trow * 2 + kf][0], s23 = sc[trow * 2 + kf][1];
-#pragma unroll
-              for (int a = 0; a < 4; ++a) {   // column 4j + a: lane j (+8 for a odd) of lane half a/2
-                const uint32_t sel = 0x4400u + 0x1111u * a;
-                const uint32_t x01 = __byte_perm(w[0], w[1], sel), x23 = __byte_perm(w[2], w[3], sel);
-                const uint32_t y01 = scale_minus_one((x01 & 0x007f007fu) | 0x3f803f80u, s01);
-                const uint32_t y23 = scale_minus_one((x23 & 0x007f007fu) | 0x3f803f80u, s23);
-                o[a >> 1][kf * 4 + (a & 1) * 2 + 0] = y01 | (x01 & 0x80008000u);
-                o[a >> 1][kf * 4 + (a & 1) * 2 + 1] = y23 | (x23 & 0x80008000u);
-              }
+            for (int a = 0; a < 4; ++a) {   // column 4j + a: lane j (+8 for a odd) of lane half a/2
+              const uint32_t sel = 0x4400u + 0x1111u * a;
+              const uint32_t x01 = __byte_perm(w[0], w[1], sel) & 0x807f807fu, x23 = __byte_perm(w[2], w[3], sel) & 0x807f807fu;
+              o[a >> 1][kf * 4 + (a & 1) * 2 + 0] = hmul2_bf16(hmul2_bf16(x01, sc1[u][0]), sc2[u][0]);
+              o[a >> 1][kf * 4 + (a & 1) * 2 + 1] = hmul2_bf16(hmul2_bf16(x23, sc1[u][1]), sc2[u][1]);
             }
           }
           const uint32_t ta = tmem_a + stage * A_COLS + trow * 16 + ((uint32_t)(q * 32) << 16);
