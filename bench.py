@@ -471,7 +471,7 @@ def measure_sharded(args, wl: str, env: "Env", gather_mode: str = "auto") -> dic
         flops = 2.0 * m * k * n
         out_bytes = m * n * 2
         kernel = f"ttlb_unpack_bfp{bits}_kernel + " + ("ttlb_gemm_bf16_kernel" if args.gemm_variant == 0 else "ttlb_gemm_bf16_2cta_kernel")
-        if bits == 8 and args.bfp8_mode in (1, 2) and world == 1:
+        if bits == 8 and (capi.BFP8_MODE_DEFAULT if args.bfp8_mode is None else args.bfp8_mode) in (1, 2) and world == 1:
             kernel = "ttlb_gemm_bfp8w_tmem_kernel"   # expansion inside the mainloop (ttlb_set_bfp8_mode)
         chunks = 2 if world > 1 else 1
 
@@ -1182,8 +1182,8 @@ def main():
     ap.add_argument("--no-dsl", action="store_true",
                     help="matmul workloads on one GPU: skip the run of the same product through @ttl.kernel")
     ap.add_argument("--bfp8-mode", type=int, default=None, choices=[0, 1, 2],
-                    help="bfp8 weights: 0 unpack kernel + GEMM (default), 1 expansion inside the GEMM mainloop (operand through tensor "
-                         "memory) for large outputs, 2 always inside")
+                    help="bfp8 weights: 0 unpack kernel + GEMM, 1 expansion inside the GEMM mainloop (operand through tensor memory) "
+                         "for large outputs (default), 2 always inside")
     ap.add_argument("--gather", default="auto",
                     help="sharded workloads: how output shards reach the other ranks (p2p: peer-to-peer copies overlapped with "
                          "compute; multicast: multimem.st re-send kernel per round under the next round's compute; fused: "

@@ -36,7 +36,7 @@ struct ttlb_ctx {
   // output region in each GPU's copy of a shared buffer, for the GEMM being launched (ttlb_matmul_*_peers)
   void *pub_peers[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   int pub_n_peers = 0;
-  int bfp8_mode = 0;  // 0: unpack kernel + bf16 GEMM; 1: unpack inside the GEMM mainloop for large outputs; 2: always inside
+  int bfp8_mode = 1;  // 0: unpack kernel + bf16 GEMM; 1: unpack inside the GEMM mainloop for large outputs; 2: always inside
   bool attn_attr_set = false;
   long long wait_limit_cycles = 4000000000LL;  // ~2 s at 1.9 GHz
   // Scratch in HBM owned by the context (bf16 expansion of bfloat8_b weights); grows on demand.

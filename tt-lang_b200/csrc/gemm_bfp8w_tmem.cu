@@ -12,14 +12,15 @@
 //     loads: the value bytes of 2 x 4 tiles (a four-dimensional view of the packed matrix, loaded with the 128-byte
 //     swizzle so that the converters' 32-bit loads hit 32 different banks) and their block exponents.  (One thread
 //     issuing all five loads of the first version needed 640 cycles per k-block and was the limit.)
-//   * warps 10..25, four groups of four that take the k-blocks in turn (a warp serves the 32 tensor-memory lanes of
+//   * warps 10..17, two groups of four that take the k-blocks in turn (a warp serves the 32 tensor-memory lanes of
 //     its quarter = one tile column), expand bytes to bf16 PAIRS ALONG k - a block's 16 values lie along n and share
 //     an exponent, so a pair (k, k+1) of one column has two exponents: one byte permute takes the column's two
-//     bytes out of the two rows' words, one logic op makes them bf16 numbers in [1, 2) with the magnitude as
-//     mantissa, one fused multiply-add with the pair (2^(Ek-126), 2^(Ek+1-126)) and its negative makes
-//     m * 2^(E-133) exactly, one logic op puts the signs back - and write them with tcgen05.st (16 lanes x 256 bits:
-//     a thread's registers are two lanes' k-pairs), then arrive on the leader CTA's barrier, on which the X bytes
-//     are counted too;
+//     bytes out of the two rows' words, one mask leaves sign and magnitude where a bf16 has sign and mantissa -
+//     with a zero exponent field that IS (-1)^s m 2^-133, a denormal - and two multiplications by pairs of powers
+//     of two (2^(E/2) and 2^(E - E/2): 2^E itself is a bf16 only up to E = 127) make (-1)^s m 2^(E-133) exactly,
+//     for every exponent - and write them with tcgen05.st (16 lanes x 256 bits: a thread's registers are two lanes'
+//     k-pairs), then arrive on the leader CTA's barrier, on which the X bytes are counted too.  The scale pairs are
+//     made once per four lanes and passed round by shuffle;
 //   * the leader's warp 1 waits on that one barrier and issues four tcgen05.mma.cta_group::2 (256 x 256 x 16),
 //     A from tensor memory.
 //
@@ -32,11 +33,12 @@
 // Shared memory per CTA: 8 stages x (16 KB X + 8 KB value bytes + 512 B exponents) + 20 KB for the epilogue.
 // Every wait is bounded.
 //
-// Measured on 4096 x 8192 x 28672: 1.48-1.52 ms against 1.38 ms for the unpack kernel + bf16 GEMM and 1.62-1.69 ms
-// for the earlier in-mainloop kernel, which wrote the expanded weights to shared memory (removed).  In cycles the
-// mainloop is at the tensor pipe's rate (506-520 per k-block for 512); what remains is the epilogue (4,500 cycles per
-// tile, 6 %) and the clock: every weight is expanded once per 256 activation rows, 16 times in all, and under
-// the power cap that work lowers the clock the tensor pipe runs at.
+// Measured on 4096 x 8192 x 28672: 1.36 ms against 1.38 ms for the unpack kernel + bf16 GEMM and 1.62-1.69 ms for the
+// earlier in-mainloop kernel, which wrote the expanded weights to shared memory (removed).  In cycles the mainloop
+// is at the tensor pipe's rate (506-520 per k-block for 512); what remains is the epilogue (4,500 cycles per tile,
+// 6 %) and the clock: every weight is expanded once per 256 activation rows, 16 times in all, and under the power
+// cap that work lowers the clock the tensor pipe runs at - which is why the expansion was cut to two integer-pipe
+// instructions per pair of values and is done by eight warps, not sixteen.
 #include <cuda_bf16.h>
 
 #include "ctx.h"
@@ -56,8 +58,9 @@ constexpr int EXP_BYTES = 2 * 4 * 64;
 constexpr int PACKED_TILE = 1088;
 constexpr int EPI_WARPS = 8;                 // two per tensor-memory lane quarter, 128 accumulator columns each
 constexpr int CONV_WARP0 = 2 + EPI_WARPS;
-constexpr int G = 4;                         // converter groups (four warps each) that take the k-blocks in turn;
-                                             // measured on 4096x8192x28672: 2 groups 1.54 ms, 3 groups 1.52 ms, 4 groups 1.48 ms
+constexpr int G = 2;                         // converter groups (four warps each) that take the k-blocks in turn;
+                                             // measured on 4096x8192x28672: 1 group 1.54 ms, 2 groups 1.36 ms, 3 groups 1.41-1.45 ms,
+                                             // 4 groups 1.45 ms (more warps cost clock under the power cap)
 constexpr int TTHREADS = (CONV_WARP0 + 4 * G + 1) * 32;   // + the packed-weights producer warp
 constexpr int T_GROUP_M = 8;
 constexpr int A_COLS = TBK / 2;             // 32 tensor-memory columns per k-block (two bf16 per column)

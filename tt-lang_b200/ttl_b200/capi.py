@@ -129,7 +129,7 @@ def rowfused_source(desc: "RowFusedDesc") -> str:
 
 ACTIVATIONS = {"relu": 1, "gelu": 2, "silu": 3, "sigmoid": 4, "tanh": 5}   # TTLB_ACT_*
 
-BFP8_MODE_DEFAULT = 0
+BFP8_MODE_DEFAULT = 1
 
 
 class BackendError(RuntimeError):
