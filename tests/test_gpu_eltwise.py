@@ -116,6 +116,38 @@ def test_repeated_calls_reuse_plan_and_stay_correct(backend):
     assert len(prog._plans) == n_plans, "the plan of an already-seen tensor signature must be reused"
 
 
+def test_kernel_calls_can_be_captured_in_a_cuda_graph(backend):
+    """Launch-bound inner loops: once a program has been seen (plan built, kernel compiled), calling it on a
+    capturing stream records its launches and nothing else - no allocation, no synchronisation - so a CUDA graph
+    of several kernel calls replays them without the host; new inputs written into the same tensors give new
+    results on the next replay."""
+    _, mods = backend
+    import ttnn
+    case = cases.by_name("bcast_row_tilecol")
+    prog = case.get_program(mods)
+    ins = [ttnn.from_torch(t) for t in case.make_inputs()]
+    outs = [ttnn.from_torch(torch.zeros(case.out_shape, dtype=case.dtype)) for _ in range(3)]
+    prog(*ins, outs[0])                                  # first call outside the capture: trace, compile
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for o in outs:
+            prog(*ins, o)
+    for o in outs:
+        o._tensor.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    want = oracle_output(case)
+    for o in outs:
+        assert torch.equal(ttnn.to_torch(o), want)
+    ins[0]._tensor.mul_(2)                               # same storage, new values
+    torch.cuda.synchronize()
+    graph.replay()
+    prog(*ins, outs[0])
+    direct = ttnn.to_torch(outs[0]).clone()
+    assert torch.equal(ttnn.to_torch(outs[2]), direct) and not torch.equal(direct, want)
+
+
 # ---- the C ABI itself: error behaviour and edge cases --------------------------------------
 def _desc(capi, x, y, out, ops, rows, cols, n_in=2):
     d = capi.EltwiseDesc()
