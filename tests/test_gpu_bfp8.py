@@ -114,6 +114,32 @@ def test_in_mainloop_expansion_is_exact_for_every_exponent():
         ctx.set_bfp8_mode(capi.BFP8_MODE_DEFAULT)
 
 
+@pytest.mark.parametrize("m,k,n", [(300, 96, 416), (512, 2048, 1024)])
+def test_bfp8w_matmul_published_to_several_buffers(m, k, n, bfp8_mode):
+    """ttlb_matmul_bfp8w_peers: the epilogue stores every tile, whole row segments at a time, into the output region
+    of several buffers (on a box with several GPUs: every GPU's copy of a shared output).  Here all buffers live on
+    this GPU: each must hold exactly what the plain call gives, and nothing may be written around the regions -
+    with the separate unpack kernel and with the expansion inside the mainloop."""
+    from ttl_b200 import capi, ops, ttnn
+    x = cases.gen((m, k), "normal", 3)
+    w = cases.gen((k, n), "normal*0.02", 4, torch.float32)
+    W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+    X = ttnn.from_torch(x)
+    plain = ttnn.to_torch(ops.matmul(X, W))
+    pad = 64
+    bufs = [torch.full((m + pad, n + pad), 3.0, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    view = ttnn.Tensor(bufs[0][32:32 + m, 32:32 + n])          # shape and pitch of the output region
+    ptrs = [b[32:, 32:].data_ptr() for b in bufs]
+    ops.launch_gemm(capi.context(), X, W, view, (0, m, 0, n), capi.current_stream(), peer_ptrs=ptrs)
+    capi.context().check_status(capi.current_stream())
+    torch.cuda.synchronize()
+    for b in bufs:
+        got = b.cpu()
+        assert torch.equal(got[32:32 + m, 32:32 + n], plain)
+        got[32:32 + m, 32:32 + n] = 3.0
+        assert (got == 3.0).all(), "the publishing epilogue wrote outside the output region"
+
+
 def test_config4_shard_slab(bfp8_mode):
     """configs[3] shapes on one 2048-column stripe (what one of 14 column blocks looks like) with 256
     activation rows checked against the oracle, plus the full 4096 rows for the exact-scaling property."""

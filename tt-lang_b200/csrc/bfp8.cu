@@ -34,7 +34,7 @@ int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const 
                                int64_t m, int64_t n, int64_t k, bool multicast, const void *bias, int64_t ldbias,
                                cudaStream_t stream);
 
-int ttlb_launch_gemm_bfp8w_tmem(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, cudaStream_t stream);
+int ttlb_launch_gemm_bfp8w_tmem(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, bool publish, cudaStream_t stream);
 
 namespace {
 
@@ -175,7 +175,7 @@ static int matmul_bfp8w_impl(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, bool m
   if (!g.ok) return ttlb_fail(ctx, TTLB_ERR_CUDA, "matmul_bfp8w: cannot select device %d", ctx->device);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // Unpack inside the GEMM mainloop (no scratch) when selected and the output fills the SM pairs.
-  const bool fused_ok = !multicast && d->m > 0 && d->m <= 0x7fffffff && d->n <= 0x7fffffff && d->k <= 0x7fffffff;
+  const bool fused_ok = d->m > 0 && d->m <= 0x7fffffff && d->n <= 0x7fffffff && d->k <= 0x7fffffff;
   if (fused_ok && (ctx->bfp8_mode == 2 ||
                    (ctx->bfp8_mode == 1 && ((d->m + 255) / 256) * ((d->n + 255) / 256) >= ctx->sm_count / 2))) {
     if (!d->a || !d->c) return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: null operand");
@@ -184,7 +184,7 @@ static int matmul_bfp8w_impl(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, bool m
                        "matmul: pointers must be 16-byte aligned and K, N and the row pitches multiples of 8");
     if (d->lda < d->k || d->ldc < d->n)
       return ttlb_fail(ctx, TTLB_ERR_INVALID_ARG, "matmul: row pitch smaller than the row");
-    return ttlb_launch_gemm_bfp8w_tmem(ctx, d, s);
+    return ttlb_launch_gemm_bfp8w_tmem(ctx, d, multicast, s);
   }
   // otherwise expand the weight window to bf16 in scratch memory owned by the context, then run the bf16 GEMM
   const size_t need = (size_t)d->k * (size_t)d->n * 2;

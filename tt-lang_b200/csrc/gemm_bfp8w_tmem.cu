@@ -64,8 +64,11 @@ constexpr int G = 2;                         // converter groups (four warps eac
 constexpr int TTHREADS = (CONV_WARP0 + 4 * G + 1) * 32;   // + the packed-weights producer warp
 constexpr int T_GROUP_M = 8;
 constexpr int A_COLS = TBK / 2;             // 32 tensor-memory columns per k-block (two bf16 per column)
-constexpr int EPI_PITCH = 80;                // bytes per row of an epilogue warp's 32 x 32 bf16 transposition tile
-constexpr int EPI_BYTES = EPI_WARPS * 32 * EPI_PITCH;
+constexpr int EPI_PITCH = 256 + 16;          // publishing epilogue: bytes per row of a transposition tile of 32 activation rows x
+                                             // 128 weight columns, one tile per half of the accumulator's columns (four warps each)
+constexpr int EPI_PITCH1 = 64 + 16;          // plain epilogue: a warp's own tile of 32 activation rows x 32 weight columns
+constexpr int EPI_BYTES = EPI_WARPS * 32 * EPI_PITCH1 > 2 * 32 * EPI_PITCH ? EPI_WARPS * 32 * EPI_PITCH1 : 2 * 32 * EPI_PITCH;
+constexpr int MAX_PEERS = 8;
 constexpr int TSMEM_BYTES = TSTAGES * (X_BYTES + MANT_BYTES + EXP_BYTES) + EPI_BYTES + 1024 + 512;
 static_assert(TBM + TSTAGES * A_COLS <= 512, "tensor memory: accumulator + A slots");
 
@@ -79,7 +82,25 @@ struct TmemParams {
   int tiles_m, tiles_n;
   int *status;
   long long wait_limit;
+  // 0: c is this GPU's output.  1: c is a multicast address (multimem.st: the switch replicates every store to all GPUs
+  // of the group).  2: every row segment is stored to peer_c[0 .. n_peers), the output in every GPU's copy of a shared
+  // buffer (peer-mapped memory, this GPU's own copy included).  Peer memory is only ever written.
+  int pub;
+  __nv_bfloat16 *peer_c[MAX_PEERS];
+  int n_peers;
 };
+
+// 16-byte store to a multicast address: the switch replicates it to every GPU of the group.
+__device__ __forceinline__ void st_multimem_16(void *p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)),
+               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+// barrier among the `threads` threads that name barrier `id` (1..15; 0 is __syncthreads')
+__device__ __forceinline__ void named_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 
 __device__ __forceinline__ void ttile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn) {
   const int per_group = T_GROUP_M * tiles_n;
@@ -131,6 +152,8 @@ __device__ __forceinline__ void scale_pairs(uint32_t e4, uint32_t sel, uint32_t 
   s2 = (u - h + 0x007f007fu) << 7;
 }
 
+// PUB: the instantiation whose epilogue publishes the output to several GPUs
+template <bool PUB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TTHREADS, 1)
 ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_mant,
                             const __grid_constant__ CUtensorMap map_exp, const TmemParams p) {
@@ -239,12 +262,16 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
     // ---- epilogue: this CTA's 128 weight columns (tensor-memory lanes) x 256 activation rows (columns); a warp takes
     // 128 of the columns of its lane quarter
     const int q = warp & 3, half = (warp - 2) >> 2;
-    // This lane holds weight column 4 * (lane % 8) + lane / 8 of the warp's 32; a 32 x 32 block is turned round in
-    // shared memory (row = activation row, 64 bytes of 32 weight columns) so that global stores are 16-byte
-    // vectors along a row of C, four lanes per row.  The next block's tcgen05.ld is in flight meanwhile.
-    uint8_t *tp = gen_epi + (warp - 2) * (32 * EPI_PITCH);
-    const int my_col = 4 * (lane & 7) + (lane >> 3);
-    const int rr = lane >> 2, rc = lane & 3;     // read side: row within a group of 8, 16-byte chunk of the row
+    // This lane holds weight column 4 * (lane % 8) + lane / 8 of its warp's 32.  A block of 32 activation rows is
+    // turned round in shared memory (row = activation row) so that global stores are 16-byte vectors along the rows of
+    // C; the next block's tcgen05.ld is in flight meanwhile.  Plain epilogue: every warp for itself, 32 weight columns
+    // (64-byte row segments).  Publishing epilogue: the four warps that share a half of the accumulator's columns work
+    // on one tile of 128 weight columns and store two whole 256-byte row segments per instruction, which is what
+    // NVLink needs (at home it measured 1 % slower than the plain one).  The four warps wait for the same barrier
+    // with the same limit, so they reach the named barriers together or not at all.
+    uint8_t *st = PUB ? gen_epi + half * (32 * EPI_PITCH) : gen_epi + (warp - 2) * (32 * EPI_PITCH1);
+    const int my_n = (PUB ? q * 32 : 0) + 4 * (lane & 7) + (lane >> 3);
+    const int wq = (warp - 2) & 3;                // publishing: this warp stores rows 8 * wq .. 8 * wq + 7 of a block
     const uint32_t my_acc = tmem_base + ((uint32_t)(q * 32) << 16) + half * 128;
     int local = 0;
     for (int t = cluster_id; t < num_tiles && !fail; t += n_clusters, ++local) {
@@ -253,22 +280,34 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       // the outcome of the wait is made the same for the whole warp: what follows is warp-collective
       if (!__all_sync(0xffffffffu, mbar_wait(tfull_bar, (uint32_t)(local & 1), abort_flag, p.wait_limit))) { fail = 3; break; }
       tc_fence_after();
-      const int col0 = tn * TBN + (int)rank * 128 + q * 32;
+      const int colb = tn * TBN + (int)rank * 128 + (PUB ? 8 * (lane & 15) : q * 32 + 8 * (lane & 3));
       auto emit = [&](const uint32_t (&r)[32], int c) {
+        constexpr int PITCH = PUB ? EPI_PITCH : EPI_PITCH1;
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          *reinterpret_cast<__nv_bfloat16 *>(tp + i * EPI_PITCH + my_col * 2) = __float2bfloat16_rn(__uint_as_float(r[i]));
-        __syncwarp();
+          *reinterpret_cast<__nv_bfloat16 *>(st + i * PITCH + my_n * 2) = __float2bfloat16_rn(__uint_as_float(r[i]));
+        if constexpr (PUB) named_barrier(1 + half, 128); else __syncwarp();
         const int row0 = tm * TBM + half * 128 + c * 32;
-        if (col0 + rc * 8 < p.n) {   // n is a multiple of 32: a group of 8 columns is all in or all out
+        if (colb < p.n) {   // n is a multiple of 32: a group of 8 columns is all in or all out
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const int row = row0 + g * 8 + rr;
-            const uint4 v = *reinterpret_cast<const uint4 *>(tp + (g * 8 + rr) * EPI_PITCH + rc * 16);
-            if (row < p.m) *reinterpret_cast<uint4 *>(p.c + (long long)row * p.ldc + col0 + rc * 8) = v;
+            // publishing: 16 lanes per row, this warp's 8 rows; plain: 4 lanes per row, all 32 rows
+            const int rl = PUB ? 8 * wq + 2 * g + (lane >> 4) : 8 * g + (lane >> 2);
+            const int row = row0 + rl;
+            const uint4 v = *reinterpret_cast<const uint4 *>(st + rl * PITCH + 16 * (PUB ? (lane & 15) : (lane & 3)));
+            if (row < p.m) {
+              const long long off = (long long)row * p.ldc + colb;
+              if constexpr (!PUB) {
+                *reinterpret_cast<uint4 *>(p.c + off) = v;
+              } else if (p.pub == 1) {
+                st_multimem_16(p.c + off, v);
+              } else {
+                for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(p.peer_c[d] + off) = v;
+              }
+            }
           }
         }
-        __syncwarp();
+        if constexpr (PUB) named_barrier(1 + half, 128); else __syncwarp();
       };
       uint32_t ra[32], rb[32];
       tmem_ld_32x32(my_acc, ra);
@@ -400,8 +439,9 @@ int make_map_u8(ttlb_ctx *ctx, CUtensorMap *map, const void *ptr, uint32_t rank,
 int ttlb_make_map_bf16_2d(ttlb_ctx *ctx, CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t outer,
                           uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer);
 
-// Arguments are validated by the caller (matmul_bfp8w_impl in bfp8.cu).
-int ttlb_launch_gemm_bfp8w_tmem(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, cudaStream_t stream) {
+// Arguments are validated by the caller (matmul_bfp8w_impl in bfp8.cu).  publish: d->c is a multicast address, or - when
+// the context holds peer pointers (ttlb_matmul_bfp8w_peers) - the output is stored to each of them.
+int ttlb_launch_gemm_bfp8w_tmem(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, bool publish, cudaStream_t stream) {
   CUtensorMap map_x, map_mant, map_exp;
   int rc = ttlb_make_map_bf16_2d(ctx, &map_x, d->a, (uint64_t)d->k, (uint64_t)d->m, (uint64_t)d->lda * 2, TBK, 128);
   if (rc) return rc;
@@ -435,15 +475,28 @@ int ttlb_launch_gemm_bfp8w_tmem(ttlb_ctx *ctx, const ttlb_gemm_bfp8_desc *d, cud
   p.tiles_n = (int)((d->n + TBN - 1) / TBN);
   p.status = ctx->d_status;
   p.wait_limit = ctx->wait_limit_cycles;
+  p.pub = publish ? 1 : 0;
+  p.n_peers = 0;
+  for (int i = 0; i < MAX_PEERS; ++i) p.peer_c[i] = nullptr;
+  if (publish && ctx->pub_n_peers > 0) {
+    p.pub = 2;
+    p.n_peers = ctx->pub_n_peers;
+    for (int i = 0; i < ctx->pub_n_peers; ++i) p.peer_c[i] = reinterpret_cast<__nv_bfloat16 *>(ctx->pub_peers[i]);
+  }
   const int tiles_out = p.tiles_m * p.tiles_n;
   int clusters = ctx->sm_count / 2;
   if (clusters > tiles_out) clusters = tiles_out;
   if (!ctx->gemm_tmem_attr_set) {
-    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bfp8w_tmem_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bfp8w_tmem_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              TSMEM_BYTES));
+    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bfp8w_tmem_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               TSMEM_BYTES));
     ctx->gemm_tmem_attr_set = true;
   }
-  ttlb_gemm_bfp8w_tmem_kernel<<<clusters * 2, TTHREADS, TSMEM_BYTES, stream>>>(map_x, map_mant, map_exp, p);
+  if (p.pub)
+    ttlb_gemm_bfp8w_tmem_kernel<true><<<clusters * 2, TTHREADS, TSMEM_BYTES, stream>>>(map_x, map_mant, map_exp, p);
+  else
+    ttlb_gemm_bfp8w_tmem_kernel<false><<<clusters * 2, TTHREADS, TSMEM_BYTES, stream>>>(map_x, map_mant, map_exp, p);
   TTLB_CUDA_CHECK(ctx, cudaGetLastError());
   ctx->launches += 1;
   return TTLB_OK;
