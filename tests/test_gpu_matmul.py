@@ -228,19 +228,21 @@ def test_config3_as_the_unchanged_tile_program_at_full_size(backend):
         assert rel_err(got[r0:r0 + 64], tile_oracle.matmul_tiles(a[r0:r0 + 64], b, "f32")) <= TOL, f"rows {r0}..{r0 + 63}"
 
 
+@pytest.mark.parametrize("variant", [0, 2], ids=["one_cta", "two_cta"])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (300, 288, 136), (1024, 2048, 512)])
-def test_c_abi_matmul_published_to_several_buffers(m, n, k):
+def test_c_abi_matmul_published_to_several_buffers(m, n, k, variant):
     """ttlb_matmul_bf16_peers: the epilogue that passes every tile through shared memory and stores it, whole
     256-byte row segments at a time, into the output region of several buffers (on a box with several GPUs: every
     GPU's copy of a shared output).  Here all buffers live on this GPU: each must hold exactly what the plain
-    matmul gives, and nothing may be written around the output regions."""
+    matmul gives, and nothing may be written around the output regions.  Both GEMM kernels have this epilogue
+    (128x256 tiles of one CTA, 256x256 tiles of a CTA pair)."""
     from ttl_b200 import capi
     g = torch.Generator().manual_seed(m + n + k)
     a = (torch.randn(m, k, generator=g) / k ** 0.5).to(torch.bfloat16)
     b = torch.randn(k, n, generator=g).to(torch.bfloat16)
     A, B = a.cuda(), b.cuda()
     ctx = capi.context()
-    ctx.set_gemm_variant(0)
+    ctx.set_gemm_variant(variant)
     try:
         plain = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
         d = capi.GemmDesc()

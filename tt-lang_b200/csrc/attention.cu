@@ -150,13 +150,6 @@ __device__ __forceinline__ void exp_pack32(const uint32_t (&src)[32], f2_t sl2e2
   }
 }
 
-// 16-byte store to a multicast address: the switch replicates it to every GPU of the group.
-__device__ __forceinline__ void st_multimem_16(void *p, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)),
-               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
-               : "memory");
-}
-
 // PUB: the instantiation whose epilogue publishes the output to several GPUs through a shared-memory stage
 template <bool PUB>
 __global__ void __launch_bounds__(ATT_THREADS, 1)

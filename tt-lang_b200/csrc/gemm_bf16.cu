@@ -77,13 +77,6 @@ struct GemmParams {
   int act = 0;                          // TTLB_ACT_*: applied to product + bias before the rounding
 };
 
-// 16-byte store to a multicast address: the switch replicates it to every GPU of the group.
-__device__ __forceinline__ void st_multimem_16(void *p, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)),
-               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
-               : "memory");
-}
-
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int &tm, int &tn) {
   const int per_group = GROUP_M * tiles_n;
   const int g = t / per_group;
@@ -340,7 +333,8 @@ int ttlb_make_map_bf16_2d(ttlb_ctx *ctx, CUtensorMap *map, const void *ptr, uint
   return make_map(ctx, map, ptr, inner, outer, pitch_bytes, box_inner, box_outer);
 }
 int ttlb_launch_gemm_bf16_2cta(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
-                               int64_t m, int64_t n, int64_t k, const void *bias, int64_t ldbias, cudaStream_t stream);
+                               int64_t m, int64_t n, int64_t k, const void *bias, int64_t ldbias, bool publish,
+                               cudaStream_t stream);
 int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
                                int64_t m, int64_t n, int64_t k, bool multicast, const void *bias, int64_t ldbias,
                                cudaStream_t stream);
@@ -384,9 +378,10 @@ int ttlb_launch_gemm_bf16_full(ttlb_ctx *ctx, const void *a, int64_t lda, const 
   if (!g.ok) return ttlb_fail(ctx, TTLB_ERR_CUDA, "matmul: cannot select device %d", ctx->device);
   // Two-CTA tiles once there are enough 256x256 tiles to give every SM pair one; smaller outputs
   // spread better as 128x256 tiles.
-  if (!multicast && (ctx->gemm_variant == 2 ||
-                     (ctx->gemm_variant == 1 && ((m + 255) / 256) * ((n + 255) / 256) >= ctx->sm_count / 2)))
-    return ttlb_launch_gemm_bf16_2cta(ctx, a, lda, b, ldb, c, ldc, m, n, k, bias, ldbias, stream);
+  if ((!multicast || (!bias && !ctx->gemm_act)) &&
+      (ctx->gemm_variant == 2 ||
+       (ctx->gemm_variant == 1 && ((m + 255) / 256) * ((n + 255) / 256) >= ctx->sm_count / 2)))
+    return ttlb_launch_gemm_bf16_2cta(ctx, a, lda, b, ldb, c, ldc, m, n, k, bias, ldbias, multicast, stream);
 
   CUtensorMap map_a, map_b;
   int rc = make_map(ctx, &map_a, a, (uint64_t)k, (uint64_t)m, (uint64_t)lda * 2, BK, BM);

@@ -31,6 +31,11 @@ constexpr int THREADS2 = 192;
 // rasterisation groups of 4 / 8 / 16 / 32 tile rows 1481 / 1522 / 1511 / 1410 TFLOP/s
 constexpr int STAGES2_DEFAULT = 6, GROUP_M2_DEFAULT = 8;
 constexpr int smem2_bytes(int stages) { return stages * STAGE2_BYTES + 1024 + 256; }
+// the publishing epilogue passes 32 rows x 128 columns per warp through a swizzled stage
+constexpr int PUB2_COLS = 128;
+constexpr int PUB2_WARP_BYTES = 32 * PUB2_COLS * 2;   // 8 KB
+constexpr int smem2_bytes_pub(int stages) { return smem2_bytes(stages) + 4 * PUB2_WARP_BYTES; }
+constexpr int MAX_PEERS2 = 8;
 
 struct Gemm2Params {
   __nv_bfloat16 *c;
@@ -42,6 +47,12 @@ struct Gemm2Params {
   const __nv_bfloat16 *bias = nullptr;  // optional [m, n] matrix added to the product before rounding
   long long ldbias = 0;                 // 0: the bias is one row of n values, added to every output row
   int act = 0;                          // TTLB_ACT_*: applied to product + bias before the rounding
+  // 0: c is this GPU's output.  1: c is a multicast address (multimem.st: the switch replicates every store to all GPUs
+  // of the group).  2: every tile is stored to peer_c[0 .. n_peers), the output in every GPU's copy of a shared buffer
+  // (peer-mapped memory, this GPU's own copy included).  Peer memory is only ever written.
+  int multicast = 0;
+  __nv_bfloat16 *peer_c[MAX_PEERS2] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  int n_peers = 0;
 };
 
 template <int GROUP_M2>
@@ -55,7 +66,8 @@ __device__ __forceinline__ void tile_coords2(int t, int tiles_m, int tiles_n, in
   tn = r / rows;
 }
 
-template <int STAGES2, int GROUP_M2, bool ACT>
+// PUB: the instantiation whose epilogue publishes the output to several GPUs through a shared-memory stage
+template <int STAGES2, int GROUP_M2, bool ACT, bool PUB = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS2, 1)
 ttlb_gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                            const Gemm2Params p) {
@@ -159,6 +171,57 @@ ttlb_gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
       // the outcome of the wait is made the same for the whole warp: what follows is warp-collective
       if (!__all_sync(0xffffffffu, mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_limit))) { fail = 3; break; }
       tc_fence_after();
+      if constexpr (PUB) {
+        // tcgen05.ld hands every thread one row; the rows go through a swizzled stage so that each store
+        // instruction of the warp writes two whole 256-byte row segments (16 lanes x 16 bytes each) - through
+        // NVLink, 16-byte stores scattered over 32 rows reach a small fraction of the link rate
+        uint8_t *stage = gen + 256 + (warp - 2) * PUB2_WARP_BYTES;
+#pragma unroll 1
+        for (int half = 0; half < BN2 / PUB2_COLS; ++half) {
+#pragma unroll 1
+          for (int cc = 0; cc < PUB2_COLS / 32; ++cc) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN2 + half * PUB2_COLS + cc * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+              const int unit = cc * 4 + v;  // 16-byte unit within the 256-byte row
+              *reinterpret_cast<uint4 *>(stage + lane * (PUB2_COLS * 2) + ((unit ^ (lane & 7)) << 4)) = o;
+            }
+          }
+          if (half == BN2 / PUB2_COLS - 1) {
+            // every accumulator column has been read: the issuer may start the next tile into this buffer
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_remote(tempty_bar(acc), 0);
+          } else {
+            __syncwarp();
+          }
+          const int unit = lane & 15;
+          const long long gcol = (long long)tn * BN2 + half * PUB2_COLS + unit * 8;
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const int rl = 2 * i + (lane >> 4);
+            const uint4 o = *reinterpret_cast<const uint4 *>(stage + rl * (PUB2_COLS * 2) + ((unit ^ (rl & 7)) << 4));
+            const long long grow = (long long)tm * BM2 + (int)rank * 128 + q * 32 + rl;
+            if (grow < p.m && gcol < p.n) {
+              const long long off = grow * p.ldc + gcol;
+              if (p.multicast == 1) {
+                st_multimem_16(p.c + off, o);
+              } else {
+                for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4 *>(p.peer_c[d] + off) = o;
+              }
+            }
+          }
+          __syncwarp();
+        }
+        continue;
+      }
       const int row = tm * BM2 + (int)rank * 128 + q * 32 + lane;
       __nv_bfloat16 *crow = p.c + (long long)row * p.ldc + (long long)tn * BN2;
       const __nv_bfloat16 *brow = p.bias ? p.bias + (long long)row * p.ldbias + (long long)tn * BN2 : nullptr;
@@ -215,9 +278,12 @@ ttlb_gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
 int ttlb_make_map_bf16_2d(ttlb_ctx *ctx, CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t outer,
                           uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_outer);
 
-// Two-CTA launch; arguments are validated by the caller (ttlb_launch_gemm_bf16_ex).
+// Two-CTA launch; arguments are validated by the caller (ttlb_launch_gemm_bf16_ex).  publish: c is a multicast address,
+// or - when the context holds peer pointers (ttlb_matmul_bf16_peers) - the output is stored to each of them; n % 8 == 0,
+// no bias, no activation.
 int ttlb_launch_gemm_bf16_2cta(ttlb_ctx *ctx, const void *a, int64_t lda, const void *b, int64_t ldb, void *c, int64_t ldc,
-                               int64_t m, int64_t n, int64_t k, const void *bias, int64_t ldbias, cudaStream_t stream) {
+                               int64_t m, int64_t n, int64_t k, const void *bias, int64_t ldbias, bool publish,
+                               cudaStream_t stream) {
   CUtensorMap map_a, map_b;
   int rc = ttlb_make_map_bf16_2d(ctx, &map_a, a, (uint64_t)k, (uint64_t)m, (uint64_t)lda * 2, BK2, 128);
   if (rc) return rc;
@@ -228,6 +294,8 @@ int ttlb_launch_gemm_bf16_2cta(ttlb_ctx *ctx, const void *a, int64_t lda, const 
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(STAGES2_DEFAULT)));
     TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bf16_2cta_kernel<STAGES2_DEFAULT, GROUP_M2_DEFAULT, true>,
                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes(STAGES2_DEFAULT)));
+    TTLB_CUDA_CHECK(ctx, cudaFuncSetAttribute(ttlb_gemm_bf16_2cta_kernel<STAGES2_DEFAULT, GROUP_M2_DEFAULT, false, true>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, smem2_bytes_pub(STAGES2_DEFAULT)));
     ctx->gemm2_attr_set = true;
   }
   Gemm2Params p;
@@ -246,7 +314,17 @@ int ttlb_launch_gemm_bf16_2cta(ttlb_ctx *ctx, const void *a, int64_t lda, const 
   const int tiles = p.tiles_m * p.tiles_n;
   int clusters = ctx->sm_count / 2;
   if (clusters > tiles) clusters = tiles;
-  if (p.act)
+  if (publish) {
+    if (bias || p.act) return ttlb_fail(ctx, TTLB_ERR_UNSUPPORTED, "matmul: bias / activation with a published output");
+    p.multicast = 1;
+    if (ctx->pub_n_peers > 0) {
+      p.multicast = 2;
+      p.n_peers = ctx->pub_n_peers;
+      for (int i = 0; i < ctx->pub_n_peers; ++i) p.peer_c[i] = reinterpret_cast<__nv_bfloat16 *>(ctx->pub_peers[i]);
+    }
+    ttlb_gemm_bf16_2cta_kernel<STAGES2_DEFAULT, GROUP_M2_DEFAULT, false, true>
+        <<<clusters * 2, THREADS2, smem2_bytes_pub(STAGES2_DEFAULT), stream>>>(map_a, map_b, p);
+  } else if (p.act)
     ttlb_gemm_bf16_2cta_kernel<STAGES2_DEFAULT, GROUP_M2_DEFAULT, true>
         <<<clusters * 2, THREADS2, smem2_bytes(STAGES2_DEFAULT), stream>>>(map_a, map_b, p);
   else

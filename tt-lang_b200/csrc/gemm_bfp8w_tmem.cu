@@ -90,13 +90,6 @@ struct TmemParams {
   int n_peers;
 };
 
-// 16-byte store to a multicast address: the switch replicates it to every GPU of the group.
-__device__ __forceinline__ void st_multimem_16(void *p, uint4 v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)),
-               "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
-               : "memory");
-}
-
 // barrier among the `threads` threads that name barrier `id` (1..15; 0 is __syncthreads')
 __device__ __forceinline__ void named_barrier(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
