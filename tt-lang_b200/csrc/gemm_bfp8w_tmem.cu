@@ -8,11 +8,11 @@
 // memory, k contiguous - from shared memory, where a TMA load puts it (each CTA loads half of the 256 rows; no load
 // is multicast).  Per 64-deep k-block and CTA:
 //
-//   * warp 0 brings 128 rows of X (16 KB); the last warp brings this CTA's packed weight tiles with two tiled TMA
+//   * warp 0 brings 128 rows of X (16 KB); warp 2 brings this CTA's packed weight tiles with two tiled TMA
 //     loads: the value bytes of 2 x 4 tiles (a four-dimensional view of the packed matrix, loaded with the 128-byte
 //     swizzle so that the converters' 32-bit loads hit 32 different banks) and their block exponents.  (One thread
 //     issuing all five loads of the first version needed 640 cycles per k-block and was the limit.)
-//   * warps 10..17, two groups of four that take the k-blocks in turn (a warp serves the 32 tensor-memory lanes of
+//   * warps 12..19, two groups of four that take the k-blocks in turn (a warp serves the 32 tensor-memory lanes of
 //     its quarter = one tile column), expand bytes to bf16 PAIRS ALONG k - a block's 16 values lie along n and share
 //     an exponent, so a pair (k, k+1) of one column has two exponents: one byte permute takes the column's two
 //     bytes out of the two rows' words, one mask leaves sign and magnitude where a bf16 has sign and mantissa -
@@ -25,20 +25,22 @@
 //     A from tensor memory.
 //
 // Tensor memory: the accumulator (256 columns) and eight 32-column A slots.  There is room for one accumulator only,
-// so the epilogue of a tile (warps 2..9, two per lane quarter: tcgen05.ld with the next block's load in flight,
-// bf16, a 32 x 32 transposition through shared memory, 16-byte stores along the rows of C) is not overlapped by
-// UMMAs; the loads and the expansion of the next tile's first eight k-blocks are.  A tensor-memory lane holds
-// weight column 4 * (lane % 8) + lane / 8 of its tile column: that is the order in which a thread's 32-bit load of
-// four neighbouring columns meets the store's lanes (t/4, t/4 + 8, and the same + 16).
+// so no UMMA runs while a tile's accumulator is being read.  To keep that short, the epilogue warps (4..11, two per
+// lane quarter) take registers from the other warpgroups (setmaxnreg: 40 for warps 0..3, 72 for the converters, 144
+// for them), read their whole 128-column slice with four tcgen05.ld, release the accumulator, and only then convert to
+// bf16, transpose 32 x 32 blocks through shared memory and store 16-byte vectors along the rows of C: 1.36 -> 1.31 ms.
+// The loads and the expansion of the next tile's first eight k-blocks run under the epilogue too.  A tensor-memory
+// lane holds weight column 4 * (lane % 8) + lane / 8 of its tile column: that is the order in which a thread's
+// 32-bit load of four neighbouring columns meets the store's lanes (t/4, t/4 + 8, and the same + 16).
 // Shared memory per CTA: 8 stages x (16 KB X + 8 KB value bytes + 512 B exponents) + 20 KB for the epilogue.
 // Every wait is bounded.
 //
-// Measured on 4096 x 8192 x 28672: 1.36 ms against 1.38 ms for the unpack kernel + bf16 GEMM and 1.62-1.69 ms for the
-// earlier in-mainloop kernel, which wrote the expanded weights to shared memory (removed).  In cycles the mainloop
-// is at the tensor pipe's rate (506-520 per k-block for 512); what remains is the epilogue (4,500 cycles per tile,
-// 6 %) and the clock: every weight is expanded once per 256 activation rows, 16 times in all, and under the power
-// cap that work lowers the clock the tensor pipe runs at - which is why the expansion was cut to two integer-pipe
-// instructions per pair of values and is done by eight warps, not sixteen.
+// Measured on 4096 x 8192 x 28672: 1.31 ms (1,471 TFLOP/s) against 1.37 ms for the unpack kernel + bf16 GEMM and
+// 1.62-1.69 ms for the earlier in-mainloop kernel, which wrote the expanded weights to shared memory (removed).  In
+// cycles the mainloop is at the tensor pipe's rate (506-520 per k-block for 512); what decides the rest is the clock:
+// every weight is expanded once per 256 activation rows, 16 times in all, and under the power cap that work lowers the
+// clock the tensor pipe runs at - which is why the expansion was cut to two integer-pipe instructions per pair of
+// values and is done by eight warps, not sixteen.
 #include <cuda_bf16.h>
 
 #include "ctx.h"
@@ -57,11 +59,18 @@ constexpr int MANT_BYTES = 2 * 4 * 1024;    // two tile rows x four tile columns
 constexpr int EXP_BYTES = 2 * 4 * 64;
 constexpr int PACKED_TILE = 1088;
 constexpr int EPI_WARPS = 8;                 // two per tensor-memory lane quarter, 128 accumulator columns each
-constexpr int CONV_WARP0 = 2 + EPI_WARPS;
+constexpr int EPI_WARP0 = 4;                 // warps 0..3: X producer, UMMA issuer, packed-weights producer, one idle
+constexpr int CONV_WARP0 = EPI_WARP0 + EPI_WARPS;
 constexpr int G = 2;                         // converter groups (four warps each) that take the k-blocks in turn;
                                              // measured on 4096x8192x28672: 1 group 1.54 ms, 2 groups 1.36 ms, 3 groups 1.41-1.45 ms,
                                              // 4 groups 1.45 ms (more warps cost clock under the power cap)
-constexpr int TTHREADS = (CONV_WARP0 + 4 * G + 1) * 32;   // + the packed-weights producer warp
+constexpr int TTHREADS = (CONV_WARP0 + 4 * G) * 32;
+// Registers move between the warpgroups (setmaxnreg): the epilogue warps hold a whole 128-column slice of the
+// accumulator, so that the accumulator is free for the next tile after four loads instead of after the stores.  The
+// three figures must fit the pool the CTA is launched with (threads x REG_LAUNCH), or the raise would wait for ever.
+constexpr int REG_LAUNCH = 96, REG_LOW = 40, REG_EPI = 144, REG_CONV = 72;
+static_assert(TTHREADS == 640 && 65536 / TTHREADS / 8 * 8 == REG_LAUNCH, "launch register count");
+static_assert(128 * REG_LOW + EPI_WARPS * 32 * REG_EPI + 4 * G * 32 * REG_CONV <= TTHREADS * REG_LAUNCH, "register pool of the CTA exceeded");
 constexpr int T_GROUP_M = 8;
 constexpr int A_COLS = TBK / 2;             // 32 tensor-memory columns per k-block (two bf16 per column)
 constexpr int EPI_PITCH = 256 + 16;          // publishing epilogue: bytes per row of a transposition tile of 32 activation rows x
@@ -89,6 +98,15 @@ struct TmemParams {
   __nv_bfloat16 *peer_c[MAX_PEERS];
   int n_peers;
 };
+
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
 
 // barrier among the `threads` threads that name barrier `id` (1..15; 0 is __syncthreads')
 __device__ __forceinline__ void named_barrier(int id, int threads) {
@@ -198,12 +216,14 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   const uint32_t tmem_a = tmem_base + TBM;
 
   int fail = 0;
-  if (warp == 0 || warp == CONV_WARP0 + 4 * G) {
+  // every role branch starts with its own register move: after a join the lower limit would apply to all
+  if (warp == 0 || warp == 2) {
+    reg_dec<REG_LOW>();
     // ---- producers, one thread each: warp 0 brings X by TMA (signals the leader), the last warp the packed weights
     // (two tiled loads per k-block: value bytes and exponents of 2 x 4 tiles; signals locally).  Tiles outside the
     // packed matrix arrive as zeros, which expand to zeros; tiles outside the column window are other columns'
     // weights, whose products are never stored.
-    const bool packed = warp != 0;
+    const bool packed = warp == 2;
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -227,6 +247,7 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       }
     }
   } else if (warp == 1) {
+    reg_dec<REG_LOW>();
     // ---- UMMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
       constexpr uint32_t idesc = idesc_bf16(TBN, TBM, false, false);   // M = weight columns, N = activation rows
@@ -251,10 +272,13 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
         umma_commit_2sm(tfull_bar);
       }
     }
+  } else if (warp < EPI_WARP0) {
+    reg_dec<REG_LOW>();
   } else if (warp < CONV_WARP0) {
+    reg_inc<REG_EPI>();
     // ---- epilogue: this CTA's 128 weight columns (tensor-memory lanes) x 256 activation rows (columns); a warp takes
     // 128 of the columns of its lane quarter
-    const int q = warp & 3, half = (warp - 2) >> 2;
+    const int q = warp & 3, half = (warp - EPI_WARP0) >> 2;
     // This lane holds weight column 4 * (lane % 8) + lane / 8 of its warp's 32.  A block of 32 activation rows is
     // turned round in shared memory (row = activation row) so that global stores are 16-byte vectors along the rows of
     // C; the next block's tcgen05.ld is in flight meanwhile.  Plain epilogue: every warp for itself, 32 weight columns
@@ -262,9 +286,9 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
     // on one tile of 128 weight columns and store two whole 256-byte row segments per instruction, which is what
     // NVLink needs (at home it measured 1 % slower than the plain one).  The four warps wait for the same barrier
     // with the same limit, so they reach the named barriers together or not at all.
-    uint8_t *st = PUB ? gen_epi + half * (32 * EPI_PITCH) : gen_epi + (warp - 2) * (32 * EPI_PITCH1);
+    uint8_t *st = PUB ? gen_epi + half * (32 * EPI_PITCH) : gen_epi + (warp - EPI_WARP0) * (32 * EPI_PITCH1);
     const int my_n = (PUB ? q * 32 : 0) + 4 * (lane & 7) + (lane >> 3);
-    const int wq = (warp - 2) & 3;                // publishing: this warp stores rows 8 * wq .. 8 * wq + 7 of a block
+    const int wq = (warp - EPI_WARP0) & 3;                // publishing: this warp stores rows 8 * wq .. 8 * wq + 7 of a block
     const uint32_t my_acc = tmem_base + ((uint32_t)(q * 32) << 16) + half * 128;
     int local = 0;
     for (int t = cluster_id; t < num_tiles && !fail; t += n_clusters, ++local) {
@@ -302,25 +326,26 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
         }
         if constexpr (PUB) named_barrier(1 + half, 128); else __syncwarp();
       };
-      uint32_t ra[32], rb[32];
-      tmem_ld_32x32(my_acc, ra);
-      tmem_ld_wait_dep(ra);
-      tmem_ld_32x32(my_acc + 32, rb);
-      emit(ra, 0);
-      tmem_ld_wait_dep(rb);
-      tmem_ld_32x32(my_acc + 64, ra);
-      emit(rb, 1);
-      tmem_ld_wait_dep(ra);
-      tmem_ld_32x32(my_acc + 96, rb);
-      emit(ra, 2);
-      tmem_ld_wait_dep(rb);
-      // the accumulator has been read: the next tile's UMMAs may start while the last block is stored
+      // the whole slice into registers, then the accumulator is free: the next tile's UMMAs run under the stores
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      tmem_ld_32x32(my_acc, r0);
+      tmem_ld_32x32(my_acc + 32, r1);
+      tmem_ld_32x32(my_acc + 64, r2);
+      tmem_ld_32x32(my_acc + 96, r3);
+      tmem_ld_wait_dep(r0);
+      tmem_ld_wait_dep(r1);
+      tmem_ld_wait_dep(r2);
+      tmem_ld_wait_dep(r3);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(tempty_bar, 0);
-      emit(rb, 3);
+      emit(r0, 0);
+      emit(r1, 1);
+      emit(r2, 2);
+      emit(r3, 3);
     }
   } else {
+    reg_dec<REG_CONV>();
     // ---- converters: packed value bytes -> bf16 pairs along k -> tensor memory.  G groups take the k-blocks in
     // turn, so the latency of one k-block's chain (wait, read, expand, store, remote arrive) is spread over G.
     const int cw = warp - CONV_WARP0;            // 0 .. 4G-1
