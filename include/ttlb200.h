@@ -496,7 +496,7 @@ TTLB_EXPORT int ttlb_set_gemm_variant(ttlb_ctx *ctx, int variant);
  *   1  inside the GEMM mainloop (packed tiles are staged in shared memory, expanded in registers and written
  *      to tensor memory, from where the tensor core reads them as an operand of the transposed product; no
  *      scratch, no bf16 copy in HBM, nothing allocated) when the output has at least one 256x256 tile per SM
- *      pair, mode 0 otherwise.  Same bits as mode 0; the default (4096x8192x28672: 1.36 ms against 1.38 ms).
+ *      pair, mode 0 otherwise.  Same bits as mode 0; the default (4096x8192x28672: 1.31 ms against 1.37 ms).
  *   2  inside the mainloop for every shape (testing) */
 TTLB_EXPORT int ttlb_set_bfp8_mode(ttlb_ctx *ctx, int mode);
 /* Mode 0 can work in up to `chunks` (1..4) column chunks: the expansion of chunk i+1 runs on a stream owned
