@@ -183,6 +183,7 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   const uint32_t tfull_bar = bars + 8u * (4 * TSTAGES), tempty_bar = bars + 8u * (4 * TSTAGES + 1);
   volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(gen_bars + 8 * (4 * TSTAGES + 2));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_bars + 8 * (4 * TSTAGES + 2) + 8);
+  volatile uint8_t *epi_ok = reinterpret_cast<volatile uint8_t *>(gen_bars + 8 * (4 * TSTAGES + 2) + 16);   // [2 halves][4 warps]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -295,7 +296,15 @@ ttlb_gemm_bfp8w_tmem_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       int tm, tn;
       ttile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       // the outcome of the wait is made the same for the whole warp: what follows is warp-collective
-      if (!__all_sync(0xffffffffu, mbar_wait(tfull_bar, (uint32_t)(local & 1), abort_flag, p.wait_limit))) { fail = 3; break; }
+      bool ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar, (uint32_t)(local & 1), abort_flag, p.wait_limit));
+      if constexpr (PUB) {
+        // the four warps of a half meet at named barriers below: they must all go on or all give up (a warp whose wait
+        // ran out a moment before the barrier completed would otherwise leave the other three waiting for ever)
+        if (lane == 0) epi_ok[half * 4 + wq] = ok ? 1 : 0;
+        named_barrier(1 + half, 128);
+        ok = epi_ok[half * 4] & epi_ok[half * 4 + 1] & epi_ok[half * 4 + 2] & epi_ok[half * 4 + 3];
+      }
+      if (!ok) { fail = 3; break; }
       tc_fence_after();
       const int colb = tn * TBN + (int)rank * 128 + (PUB ? 8 * (lane & 15) : q * 32 + 8 * (lane & 3));
       auto emit = [&](const uint32_t (&r)[32], int c) {
