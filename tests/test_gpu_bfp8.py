@@ -140,6 +140,28 @@ def test_bfp8w_matmul_published_to_several_buffers(m, k, n, bfp8_mode):
         assert (got == 3.0).all(), "the publishing epilogue wrote outside the output region"
 
 
+def test_default_path_is_one_launch_for_large_outputs_and_two_for_small():
+    """The default (`ttlb_set_bfp8_mode` 1): an output with at least one 256x256 tile per SM pair is computed by ONE
+    launch that expands the weights inside the GEMM mainloop (no scratch, nothing written but the result); smaller
+    outputs take the unpack kernel and the bf16 GEMM.  Same bits either way."""
+    from ttl_b200 import capi, ops, ttnn
+    ctx = capi.context()
+    ctx.set_bfp8_mode(capi.BFP8_MODE_DEFAULT)
+    k = 256
+    w = cases.gen((k, 6144), "normal*0.02", 5, torch.float32)
+    W = ttnn.from_torch(w, dtype=ttnn.bfloat8_b)
+    for m, launches in ((1024, 1), (256, 2)):       # 4 x 24 = 96 tiles of 256 x 256 / 1 x 24
+        X = ttnn.from_torch(cases.gen((m, k), "normal", 6))
+        n0 = ctx.launch_count()
+        got = ttnn.to_torch(ops.matmul(X, W))
+        assert ctx.launch_count() - n0 == launches
+        ctx.set_bfp8_mode(0)
+        try:
+            assert torch.equal(ttnn.to_torch(ops.matmul(X, W)), got)
+        finally:
+            ctx.set_bfp8_mode(capi.BFP8_MODE_DEFAULT)
+
+
 def test_config4_shard_slab(bfp8_mode):
     """configs[3] shapes on one 2048-column stripe (what one of 14 column blocks looks like) with 256
     activation rows checked against the oracle, plus the full 4096 rows for the exact-scaling property."""
